@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight matmul path on B200.
+
+Headline workload (BASELINE.json configs[1], decode): a Qwen3-4B-shaped stack of 4-bit
+group-64 linears (36 layers x {q 2560->4096, k, v 2560->1024, o 4096->2560, gate, up
+2560->9728, down 9728->2560}), random-init, one token (M=1) per step.  Metric: HBM GB/s on
+the algorithmic bytes of a token (packed codes + bf16 scales/biases + activations in/out).
+Every linear is one call of the C ABI (`lisa_cuda_quantized_matmul_ex`), 252 launches per
+token, replayed from a CUDA graph.  The weights of a token (2.04 GB) are far larger than
+L2, so no flush is needed between steps.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One JSON line on stdout (rank 0).  With N > 1 (torchrun) each rank decodes its own token
+stream through its own replica ("replicas only": this config has no exchange step), value is
+the aggregate.  `--impl reference` times the CPU restatement of the reference's Rust dequant
++ scalar matmul (oracle/) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, Q_OUT, KV_OUT, INTER, LAYERS = 2560, 4096, 1024, 9728, 36
+GROUP, BITS = 64, 4
+# (name, K, N, which input buffer)
+LINEARS = [("q", HIDDEN, Q_OUT, "h"), ("k", HIDDEN, KV_OUT, "h"), ("v", HIDDEN, KV_OUT, "h"),
+           ("o", Q_OUT, HIDDEN, "a"), ("gate", HIDDEN, INTER, "h"), ("up", HIDDEN, INTER, "h"),
+           ("down", INTER, HIDDEN, "i")]
+
+
+def linear_bytes(k: int, n: int, m: int = 1) -> int:
+    """Algorithmic bytes of one linear: codes + bf16 scale and bias + x in + y out."""
+    return n * k * BITS // 8 + 2 * n * (k // GROUP) * 2 + m * k * 2 + m * n * 2
+
+
+def token_bytes(layers: int = LAYERS) -> int:
+    return layers * sum(linear_bytes(k, n) for _, k, n, _ in LINEARS)
+
+
+def token_weights(layers: int = LAYERS) -> int:
+    return layers * sum(k * n for _, k, n, _ in LINEARS)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                for name, val in zip(names, r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample_layers() -> int:
+    return 4
+
+
+_CPU_MATS = {}
+
+
+def cpu_sample(seed: int, layers: int):
+    """Host copies of `layers` layers of the stack (same shapes and distributions, seed `seed`)."""
+    import numpy as np
+    from tests import util
+
+    key = (seed, layers)
+    if key not in _CPU_MATS:
+        rng = np.random.default_rng(seed)
+        mats = []
+        for _ in range(layers):
+            for _, k, n, _ in LINEARS:
+                mats.append((util.affine_weights(rng, n, k, BITS, GROUP), util.activations(rng, 1, k)))
+        _CPU_MATS[key] = mats
+    return _CPU_MATS[key]
+
+
+def run_cpu_baseline(seed: int, layers: int):
+    """Times the oracle (port of the reference's Rust dequant + scalar f32 matmul, output rows
+    split over all host cores) on `layers` layers of the stack.  Returns (GB/s, seconds, cores)."""
+    from oracle import oracle as O
+
+    cores = os.cpu_count() or 1
+    mats = cpu_sample(seed, layers)
+    t0 = time.perf_counter()
+    for (w, s, b), x in mats:
+        O.affine_matmul(x, w, s, b, GROUP, BITS, round_weight_bf16=True, threads=cores)
+    dt = time.perf_counter() - t0
+    return token_bytes(layers) / dt / 1e9, dt, cores
+
+
+def reference_arm(args, rank: int):
+    if rank != 0:
+        return
+    layers = cpu_sample_layers()
+    times = []
+    for _ in range(args.warmup):
+        run_cpu_baseline(0, layers)
+    cores = os.cpu_count() or 1
+    for _ in range(args.steps):
+        gbs, dt, cores = run_cpu_baseline(0, layers)
+        times.append(dt)
+    dt = statistics.mean(times)
+    value = token_bytes(layers) / dt / 1e9
+    sample = f"{layers} of {LAYERS} layers of the stack (7 linears each), M=1, seed 0; weights generated on the host"
+    line = {
+        "impl": "reference", "metric": "4-bit qmv HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * LAYERS / layers,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference's Rust dequant + scalar f32 matmul (the Rust crate cannot be "
+                "built here: no Rust toolchain); ms_per_step is the sample scaled to a full token",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {"workload": "configs[1] decode: Qwen3-4B-shaped 4-bit gs64 linear stack, 36 layers x 7 linears, M=1",
+            "bytes_per_token": token_bytes(), "weights_per_token": token_weights(), "launches_per_token": LAYERS * 7,
+            "l2": "inputs larger than L2 (2.04 GB of weights per step)",
+            "parallelism": "replicas only" if n_gpus > 1 else "single GPU"}
+
+
+class DecodeStack:
+    """Device-resident synthetic weights and the per-token launch sequence."""
+
+    def __init__(self, dev, seed: int, layers: int = LAYERS):
+        import torch
+        from lisa_b200 import _cabi
+
+        self.torch = torch
+        self.dev = dev
+        self.layers = layers
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+        self.weights = []
+        for _ in range(layers):
+            per = []
+            for _, k, n, src in LINEARS:
+                w = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k * BITS // 32), dtype=torch.int32, device=dev, generator=g)
+                s = (torch.randn((n, k // GROUP), device=dev, generator=g) * 0.02).abs().to(torch.bfloat16)
+                b = (torch.randn((n, k // GROUP), device=dev, generator=g) * 0.01).to(torch.bfloat16)
+                y = torch.empty((1, n), dtype=torch.bfloat16, device=dev)
+                per.append((w, s, b, y, k, n, src))
+            self.weights.append(per)
+        self.inputs = {"h": torch.randn((1, HIDDEN), device=dev, generator=g).to(torch.bfloat16),
+                       "a": torch.randn((1, Q_OUT), device=dev, generator=g).to(torch.bfloat16),
+                       "i": torch.randn((1, INTER), device=dev, generator=g).to(torch.bfloat16)}
+        self.flags = _cabi.FLAG_PDL if os.environ.get("LISA_BENCH_PDL", "1") != "0" else 0
+        if os.environ.get("LISA_BENCH_SIMPLE", "0") == "1":
+            self.flags |= _cabi.FLAG_FORCE_QMV_SIMPLE
+        self.graph = None
+
+    def token(self):
+        from lisa_b200 import _cabi
+
+        lib = _cabi.lib()
+        stream = self.torch.cuda.current_stream().cuda_stream
+        for per in self.weights:
+            for w, s, b, y, k, n, src in per:
+                rc = lib.lisa_cuda_quantized_matmul_ex(stream, self.inputs[src].data_ptr(), 1, k, w.data_ptr(),
+                                                       s.data_ptr(), b.data_ptr(), n, 1, GROUP, BITS, 0, y.data_ptr(),
+                                                       self.flags)
+                _cabi.check(rc)
+
+    def capture(self):
+        torch = self.torch
+        self.token()  # sets kernel attributes outside capture
+        torch.cuda.synchronize()
+        if os.environ.get("LISA_BENCH_GRAPH", "1") == "0":
+            return
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                self.token()
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = graph
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.token()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures only")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
+    if rank == 0:
+        entry.build()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+    from lisa_b200 import ops
+
+    warmup = max(args.warmup, 3)
+    stack = DecodeStack(dev, seed=rank, layers=args.layers)
+    before = ops.launch_count()
+    stack.capture()
+    launches_per_token = (ops.launch_count() - before) // (2 if stack.graph is not None else 1)
+    bytes_token = token_bytes(args.layers)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        stack.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # ---- device-resident timing: inputs already in HBM
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        stack.step()
+        ev[i + 1].record()
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    # ---- end to end: host buffers in, host result out, every step
+    pinned_in = {k: v.cpu().pin_memory() for k, v in stack.inputs.items()}
+    last_y = stack.weights[-1][-1][3]
+    pinned_out = torch.empty_like(last_y, device="cpu").pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in pinned_in.values())
+    d2h = pinned_out.numel() * pinned_out.element_size()
+    for _ in range(2):
+        for k, v in pinned_in.items():
+            stack.inputs[k].copy_(v, non_blocking=True)
+        stack.step()
+        pinned_out.copy_(last_y, non_blocking=True)
+        torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        for k, v in pinned_in.items():
+            stack.inputs[k].copy_(v, non_blocking=True)
+        stack.step()
+        pinned_out.copy_(last_y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result before the next token
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(t[0]), float(t[1])
+    status = ops.device_status()
+
+    if rank == 0:
+        value = world * bytes_token * args.steps / (total_ms * 1e-3) / 1e9
+        e2e_value = world * bytes_token * args.steps / (e2e_ms * 1e-3) / 1e9
+        peak, peak_src = peaks()
+        per_gpu = bytes_token * args.steps / (total_ms * 1e-3) / 1e9
+        line = {
+            "metric": "4-bit qmv HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world),
+            "pct_of_8TBps": 100.0 * per_gpu / 8000.0,
+            "tokens_per_s": world * args.steps / (total_ms * 1e-3),
+            "ms_per_step_median": statistics.median(step_ms),
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "traffic": None, "kernel": "qmv_stream_kernel<4,*,1>", "peak_source": peak_src,
+                         "bytes_per_launch_avg": bytes_token / max(launches_per_token, 1),
+                         "us_per_launch_avg": 1e3 * total_ms / args.steps / max(launches_per_token, 1)},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches_per_token * args.steps,
+            "clocks": clocks, "device_status": status,
+            "launch": {"graph": stack.graph is not None, "pdl": bool(stack.flags & 8), "layers": args.layers},
+        }
+        if not args.skip_cpu:
+            layers = cpu_sample_layers()
+            gbs, dt, cores = run_cpu_baseline(0, layers)
+            line["cpu_baseline"] = {
+                "value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                "sample": f"{layers} of {LAYERS} layers (7 linears each), M=1, seed 0, {dt:.2f} s; "
+                          "restatement of the reference's Rust dequant + scalar f32 matmul"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,160 @@
+/*
+ * lisa_cuda — C ABI of the B200 (sm_100a) quantized-weight matmul library.
+ *
+ * One entry point per operator that lisa-engine dispatches on this path.  Each
+ * comment names the reference interface the entry point replaces (paths are
+ * relative to the agnosticeng/lisa repository).
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer to contiguous row-major memory that the
+ *    caller owns; the library never allocates, frees or retains memory.
+ *    Weights are read-only.  Workspaces, where an op needs one, are sized by a
+ *    *_workspace_bytes query and passed in by the caller.
+ *  - `stream` is a cudaStream_t.  Calls validate their arguments on the host,
+ *    enqueue work on `stream` and return; they do not synchronise.
+ *  - Return value: 0 on success, a negative lisa_status otherwise; nothing has
+ *    been enqueued when a call fails.  lisa_cuda_last_error_string() describes
+ *    the calling thread's last failure.
+ *  - bf16 / f16 tensors are 16-bit, f32 32-bit, packed weights are uint32 words
+ *    with code i of a word in bits [bits*i, bits*i+bits) (low code first).
+ *  - Alignment: x, w, scales, biases, y must be 16-byte aligned.
+ */
+#ifndef LISA_CUDA_H
+#define LISA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *lisa_stream_t; /* cudaStream_t */
+
+typedef enum lisa_status {
+    LISA_OK = 0,
+    LISA_ERR_BAD_ARG = -1,     /* null pointer, non-positive size, inconsistent shapes */
+    LISA_ERR_UNSUPPORTED = -2, /* bits / group size / dtype / transpose=false / lhs_indices ... */
+    LISA_ERR_MISALIGNED = -3,
+    LISA_ERR_OVERFLOW = -4,
+    LISA_ERR_CUDA = -5,
+    LISA_ERR_WORKSPACE = -6, /* workspace missing or too small */
+    LISA_ERR_LIMIT = -7      /* a documented size limit was exceeded */
+} lisa_status;
+
+typedef enum lisa_dtype { LISA_BF16 = 0, LISA_F16 = 1, LISA_F32 = 2 } lisa_dtype;
+
+/* GGML tensor type ids, crates/lisa-gguf/src/lib.rs:24-32. */
+typedef enum lisa_gguf_format { LISA_GGUF_Q2_K = 10, LISA_GGUF_Q4_K = 12 } lisa_gguf_format;
+
+/* Dispatch overrides for lisa_cuda_quantized_matmul_ex. */
+enum {
+    LISA_FLAG_NONE = 0,
+    LISA_FLAG_FORCE_QMV = 1 << 0,     /* CUDA-core streaming kernel (staged ring) */
+    LISA_FLAG_FORCE_QMV_SIMPLE = 1 << 1, /* CUDA-core generic kernel (direct loads) */
+    LISA_FLAG_FORCE_QMM = 1 << 2,     /* tcgen05 tensor-core kernel */
+    LISA_FLAG_PDL = 1 << 3            /* launch with programmatic stream serialization: the
+                                         kernel prefetches weights before waiting on the
+                                         previous kernel in the stream */
+};
+
+const char *lisa_cuda_last_error_string(void);
+int lisa_cuda_version(void);
+/* Number of kernels this library has launched from the calling process. */
+uint64_t lisa_cuda_launch_count(void);
+/* Device-side status word: 0, or non-zero after a kernel gave up on one of its bounded
+ * waits (its output is then undefined).  Synchronises the current device. */
+int lisa_cuda_device_status(void);
+
+/* ops::quantized_matmul(x, w, scales, biases, transpose, group_size, bits)
+ *   crates/lisa-mlx/src/ops/array_ops.rs:378-493
+ * y[m, n] = x[m, k] . dequant(W)[n, k]^T, fp32 accumulate, output in `dtype`.
+ *   x [m,k] dtype; w uint32 [n, k*bits/32]; scales, biases dtype [n, k/group_size];
+ *   y [m,n] dtype.  m >= 1.  Like the reference: transpose must be non-zero and
+ *   biases non-null (array_ops.rs:387-392).  bits in {2,4}, group_size in
+ *   {32,64,128}, dtype LISA_BF16.  Dispatch by m mirrors array_ops.rs:405-488:
+ *   small m streams the weights once on CUDA cores, large m runs the tcgen05 GEMM. */
+int lisa_cuda_quantized_matmul(lisa_stream_t stream, const void *x, int64_t m, int64_t k,
+                               const uint32_t *w, const void *scales, const void *biases,
+                               int64_t n, int transpose, int group_size, int bits, int dtype,
+                               void *y);
+int lisa_cuda_quantized_matmul_ex(lisa_stream_t stream, const void *x, int64_t m, int64_t k,
+                                  const uint32_t *w, const void *scales, const void *biases,
+                                  int64_t n, int transpose, int group_size, int bits, int dtype,
+                                  void *y, unsigned flags);
+
+/* ops::quantized_matmul_serial_rows, array_ops.rs:500-555: independent decode
+ * rows; every row's result is bit-identical to its own m=1 call. */
+int lisa_cuda_quantized_matmul_serial_rows(lisa_stream_t stream, const void *x, int64_t rows,
+                                           int64_t k, const uint32_t *w, const void *scales,
+                                           const void *biases, int64_t n, int transpose,
+                                           int group_size, int bits, int dtype, void *y);
+
+/* ops::dequantize(w, scales, biases, group_size, bits), array_ops.rs:37-84 and
+ * jit::affine_dequantize, crates/lisa-mlx/src/jit/matmul.rs:1316-1402.
+ * out[r, c] = dtype( f32(q) * f32(scale) + f32(bias) ): the host law of
+ * array_ops.rs:69-83, which is also what the GEMM tiles use. */
+int lisa_cuda_dequantize(lisa_stream_t stream, const uint32_t *w, const void *scales,
+                         const void *biases, int64_t rows, int64_t k, int group_size, int bits,
+                         int dtype, void *out);
+
+/* ops::gather_qmm(x, w, scales, biases, lhs_indices, rhs_indices, transpose,
+ *                 group_size, bits, sorted_indices), array_ops.rs:561-642.
+ * x [rows,k]; w uint32 [experts, n, k*bits/32]; scales/biases [experts, n, k/gs];
+ * rhs_indices int32 [rows], non-decreasing; y [rows,n].  Row r uses expert
+ * rhs_indices[r]; an id outside [0,experts) writes zeros and touches no weight.
+ * Like the reference: transpose non-zero, lhs_indices null, sorted_indices
+ * non-zero, rhs_indices and biases non-null (array_ops.rs:573-585). */
+size_t lisa_cuda_gather_qmm_workspace_bytes(int64_t rows, int64_t experts);
+int lisa_cuda_gather_qmm(lisa_stream_t stream, const void *x, int64_t rows, int64_t k,
+                         const uint32_t *w, const void *scales, const void *biases,
+                         const int32_t *lhs_indices, const int32_t *rhs_indices, int64_t experts,
+                         int64_t n, int transpose, int group_size, int bits, int sorted_indices,
+                         int dtype, void *y, void *workspace, size_t workspace_bytes);
+
+/* deepseek41::packed_matvec(format, weights, input), crates/lisa-mlx/src/models/deepseek41.rs:93-110.
+ * w uint8 [rows, row_bytes] of GGUF blocks; x f32 [tokens, K], K = row_bytes/block*256;
+ * y f32 [tokens, rows].  Same limits: rows % 8 == 0, row_bytes % block == 0,
+ * 1 <= tokens <= 65535 (deepseek41.rs:50-65,100-101). */
+int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows,
+                                 int64_t row_bytes, const float *x, int64_t tokens, float *y);
+
+/* deepseek41::expert_matvec(format, weights, input, ids), deepseek41.rs:204-283.
+ * w uint8 [experts, rows, row_bytes]; x f32 [tokens, slots, K], slots in {1, top_k};
+ * ids int32 [tokens, top_k], top_k <= 32; y f32 [tokens, top_k, rows].
+ * An id < 0 or >= experts writes zeros without touching weight memory. */
+int lisa_cuda_gguf_expert_matvec(lisa_stream_t stream, int format, const uint8_t *w,
+                                 int64_t experts, int64_t rows, int64_t row_bytes, const float *x,
+                                 int64_t tokens, int64_t slots, const int32_t *ids, int64_t top_k,
+                                 float *y);
+
+/* Routing around gather_qmm, crates/lisa-engine/src/models/qwen4/moe.rs:352-481.
+ * moe_route: top-k by value (ties to the lowest expert), idx in descending-logit
+ *   order, weights = softmax over the k selected logits (moe.rs:143-146;
+ *   crates/lisa-mlx/src/shaders/qwen4/route.metal).  logits f32 [tokens, experts]. */
+int lisa_cuda_moe_route(lisa_stream_t stream, const float *logits, int64_t tokens, int64_t experts,
+                        int top_k, int32_t *idx, float *weights);
+/* moe_sort: stable sort of the tokens*top_k slots by expert (moe.rs:368-374;
+ *   crates/lisa-mlx/src/models/qwen4/kernels/moe.rs:72-77).  sorted_ids[i],
+ *   token_rows[i] = slot/top_k, inverse[slot] = position.  workspace: see query. */
+size_t lisa_cuda_moe_sort_workspace_bytes(int64_t slots, int64_t experts);
+int lisa_cuda_moe_sort(lisa_stream_t stream, const int32_t *idx, int64_t slots, int64_t experts,
+                       int top_k, int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse,
+                       void *workspace, size_t workspace_bytes);
+/* x_sorted[i, :] = x[token_rows[i], :] (gatherSort, moe.rs:375-377). */
+int lisa_cuda_gather_rows(lisa_stream_t stream, const void *x, const int32_t *token_rows,
+                          int64_t rows, int64_t width, int dtype, void *out);
+/* act = bf16(bf16(g * sigmoid(g)) * u), crates/lisa-mlx/src/shaders/common/exact_header.metal:2-11. */
+int lisa_cuda_swiglu(lisa_stream_t stream, const void *gate, const void *up, int64_t count,
+                     int dtype, void *act);
+/* moe_combine without the shared expert (moe.rs:436-481): out[t, h] =
+ *   dtype( sum_j f32(down_sorted[inverse[t*top_k + j], h]) * weights[t, j] ), slots
+ *   folded in original order. */
+int lisa_cuda_moe_combine(lisa_stream_t stream, const void *down_sorted, const float *weights,
+                          const int32_t *inverse, int64_t tokens, int top_k, int64_t hidden,
+                          int dtype, void *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,269 @@
+// C ABI of the library (include/lisa_cuda.h): argument validation, error reporting and the
+// dispatch rules of the reference's operator layer
+// (crates/lisa-mlx/src/ops/array_ops.rs:378-642, crates/lisa-mlx/src/models/deepseek41.rs:50-283).
+// Nothing here allocates device memory or synchronises.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+#include <sstream>
+#include <string>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lisa {
+
+static thread_local std::string t_last_error;
+static std::atomic<uint64_t> g_launches{0};
+
+void set_error(const std::string &msg) { t_last_error = msg; }
+int fail(int code, const std::string &msg) {
+    t_last_error = msg;
+    return code;
+}
+int cuda_fail(cudaError_t err, const char *what) {
+    std::ostringstream os;
+    os << "CUDA error " << static_cast<int>(err) << " (" << cudaGetErrorString(err) << ") in " << what;
+    t_last_error = os.str();
+    return LISA_ERR_CUDA;
+}
+void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+struct DeviceInfo {
+    int sms = 0;
+    int smem_optin = 0;
+};
+static DeviceInfo g_dev[64];
+static std::once_flag g_dev_once[64];
+
+static const DeviceInfo &device_info() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    std::call_once(g_dev_once[dev], [dev]() {
+        cudaDeviceGetAttribute(&g_dev[dev].sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&g_dev[dev].smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    });
+    return g_dev[dev];
+}
+int sm_count() { return device_info().sms > 0 ? device_info().sms : 148; }
+int max_smem_optin() { return device_info().smem_optin > 0 ? device_info().smem_optin : 232448; }
+
+static int check_affine(const char *op, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                        const void *biases, int64_t n, int group_size, int bits, int dtype, const void *y) {
+    std::string name(op);
+    if (!biases) return fail(LISA_ERR_BAD_ARG, name + ": affine biases required");
+    if (!x || !w || !scales || !y) return fail(LISA_ERR_BAD_ARG, name + ": null pointer");
+    if (m < 1 || n < 1 || k < 1) return fail(LISA_ERR_BAD_ARG, name + ": sizes must be positive");
+    if (bits != 2 && bits != 4) return fail(LISA_ERR_UNSUPPORTED, name + ": bits must be 2 or 4");
+    if (group_size != 32 && group_size != 64 && group_size != 128)
+        return fail(LISA_ERR_UNSUPPORTED, name + ": group_size must be 32, 64 or 128");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, name + ": unsupported compute dtype (bf16 only)");
+    if (k % group_size != 0) return fail(LISA_ERR_BAD_ARG, name + ": k is not a multiple of group_size");
+    if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30) || m * n > (1ll << 40) || n * k > (1ll << 42))
+        return fail(LISA_ERR_OVERFLOW, name + ": shape too large");
+    if (!aligned16(x) || !aligned16(w) || !aligned16(scales) || !aligned16(biases) || !aligned16(y))
+        return fail(LISA_ERR_MISALIGNED, name + ": pointers must be 16-byte aligned");
+    return LISA_OK;
+}
+
+// Row count from which the tensor-core GEMM takes over from the CUDA-core streaming kernel.
+// The reference switches at qmv_batch_limit (crates/lisa-mlx/src/jit/matmul.rs:1873-1881);
+// here the CUDA-core kernel keeps up with HBM only while the per-weight FMA work stays small.
+static const int64_t kQmvMaxRows = 4;
+
+static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
+                                 const void *scales, const void *biases, int64_t n, int transpose, int group_size,
+                                 int bits, int dtype, void *y, unsigned flags) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: only transpose=true supported");
+    int rc = check_affine("quantized_matmul", x, m, k, w, scales, biases, n, group_size, bits, dtype, y);
+    if (rc != LISA_OK) return rc;
+    const bool force_qmv = (flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) != 0;
+    const bool force_qmm = (flags & LISA_FLAG_FORCE_QMM) != 0;
+    if (force_qmv && force_qmm) return fail(LISA_ERR_BAD_ARG, "quantized_matmul: contradictory flags");
+    const bool qmm_ok = qmm_affine_supported(m, k, n, group_size, bits);
+    if (force_qmm && !qmm_ok) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the GEMM kernel");
+    if (force_qmm || (!force_qmv && m > kQmvMaxRows && qmm_ok))
+        return qmm_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
+    return qmv_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
+}
+
+}  // namespace lisa
+
+using namespace lisa;
+
+extern "C" {
+
+const char *lisa_cuda_last_error_string(void) { return t_last_error.c_str(); }
+int lisa_cuda_version(void) { return 100; }
+uint64_t lisa_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int lisa_cuda_device_status(void) {
+    // Non-zero after a kernel gave up on a bounded wait.  Synchronises the device.
+    const int a = qmv_device_status();
+    const int b = qmm_device_status();
+    if (a < 0 || b < 0) return -1;
+    return a | (b << 8);
+}
+
+int lisa_cuda_quantized_matmul(lisa_stream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
+                               const void *scales, const void *biases, int64_t n, int transpose, int group_size,
+                               int bits, int dtype, void *y) {
+    return quantized_matmul_impl(static_cast<cudaStream_t>(stream), x, m, k, w, scales, biases, n, transpose,
+                                 group_size, bits, dtype, y, LISA_FLAG_NONE);
+}
+
+int lisa_cuda_quantized_matmul_ex(lisa_stream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
+                                  const void *scales, const void *biases, int64_t n, int transpose, int group_size,
+                                  int bits, int dtype, void *y, unsigned flags) {
+    return quantized_matmul_impl(static_cast<cudaStream_t>(stream), x, m, k, w, scales, biases, n, transpose,
+                                 group_size, bits, dtype, y, flags);
+}
+
+int lisa_cuda_quantized_matmul_serial_rows(lisa_stream_t stream, const void *x, int64_t rows, int64_t k,
+                                           const uint32_t *w, const void *scales, const void *biases, int64_t n,
+                                           int transpose, int group_size, int bits, int dtype, void *y) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_serial_rows: only transpose=true supported");
+    // Outside 2..8 rows the reference hands over to quantized_matmul (array_ops.rs:521-523).
+    if (rows <= 1 || rows > 8)
+        return quantized_matmul_impl(static_cast<cudaStream_t>(stream), x, rows, k, w, scales, biases, n, transpose,
+                                     group_size, bits, dtype, y, LISA_FLAG_NONE);
+    int rc = check_affine("quantized_matmul_serial_rows", x, rows, k, w, scales, biases, n, group_size, bits, dtype, y);
+    if (rc != LISA_OK) return rc;
+    // The streaming kernel accumulates every input row in the same order whatever the row
+    // count, so each row equals its own m=1 call bit for bit.
+    return qmv_affine(static_cast<cudaStream_t>(stream), x, rows, k, w, scales, biases, n, group_size, bits, y,
+                      LISA_FLAG_NONE);
+}
+
+int lisa_cuda_dequantize(lisa_stream_t stream, const uint32_t *w, const void *scales, const void *biases,
+                         int64_t rows, int64_t k, int group_size, int bits, int dtype, void *out) {
+    if (!w || !scales || !biases || !out) return fail(LISA_ERR_BAD_ARG, "dequantize: null pointer");
+    if (rows < 1 || k < 1) return fail(LISA_ERR_BAD_ARG, "dequantize: sizes must be positive");
+    if (bits != 2 && bits != 4 && bits != 8) return fail(LISA_ERR_UNSUPPORTED, "dequantize: bits must be 2, 4 or 8");
+    if (group_size != 32 && group_size != 64 && group_size != 128)
+        return fail(LISA_ERR_UNSUPPORTED, "dequantize: group_size must be 32, 64 or 128");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "dequantize: unsupported dtype (bf16 only)");
+    if (k % group_size != 0) return fail(LISA_ERR_BAD_ARG, "dequantize: k is not a multiple of group_size");
+    if (rows * k > (1ll << 42)) return fail(LISA_ERR_OVERFLOW, "dequantize: shape too large");
+    if (!aligned16(w) || !aligned16(scales) || !aligned16(biases) || !aligned16(out))
+        return fail(LISA_ERR_MISALIGNED, "dequantize: pointers must be 16-byte aligned");
+    return dequantize_affine(static_cast<cudaStream_t>(stream), w, scales, biases, rows, k, group_size, bits, out);
+}
+
+size_t lisa_cuda_gather_qmm_workspace_bytes(int64_t rows, int64_t experts) {
+    return gather_qmm_workspace_bytes(rows, experts);
+}
+
+int lisa_cuda_gather_qmm(lisa_stream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
+                         const void *scales, const void *biases, const int32_t *lhs_indices,
+                         const int32_t *rhs_indices, int64_t experts, int64_t n, int transpose, int group_size,
+                         int bits, int sorted_indices, int dtype, void *y, void *workspace, size_t workspace_bytes) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "gather_qmm: only transpose=true supported");
+    if (lhs_indices) return fail(LISA_ERR_UNSUPPORTED, "gather_qmm: lhs_indices path not ported");
+    if (!sorted_indices) return fail(LISA_ERR_UNSUPPORTED, "gather_qmm: only sorted_indices=true supported");
+    if (!rhs_indices) return fail(LISA_ERR_BAD_ARG, "gather_qmm: rhs_indices required");
+    int rc = check_affine("gather_qmm", x, rows, k, w, scales, biases, n, group_size, bits, dtype, y);
+    if (rc != LISA_OK) return rc;
+    if (experts < 1 || experts > (1 << 20)) return fail(LISA_ERR_BAD_ARG, "gather_qmm: bad expert count");
+    if (experts * n * k > (1ll << 44)) return fail(LISA_ERR_OVERFLOW, "gather_qmm: shape too large");
+    const size_t need = gather_qmm_workspace_bytes(rows, experts);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return fail(LISA_ERR_WORKSPACE, "gather_qmm: workspace missing or too small");
+    if (workspace && !aligned16(workspace)) return fail(LISA_ERR_MISALIGNED, "gather_qmm: workspace must be 16-byte aligned");
+    return gather_qmm_affine(static_cast<cudaStream_t>(stream), x, rows, k, w, scales, biases, rhs_indices, experts, n,
+                             group_size, bits, y, workspace, workspace_bytes);
+}
+
+static int gguf_geometry(const char *op, int format, int64_t rows, int64_t row_bytes, int *block_bytes) {
+    std::string name(op);
+    if (format == LISA_GGUF_Q2_K) *block_bytes = 84;
+    else if (format == LISA_GGUF_Q4_K) *block_bytes = 144;
+    else return fail(LISA_ERR_UNSUPPORTED, name + ": unsupported GGUF block format");
+    // deepseek41.rs:50-65
+    if (rows <= 0 || row_bytes <= 0 || rows % 8 != 0 || row_bytes % *block_bytes != 0)
+        return fail(LISA_ERR_BAD_ARG, name + ": unsupported GGUF quantized matvec layout");
+    if (row_bytes / *block_bytes > (1 << 22)) return fail(LISA_ERR_OVERFLOW, name + ": GGUF quantized input width overflow");
+    return LISA_OK;
+}
+
+int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes,
+                                 const float *x, int64_t tokens, float *y) {
+    int block = 0;
+    int rc = gguf_geometry("packed_matvec", format, rows, row_bytes, &block);
+    if (rc != LISA_OK) return rc;
+    if (!w || !x || !y) return fail(LISA_ERR_BAD_ARG, "packed_matvec: null pointer");
+    if (tokens < 1 || tokens > 65535) return fail(LISA_ERR_BAD_ARG, "invalid GGUF matvec input rows");
+    if ((reinterpret_cast<uintptr_t>(w) & 1u) != 0) return fail(LISA_ERR_MISALIGNED, "packed_matvec: weights must be 2-byte aligned");
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 3u) != 0)
+        return fail(LISA_ERR_MISALIGNED, "packed_matvec: x must be 16-byte and y 4-byte aligned");
+    return gguf_matvec(static_cast<cudaStream_t>(stream), format, w, 1, rows, row_bytes, x, tokens, 1, nullptr, 1, y);
+}
+
+int lisa_cuda_gguf_expert_matvec(lisa_stream_t stream, int format, const uint8_t *w, int64_t experts, int64_t rows,
+                                 int64_t row_bytes, const float *x, int64_t tokens, int64_t slots, const int32_t *ids,
+                                 int64_t top_k, float *y) {
+    int block = 0;
+    int rc = gguf_geometry("expert_matvec", format, rows, row_bytes, &block);
+    if (rc != LISA_OK) return rc;
+    if (!w || !x || !y || !ids) return fail(LISA_ERR_BAD_ARG, "expert_matvec: null pointer");
+    // deepseek41.rs:216-228
+    if (experts < 1 || tokens < 1 || tokens > 65535 || top_k < 1 || top_k > 32 || (slots != 1 && slots != top_k))
+        return fail(LISA_ERR_BAD_ARG, "invalid GGUF expert matvec geometry");
+    if ((reinterpret_cast<uintptr_t>(w) & 1u) != 0) return fail(LISA_ERR_MISALIGNED, "expert_matvec: weights must be 2-byte aligned");
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 3u) != 0 || (reinterpret_cast<uintptr_t>(ids) & 3u) != 0)
+        return fail(LISA_ERR_MISALIGNED, "expert_matvec: x must be 16-byte, y and ids 4-byte aligned");
+    return gguf_matvec(static_cast<cudaStream_t>(stream), format, w, experts, rows, row_bytes, x, tokens, slots, ids, top_k, y);
+}
+
+int lisa_cuda_moe_route(lisa_stream_t stream, const float *logits, int64_t tokens, int64_t experts, int top_k,
+                        int32_t *idx, float *weights) {
+    if (!logits || !idx || !weights) return fail(LISA_ERR_BAD_ARG, "moe_route: null pointer");
+    if (tokens < 1 || experts < 1 || top_k < 1 || top_k > experts) return fail(LISA_ERR_BAD_ARG, "moe_route: bad sizes");
+    if (top_k > 32 || experts > 1024) return fail(LISA_ERR_LIMIT, "moe_route: top_k <= 32 and experts <= 1024");
+    return moe_route(static_cast<cudaStream_t>(stream), logits, tokens, experts, top_k, idx, weights);
+}
+
+size_t lisa_cuda_moe_sort_workspace_bytes(int64_t slots, int64_t experts) { return moe_sort_workspace_bytes(slots, experts); }
+
+int lisa_cuda_moe_sort(lisa_stream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k,
+                       int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse, void *workspace,
+                       size_t workspace_bytes) {
+    if (!idx || !sorted_ids || !token_rows || !inverse) return fail(LISA_ERR_BAD_ARG, "moe_sort: null pointer");
+    if (slots < 1 || experts < 1 || top_k < 1 || slots > (1ll << 30)) return fail(LISA_ERR_BAD_ARG, "moe_sort: bad sizes");
+    if (experts > 4096) return fail(LISA_ERR_LIMIT, "moe_sort: experts <= 4096");
+    if (!workspace || workspace_bytes < moe_sort_workspace_bytes(slots, experts))
+        return fail(LISA_ERR_WORKSPACE, "moe_sort: workspace missing or too small");
+    if (!aligned16(workspace)) return fail(LISA_ERR_MISALIGNED, "moe_sort: workspace must be 16-byte aligned");
+    return moe_sort(static_cast<cudaStream_t>(stream), idx, slots, experts, top_k, sorted_ids, token_rows, inverse,
+                    workspace);
+}
+
+int lisa_cuda_gather_rows(lisa_stream_t stream, const void *x, const int32_t *token_rows, int64_t rows, int64_t width,
+                          int dtype, void *out) {
+    if (!x || !token_rows || !out) return fail(LISA_ERR_BAD_ARG, "gather_rows: null pointer");
+    if (rows < 1 || width < 1) return fail(LISA_ERR_BAD_ARG, "gather_rows: bad sizes");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "gather_rows: bf16 only");
+    if (width % 8 != 0 || !aligned16(x) || !aligned16(out))
+        return fail(LISA_ERR_MISALIGNED, "gather_rows: width must be a multiple of 8 and pointers 16-byte aligned");
+    return moe_gather_rows(static_cast<cudaStream_t>(stream), x, token_rows, rows, width, out);
+}
+
+int lisa_cuda_swiglu(lisa_stream_t stream, const void *gate, const void *up, int64_t count, int dtype, void *act) {
+    if (!gate || !up || !act) return fail(LISA_ERR_BAD_ARG, "swiglu: null pointer");
+    if (count < 1) return fail(LISA_ERR_BAD_ARG, "swiglu: bad size");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "swiglu: bf16 only");
+    return moe_swiglu(static_cast<cudaStream_t>(stream), gate, up, count, act);
+}
+
+int lisa_cuda_moe_combine(lisa_stream_t stream, const void *down_sorted, const float *weights, const int32_t *inverse,
+                          int64_t tokens, int top_k, int64_t hidden, int dtype, void *out) {
+    if (!down_sorted || !weights || !inverse || !out) return fail(LISA_ERR_BAD_ARG, "moe_combine: null pointer");
+    if (tokens < 1 || top_k < 1 || hidden < 1) return fail(LISA_ERR_BAD_ARG, "moe_combine: bad sizes");
+    if (top_k > 32) return fail(LISA_ERR_LIMIT, "moe_combine: top_k <= 32");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "moe_combine: bf16 only");
+    return moe_combine(static_cast<cudaStream_t>(stream), down_sorted, weights, inverse, tokens, top_k, hidden, out);
+}
+
+}  // extern "C"

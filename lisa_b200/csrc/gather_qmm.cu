@@ -1,0 +1,107 @@
+// MoE routed-expert matmul: y[r, :] = x[r, :] . dequant(W[ids[r]])^T for rows sorted by expert.
+//
+// Replaces ops::gather_qmm -> gather_qmm_rhs_nax / the per-run host loop
+// (crates/lisa-mlx/src/ops/array_ops.rs:561-642, crates/lisa-mlx/src/jit/nax.rs:224-301).
+// Unlike the reference's non-NAX path there is no host read-back of the ids: the expert of
+// every row is looked up on the device.
+//
+// Rows-per-expert decides the kernel: few rows per expert (decode, small batches) is a
+// weight-streaming problem handled by gather_qmv_kernel, one warp per (row, output column);
+// many rows per expert is a grouped GEMM over a tile table (qmm_affine.cu).
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lisa {
+
+struct GatherParams {
+    const uint32_t *w;
+    const uint16_t *scales;
+    const uint16_t *biases;
+    const uint16_t *x;
+    const int32_t *ids;
+    uint16_t *y;
+    int64_t expert_words;   // n * k * bits / 32
+    int64_t expert_groups;  // n * k / group_size
+    int n, k, experts, group_size, words_per_row, groups_per_row;
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(256) gather_qmv_kernel(const GatherParams p, int64_t row_base) {
+    constexpr int CPW = 32 / BITS;
+    const int lane = threadIdx.x & 31;
+    const int col = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t row = row_base + blockIdx.y;
+    if (col >= p.n) return;
+    const int e = __ldg(p.ids + row);
+    if (e < 0 || e >= p.experts) {  // no weight access for an id outside the table
+        if (lane == 0) p.y[row * p.n + col] = 0;
+        return;
+    }
+    const uint32_t *wr = p.w + e * p.expert_words + static_cast<int64_t>(col) * p.words_per_row;
+    const uint16_t *sr = p.scales + e * p.expert_groups + static_cast<int64_t>(col) * p.groups_per_row;
+    const uint16_t *br = p.biases + e * p.expert_groups + static_cast<int64_t>(col) * p.groups_per_row;
+    const uint16_t *xr = p.x + row * p.k;
+    float result = 0.f;
+    for (int wi = lane; wi < p.words_per_row; wi += 32) {
+        const uint32_t word = __ldg(wr + wi);
+        const int k0 = wi * CPW;
+        const int g = k0 / p.group_size;
+        float accum = 0.f, xsum = 0.f;
+#pragma unroll
+        for (int j = 0; j < CPW; j += 2) {
+            const uint32_t xx = __ldg(reinterpret_cast<const uint32_t *>(xr + k0 + j));
+            const float x0 = bf16_bits_to_f32(xx & 0xffffu), x1 = __uint_as_float(xx & 0xffff0000u);
+            const uint32_t q0 = (word >> (j * BITS)) & ((1u << BITS) - 1u);
+            const uint32_t q1 = (word >> ((j + 1) * BITS)) & ((1u << BITS) - 1u);
+            accum = fmaf(x0, static_cast<float>(q0), accum);
+            accum = fmaf(x1, static_cast<float>(q1), accum);
+            xsum += x0 + x1;
+        }
+        result = fmaf(bf16_bits_to_f32(__ldg(sr + g)), accum, result);
+        result = fmaf(bf16_bits_to_f32(__ldg(br + g)), xsum, result);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) result += __shfl_xor_sync(0xffffffffu, result, off);
+    if (lane == 0) p.y[row * p.n + col] = static_cast<uint16_t>(f32_to_bf16_bits(result));
+}
+
+size_t gather_qmm_workspace_bytes(int64_t rows, int64_t experts) {
+    // Tile table of the grouped GEMM: (ceil(rows/128) + experts) tiles of 4 int32, plus a counter block.
+    const int64_t tiles = (rows + 127) / 128 + experts;
+    return static_cast<size_t>(tiles * 16 + 256);
+}
+
+int gather_qmm_affine(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
+                      const void *scales, const void *biases, const int32_t *ids, int64_t experts, int64_t n,
+                      int group_size, int bits, void *y, void *workspace, size_t workspace_bytes) {
+    (void)workspace;
+    (void)workspace_bytes;
+    GatherParams p{};
+    p.w = w;
+    p.scales = reinterpret_cast<const uint16_t *>(scales);
+    p.biases = reinterpret_cast<const uint16_t *>(biases);
+    p.x = reinterpret_cast<const uint16_t *>(x);
+    p.ids = ids;
+    p.y = reinterpret_cast<uint16_t *>(y);
+    p.n = static_cast<int>(n);
+    p.k = static_cast<int>(k);
+    p.experts = static_cast<int>(experts);
+    p.group_size = group_size;
+    p.words_per_row = static_cast<int>(k * bits / 32);
+    p.groups_per_row = static_cast<int>(k / group_size);
+    p.expert_words = n * p.words_per_row;
+    p.expert_groups = n * p.groups_per_row;
+    const unsigned gx = static_cast<unsigned>((n + 7) / 8);
+    for (int64_t base = 0; base < rows; base += 65535) {
+        const unsigned gy = static_cast<unsigned>(rows - base < 65535 ? rows - base : 65535);
+        if (bits == 4) gather_qmv_kernel<4><<<dim3(gx, gy), 256, 0, stream>>>(p, base);
+        else gather_qmv_kernel<2><<<dim3(gx, gy), 256, 0, stream>>>(p, base);
+        LISA_CUDA_TRY(cudaGetLastError());
+        count_launch();
+    }
+    return LISA_OK;
+}
+
+}  // namespace lisa

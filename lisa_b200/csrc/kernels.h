@@ -1,0 +1,48 @@
+// Internal launch functions, one group per translation unit.  Arguments are already
+// validated by api.cu; every function enqueues on `stream` and returns a lisa_status.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace lisa {
+
+// qmv_affine.cu
+int qmv_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+               const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
+int qmv_device_status();
+
+// qmm_affine.cu
+bool qmm_affine_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);
+int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+               const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
+int qmm_device_status();
+
+// dequantize.cu
+int dequantize_affine(cudaStream_t stream, const uint32_t *w, const void *scales, const void *biases, int64_t rows,
+                      int64_t k, int group_size, int bits, void *out);
+
+// gather_qmm.cu
+size_t gather_qmm_workspace_bytes(int64_t rows, int64_t experts);
+int gather_qmm_affine(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
+                      const void *scales, const void *biases, const int32_t *ids, int64_t experts, int64_t n,
+                      int group_size, int bits, void *y, void *workspace, size_t workspace_bytes);
+
+// gguf_matvec.cu: ids == nullptr selects the dense matvec (experts = slots = top_k = 1).
+int gguf_matvec(cudaStream_t stream, int format, const uint8_t *w, int64_t experts, int64_t rows, int64_t row_bytes,
+                const float *x, int64_t tokens, int64_t slots, const int32_t *ids, int64_t top_k, float *y);
+
+// moe.cu
+int moe_route(cudaStream_t stream, const float *logits, int64_t tokens, int64_t experts, int top_k, int32_t *idx,
+              float *weights);
+size_t moe_sort_workspace_bytes(int64_t slots, int64_t experts);
+int moe_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k, int32_t *sorted_ids,
+             int32_t *token_rows, int32_t *inverse, void *workspace);
+int moe_gather_rows(cudaStream_t stream, const void *x, const int32_t *token_rows, int64_t rows, int64_t width,
+                    void *out);
+int moe_swiglu(cudaStream_t stream, const void *gate, const void *up, int64_t count, void *act);
+int moe_combine(cudaStream_t stream, const void *down_sorted, const float *weights, const int32_t *inverse,
+                int64_t tokens, int top_k, int64_t hidden, void *out);
+
+}  // namespace lisa

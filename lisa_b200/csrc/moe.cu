@@ -1,0 +1,276 @@
+// Routing kernels around gather_qmm: top-k route, stable sort of slots by expert, row
+// gather, SwiGLU and the weighted un-sort.
+//
+// Replaces track_moe_route (crates/lisa-mlx/src/shaders/qwen4/route.metal), the two-launch
+// counting sort (crates/lisa-mlx/src/shaders/qwen4/route_counting_scatter.metal,
+// crates/lisa-mlx/src/models/qwen4/kernels/moe.rs:72-77), bf16 SwiGLU
+// (crates/lisa-mlx/src/shaders/common/exact_header.metal:2-11) and moe_combine without its
+// shared-expert term (crates/lisa-mlx/src/shaders/qwen4/moe_combine.metal); the call order
+// is that of SparseMoeBlock::forward (crates/lisa-engine/src/models/qwen4/moe.rs:352-481).
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lisa {
+
+// ---------------------------------------------------------------- route
+// One warp per token.  k rounds of "largest logit not yet taken, ties to the lowest
+// expert index"; weights = softmax over the k selected logits in f32.
+constexpr int kRouteMaxPerLane = 32;  // experts <= 1024
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict__ logits, int tokens, int experts,
+                                                        int top_k, int32_t *__restrict__ idx,
+                                                        float *__restrict__ weights) {
+    const int lane = threadIdx.x & 31;
+    const int token = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (token >= tokens) return;
+    const float *l = logits + static_cast<int64_t>(token) * experts;
+    float v[kRouteMaxPerLane];
+    const int per_lane = (experts + 31) / 32;
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+        const int e = i * 32 + lane;
+        v[i] = (i < per_lane && e < experts) ? __ldg(l + e) : -INFINITY;
+    }
+    uint32_t taken = 0;  // bit i: this lane's i-th expert was selected
+    float my_logit = 0.f;
+    int my_idx = 0;
+    float mx = -INFINITY;
+    for (int j = 0; j < top_k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kRouteMaxPerLane; ++i) {
+            const int e = i * 32 + lane;
+            const bool free_slot = i < per_lane && e < experts && !((taken >> i) & 1u);
+            if (free_slot && (v[i] > best || best_e == 0x7fffffff)) {  // first free candidate or strictly larger
+                best = v[i];
+                best_e = e;
+            }
+        }
+        // warp argmax with ties to the lowest index
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+            const bool other_valid = oe != 0x7fffffff, mine_valid = best_e != 0x7fffffff;
+            if (other_valid && (!mine_valid || ob > best || (ob == best && oe < best_e))) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
+        if (j == 0) mx = best;
+        if (lane == j) {
+            my_logit = best;
+            my_idx = best_e;
+        }
+    }
+    // softmax over the selected logits (lane j holds the j-th)
+    float ex = (lane < top_k) ? expf(my_logit - mx) : 0.f;
+    float sum = ex;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane < top_k) {
+        idx[static_cast<int64_t>(token) * top_k + lane] = my_idx;
+        weights[static_cast<int64_t>(token) * top_k + lane] = ex / sum;
+    }
+}
+
+int moe_route(cudaStream_t stream, const float *logits, int64_t tokens, int64_t experts, int top_k, int32_t *idx,
+              float *weights) {
+    const unsigned blocks = static_cast<unsigned>((tokens + 3) / 4);
+    moe_route_kernel<<<blocks, 128, 0, stream>>>(logits, static_cast<int>(tokens), static_cast<int>(experts), top_k,
+                                                 idx, weights);
+    LISA_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return LISA_OK;
+}
+
+// ---------------------------------------------------------------- stable counting sort
+// Slots are cut into chunks of 256.  (1) per-chunk histogram -> counts[chunk][expert];
+// (2) one block turns counts into start offsets (expert-major, chunk-minor);
+// (3) each chunk scatters its slots in order, warp by warp, so equal experts keep their
+// original order.  Workspace: counts, (chunks x experts) int32.
+constexpr int kSortChunk = 256;
+
+size_t moe_sort_workspace_bytes(int64_t slots, int64_t experts) {
+    const int64_t chunks = (slots + kSortChunk - 1) / kSortChunk;
+    return static_cast<size_t>(chunks * experts) * sizeof(int32_t);
+}
+
+__global__ void __launch_bounds__(kSortChunk) moe_sort_hist_kernel(const int32_t *__restrict__ idx, int slots,
+                                                                   int experts, int32_t *__restrict__ counts) {
+    extern __shared__ int32_t hist[];
+    for (int e = threadIdx.x; e < experts; e += kSortChunk) hist[e] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * kSortChunk + threadIdx.x;
+    if (i < slots) {
+        const int e = __ldg(idx + i);
+        if (e >= 0 && e < experts) atomicAdd(&hist[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += kSortChunk) counts[static_cast<int64_t>(blockIdx.x) * experts + e] = hist[e];
+}
+
+// counts[chunk][e] -> exclusive start of (e, chunk) in the sorted order.
+__global__ void __launch_bounds__(1024) moe_sort_scan_kernel(int32_t *__restrict__ counts, int chunks, int experts) {
+    extern __shared__ int32_t totals[];  // experts + 1
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int run = 0;
+        for (int c = 0; c < chunks; ++c) {
+            const int64_t at = static_cast<int64_t>(c) * experts + e;
+            const int v = counts[at];
+            counts[at] = run;
+            run += v;
+        }
+        totals[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < experts; ++e) {
+            const int v = totals[e];
+            totals[e] = run;
+            run += v;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const int base = totals[e];
+        for (int c = 0; c < chunks; ++c) counts[static_cast<int64_t>(c) * experts + e] += base;
+    }
+}
+
+__global__ void __launch_bounds__(kSortChunk) moe_sort_scatter_kernel(const int32_t *__restrict__ idx, int slots,
+                                                                      int experts, int top_k,
+                                                                      const int32_t *__restrict__ counts,
+                                                                      int32_t *__restrict__ sorted_ids,
+                                                                      int32_t *__restrict__ token_rows,
+                                                                      int32_t *__restrict__ inverse) {
+    extern __shared__ int32_t next[];  // next free position per expert for this chunk
+    for (int e = threadIdx.x; e < experts; e += kSortChunk) next[e] = counts[static_cast<int64_t>(blockIdx.x) * experts + e];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int i = blockIdx.x * kSortChunk + threadIdx.x;
+    const bool live = i < slots;
+    const int e = live ? __ldg(idx + i) : -1;
+    const bool ok = live && e >= 0 && e < experts;
+    for (int wv = 0; wv < kSortChunk / 32; ++wv) {
+        if (warp == wv) {
+            const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+            if (ok) {
+                const int rank = __popc(peers & ((1u << lane) - 1u));
+                const int pos = next[e] + rank;
+                sorted_ids[pos] = e;
+                token_rows[pos] = i / top_k;
+                inverse[i] = pos;
+            }
+            __syncwarp();
+            if (ok && (peers >> lane) == 1u) next[e] += __popc(peers);  // highest lane of the group
+        }
+        __syncthreads();
+    }
+}
+
+int moe_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k, int32_t *sorted_ids,
+             int32_t *token_rows, int32_t *inverse, void *workspace) {
+    const int chunks = static_cast<int>((slots + kSortChunk - 1) / kSortChunk);
+    int32_t *counts = reinterpret_cast<int32_t *>(workspace);
+    const size_t esm = static_cast<size_t>(experts) * sizeof(int32_t);
+    moe_sort_hist_kernel<<<chunks, kSortChunk, esm, stream>>>(idx, static_cast<int>(slots), static_cast<int>(experts), counts);
+    LISA_CUDA_TRY(cudaGetLastError());
+    moe_sort_scan_kernel<<<1, 1024, esm + sizeof(int32_t), stream>>>(counts, chunks, static_cast<int>(experts));
+    LISA_CUDA_TRY(cudaGetLastError());
+    moe_sort_scatter_kernel<<<chunks, kSortChunk, esm, stream>>>(idx, static_cast<int>(slots), static_cast<int>(experts),
+                                                                 top_k, counts, sorted_ids, token_rows, inverse);
+    LISA_CUDA_TRY(cudaGetLastError());
+    count_launch(3);
+    return LISA_OK;
+}
+
+// ---------------------------------------------------------------- row gather
+__global__ void __launch_bounds__(256) moe_gather_rows_kernel(const uint4 *__restrict__ x,
+                                                              const int32_t *__restrict__ token_rows, int64_t rows,
+                                                              int vec_per_row, uint4 *__restrict__ out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * vec_per_row) return;
+    const int64_t r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row);
+    out[i] = __ldg(x + static_cast<int64_t>(__ldg(token_rows + r)) * vec_per_row + c);
+}
+
+int moe_gather_rows(cudaStream_t stream, const void *x, const int32_t *token_rows, int64_t rows, int64_t width,
+                    void *out) {
+    const int vec = static_cast<int>(width / 8);
+    const int64_t total = rows * vec;
+    moe_gather_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint4 *>(x), token_rows, rows, vec, reinterpret_cast<uint4 *>(out));
+    LISA_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return LISA_OK;
+}
+
+// ---------------------------------------------------------------- SwiGLU
+__device__ __forceinline__ float round_bf16(float v) { return bf16_bits_to_f32(f32_to_bf16_bits(v)); }
+
+__global__ void __launch_bounds__(256) moe_swiglu_kernel(const uint16_t *__restrict__ gate,
+                                                         const uint16_t *__restrict__ up, int64_t count,
+                                                         uint16_t *__restrict__ act) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const float g = bf16_bits_to_f32(__ldg(gate + i)), u = bf16_bits_to_f32(__ldg(up + i));
+    const float y = 1.0f / (1.0f + expf(fabsf(g)));
+    const float s = round_bf16(g < 0.f ? y : 1.0f - y);
+    const float silu = round_bf16(g * s);
+    act[i] = static_cast<uint16_t>(f32_to_bf16_bits(silu * u));
+}
+
+int moe_swiglu(cudaStream_t stream, const void *gate, const void *up, int64_t count, void *act) {
+    moe_swiglu_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint16_t *>(gate), reinterpret_cast<const uint16_t *>(up), count,
+        reinterpret_cast<uint16_t *>(act));
+    LISA_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return LISA_OK;
+}
+
+// ---------------------------------------------------------------- combine
+// out[t, h] = bf16( fold_j f32(down[inverse[t*k + j], h]) * w[t, j] ), fold order of
+// mlx_colsum_small_f32 (exact_header.metal:12-24).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t *__restrict__ down,
+                                                          const float *__restrict__ weights,
+                                                          const int32_t *__restrict__ inverse, int64_t tokens,
+                                                          int top_k, int64_t hidden, uint16_t *__restrict__ out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= tokens * hidden) return;
+    const int64_t t = i / hidden, h = i - t * hidden;
+    const int ty = top_k < 8 ? top_k : 8;
+    float part[8];
+    for (int y = 0; y < ty; ++y) {
+        float acc = 0.f;
+        for (int rr = y; rr < top_k; rr += ty) {
+            const int64_t row = __ldg(inverse + t * top_k + rr);
+            const float r = bf16_bits_to_f32(__ldg(down + row * hidden + h)) * __ldg(weights + t * top_k + rr);
+            acc = r + acc;
+        }
+        part[y] = acc;
+    }
+    float total = part[0];
+    for (int j = 1; j < ty; ++j) total = part[j] + total;
+    out[i] = static_cast<uint16_t>(f32_to_bf16_bits(total));
+}
+
+int moe_combine(cudaStream_t stream, const void *down_sorted, const float *weights, const int32_t *inverse,
+                int64_t tokens, int top_k, int64_t hidden, void *out) {
+    const int64_t total = tokens * hidden;
+    moe_combine_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint16_t *>(down_sorted), weights, inverse, tokens, top_k, hidden,
+        reinterpret_cast<uint16_t *>(out));
+    LISA_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return LISA_OK;
+}
+
+}  // namespace lisa

@@ -1,0 +1,78 @@
+"""Engine-side holders of quantized weights, mirroring ``lisa-engine``'s callers of the path.
+
+``QuantizedLinear`` / ``detect_group_size`` follow crates/lisa-engine/src/core/quant.rs:273-321;
+``SwitchGlu.forward`` is the generic routed-expert block of
+crates/lisa-engine/src/models/qwen4/moe.rs:352-481 without the Qwen4-specific shared expert.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import ops
+
+
+def detect_group_size(weight_cols: int, scales_cols: int, bits: int) -> Optional[int]:
+    """Group size implied by the packed shapes, or None when they are inconsistent
+    (quant.rs:273-287)."""
+    if weight_cols <= 0 or scales_cols <= 0 or bits <= 0 or 32 % bits != 0:
+        return None
+    k = weight_cols * (32 // bits)
+    if k % scales_cols != 0:
+        return None
+    group = k // scales_cols
+    return group if 1 <= group <= 4096 else None
+
+
+@dataclass
+class QuantizedLinear:
+    """weight uint32 [N, K*bits/32]; scales, biases bf16 [N, K/group_size] (quant.rs:292-299)."""
+    weight: torch.Tensor
+    scales: torch.Tensor
+    biases: torch.Tensor
+    group_size: int = 64
+    bits: int = 4
+
+    def dims_out(self) -> int:
+        return self.weight.shape[0]
+
+    def forward(self, x: torch.Tensor, *, flags: int = 0) -> torch.Tensor:
+        """[..., K] -> [..., N]; the input is flattened to 2-D first (quant.rs:306-321)."""
+        k = x.shape[-1]
+        flat = x.reshape(-1, k)
+        out = ops.quantized_matmul(flat, self.weight, self.scales, self.biases, True, self.group_size,
+                                   self.bits, flags=flags)
+        return out.reshape(*x.shape[:-1], self.dims_out())
+
+    def forward_serial_rows(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.quantized_matmul_serial_rows(x, self.weight, self.scales, self.biases, True,
+                                                self.group_size, self.bits)
+
+
+@dataclass
+class SwitchGlu:
+    """Routed experts: gate/up [E, inter, hidden*bits/32], down [E, hidden, inter*bits/32]."""
+    gate: QuantizedLinear
+    up: QuantizedLinear
+    down: QuantizedLinear
+    top_k: int
+
+    def forward(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        """x [tokens, hidden] bf16, router_logits f32 [tokens, E] -> [tokens, hidden]:
+        route, stable sort by expert, gate/up gather_qmm, SwiGLU, down gather_qmm, weighted
+        un-sort (moe.rs:352-481)."""
+        experts = self.gate.weight.shape[0]
+        gs, bits = self.gate.group_size, self.gate.bits
+        idx, weights = ops.moe_route(router_logits, self.top_k)
+        sorted_ids, token_rows, inverse = ops.moe_sort(idx, experts, self.top_k)
+        x_sorted = ops.gather_rows(x, token_rows)
+        g = ops.gather_qmm(x_sorted, self.gate.weight, self.gate.scales, self.gate.biases, None, sorted_ids,
+                           True, gs, bits, True)
+        u = ops.gather_qmm(x_sorted, self.up.weight, self.up.scales, self.up.biases, None, sorted_ids,
+                           True, gs, bits, True)
+        act = ops.swiglu(g, u)
+        d = ops.gather_qmm(act, self.down.weight, self.down.scales, self.down.biases, None, sorted_ids,
+                           True, gs, bits, True)
+        return ops.moe_combine(d, weights, inverse, self.top_k)

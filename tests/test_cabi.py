@@ -1,0 +1,99 @@
+"""The C-ABI library loads without a GPU, exports every symbol the header declares, and
+rejects bad arguments on the host before touching CUDA."""
+import ctypes
+import os
+import re
+
+import pytest
+
+import __graft_entry__ as entry
+from lisa_b200 import _cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(_cabi.LIB_PATH):
+        entry.build()
+    return _cabi.lib()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "lisa_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(lisa_cuda_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 18
+    for name in names:
+        assert hasattr(lib, name), name
+    assert set(names) == set(_cabi.SIGNATURES), "ctypes table and header disagree"
+
+
+def test_version(lib):
+    assert lib.lisa_cuda_version() >= 100
+
+
+def _qmm(lib, **kw):
+    a = dict(stream=None, x=16, m=1, k=64, w=16, scales=16, biases=16, n=8, transpose=1, gs=64, bits=4, dtype=0, y=16)
+    a.update(kw)
+    return lib.lisa_cuda_quantized_matmul(a["stream"], a["x"], a["m"], a["k"], a["w"], a["scales"], a["biases"],
+                                          a["n"], a["transpose"], a["gs"], a["bits"], a["dtype"], a["y"])
+
+
+def test_quantized_matmul_rejections_mirror_the_reference(lib):
+    # array_ops.rs:387-392: transpose=false and missing biases are refused
+    assert _qmm(lib, transpose=0) == _cabi.ERR_UNSUPPORTED
+    assert "only transpose=true supported" in _cabi.last_error()
+    assert _qmm(lib, biases=None) == _cabi.ERR_BAD_ARG
+    assert "affine biases required" in _cabi.last_error()
+    assert _qmm(lib, bits=3) == _cabi.ERR_UNSUPPORTED
+    assert _qmm(lib, gs=48) == _cabi.ERR_UNSUPPORTED
+    assert _qmm(lib, dtype=2) == _cabi.ERR_UNSUPPORTED
+    assert _qmm(lib, k=96) == _cabi.ERR_BAD_ARG  # not a multiple of the group size
+    assert _qmm(lib, m=0) == _cabi.ERR_BAD_ARG
+    assert _qmm(lib, x=8) == _cabi.ERR_MISALIGNED
+    assert _qmm(lib, k=1 << 31) == _cabi.ERR_OVERFLOW
+
+
+def test_gather_qmm_rejections(lib):
+    def call(**kw):
+        a = dict(x=16, rows=4, k=64, w=16, s=16, b=16, lhs=None, rhs=16, e=2, n=8, t=1, gs=64, bits=4, sorted=1,
+                 dtype=0, y=16, ws=None, wsb=0)
+        a.update(kw)
+        return lib.lisa_cuda_gather_qmm(None, a["x"], a["rows"], a["k"], a["w"], a["s"], a["b"], a["lhs"], a["rhs"],
+                                        a["e"], a["n"], a["t"], a["gs"], a["bits"], a["sorted"], a["dtype"], a["y"],
+                                        a["ws"], a["wsb"])
+    # array_ops.rs:573-585
+    assert call(t=0) == _cabi.ERR_UNSUPPORTED
+    assert call(lhs=16) == _cabi.ERR_UNSUPPORTED and "lhs_indices path not ported" in _cabi.last_error()
+    assert call(sorted=0) == _cabi.ERR_UNSUPPORTED
+    assert call(rhs=None) == _cabi.ERR_BAD_ARG and "rhs_indices required" in _cabi.last_error()
+    assert call(b=None) == _cabi.ERR_BAD_ARG
+    assert call() == _cabi.ERR_WORKSPACE  # no workspace given
+    assert lib.lisa_cuda_gather_qmm_workspace_bytes(512, 128) > 0
+
+
+def test_gguf_rejections(lib):
+    f = lib.lisa_cuda_gguf_packed_matvec
+    # deepseek41.rs:50-65,100-101
+    assert f(None, 10, 16, 12, 84, 16, 1, 16) == _cabi.ERR_BAD_ARG      # rows % 8
+    assert f(None, 10, 16, 16, 85, 16, 1, 16) == _cabi.ERR_BAD_ARG      # row_bytes % block
+    assert f(None, 10, 16, 16, 84, 16, 0, 16) == _cabi.ERR_BAD_ARG      # tokens < 1
+    assert f(None, 10, 16, 16, 84, 16, 65536, 16) == _cabi.ERR_BAD_ARG  # tokens > 65535
+    assert f(None, 11, 16, 16, 84, 16, 1, 16) == _cabi.ERR_UNSUPPORTED  # Q3_K is not on the path
+    g = lib.lisa_cuda_gguf_expert_matvec
+    assert g(None, 12, 16, 4, 8, 144, 16, 2, 3, 16, 6, 16) == _cabi.ERR_BAD_ARG   # slots not in {1, top_k}
+    assert g(None, 12, 16, 4, 8, 144, 16, 2, 1, 16, 33, 16) == _cabi.ERR_BAD_ARG  # top_k > 32
+
+
+def test_product_package_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "lisa_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower() or f == "__never__", f"{f} mentions the oracle"

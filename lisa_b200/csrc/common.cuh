@@ -80,16 +80,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)  // may sleep up to ~2 us before reporting "not yet"
         : "memory");
     return ok != 0;
 }
 // Bounded wait: gives up after `limit` polls and returns false, so a lost
 // arrival ends in an error status instead of a hung GPU.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
-                                          uint32_t limit = 20000000u) {
+                                          uint32_t limit = 4000000u) {
     for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;

@@ -23,10 +23,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-#include <mutex>
-
 #include "common.cuh"
 #include "kernels.h"
+#include "tensor_map.h"
 
 namespace lisa {
 
@@ -400,36 +399,12 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 // ---------------------------------------------------------------------------------------
 // Host side: tensor maps and launch.
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, []() {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    });
-    return fn;
-}
-
-static int make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, const void *base, uint64_t inner,
-                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return fail(LISA_ERR_CUDA, "qmm: cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {row_stride_bytes};
-    cuuint32_t box[2] = {box_inner, box_outer};
-    cuuint32_t estr[2] = {1, 1};
-    (void)elem_bytes;
-    CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(LISA_ERR_CUDA, "qmm: cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
-    return LISA_OK;
+static int make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+    const uint64_t dims[2] = {inner, outer};
+    const uint64_t strides[1] = {row_stride_bytes};
+    const uint32_t box[2] = {box_inner, box_outer};
+    return make_tensor_map(map, dt, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 bool qmm_affine_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits) {
@@ -461,11 +436,11 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
     p.num_kb = static_cast<int>((k + kBK - 1) / kBK);
 
     CUtensorMap map_x, map_w;
-    int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, static_cast<uint64_t>(k),
+    int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, static_cast<uint64_t>(k),
                          static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBK, static_cast<uint32_t>(bt));
     if (rc != LISA_OK) return rc;
     const uint64_t wrow_bytes = static_cast<uint64_t>(k) * bits / 8;
-    rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, wrow_bytes, static_cast<uint64_t>(n), wrow_bytes, 128,
+    rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, wrow_bytes, static_cast<uint64_t>(n), wrow_bytes, 128,
                      kBN);
     if (rc != LISA_OK) return rc;
 

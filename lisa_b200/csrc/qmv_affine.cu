@@ -1,29 +1,47 @@
-// Decode GEMV for MLX affine 2-/4-bit weights: y[m, n] = sum_k x[m, k] * (scale * q + bias).
+// Decode GEMV for MLX affine 2-/4-bit weights: y[m, n] = sum_k x[m, k] * (scale * q + bias), m <= 8
+// rows of x per launch.
 //
-// Replaces affine_qmv_fast / affine_qmv / affine_qmv_wide
+// Replaces affine_qmv_fast / affine_qmv / affine_qmv_wide and the small-M verify tiles
 // (crates/lisa-mlx/src/shaders/common/matmul/quantized.metal:762-1088, host side
-// crates/lisa-mlx/src/jit/matmul.rs:186-302,1799-1869).  Same factorisation as the
-// reference's qdot (quantized.metal:196-295): per group  scale * sum(q*x) + bias * sum(x),
-// accumulated in f32, rounded once to bf16.
+// crates/lisa-mlx/src/jit/matmul.rs:186-302,1799-1869).  Same factorisation as the reference's
+// qdot (quantized.metal:196-295): per 64 codes  scale * sum(q*x) + bias * sum(x), in f32, one
+// rounding to bf16 at the end.
 //
-// Streaming kernel (qmv_stream_kernel): one persistent CTA per SM (or two), each owning a
-// contiguous range of output rows, so the packed rows, scales and biases it needs are three
-// contiguous byte ranges.  A producer warp moves them into a shared-memory ring with bulk
-// async copies (TMA, untiled) that complete on mbarriers; consumer warps split K between
-// all their threads, decode codes in registers (qmv_math.h) and keep one accumulator per
-// row of the tile; a transposed warp-shuffle reduction plus one cross-warp step finishes a
-// tile.  Weights never depend on the previous kernel in the stream, so the producer starts
-// before griddepcontrol.wait: launched with programmatic stream serialization the ring of
-// kernel i+1 fills while kernel i drains.
+// Two measured facts of sm_100 shape the kernel.  (1) The SM-to-L2 path moves one request of up
+// to 128 bytes every few clocks: loads that touch 32 or 64 bytes of a line reach a quarter or a
+// half of HBM speed whatever the prefetch depth, so packed rows are fetched as whole 128-byte
+// lines by tiled TMA copies, never by per-lane loads shaped like an MMA fragment.  (2) The
+// logic/shift pipe issues 64 lanes per clock per SM, half the FMA rate, and a 4-bit stream at
+// HBM speed delivers about 45 codes per clock per SM: one LOP3 per code is that pipe's whole
+// budget.  Here one LOP3 lifts TWO codes into a bf16 pair (mask 0x000F000F, OR 0x43004300: each
+// half is 128 + q exactly), the pairs are the A fragments of mma.sync.m16n8k16 (bf16 x bf16, f32
+// accumulate, products exact), the activations are the B fragment, and the constant 128 is
+// removed with sum(x):  sum(q*x) = sum((128+q)*x) - 128*sum(x).  The kernel stays a
+// weight-streaming GEMV bound by HBM; the tensor pipe is nearly idle.
 //
-// Generic kernel (qmv_simple_kernel): one warp per output row, direct coalesced loads; any
-// shape, any m.  Used when the streaming kernel's shared-memory plan does not fit.
+// Streaming kernel (qmv_mma_kernel): persistent CTAs, each owning a contiguous range of output
+// rows walked in tiles of 16 rows.  A producer warp fills a shared-memory ring with one 3-D
+// tensor copy per stage (box: 128 bytes x L lines x 16 rows, 128-byte swizzle; a ragged last
+// tile uses single-row boxes at the same offsets), completing on mbarriers.  With L = 2 mod 4
+// (4-bit) or L odd (2-bit) the swizzle makes the fragment-shaped shared-memory reads of the
+// eight consumer warps bank-conflict free.  The consumers split the 64-code units of a stage
+// between them; scales and biases of the next tile arrive through cp.async while the current
+// tile computes; the activations are staged once per CTA and permuted in place into B-fragment
+// order.  A tile ends with one cross-warp reduction.  Weights do not depend on the previous
+// kernel in the stream, so the producer runs ahead of griddepcontrol.wait: launched with
+// programmatic stream serialization, the ring of kernel i+1 fills while kernel i drains.
+//
+// Generic kernel (qmv_simple_kernel): one warp per output row, direct loads, plain f32 math;
+// any shape.  Used for group size 32, for rows that are not whole 128-byte lines and when the
+// shared-memory plan does not fit.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
 
 #include "common.cuh"
-#include "qmv_math.h"
+#include "kernels.h"
+#include "tensor_map.h"
 
 namespace lisa {
 
@@ -35,63 +53,59 @@ int qmv_device_status() {
     return v;
 }
 
+constexpr int kTileRows = 16;  // MMA M
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kQmvThreads = kConsumers + 32;  // + producer warp
+constexpr int kMaxStages = 8;
+
 struct QmvParams {
-    const uint8_t *w;
     const uint8_t *scales;
     const uint8_t *biases;
     const uint16_t *x;
     uint16_t *y;
-    int n, k, m;
-    int wrow_bytes;   // K * bits / 8
-    int srow_bytes;   // (K / group_size) * 2
-    int nchunks;      // 8-byte chunks per packed row
-    int gshift;       // chunk index >> gshift = group index
-    int stages;       // ring depth
-    int stage_bytes;  // bytes of one ring stage (multiple of 128)
-    int w_region;     // bytes reserved for packed rows in a stage (multiple of 16)
-    int s_region;     // bytes reserved for scales (and for biases) in a stage
-    int consumers;    // consumer threads (multiple of 32)
-    int w_bulk, s_bulk;  // 1: rows are multiples of 16 bytes, bulk copies allowed
+    int n, k, m;        // m <= 8
+    int srow_bytes;     // (K / group_size) * 2
+    int units;          // K / 64
+    int ushift;         // unit >> ushift = group (0 for group 64, 1 for group 128)
+    int xstride;        // bytes between rows of the staged activations (padded)
+    int s_chunk;        // async-copy granularity of scale rows: 16, 8 or 4 bytes; 0: 2-byte plain copies
+    int l1, n1, l2;     // k-segments of a row: n1 segments of l1 lines, then one of l2 lines (l2 may be 0)
+    int stages;
+    int stage_bytes;    // 16 * max(l1, l2) * 128
 };
 
-template <int BITS>
-struct QmvGeom {
-    static constexpr int kCodesPerChunk = 64 / BITS;       // one chunk = two words = 8 bytes
-    static constexpr int kQuads = kCodesPerChunk / 4;      // float4 of pre-scaled x per chunk
-    static constexpr int kPairsPerWord = QmvCode<BITS>::kPairsPerWord;
-};
-
-// Shared-memory plan (bytes), shared by host and device.
+// Shared-memory plan (bytes from the 1024-aligned base), shared by host and device.
 struct QmvSmemPlan {
-    int bars, xt, sx, xu, part, ring, total;
+    int ring, xb, xsum, sc, st, part, bars, total;
 };
-template <int BITS>
-__host__ __device__ inline QmvSmemPlan qmv_plan(int k, int m, int nwarps, int tr, int stages,
+__host__ __device__ inline QmvSmemPlan qmv_plan(int units, int m, int xstride, int srow_bytes, int stages,
                                                 int stage_bytes) {
     QmvSmemPlan p;
-    const int nchunks = k / QmvGeom<BITS>::kCodesPerChunk;
-    p.bars = 0;
-    int off = 256;  // [0,128): 2 * stages mbarriers (stages <= 8); [128,132): abort flag
-    p.xt = off;
-    off += m * k * 4;
-    p.sx = off;
-    off += m * nchunks * 4;
-    p.xu = off;
-    off += m * nchunks * 4;
-    off = (off + 15) & ~15;
-    p.part = off;
-    off += 2 * nwarps * tr * m * 4;
-    off = (off + 127) & ~127;
-    p.ring = off;
+    int off = 0;
+    p.ring = off;            // stages x stage_bytes, every stage 1024-aligned (swizzle atom)
     off += stages * stage_bytes;
-    p.total = off;
+    p.xb = off;
+    off += m * xstride;      // activations, permuted in place into B fragments
+    off = (off + 15) & ~15;
+    p.xsum = off;
+    off += units * 8 * 4;    // sum(x) per unit and column
+    off = (off + 15) & ~15;
+    p.sc = off;              // raw [scales | biases][16 rows][srow_bytes], as fetched
+    off += 2 * ((kTileRows * srow_bytes + 15) & ~15);
+    p.st = off;              // [2 buffers][16 rows][groups] of f32 {scale, bias - 128 * scale}
+    off += 2 * kTileRows * (srow_bytes / 2) * 8;
+    p.part = off;
+    off += 2 * kConsumerWarps * 128 * 4;
+    p.bars = off;            // 2 * kMaxStages mbarriers, abort flag
+    off += 2 * kMaxStages * 8 + 16;
+    p.total = off + 1024;    // slack to align the base
     return p;
 }
 
-// Bounded wait shared by producer and consumers: once any thread of the CTA has given up,
-// every later wait returns at once so that all threads still reach every barrier.
-__device__ __forceinline__ void wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                              int code) {
+// Bounded wait: once any thread of the CTA has given up, every later wait returns at once so
+// that all threads still reach every barrier and the kernel ends with an error status.
+__device__ __forceinline__ void wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int code) {
     if (*abort_flag) return;
     if (!mbar_wait(bar, parity)) {
         *abort_flag = 1;
@@ -99,74 +113,139 @@ __device__ __forceinline__ void wait_or_abort(uint64_t *bar, uint32_t parity, vo
     }
 }
 
-// Transposed butterfly: on return lane l holds in v[0] the warp-wide sum of value index
-// `reduced_index<NV>(l)`.
-template <int NV>
-__device__ __forceinline__ void warp_reduce_many(float (&v)[NV], int lane) {
-    int n = NV;
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-        if (n > 1) {
-            n >>= 1;
-            const bool upper = (lane & off) != 0;
-#pragma unroll
-            for (int i = 0; i < NV / 2; ++i) {
-                if (i < n) {
-                    const float send = upper ? v[i] : v[i + n];
-                    const float keep = upper ? v[i + n] : v[i];
-                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-                }
-            }
-        } else {
-            v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
-        }
-    }
-}
-template <int NV>
-__device__ __forceinline__ int reduced_index(int lane) {
-    int n = NV, idx = 0;
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-        if (n > 1) {
-            n >>= 1;
-            if (lane & off) idx += n;
-        }
-    }
-    return idx;
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int c0, int c1, int c2, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
 }
 
-template <int BITS, int TR, int MT>
-__global__ void __launch_bounds__(288, 1) qmv_stream_kernel(const QmvParams p) {
-    using G = QmvGeom<BITS>;
-    using Code = QmvCode<BITS>;
-    constexpr int NV = TR * MT;
-    extern __shared__ __align__(128) uint8_t smem[];
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int BITS>
+struct UnitGeom {
+    static constexpr int kUnitBytes = 64 * BITS / 8;   // packed bytes of 64 codes: 32 (4-bit), 16 (2-bit)
+    static constexpr int kLaneBytes = kUnitBytes / 4;  // per lane of a 4-lane group: 8 / 4
+    static constexpr int kUnitsPerLine = 128 / kUnitBytes;
+};
+
+// Shared-memory loads by 32-bit shared-space address (keeps the address math in 32 bits).
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+    return v;
+}
+
+// Eight bf16 pairs (128 + q each) from the 16 codes a lane owns, in the order the four MMAs of
+// a unit consume them.  Pair i holds codes (lo_k(i), hi_k(i)) of the lane's 16 consecutive k.
+template <int BITS>
+__device__ __forceinline__ void decode16(uint32_t src, uint32_t m, uint32_t c, uint32_t (&r)[8]);
+// (a & b) | c in one LOP3 with all three operands in registers (two immediates would cost two).
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// A constant the compiler must keep in a register.
+__device__ __forceinline__ uint32_t reg_const(uint32_t v) {
+    uint32_t d;
+    asm volatile("mov.u32 %0, %1;" : "=r"(d) : "r"(v));
+    return d;
+}
+template <>
+__device__ __forceinline__ void decode16<4>(uint32_t src, uint32_t m, uint32_t c, uint32_t (&r)[8]) {
+    const uint2 v = lds_v2(src);
+    r[0] = and_or(v.x, m, c);
+    r[1] = and_or(v.x >> 4, m, c);
+    r[2] = and_or(v.x >> 8, m, c);
+    r[3] = and_or(v.x >> 12, m, c);
+    r[4] = and_or(v.y, m, c);
+    r[5] = and_or(v.y >> 4, m, c);
+    r[6] = and_or(v.y >> 8, m, c);
+    r[7] = and_or(v.y >> 12, m, c);
+}
+template <>
+__device__ __forceinline__ void decode16<2>(uint32_t src, uint32_t m, uint32_t c, uint32_t (&r)[8]) {
+    const uint32_t v = lds_u32(src);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = and_or(v >> (2 * i), m, c);
+}
+// The lane's 16 consecutive activations (8 words of two bf16) rearranged into the pair order of
+// decode16: pair i = (k_i, k_{i+4}) within each half for 4-bit, (k_i, k_{i+8}) for 2-bit.
+template <int BITS>
+__device__ __forceinline__ void permute_x(const uint32_t (&raw)[8], uint32_t (&xw)[8]) {
+    if (BITS == 4) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            xw[4 * h + 0] = __byte_perm(raw[4 * h + 0], raw[4 * h + 2], 0x5410);
+            xw[4 * h + 1] = __byte_perm(raw[4 * h + 0], raw[4 * h + 2], 0x7632);
+            xw[4 * h + 2] = __byte_perm(raw[4 * h + 1], raw[4 * h + 3], 0x5410);
+            xw[4 * h + 3] = __byte_perm(raw[4 * h + 1], raw[4 * h + 3], 0x7632);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            xw[2 * j] = __byte_perm(raw[j], raw[4 + j], 0x5410);
+            xw[2 * j + 1] = __byte_perm(raw[j], raw[4 + j], 0x7632);
+        }
+    }
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kQmvThreads, 2)
+qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constant__ CUtensorMap map_a1,
+               const __grid_constant__ CUtensorMap map_b16, const __grid_constant__ CUtensorMap map_b1,
+               const QmvParams p) {
+    using U = UnitGeom<BITS>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const int T = p.consumers;
-    const int nwarps = T >> 5;  // consumer warps; warp `nwarps` is the producer
-    const QmvSmemPlan plan = qmv_plan<BITS>(p.k, MT, nwarps, TR, p.stages, p.stage_bytes);
-
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-    uint64_t *empty = full + p.stages;
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 128);
-    float4 *xt = reinterpret_cast<float4 *>(smem + plan.xt);
-    float *sx = reinterpret_cast<float *>(smem + plan.sx);
-    float *xu = reinterpret_cast<float *>(smem + plan.xu);
-    float *part = reinterpret_cast<float *>(smem + plan.part);
+    const QmvSmemPlan plan = qmv_plan(p.units, p.m, p.xstride, p.srow_bytes, p.stages, p.stage_bytes);
     uint8_t *ring = smem + plan.ring;
+    uint8_t *xb = smem + plan.xb;
+    float *xsum = reinterpret_cast<float *>(smem + plan.xsum);
+    uint8_t *scbuf = smem + plan.sc;
+    float *part = reinterpret_cast<float *>(smem + plan.part);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + plan.bars);
+    uint64_t *empty = full + kMaxStages;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kMaxStages);
+    const int sc_half = (kTileRows * p.srow_bytes + 15) & ~15;  // bytes of one raw [16 rows] block
 
     // Rows of this CTA: an even split of n at single-row granularity.
     const int row_begin = static_cast<int>((static_cast<int64_t>(blockIdx.x) * p.n) / gridDim.x);
     const int row_end = static_cast<int>((static_cast<int64_t>(blockIdx.x + 1) * p.n) / gridDim.x);
-    const int ntiles = (row_end - row_begin + TR - 1) / TR;
+    const int ntiles = (row_end - row_begin + kTileRows - 1) / kTileRows;
+    const int nseg = p.n1 + (p.l2 > 0 ? 1 : 0);
+    const int nsteps = ntiles * nseg;  // ring steps: (tile, k-segment)
 
     if (tid == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], nwarps);
+            mbar_init(&empty[s], kConsumerWarps);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -174,196 +253,233 @@ __global__ void __launch_bounds__(288, 1) qmv_stream_kernel(const QmvParams p) {
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == nwarps) {
-        // ---------------- producer warp: weights do not depend on the previous kernel.
-        int issued = 0;
-        for (int it = 0; it < ntiles; ++it) {
-            const int s = it % p.stages;
-            if (it >= p.stages) wait_or_abort(&empty[s], ((it / p.stages) - 1) & 1, abort_flag, 1);
-            if (*abort_flag) break;
-            const int r0 = row_begin + it * TR;
-            const int rows = min(TR, row_end - r0);
-            uint8_t *st = ring + static_cast<size_t>(s) * p.stage_bytes;
-            const uint8_t *gw = p.w + static_cast<size_t>(r0) * p.wrow_bytes;
-            const uint8_t *gs = p.scales + static_cast<size_t>(r0) * p.srow_bytes;
-            const uint8_t *gb = p.biases + static_cast<size_t>(r0) * p.srow_bytes;
-            const uint32_t wbytes = rows * p.wrow_bytes, sbytes = rows * p.srow_bytes;
-            // Rows that are not multiples of 16 bytes cannot use bulk copies: plain copy.
-            if (!p.w_bulk) {
-                for (uint32_t i = lane * 4; i < wbytes; i += 128)
-                    *reinterpret_cast<uint32_t *>(st + i) = *reinterpret_cast<const uint32_t *>(gw + i);
-            }
-            if (!p.s_bulk) {
-                for (uint32_t i = lane * 2; i < sbytes; i += 64) {
-                    *reinterpret_cast<uint16_t *>(st + p.w_region + i) =
-                        *reinterpret_cast<const uint16_t *>(gs + i);
-                    *reinterpret_cast<uint16_t *>(st + p.w_region + p.s_region + i) =
-                        *reinterpret_cast<const uint16_t *>(gb + i);
+    if (warp == kConsumerWarps) {
+        // ---------------- producer: packed codes do not depend on the previous kernel in the stream
+        if (lane == 0) {
+            int issued = 0, s = 0, phase = 0, it = 0, sg = 0;
+            for (int q = 0; q < nsteps; ++q) {
+                if (q >= p.stages) wait_or_abort(&empty[s], phase ^ 1, abort_flag, 1);
+                if (*abort_flag) break;
+                const int r0 = row_begin + it * kTileRows;
+                const int rows = min(kTileRows, row_end - r0);
+                const bool first = sg < p.n1;
+                const int lines = first ? p.l1 : p.l2;
+                const int line0 = first ? sg * p.l1 : p.n1 * p.l1;
+                uint8_t *st = ring + static_cast<size_t>(s) * p.stage_bytes;
+                if (rows == kTileRows) {
+                    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(kTileRows * lines * 128));
+                    tma_load_3d(st, first ? &map_a16 : &map_b16, 0, line0, r0, &full[s]);
+                } else {
+                    // ragged last tile: one single-row box per row, at the offsets the 16-row box uses
+                    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(rows * lines * 128));
+                    for (int r = 0; r < rows; ++r)
+                        tma_load_3d(st + r * lines * 128, first ? &map_a1 : &map_b1, 0, line0, r0 + r, &full[s]);
+                }
+                issued = q + 1;
+                if (++s == p.stages) {
+                    s = 0;
+                    phase ^= 1;
+                }
+                if (++sg == nseg) {
+                    sg = 0;
+                    ++it;
                 }
             }
-            __syncwarp();
-            if (lane == 0) {
-                const uint32_t tx = (p.w_bulk ? wbytes : 0u) + (p.s_bulk ? 2u * sbytes : 0u);
-                mbar_arrive_expect_tx(&full[s], tx);
-                if (p.w_bulk) bulk_g2s(st, gw, wbytes, &full[s]);
-                if (p.s_bulk) {
-                    bulk_g2s(st + p.w_region, gs, sbytes, &full[s]);
-                    bulk_g2s(st + p.w_region + p.s_region, gb, sbytes, &full[s]);
-                }
+            // After an abort, let copies already issued land before the CTA releases its memory.
+            if (*abort_flag) {
+                for (int q = max(0, issued - p.stages); q < issued; ++q)
+                    mbar_wait(&full[q % p.stages], (q / p.stages) & 1, 4000000u);
             }
-            issued = it + 1;
-        }
-        // After an abort, let copies already issued land before the CTA releases its memory.
-        if (*abort_flag && lane == 0) {
-            for (int it = max(0, issued - p.stages); it < issued; ++it)
-                mbar_wait(&full[it % p.stages], (it / p.stages) & 1, 4000000u);
         }
         return;
     }
 
     // ---------------- consumers
-    pdl_wait();  // x is produced by the previous kernel in the stream
+    const int g = lane >> 2, tig = lane & 3;  // MMA fragment coordinates
 
-    // Stage the activations: pre-scaled and permuted to the decode order, with the
-    // per-chunk sums the factorisation needs.
-    for (int item = tid; item < MT * p.nchunks; item += T) {
-        const int mrow = item / p.nchunks, c = item - mrow * p.nchunks;
-        float xs_sum = 0.f, x_sum = 0.f;
-        float xv[G::kCodesPerChunk];
-        if (mrow < p.m) {
-            const uint4 *src =
-                reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(mrow) * p.k + c * G::kCodesPerChunk);
-#pragma unroll
-            for (int i = 0; i < G::kCodesPerChunk / 8; ++i) {
-                const uint4 v = __ldg(src + i);
-                const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    xv[i * 8 + j * 2] = bf16_bits_to_f32(u[j] & 0xffffu);
-                    xv[i * 8 + j * 2 + 1] = __uint_as_float(u[j] & 0xffff0000u);
+    // Scales and biases of tile `it` are fetched raw with asynchronous copies (rows whose size allows
+    // no 4-byte granularity are copied synchronously); the thread that fetched a chunk later turns
+    // it into f32 pairs {scale, bias - 128 * scale}, the form the inner loop consumes.
+    const int groups_row = p.srow_bytes >> 1;
+    const int chunk = p.s_chunk ? p.s_chunk : 2;
+    uint8_t *raw_s = scbuf, *raw_b = scbuf + sc_half;
+    float2 *stbuf = reinterpret_cast<float2 *>(smem + plan.st);
+    auto fetch_scales = [&](int it) {
+        if (it < ntiles) {
+            const int r0 = row_begin + it * kTileRows;
+            const int rows = min(kTileRows, row_end - r0);
+            const size_t off = static_cast<size_t>(r0) * p.srow_bytes;
+            const int nbytes = rows * p.srow_bytes;
+            for (int c = tid * chunk; c < nbytes; c += kConsumers * chunk) {
+                if (p.s_chunk == 16) {
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(raw_s + c)), "l"(p.scales + off + c) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(raw_b + c)), "l"(p.biases + off + c) : "memory");
+                } else if (p.s_chunk == 8) {
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(raw_s + c)), "l"(p.scales + off + c) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(raw_b + c)), "l"(p.biases + off + c) : "memory");
+                } else if (p.s_chunk == 4) {
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(raw_s + c)), "l"(p.scales + off + c) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(raw_b + c)), "l"(p.biases + off + c) : "memory");
+                } else {
+                    *reinterpret_cast<uint16_t *>(raw_s + c) = __ldg(reinterpret_cast<const uint16_t *>(p.scales + off + c));
+                    *reinterpret_cast<uint16_t *>(raw_b + c) = __ldg(reinterpret_cast<const uint16_t *>(p.biases + off + c));
                 }
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < G::kCodesPerChunk; ++i) xv[i] = 0.f;
         }
-#pragma unroll
-        for (int q = 0; q < G::kQuads; ++q) {
-            float o[4];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int pair = q * 2 + h;            // pair index within the chunk
-                const int word = pair / G::kPairsPerWord;
-                const int pw = pair % G::kPairsPerWord;
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int kk = word * Code::kCodesPerWord + Code::code_of(pw, e);
-                    const float v = xv[kk] * Code::xscale_of(pw, e);
-                    o[h * 2 + e] = v;
-                    xs_sum += v;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // Converts the chunks this thread fetched for tile `it` into buffer `b`; call after wait_group.
+    auto convert_scales = [&](int it, int b) {
+        if (it < ntiles) {
+            const int r0 = row_begin + it * kTileRows;
+            const int nbytes = min(kTileRows, row_end - r0) * p.srow_bytes;
+            float2 *dst = stbuf + b * kTileRows * groups_row;
+            for (int c = tid * chunk; c < nbytes; c += kConsumers * chunk) {
+                for (int e = 0; e < chunk; e += 2) {
+                    const float sv = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(raw_s + c + e));
+                    const float bv = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(raw_b + c + e));
+                    dst[(c + e) >> 1] = make_float2(sv, fmaf(-128.f, sv, bv));
                 }
             }
-            xt[(mrow * G::kQuads + q) * p.nchunks + c] = make_float4(o[0], o[1], o[2], o[3]);
         }
-#pragma unroll
-        for (int i = 0; i < G::kCodesPerChunk; ++i) x_sum += xv[i];
-        sx[mrow * p.nchunks + c] = xs_sum;
-        xu[mrow * p.nchunks + c] = x_sum;
+    };
+    auto scales_landed = [&]() { asm volatile("cp.async.wait_group 0;" ::: "memory"); };
+    auto consumer_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"r"(kConsumers) : "memory"); };
+    fetch_scales(0);  // weights: independent of the previous kernel
+
+    // ---- activations: produced by the previous kernel in the stream
+    pdl_wait();
+    {
+        const int vec_per_row = p.k / 8;  // uint4 per row of x
+        for (int i = tid; i < p.m * vec_per_row; i += kConsumers) {
+            const int r = i / vec_per_row, c = i - r * vec_per_row;
+            *reinterpret_cast<uint4 *>(xb + r * p.xstride + c * 16) =
+                __ldg(reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(r) * p.k) + c);
+        }
     }
-    asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory");
+    scales_landed();
+    convert_scales(0, 0);
+    consumer_sync();
+    fetch_scales(1);
+    // Permute every lane's 16 consecutive k in place into B-fragment order, and sum them.
+    for (int u = warp; u < p.units; u += kConsumerWarps) {
+        const int ncol = g;
+        float s16 = 0.f;
+        if (ncol < p.m) {
+            uint4 *slot = reinterpret_cast<uint4 *>(xb + ncol * p.xstride + u * 128 + tig * 32);
+            const uint4 v0 = slot[0], v1 = slot[1];
+            const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            uint32_t xw[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s16 += bf16_bits_to_f32(raw[i] & 0xffffu) + __uint_as_float(raw[i] & 0xffff0000u);
+            permute_x<BITS>(raw, xw);
+            slot[0] = make_uint4(xw[0], xw[1], xw[2], xw[3]);
+            slot[1] = make_uint4(xw[4], xw[5], xw[6], xw[7]);
+        }
+        s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+        s16 += __shfl_xor_sync(0xffffffffu, s16, 2);
+        if (tig == 0) xsum[u * 8 + ncol] = s16;
+    }
+    consumer_sync();
 
-    int buf = 0;
+    // Columns beyond m read column m-1 again: their results are never stored.
+    const uint32_t xlane = smem_u32(xb) + min(g, p.m - 1) * p.xstride + tig * 32;
+    const uint32_t xsum_lane = smem_u32(xsum) + 8 * tig;
+    const uint32_t ring32 = smem_u32(ring);
+    // Unit ul = warp + 8 i of a segment starts at byte b0 + i * step of the row segment: the offset
+    // inside the 128-byte line is the same for every i.
+    constexpr int kStep = kConsumerWarps * U::kUnitBytes;          // 256 (4-bit) / 128 (2-bit)
+    constexpr int kLineStep = kStep >> 7;                          // lines per trip
+    const int b0 = warp * U::kUnitBytes + tig * U::kLaneBytes;
+    const int line0 = b0 >> 7, chunk0 = (b0 >> 4) & 7, inner = b0 & 15;
+    const uint32_t kmask = reg_const(BITS == 4 ? 0x000f000fu : 0x00030003u), kmagic = reg_const(0x43004300u);
+    int buf = 0, s = 0, phase = 0;
     for (int it = 0; it < ntiles; ++it) {
-        const int s = it % p.stages;
-        const int r0 = row_begin + it * TR;
-        const int rows = min(TR, row_end - r0);
-        const uint8_t *st = ring + static_cast<size_t>(s) * p.stage_bytes;
-        const uint8_t *st_s = st + p.w_region;
-        const uint8_t *st_b = st_s + p.s_region;
-
-        float rsum[NV];
-#pragma unroll
-        for (int i = 0; i < NV; ++i) rsum[i] = 0.f;
-
-        wait_or_abort(&full[s], (it / p.stages) & 1, abort_flag, 2);
-
-        for (int c = tid; c < p.nchunks; c += T) {
-            // pre-scaled activations of this chunk, one set per input row
-            float2 xq[MT][G::kQuads * 2];
-            float sxc[MT], xuc[MT];
-#pragma unroll
-            for (int mm = 0; mm < MT; ++mm) {
-#pragma unroll
-                for (int q = 0; q < G::kQuads; ++q) {
-                    const float4 v = xt[(mm * G::kQuads + q) * p.nchunks + c];
-                    xq[mm][q * 2] = make_float2(v.x, v.y);
-                    xq[mm][q * 2 + 1] = make_float2(v.z, v.w);
-                }
-                sxc[mm] = sx[mm * p.nchunks + c];
-                xuc[mm] = xu[mm * p.nchunks + c];
+        const int r0 = row_begin + it * kTileRows;
+        const int rows = min(kTileRows, row_end - r0);
+        float rs[4] = {0.f, 0.f, 0.f, 0.f};  // (row g, col 2tig), (g, 2tig+1), (g+8, 2tig), (g+8, 2tig+1)
+        const uint32_t st_lo = smem_u32(stbuf) + ((buf * kTileRows + g) * groups_row) * 8;
+        const uint32_t st_hi = st_lo + 8 * groups_row * 8;
+        int ubase = 0;  // first unit of the segment
+        for (int sg = 0; sg < nseg; ++sg) {
+            const int lines = (sg < p.n1) ? p.l1 : p.l2;
+            const int nu = lines * U::kUnitsPerLine;
+            // lane (g, tig) reads row g and row g + 8 of the stage; both rows share the swizzle key
+            const uint32_t rowp = ring32 + s * p.stage_bytes + g * lines * 128 + inner;
+            const int keyg = g * lines;
+            const uint32_t hi_off = 8 * lines * 128;
+            wait_or_abort(&full[s], phase, abort_flag, 2);
+            // one unit: 16 rows x 64 codes against up to 8 columns of x.  `line` is the 128-byte line
+            // of the row segment, `uo` the unit index within the whole row.
+            auto unit = [&](int line, int uo) {
+                const uint32_t src = rowp + line * 128 + ((chunk0 ^ ((keyg + line) & 7)) << 4);
+                uint32_t ra[8], rb[8];
+                decode16<BITS>(src, kmask, kmagic, ra);
+                decode16<BITS>(src + hi_off, kmask, kmagic, rb);
+                const uint4 x0 = lds_v4(xlane + uo * 128), x1 = lds_v4(xlane + uo * 128 + 16);
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_bf16_16x8x16(c, ra[0], rb[0], ra[1], rb[1], x0.x, x0.y);
+                mma_bf16_16x8x16(c, ra[2], rb[2], ra[3], rb[3], x0.z, x0.w);
+                mma_bf16_16x8x16(c, ra[4], rb[4], ra[5], rb[5], x1.x, x1.y);
+                mma_bf16_16x8x16(c, ra[6], rb[6], ra[7], rb[7], x1.z, x1.w);
+                const int gi = (uo >> p.ushift) * 8;
+                const float2 lo = lds_f2(st_lo + gi), hi = lds_f2(st_hi + gi);  // {scale, bias - 128 scale}
+                const float2 xs = lds_f2(xsum_lane + uo * 32);
+                // scale * (c - 128 * sum(x)) + bias * sum(x)  ==  scale * c + (bias - 128 * scale) * sum(x)
+                rs[0] = fmaf(lo.x, c[0], fmaf(lo.y, xs.x, rs[0]));
+                rs[1] = fmaf(lo.x, c[1], fmaf(lo.y, xs.y, rs[1]));
+                rs[2] = fmaf(hi.x, c[2], fmaf(hi.y, xs.x, rs[2]));
+                rs[3] = fmaf(hi.x, c[3], fmaf(hi.y, xs.y, rs[3]));
+            };
+            int ul = warp, line = line0, u = ubase + warp;
+            for (; ul + kConsumerWarps < nu; ul += 2 * kConsumerWarps, line += 2 * kLineStep, u += 2 * kConsumerWarps) {
+                unit(line, u);  // two independent chains per trip
+                unit(line + kLineStep, u + kConsumerWarps);
             }
-            const int g2 = (c >> p.gshift) * 2;
-#pragma unroll
-            for (int r = 0; r < TR; ++r) {
-                if (r < rows) {
-                    const uint2 wv = *reinterpret_cast<const uint2 *>(st + r * p.wrow_bytes + c * 8);
-                    const float sc = bf16_bits_to_f32(
-                        *reinterpret_cast<const uint16_t *>(st_s + r * p.srow_bytes + g2));
-                    const float bi = bf16_bits_to_f32(
-                        *reinterpret_cast<const uint16_t *>(st_b + r * p.srow_bytes + g2));
-                    uint32_t lo[2][G::kPairsPerWord], hi[2][G::kPairsPerWord];
-                    Code::decode(wv.x, lo[0], hi[0]);
-                    Code::decode(wv.y, lo[1], hi[1]);
-#pragma unroll
-                    for (int mm = 0; mm < MT; ++mm) {
-                        float2 a0 = make_float2(0.f, 0.f), a1 = make_float2(0.f, 0.f);
-#pragma unroll
-                        for (int wd = 0; wd < 2; ++wd) {
-#pragma unroll
-                            for (int pp = 0; pp < G::kPairsPerWord; ++pp) {
-                                const float2 t =
-                                    make_float2(__uint_as_float(lo[wd][pp]), __uint_as_float(hi[wd][pp]));
-                                const float2 xv2 = xq[mm][wd * G::kPairsPerWord + pp];
-                                if (pp & 1) a1 = ffma2(t, xv2, a1);
-                                else a0 = ffma2(t, xv2, a0);
-                            }
-                        }
-                        const float acc = (a0.x + a0.y) + (a1.x + a1.y);
-                        float rs = rsum[r * MT + mm];
-                        rs = fmaf(sc, acc - sxc[mm], rs);
-                        rs = fmaf(bi, xuc[mm], rs);
-                        rsum[r * MT + mm] = rs;
-                    }
-                }
+            if (ul < nu) unit(line, u);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);  // this warp is done reading the stage
+            ubase += nu;
+            if (++s == p.stages) {
+                s = 0;
+                phase ^= 1;
             }
         }
-
-        // this warp is done reading the stage
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
-
-        warp_reduce_many<NV>(rsum, lane);
-        const int ridx = reduced_index<NV>(lane);
-        constexpr int kHolders = 32 / NV;  // lanes holding the same reduced value (NV <= 32)
-        if ((lane % (kHolders > 0 ? kHolders : 1)) == 0)
-            part[(buf * nwarps + warp) * NV + ridx] = rsum[0];
-        asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory");
-        if (tid < NV) {
+        // cross-warp reduction of the 16 x 8 tile
+        *reinterpret_cast<float4 *>(part + ((buf * kConsumerWarps + warp) * 32 + lane) * 4) =
+            make_float4(rs[0], rs[1], rs[2], rs[3]);
+        scales_landed();                 // raw scales of the next tile, requested a tile ago
+        convert_scales(it + 1, buf ^ 1);
+        consumer_sync();
+        fetch_scales(it + 2);
+        if (tid < 128) {
             float total = 0.f;
-            for (int wi = 0; wi < nwarps; ++wi) total += part[(buf * nwarps + wi) * NV + tid];
-            const int r = tid / MT, mm = tid - r * MT;
-            if (r < rows && mm < p.m)
-                p.y[static_cast<size_t>(mm) * p.n + r0 + r] = static_cast<uint16_t>(f32_to_bf16_bits(total));
+#pragma unroll
+            for (int wi = 0; wi < kConsumerWarps; ++wi) total += part[(buf * kConsumerWarps + wi) * 128 + tid];
+            const int l = tid >> 2, i = tid & 3;
+            const int row = (l >> 2) + 8 * (i >> 1), col = 2 * (l & 3) + (i & 1);
+            if (row < rows && col < p.m)
+                p.y[static_cast<size_t>(col) * p.n + r0 + row] = static_cast<uint16_t>(f32_to_bf16_bits(total));
         }
         buf ^= 1;
     }
 }
 
 // ---------------------------------------------------------------------------------------
-// Generic kernel: warp per output row, lanes stride over 8-byte chunks, f32 math with the
-// same factorisation.  Handles any n, any k that is a multiple of the group size, any m.
+// Generic kernel: warp per output row, lanes stride over packed words, f32 math with the same
+// factorisation.  Any n, any k that is a multiple of the group size, any m (grid.y).
+struct SimpleParams {
+    const uint8_t *w;
+    const uint8_t *scales;
+    const uint8_t *biases;
+    const uint16_t *x;
+    uint16_t *y;
+    int n, k, wrow_bytes, srow_bytes, group_size;
+};
+
 template <int BITS>
-__global__ void __launch_bounds__(256) qmv_simple_kernel(const QmvParams p, int group_size) {
+__global__ void __launch_bounds__(256) qmv_simple_kernel(const SimpleParams p) {
+    const int group_size = p.group_size;
     constexpr int CPW = 32 / BITS;  // codes per word
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -380,17 +496,17 @@ __global__ void __launch_bounds__(256) qmv_simple_kernel(const QmvParams p, int 
     for (int wi = lane; wi < nwords; wi += 32) {
         const uint32_t word = __ldg(wr + wi);
         const int k0 = wi * CPW;
-        const int g = k0 / group_size;  // a word never straddles a group (group_size >= 32 >= CPW)
+        const int gi = k0 / group_size;  // a word never straddles a group (group_size >= 32 >= CPW)
         float accum = 0.f, xsum = 0.f;
 #pragma unroll
         for (int j = 0; j < CPW; ++j) {
             const float xv = bf16_bits_to_f32(__ldg(xr + k0 + j));
-            const uint32_t q = (word >> (j * BITS)) & ((1u << BITS) - 1u);
-            accum = fmaf(xv, static_cast<float>(q), accum);
+            const uint32_t qv = (word >> (j * BITS)) & ((1u << BITS) - 1u);
+            accum = fmaf(xv, static_cast<float>(qv), accum);
             xsum += xv;
         }
-        result = fmaf(bf16_bits_to_f32(__ldg(sr + g)), accum, result);
-        result = fmaf(bf16_bits_to_f32(__ldg(br + g)), xsum, result);
+        result = fmaf(bf16_bits_to_f32(__ldg(sr + gi)), accum, result);
+        result = fmaf(bf16_bits_to_f32(__ldg(br + gi)), xsum, result);
     }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) result += __shfl_xor_sync(0xffffffffu, result, off);
@@ -400,184 +516,152 @@ __global__ void __launch_bounds__(256) qmv_simple_kernel(const QmvParams p, int 
 // ---------------------------------------------------------------------------------------
 // Host-side planning and launch.
 
-struct QmvLaunchPlan {
-    bool ok;
-    int tr, stages, stage_bytes, w_region, s_region, consumers, grid, smem;
-};
+// Splits `lines` (128-byte lines per packed row) into n1 segments of l1 lines plus an optional
+// segment of l2 lines, all from the set of line counts whose swizzle keeps the fragment reads
+// conflict free: 2 mod 4 for 4-bit (8-byte lane reads), odd for 2-bit (4-byte lane reads).
+template <int BITS>
+static bool split_lines(int lines, int max_lines, int &l1, int &n1, int &l2) {
+    auto valid = [](int l) { return BITS == 4 ? (l % 4 == 2) : (l % 2 == 1); };
+    int best_cnt = 1 << 30, best_small = -1;
+    for (int a = max_lines; a >= 1; --a) {
+        if (!valid(a)) continue;
+        for (int cnt = lines / a; cnt >= 1; --cnt) {
+            const int rem = lines - cnt * a;
+            if (rem != 0 && !(valid(rem) && rem <= max_lines)) continue;
+            const int total = cnt + (rem ? 1 : 0);
+            const int small = rem ? std::min(a, rem) : a;  // ties: the split with the largest smallest part
+            if (total < best_cnt || (total == best_cnt && small > best_small)) {
+                best_cnt = total;
+                best_small = small;
+                l1 = a;
+                n1 = cnt;
+                l2 = rem;
+            }
+        }
+    }
+    return best_cnt != (1 << 30);
+}
 
 template <int BITS>
-static QmvLaunchPlan plan_stream(int64_t n, int64_t k, int group_size, int mt) {
-    QmvLaunchPlan lp{};
-    lp.ok = false;
-    const int cpc = QmvGeom<BITS>::kCodesPerChunk;
-    if (k % cpc != 0 || k % 8 != 0) return lp;  // chunks must tile a row; x rows must be 16-byte multiples
-    const int nchunks = static_cast<int>(k / cpc);
-    const int wrow = static_cast<int>(k * BITS / 8), srow = static_cast<int>(k / group_size * 2);
+static bool plan_mma(int64_t n, int64_t k, int group_size, int m, QmvParams &p, int &grid, int &smem) {
+    if (group_size != 64 && group_size != 128) return false;
+    if (k % 64 != 0 || k % group_size != 0) return false;
+    const int64_t row_bytes = k * BITS / 8;
+    if (row_bytes % 128 != 0) return false;  // whole lines only
+    const int lines = static_cast<int>(row_bytes / 128);
+    if (!split_lines<BITS>(lines, 14, p.l1, p.n1, p.l2)) return false;
+    p.units = static_cast<int>(k / 64);
+    p.ushift = (group_size == 128) ? 1 : 0;
+    p.s_chunk = (p.srow_bytes % 16 == 0) ? 16 : (p.srow_bytes % 8 == 0) ? 8 : (p.srow_bytes % 4 == 0) ? 4 : 0;
+    // rows of staged x sit 16 bytes past a multiple of 128 so that the lanes of different columns
+    // hit different banks
+    p.xstride = static_cast<int>(((k * 2 + 127) / 128) * 128 + 16);
+    p.stage_bytes = kTileRows * std::max(p.l1, p.l2) * 128;
     const int sms = sm_count();
     const int smem_max = max_smem_optin();
-    // consumer threads: enough to cover the chunks of a row with few idle lanes, at most 256
-    int best_t = 32;
-    double best_u = 0.0;
-    for (int t = 256; t >= 32; t -= 32) {
-        const int iters = (nchunks + t - 1) / t;
-        const double u = static_cast<double>(nchunks) / (static_cast<double>(iters) * t);
-        if (u > best_u + 0.02) {
-            best_u = u;
-            best_t = t;
-        }
-    }
-    lp.consumers = best_t;
-    const int nwarps = best_t / 32;
-    // Two CTAs per SM when every CTA still gets a few full tiles; else one.
-    const int per_sm = (n / (2 * sms) >= 16) ? 2 : 1;
-    lp.grid = static_cast<int>(std::min<int64_t>(n, static_cast<int64_t>(sms) * per_sm));
-    const int budget = (per_sm == 2 ? smem_max / 2 - 2048 : smem_max) ;
-    for (int tr : {16, 8}) {
-        if (tr * mt > 32) continue;
-        const int w_region = (tr * wrow + 15) & ~15;
-        const int s_region = (tr * srow + 15) & ~15;
-        const int stage_bytes = (w_region + 2 * s_region + 127) & ~127;
-        for (int stages = 8; stages >= 2; --stages) {
-            if (stages * stage_bytes > 96 * 1024 && stages > 3) continue;  // deep rings only while small
-            const QmvSmemPlan sp = qmv_plan<BITS>(static_cast<int>(k), mt, nwarps, tr, stages, stage_bytes);
+    // Two CTAs per SM when every CTA still gets a couple of full tiles; else one.
+    const int per_sm = (n / (2 * sms) >= 2 * kTileRows) ? 2 : 1;
+    for (int ps = per_sm; ps >= 1; --ps) {
+        const int budget = (ps == 2) ? smem_max / 2 - 1024 : smem_max;
+        for (int stages = kMaxStages; stages >= 2; --stages) {
+            if (stages > 4 && stages * p.stage_bytes > 96 * 1024) continue;  // deep rings only while small
+            const QmvSmemPlan sp = qmv_plan(p.units, m, p.xstride, p.srow_bytes, stages, p.stage_bytes);
             if (sp.total <= budget) {
-                lp.ok = true;
-                lp.tr = tr;
-                lp.stages = stages;
-                lp.stage_bytes = stage_bytes;
-                lp.w_region = w_region;
-                lp.s_region = s_region;
-                lp.smem = sp.total;
-                return lp;
+                p.stages = stages;
+                smem = sp.total;
+                grid = static_cast<int>(std::min<int64_t>((n + kTileRows - 1) / kTileRows, static_cast<int64_t>(sms) * ps));
+                return true;
             }
         }
     }
-    if (per_sm == 2) {
-        // retry with the whole SM
-        lp.grid = static_cast<int>(std::min<int64_t>(n, sms));
-        for (int tr : {16, 8}) {
-            if (tr * mt > 32) continue;
-            const int w_region = (tr * wrow + 15) & ~15;
-            const int s_region = (tr * srow + 15) & ~15;
-            const int stage_bytes = (w_region + 2 * s_region + 127) & ~127;
-            for (int stages = 4; stages >= 2; --stages) {
-                const QmvSmemPlan sp = qmv_plan<BITS>(static_cast<int>(k), mt, nwarps, tr, stages, stage_bytes);
-                if (sp.total <= smem_max) {
-                    lp.ok = true;
-                    lp.tr = tr;
-                    lp.stages = stages;
-                    lp.stage_bytes = stage_bytes;
-                    lp.w_region = w_region;
-                    lp.s_region = s_region;
-                    lp.smem = sp.total;
-                    return lp;
-                }
-            }
-        }
-    }
-    return lp;
+    return false;
 }
 
-template <typename Kern>
-static int launch_kernel(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
-                         const QmvParams &p) {
-    if (smem > 48 * 1024) {
-        LISA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    }
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
-    count_launch();
-    return LISA_OK;
-}
-
-template <int BITS, int TR, int MT>
-static int launch_stream(const QmvParams &p, const QmvLaunchPlan &lp, cudaStream_t stream, bool pdl) {
-    return launch_kernel(qmv_stream_kernel<BITS, TR, MT>, dim3(lp.grid), dim3(lp.consumers + 32), lp.smem,
-                         stream, pdl, p);
+static int make_code_map(CUtensorMap *map, const void *w, int64_t n, int64_t row_bytes, int lines_box, int rows_box) {
+    const uint64_t dims[3] = {128, static_cast<uint64_t>(row_bytes / 128), static_cast<uint64_t>(n)};
+    const uint64_t strides[2] = {128, static_cast<uint64_t>(row_bytes)};
+    const uint32_t box[3] = {128, static_cast<uint32_t>(lines_box), static_cast<uint32_t>(rows_box)};
+    return make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 template <int BITS>
 static int qmv_dispatch(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
-                        const void *scales, const void *biases, int64_t n, int group_size, void *y,
-                        unsigned flags) {
+                        const void *scales, const void *biases, int64_t n, int group_size, void *y, unsigned flags) {
     QmvParams p{};
-    p.w = reinterpret_cast<const uint8_t *>(w);
     p.scales = reinterpret_cast<const uint8_t *>(scales);
     p.biases = reinterpret_cast<const uint8_t *>(biases);
     p.n = static_cast<int>(n);
     p.k = static_cast<int>(k);
-    p.wrow_bytes = static_cast<int>(k * BITS / 8);
     p.srow_bytes = static_cast<int>(k / group_size * 2);
-    const int cpc = QmvGeom<BITS>::kCodesPerChunk;
-    p.nchunks = static_cast<int>(k / cpc);
-    int gshift = 0;
-    while ((cpc << gshift) < group_size) ++gshift;
-    p.gshift = gshift;
-    p.w_bulk = (p.wrow_bytes % 16 == 0) ? 1 : 0;
-    p.s_bulk = (p.srow_bytes % 16 == 0) ? 1 : 0;
+    const int64_t row_bytes = k * BITS / 8;
     const bool pdl = (flags & LISA_FLAG_PDL) != 0;
     const bool force_simple = (flags & LISA_FLAG_FORCE_QMV_SIMPLE) != 0;
-
     const uint16_t *xp = reinterpret_cast<const uint16_t *>(x);
     uint16_t *yp = reinterpret_cast<uint16_t *>(y);
+
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+
+    CUtensorMap maps[4];
+    bool maps_ready = false;
     int64_t done = 0;
     while (done < m) {
         const int64_t left = m - done;
-        int mt = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
-        QmvLaunchPlan lp{};
-        if (!force_simple && group_size >= cpc) {
-            for (; mt >= 1; mt >>= 1) {
-                lp = plan_stream<BITS>(n, k, group_size, mt);
-                if (lp.ok) break;
+        int mc = static_cast<int>(std::min<int64_t>(left, 8));
+        int grid = 0, smem = 0;
+        bool ok = false;
+        if (!force_simple && k % 8 == 0) {
+            for (; mc >= 1; mc = (mc > 1) ? (mc + 1) / 2 : 0) {
+                if (plan_mma<BITS>(n, k, group_size, mc, p, grid, smem)) {
+                    ok = true;
+                    break;
+                }
             }
         }
-        if (!lp.ok) {
+        cudaLaunchConfig_t cfg{};
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        if (!ok) {
             // generic kernel, all remaining rows in one launch
-            p.x = xp + done * k;
-            p.y = yp + done * n;
-            p.m = static_cast<int>(left);
+            SimpleParams sp{};
+            sp.w = reinterpret_cast<const uint8_t *>(w);
+            sp.scales = p.scales;
+            sp.biases = p.biases;
+            sp.x = xp + done * k;
+            sp.y = yp + done * n;
+            sp.n = p.n;
+            sp.k = p.k;
+            sp.wrow_bytes = static_cast<int>(row_bytes);
+            sp.srow_bytes = p.srow_bytes;
+            sp.group_size = group_size;
             if (left > 65535) return fail(LISA_ERR_LIMIT, "qmv: more than 65535 rows for the generic kernel");
-            const int rows_per_block = 8;
-            dim3 grid(static_cast<unsigned>((n + rows_per_block - 1) / rows_per_block), static_cast<unsigned>(left));
-            cudaLaunchConfig_t cfg{};
-            cfg.gridDim = grid;
-            cfg.blockDim = dim3(rows_per_block * 32);
-            cfg.stream = stream;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = attr;
-            cfg.numAttrs = pdl ? 1 : 0;
-            LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_simple_kernel<BITS>, p, group_size));
+            cfg.gridDim = dim3(static_cast<unsigned>((n + 7) / 8), static_cast<unsigned>(left));
+            cfg.blockDim = dim3(256);
+            LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_simple_kernel<BITS>, sp));
             count_launch();
             return LISA_OK;
         }
+        if (!maps_ready) {
+            int rc = make_code_map(&maps[0], w, n, row_bytes, p.l1, kTileRows);
+            if (rc == LISA_OK) rc = make_code_map(&maps[1], w, n, row_bytes, p.l1, 1);
+            if (rc == LISA_OK) rc = make_code_map(&maps[2], w, n, row_bytes, p.l2 > 0 ? p.l2 : p.l1, kTileRows);
+            if (rc == LISA_OK) rc = make_code_map(&maps[3], w, n, row_bytes, p.l2 > 0 ? p.l2 : p.l1, 1);
+            if (rc != LISA_OK) return rc;
+            maps_ready = true;
+        }
         p.x = xp + done * k;
         p.y = yp + done * n;
-        p.m = static_cast<int>(std::min<int64_t>(left, mt));
-        p.stages = lp.stages;
-        p.stage_bytes = lp.stage_bytes;
-        p.w_region = lp.w_region;
-        p.s_region = lp.s_region;
-        p.consumers = lp.consumers;
-        int rc = LISA_OK;
-        if (lp.tr == 16 && mt == 1) rc = launch_stream<BITS, 16, 1>(p, lp, stream, pdl);
-        else if (lp.tr == 16 && mt == 2) rc = launch_stream<BITS, 16, 2>(p, lp, stream, pdl);
-        else if (lp.tr == 8 && mt == 1) rc = launch_stream<BITS, 8, 1>(p, lp, stream, pdl);
-        else if (lp.tr == 8 && mt == 2) rc = launch_stream<BITS, 8, 2>(p, lp, stream, pdl);
-        else if (lp.tr == 8 && mt == 4) rc = launch_stream<BITS, 8, 4>(p, lp, stream, pdl);
-        else return fail(LISA_ERR_UNSUPPORTED, "qmv: no kernel for the planned tile");
-        if (rc != LISA_OK) return rc;
-        done += p.m;
+        p.m = mc;
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kQmvThreads);
+        cfg.dynamicSmemBytes = smem;
+        if (smem > 48 * 1024)
+            LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_mma_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_mma_kernel<BITS>, maps[0], maps[1], maps[2], maps[3], p));
+        count_launch();
+        done += mc;
     }
     return LISA_OK;
 }

@@ -361,24 +361,34 @@ qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constan
     convert_scales(0, 0);
     consumer_sync();
     fetch_scales(1);
-    // Permute every lane's 16 consecutive k in place into B-fragment order, and sum them.
-    for (int u = warp; u < p.units; u += kConsumerWarps) {
-        const int ncol = g;
-        float s16 = 0.f;
-        if (ncol < p.m) {
-            uint4 *slot = reinterpret_cast<uint4 *>(xb + ncol * p.xstride + u * 128 + tig * 32);
-            const uint4 v0 = slot[0], v1 = slot[1];
-            const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-            uint32_t xw[8];
+    // Permute every 16 consecutive k of x in place into B-fragment order, and sum them: one thread
+    // per (unit, column, quarter of the unit); the four quarters of a unit sit in adjacent lanes.
+    for (int e = tid; e < p.units * 8; e += kConsumers)
+        if ((e & 7) >= p.m) xsum[e] = 0.f;  // columns that do not exist
+    {
+        const int items = p.units * p.m * 4;
+        for (int base = 0; base < items; base += kConsumers) {
+            const int item = base + tid;
+            const bool ok = item < items;
+            const int tq = item & 3, un = item >> 2;
+            const int u = un / p.m, ncol = un - u * p.m;
+            float s16 = 0.f;
+            if (ok) {
+                uint4 *slot = reinterpret_cast<uint4 *>(xb + ncol * p.xstride + u * 128 + tq * 32);
+                const uint4 v0 = slot[0], v1 = slot[1];
+                const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                uint32_t xw[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) s16 += bf16_bits_to_f32(raw[i] & 0xffffu) + __uint_as_float(raw[i] & 0xffff0000u);
-            permute_x<BITS>(raw, xw);
-            slot[0] = make_uint4(xw[0], xw[1], xw[2], xw[3]);
-            slot[1] = make_uint4(xw[4], xw[5], xw[6], xw[7]);
+                for (int i = 0; i < 8; ++i)
+                    s16 += bf16_bits_to_f32(raw[i] & 0xffffu) + __uint_as_float(raw[i] & 0xffff0000u);
+                permute_x<BITS>(raw, xw);
+                slot[0] = make_uint4(xw[0], xw[1], xw[2], xw[3]);
+                slot[1] = make_uint4(xw[4], xw[5], xw[6], xw[7]);
+            }
+            s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+            s16 += __shfl_xor_sync(0xffffffffu, s16, 2);
+            if (ok && tq == 0) xsum[u * 8 + ncol] = s16;
         }
-        s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
-        s16 += __shfl_xor_sync(0xffffffffu, s16, 2);
-        if (tig == 0) xsum[u * 8 + ncol] = s16;
     }
     consumer_sync();
 
@@ -411,32 +421,39 @@ qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constan
             wait_or_abort(&full[s], phase, abort_flag, 2);
             // one unit: 16 rows x 64 codes against up to 8 columns of x.  `line` is the 128-byte line
             // of the row segment, `uo` the unit index within the whole row.
-            auto unit = [&](int line, int uo) {
+            auto unit = [&](int line, uint32_t xo, uint32_t xso, uint32_t go) {
                 const uint32_t src = rowp + line * 128 + ((chunk0 ^ ((keyg + line) & 7)) << 4);
                 uint32_t ra[8], rb[8];
                 decode16<BITS>(src, kmask, kmagic, ra);
                 decode16<BITS>(src + hi_off, kmask, kmagic, rb);
-                const uint4 x0 = lds_v4(xlane + uo * 128), x1 = lds_v4(xlane + uo * 128 + 16);
+                const uint4 x0 = lds_v4(xo), x1 = lds_v4(xo + 16);
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
                 mma_bf16_16x8x16(c, ra[0], rb[0], ra[1], rb[1], x0.x, x0.y);
                 mma_bf16_16x8x16(c, ra[2], rb[2], ra[3], rb[3], x0.z, x0.w);
                 mma_bf16_16x8x16(c, ra[4], rb[4], ra[5], rb[5], x1.x, x1.y);
                 mma_bf16_16x8x16(c, ra[6], rb[6], ra[7], rb[7], x1.z, x1.w);
-                const int gi = (uo >> p.ushift) * 8;
-                const float2 lo = lds_f2(st_lo + gi), hi = lds_f2(st_hi + gi);  // {scale, bias - 128 scale}
-                const float2 xs = lds_f2(xsum_lane + uo * 32);
+                const float2 lo = lds_f2(st_lo + go), hi = lds_f2(st_hi + go);  // {scale, bias - 128 scale}
+                const float2 xs = lds_f2(xso);
                 // scale * (c - 128 * sum(x)) + bias * sum(x)  ==  scale * c + (bias - 128 * scale) * sum(x)
                 rs[0] = fmaf(lo.x, c[0], fmaf(lo.y, xs.x, rs[0]));
                 rs[1] = fmaf(lo.x, c[1], fmaf(lo.y, xs.y, rs[1]));
                 rs[2] = fmaf(hi.x, c[2], fmaf(hi.y, xs.x, rs[2]));
                 rs[3] = fmaf(hi.x, c[3], fmaf(hi.y, xs.y, rs[3]));
             };
-            int ul = warp, line = line0, u = ubase + warp;
-            for (; ul + kConsumerWarps < nu; ul += 2 * kConsumerWarps, line += 2 * kLineStep, u += 2 * kConsumerWarps) {
-                unit(line, u);  // two independent chains per trip
-                unit(line + kLineStep, u + kConsumerWarps);
+            // unit u = ubase + warp + 8 i: all byte offsets advance by constants per trip
+            const int u0 = ubase + warp;
+            uint32_t xo = xlane + u0 * 128, xso = xsum_lane + u0 * 32, go = (u0 >> p.ushift) * 8;
+            const uint32_t gstep = (kConsumerWarps >> p.ushift) * 8;
+            int ul = warp, line = line0;
+            for (; ul + kConsumerWarps < nu; ul += 2 * kConsumerWarps) {
+                unit(line, xo, xso, go);  // two independent chains per trip
+                unit(line + kLineStep, xo + kConsumerWarps * 128, xso + kConsumerWarps * 32, go + gstep);
+                line += 2 * kLineStep;
+                xo += 2 * kConsumerWarps * 128;
+                xso += 2 * kConsumerWarps * 32;
+                go += 2 * gstep;
             }
-            if (ul < nu) unit(line, u);
+            if (ul < nu) unit(line, xo, xso, go);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);  // this warp is done reading the stage
             ubase += nu;

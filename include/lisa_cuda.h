@@ -141,6 +141,22 @@ size_t lisa_cuda_moe_sort_workspace_bytes(int64_t slots, int64_t experts);
 int lisa_cuda_moe_sort(lisa_stream_t stream, const int32_t *idx, int64_t slots, int64_t experts,
                        int top_k, int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse,
                        void *workspace, size_t workspace_bytes);
+/* lisa_cuda_moe_sort_static: the same stable sort, for callers that must not allocate device
+ *   memory.  It has no counterpart in the reference.  Some hosts of this library run where
+ *   cudaMalloc is off limits: a real-time decode loop that may not stall on the allocator, an
+ *   engine that has already handed the whole GPU to its own pool, a plugin that is only given
+ *   the buffers of its inputs and outputs.  For them the (chunk x expert) count table lives in
+ *   a device array built into the library (256 KiB, resident on every GPU that loads the
+ *   library until the process exits) instead of a caller workspace.
+ *   Limit: ceil(slots / 256) * experts <= 65536; larger problems are refused with
+ *   LISA_ERR_LIMIT (use lisa_cuda_moe_sort with a workspace).  The call allocates and frees
+ *   nothing.  Its first call on a device looks up the array's device address (a blocking
+ *   runtime query), so make that first call outside any stream capture.  All calls on a device
+ *   share the one array, which keeps whatever the last call left in it; every counter a call
+ *   reads is written earlier by the same call, so nothing needs clearing, but two calls that
+ *   may overlap on the GPU (different streams) race on it and must be ordered by the caller. */
+int lisa_cuda_moe_sort_static(lisa_stream_t stream, const int32_t *idx, int64_t slots, int64_t experts,
+                              int top_k, int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse);
 /* x_sorted[i, :] = x[token_rows[i], :] (gatherSort, moe.rs:375-377). */
 int lisa_cuda_gather_rows(lisa_stream_t stream, const void *x, const int32_t *token_rows,
                           int64_t rows, int64_t width, int dtype, void *out);

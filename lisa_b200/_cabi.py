@@ -49,6 +49,7 @@ SIGNATURES = {
     "lisa_cuda_moe_route": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp]),
     "lisa_cuda_moe_sort_workspace_bytes": (_sz, [_i64, _i64]),
     "lisa_cuda_moe_sort": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _sz]),
+    "lisa_cuda_moe_sort_static": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "lisa_cuda_gather_rows": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "lisa_cuda_swiglu": (_int, [_vp, _vp, _vp, _i64, _int, _vp]),
     "lisa_cuda_moe_combine": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _i64, _int, _vp]),

@@ -240,6 +240,14 @@ int lisa_cuda_moe_sort(lisa_stream_t stream, const int32_t *idx, int64_t slots, 
                     workspace);
 }
 
+int lisa_cuda_moe_sort_static(lisa_stream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k,
+                              int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse) {
+    if (!idx || !sorted_ids || !token_rows || !inverse) return fail(LISA_ERR_BAD_ARG, "moe_sort_static: null pointer");
+    if (slots < 1 || experts < 1 || top_k < 1 || slots > (1ll << 30)) return fail(LISA_ERR_BAD_ARG, "moe_sort_static: bad sizes");
+    if (experts > 4096) return fail(LISA_ERR_LIMIT, "moe_sort_static: experts <= 4096");
+    return moe_sort_static(static_cast<cudaStream_t>(stream), idx, slots, experts, top_k, sorted_ids, token_rows, inverse);
+}
+
 int lisa_cuda_gather_rows(lisa_stream_t stream, const void *x, const int32_t *token_rows, int64_t rows, int64_t width,
                           int dtype, void *out) {
     if (!x || !token_rows || !out) return fail(LISA_ERR_BAD_ARG, "gather_rows: null pointer");

@@ -39,6 +39,9 @@ int moe_route(cudaStream_t stream, const float *logits, int64_t tokens, int64_t 
 size_t moe_sort_workspace_bytes(int64_t slots, int64_t experts);
 int moe_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k, int32_t *sorted_ids,
              int32_t *token_rows, int32_t *inverse, void *workspace);
+int64_t moe_sort_static_capacity();
+int moe_sort_static(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k,
+                    int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse);
 int moe_gather_rows(cudaStream_t stream, const void *x, const int32_t *token_rows, int64_t rows, int64_t width,
                     void *out);
 int moe_swiglu(cudaStream_t stream, const void *gate, const void *up, int64_t count, void *act);

@@ -9,6 +9,8 @@
 // is that of SparseMoeBlock::forward (crates/lisa-engine/src/models/qwen4/moe.rs:352-481).
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -174,10 +176,9 @@ __global__ void __launch_bounds__(kSortChunk) moe_sort_scatter_kernel(const int3
     }
 }
 
-int moe_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k, int32_t *sorted_ids,
-             int32_t *token_rows, int32_t *inverse, void *workspace) {
+static int launch_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k,
+                       int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse, int32_t *counts) {
     const int chunks = static_cast<int>((slots + kSortChunk - 1) / kSortChunk);
-    int32_t *counts = reinterpret_cast<int32_t *>(workspace);
     const size_t esm = static_cast<size_t>(experts) * sizeof(int32_t);
     moe_sort_hist_kernel<<<chunks, kSortChunk, esm, stream>>>(idx, static_cast<int>(slots), static_cast<int>(experts), counts);
     LISA_CUDA_TRY(cudaGetLastError());
@@ -188,6 +189,45 @@ int moe_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t exp
     LISA_CUDA_TRY(cudaGetLastError());
     count_launch(3);
     return LISA_OK;
+}
+
+int moe_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k, int32_t *sorted_ids,
+             int32_t *token_rows, int32_t *inverse, void *workspace) {
+    return launch_sort(stream, idx, slots, experts, top_k, sorted_ids, token_rows, inverse,
+                       reinterpret_cast<int32_t *>(workspace));
+}
+
+// ---- the same sort for callers that cannot allocate: the (chunk x expert) count table lives in a
+// file-scope device array instead of a caller workspace.  In host code the array's name is only a
+// stand-in for the symbol; the device address comes from cudaGetSymbolAddress, once per device.
+constexpr int64_t kStaticSortInts = 64 * 1024;  // 256 KiB, held by every GPU that loads the library
+static __device__ __align__(256) int32_t g_sort_scratch[kStaticSortInts];
+static std::mutex g_sort_scratch_mutex;
+static int32_t *g_sort_scratch_ptr[64] = {nullptr};
+
+int64_t moe_sort_static_capacity() { return kStaticSortInts; }
+
+int moe_sort_static(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k,
+                    int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse) {
+    const int64_t chunks = (slots + kSortChunk - 1) / kSortChunk;
+    if (chunks * experts > kStaticSortInts)
+        return fail(LISA_ERR_LIMIT, "moe_sort_static: ceil(slots/256) * experts exceeds the built-in scratch of 65536 counters");
+    int dev = 0;
+    LISA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(LISA_ERR_LIMIT, "moe_sort_static: device ordinal above 63");
+    int32_t *counts = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_sort_scratch_mutex);
+        if (!g_sort_scratch_ptr[dev]) {
+            void *ptr = nullptr;
+            LISA_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_sort_scratch));  // address on the current device
+            g_sort_scratch_ptr[dev] = reinterpret_cast<int32_t *>(ptr);
+        }
+        counts = g_sort_scratch_ptr[dev];
+    }
+    // Every counter the scan and scatter kernels read is first written by the histogram kernel of
+    // the same call, so nothing has to start at zero.
+    return launch_sort(stream, idx, slots, experts, top_k, sorted_ids, token_rows, inverse, counts);
 }
 
 // ---------------------------------------------------------------- row gather

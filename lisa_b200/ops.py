@@ -213,6 +213,21 @@ def moe_sort(idx: torch.Tensor, experts: int, top_k: int, *, stream=None):
     return sorted_ids, token_rows, inverse
 
 
+def moe_sort_static(idx: torch.Tensor, experts: int, top_k: int, out=None, *, stream=None):
+    """``moe_sort`` through the entry point that allocates nothing: the count table is a device
+    array built into the library.  Pass ``out=(sorted_ids, token_rows, inverse)`` to reuse the
+    caller's buffers, as a caller that cannot allocate would; limit ceil(slots/256)*experts <= 65536."""
+    _need_cuda(idx)
+    flat = idx.reshape(-1).contiguous()
+    slots = flat.numel()
+    if out is None:
+        out = tuple(torch.empty(slots, dtype=torch.int32, device=flat.device) for _ in range(3))
+    sorted_ids, token_rows, inverse = out
+    check(lib().lisa_cuda_moe_sort_static(_stream(stream), flat.data_ptr(), slots, experts, top_k,
+                                          sorted_ids.data_ptr(), token_rows.data_ptr(), inverse.data_ptr()))
+    return sorted_ids, token_rows, inverse
+
+
 def gather_rows(x: torch.Tensor, token_rows: torch.Tensor, *, stream=None) -> torch.Tensor:
     _need_cuda(x, token_rows)
     x = x.contiguous()

@@ -53,7 +53,6 @@ int qmv_device_status() {
     return v;
 }
 
-constexpr int kTileRows = 16;  // MMA M
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kQmvThreads = kConsumers + 32;  // + producer warp
@@ -65,6 +64,7 @@ struct QmvParams {
     const uint16_t *x;
     uint16_t *y;
     int n, k, m;        // m <= 8
+    int mc2;            // m rounded up to even: columns kept in the cross-warp reduction
     int srow_bytes;     // (K / group_size) * 2
     int units;          // K / 64
     int ushift;         // unit >> ushift = group (0 for group 64, 1 for group 128)
@@ -72,15 +72,16 @@ struct QmvParams {
     int s_chunk;        // async-copy granularity of scale rows: 16, 8 or 4 bytes; 0: 2-byte plain copies
     int l1, n1, l2;     // k-segments of a row: n1 segments of l1 lines, then one of l2 lines (l2 may be 0)
     int stages;
-    int stage_bytes;    // 16 * max(l1, l2) * 128
+    int stage_bytes;    // TR * max(l1, l2) * 128
 };
 
 // Shared-memory plan (bytes from the 1024-aligned base), shared by host and device.
+// `tr` = rows per tile (16 or 32).
 struct QmvSmemPlan {
     int ring, xb, xsum, sc, st, part, bars, total;
 };
-__host__ __device__ inline QmvSmemPlan qmv_plan(int units, int m, int xstride, int srow_bytes, int stages,
-                                                int stage_bytes) {
+__host__ __device__ inline QmvSmemPlan qmv_plan(int tr, int units, int m, int mc2, int xstride, int srow_bytes,
+                                                int stages, int stage_bytes) {
     QmvSmemPlan p;
     int off = 0;
     p.ring = off;            // stages x stage_bytes, every stage 1024-aligned (swizzle atom)
@@ -91,12 +92,13 @@ __host__ __device__ inline QmvSmemPlan qmv_plan(int units, int m, int xstride, i
     p.xsum = off;
     off += units * 8 * 4;    // sum(x) per unit and column
     off = (off + 15) & ~15;
-    p.sc = off;              // raw [scales | biases][16 rows][srow_bytes], as fetched
-    off += 2 * ((kTileRows * srow_bytes + 15) & ~15);
-    p.st = off;              // [2 buffers][16 rows][groups] of f32 {scale, bias - 128 * scale}
-    off += 2 * kTileRows * (srow_bytes / 2) * 8;
-    p.part = off;
-    off += 2 * kConsumerWarps * 128 * 4;
+    p.sc = off;              // raw [scales | biases][tr rows][srow_bytes], as fetched
+    off += 2 * ((tr * srow_bytes + 15) & ~15);
+    p.st = off;              // [2 buffers][tr rows][groups] of f32 {scale, bias - 128 * scale}
+    off += 2 * tr * (srow_bytes / 2) * 8;
+    p.part = off;            // [2 buffers][warps][tr rows][mc2 columns] partial sums
+    off += 2 * kConsumerWarps * tr * mc2 * 4;
+    off = (off + 15) & ~15;
     p.bars = off;            // 2 * kMaxStages mbarriers, abort flag
     off += 2 * kMaxStages * 8 + 16;
     p.total = off + 1024;    // slack to align the base
@@ -212,19 +214,24 @@ __device__ __forceinline__ void permute_x(const uint32_t (&raw)[8], uint32_t (&x
     }
 }
 
-template <int BITS>
+// Box heights of the code tensor maps, largest first; a tile is fetched with the fewest boxes.
+struct QmvMaps {
+    CUtensorMap a32, a16, a1;  // segments of l1 lines
+    CUtensorMap b32, b16, b1;  // the last segment of l2 lines
+};
+
+template <int BITS, int TR>
 __global__ void __launch_bounds__(kQmvThreads, 2)
-qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constant__ CUtensorMap map_a1,
-               const __grid_constant__ CUtensorMap map_b16, const __grid_constant__ CUtensorMap map_b1,
-               const QmvParams p) {
+qmv_mma_kernel(const __grid_constant__ QmvMaps maps, const QmvParams p) {
     using U = UnitGeom<BITS>;
+    constexpr int NH = TR / 8;  // 8-row groups per tile: lane (g, tig) owns rows g + 8 h
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const QmvSmemPlan plan = qmv_plan(p.units, p.m, p.xstride, p.srow_bytes, p.stages, p.stage_bytes);
+    const QmvSmemPlan plan = qmv_plan(TR, p.units, p.m, p.mc2, p.xstride, p.srow_bytes, p.stages, p.stage_bytes);
     uint8_t *ring = smem + plan.ring;
     uint8_t *xb = smem + plan.xb;
     float *xsum = reinterpret_cast<float *>(smem + plan.xsum);
@@ -233,12 +240,12 @@ qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constan
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + plan.bars);
     uint64_t *empty = full + kMaxStages;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + kMaxStages);
-    const int sc_half = (kTileRows * p.srow_bytes + 15) & ~15;  // bytes of one raw [16 rows] block
+    const int sc_half = (TR * p.srow_bytes + 15) & ~15;  // bytes of one raw [TR rows] block
 
     // Rows of this CTA: an even split of n at single-row granularity.
     const int row_begin = static_cast<int>((static_cast<int64_t>(blockIdx.x) * p.n) / gridDim.x);
     const int row_end = static_cast<int>((static_cast<int64_t>(blockIdx.x + 1) * p.n) / gridDim.x);
-    const int ntiles = (row_end - row_begin + kTileRows - 1) / kTileRows;
+    const int ntiles = (row_end - row_begin + TR - 1) / TR;
     const int nseg = p.n1 + (p.l2 > 0 ? 1 : 0);
     const int nsteps = ntiles * nseg;  // ring steps: (tile, k-segment)
 
@@ -260,21 +267,26 @@ qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constan
             for (int q = 0; q < nsteps; ++q) {
                 if (q >= p.stages) wait_or_abort(&empty[s], phase ^ 1, abort_flag, 1);
                 if (*abort_flag) break;
-                const int r0 = row_begin + it * kTileRows;
-                const int rows = min(kTileRows, row_end - r0);
+                const int r0 = row_begin + it * TR;
+                const int rows = min(TR, row_end - r0);
                 const bool first = sg < p.n1;
                 const int lines = first ? p.l1 : p.l2;
                 const int line0 = first ? sg * p.l1 : p.n1 * p.l1;
                 uint8_t *st = ring + static_cast<size_t>(s) * p.stage_bytes;
-                if (rows == kTileRows) {
-                    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(kTileRows * lines * 128));
-                    tma_load_3d(st, first ? &map_a16 : &map_b16, 0, line0, r0, &full[s]);
-                } else {
-                    // ragged last tile: one single-row box per row, at the offsets the 16-row box uses
-                    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(rows * lines * 128));
-                    for (int r = 0; r < rows; ++r)
-                        tma_load_3d(st + r * lines * 128, first ? &map_a1 : &map_b1, 0, line0, r0 + r, &full[s]);
+                mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(rows * lines * 128));
+                // the fewest boxes that cover `rows`: 32, then 16, then single rows, each at the
+                // shared-memory offset the full box would put that row (same swizzle)
+                int r = 0;
+                if (TR == 32 && rows - r >= 32) {
+                    tma_load_3d(st, first ? &maps.a32 : &maps.b32, 0, line0, r0, &full[s]);
+                    r += 32;
                 }
+                if (rows - r >= 16) {
+                    tma_load_3d(st + r * lines * 128, first ? &maps.a16 : &maps.b16, 0, line0, r0 + r, &full[s]);
+                    r += 16;
+                }
+                for (; r < rows; ++r)
+                    tma_load_3d(st + r * lines * 128, first ? &maps.a1 : &maps.b1, 0, line0, r0 + r, &full[s]);
                 issued = q + 1;
                 if (++s == p.stages) {
                     s = 0;
@@ -306,8 +318,8 @@ qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constan
     float2 *stbuf = reinterpret_cast<float2 *>(smem + plan.st);
     auto fetch_scales = [&](int it) {
         if (it < ntiles) {
-            const int r0 = row_begin + it * kTileRows;
-            const int rows = min(kTileRows, row_end - r0);
+            const int r0 = row_begin + it * TR;
+            const int rows = min(TR, row_end - r0);
             const size_t off = static_cast<size_t>(r0) * p.srow_bytes;
             const int nbytes = rows * p.srow_bytes;
             for (int c = tid * chunk; c < nbytes; c += kConsumers * chunk) {
@@ -331,9 +343,9 @@ qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constan
     // Converts the chunks this thread fetched for tile `it` into buffer `b`; call after wait_group.
     auto convert_scales = [&](int it, int b) {
         if (it < ntiles) {
-            const int r0 = row_begin + it * kTileRows;
-            const int nbytes = min(kTileRows, row_end - r0) * p.srow_bytes;
-            float2 *dst = stbuf + b * kTileRows * groups_row;
+            const int r0 = row_begin + it * TR;
+            const int nbytes = min(TR, row_end - r0) * p.srow_bytes;
+            float2 *dst = stbuf + b * TR * groups_row;
             for (int c = tid * chunk; c < nbytes; c += kConsumers * chunk) {
                 for (int e = 0; e < chunk; e += 2) {
                     const float sv = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(raw_s + c + e));
@@ -403,57 +415,65 @@ qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constan
     const int b0 = warp * U::kUnitBytes + tig * U::kLaneBytes;
     const int line0 = b0 >> 7, chunk0 = (b0 >> 4) & 7, inner = b0 & 15;
     const uint32_t kmask = reg_const(BITS == 4 ? 0x000f000fu : 0x00030003u), kmagic = reg_const(0x43004300u);
+    const uint32_t gstep = (kConsumerWarps >> p.ushift) * 8;
+    const bool part_writer = 2 * tig < p.mc2;  // lanes whose columns take part in the reduction
     int buf = 0, s = 0, phase = 0;
     for (int it = 0; it < ntiles; ++it) {
-        const int r0 = row_begin + it * kTileRows;
-        const int rows = min(kTileRows, row_end - r0);
-        float rs[4] = {0.f, 0.f, 0.f, 0.f};  // (row g, col 2tig), (g, 2tig+1), (g+8, 2tig), (g+8, 2tig+1)
-        const uint32_t st_lo = smem_u32(stbuf) + ((buf * kTileRows + g) * groups_row) * 8;
-        const uint32_t st_hi = st_lo + 8 * groups_row * 8;
+        const int r0 = row_begin + it * TR;
+        const int rows = min(TR, row_end - r0);
+        // rs[2h], rs[2h+1]: (row g + 8h, col 2tig), (row g + 8h, col 2tig + 1)
+        float rs[2 * NH];
+#pragma unroll
+        for (int i = 0; i < 2 * NH; ++i) rs[i] = 0.f;
+        const uint32_t st_g = smem_u32(stbuf) + ((buf * TR + g) * groups_row) * 8;
+        const uint32_t st_step = 8 * groups_row * 8;  // 8 rows further
         int ubase = 0;  // first unit of the segment
         for (int sg = 0; sg < nseg; ++sg) {
             const int lines = (sg < p.n1) ? p.l1 : p.l2;
             const int nu = lines * U::kUnitsPerLine;
-            // lane (g, tig) reads row g and row g + 8 of the stage; both rows share the swizzle key
+            // lane (g, tig) reads rows g + 8 h of the stage; they share the swizzle key
             const uint32_t rowp = ring32 + s * p.stage_bytes + g * lines * 128 + inner;
             const int keyg = g * lines;
-            const uint32_t hi_off = 8 * lines * 128;
+            const uint32_t h_off = 8 * lines * 128;
             wait_or_abort(&full[s], phase, abort_flag, 2);
-            // one unit: 16 rows x 64 codes against up to 8 columns of x.  `line` is the 128-byte line
-            // of the row segment, `uo` the unit index within the whole row.
-            auto unit = [&](int line, uint32_t xo, uint32_t xso, uint32_t go) {
-                const uint32_t src = rowp + line * 128 + ((chunk0 ^ ((keyg + line) & 7)) << 4);
-                uint32_t ra[8], rb[8];
-                decode16<BITS>(src, kmask, kmagic, ra);
-                decode16<BITS>(src + hi_off, kmask, kmagic, rb);
-                const uint4 x0 = lds_v4(xo), x1 = lds_v4(xo + 16);
-                float c[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_bf16_16x8x16(c, ra[0], rb[0], ra[1], rb[1], x0.x, x0.y);
-                mma_bf16_16x8x16(c, ra[2], rb[2], ra[3], rb[3], x0.z, x0.w);
-                mma_bf16_16x8x16(c, ra[4], rb[4], ra[5], rb[5], x1.x, x1.y);
-                mma_bf16_16x8x16(c, ra[6], rb[6], ra[7], rb[7], x1.z, x1.w);
-                const float2 lo = lds_f2(st_lo + go), hi = lds_f2(st_hi + go);  // {scale, bias - 128 scale}
-                const float2 xs = lds_f2(xso);
-                // scale * (c - 128 * sum(x)) + bias * sum(x)  ==  scale * c + (bias - 128 * scale) * sum(x)
-                rs[0] = fmaf(lo.x, c[0], fmaf(lo.y, xs.x, rs[0]));
-                rs[1] = fmaf(lo.x, c[1], fmaf(lo.y, xs.y, rs[1]));
-                rs[2] = fmaf(hi.x, c[2], fmaf(hi.y, xs.x, rs[2]));
-                rs[3] = fmaf(hi.x, c[3], fmaf(hi.y, xs.y, rs[3]));
-            };
-            // unit u = ubase + warp + 8 i: all byte offsets advance by constants per trip
             const int u0 = ubase + warp;
             uint32_t xo = xlane + u0 * 128, xso = xsum_lane + u0 * 32, go = (u0 >> p.ushift) * 8;
-            const uint32_t gstep = (kConsumerWarps >> p.ushift) * 8;
-            int ul = warp, line = line0;
-            for (; ul + kConsumerWarps < nu; ul += 2 * kConsumerWarps) {
-                unit(line, xo, xso, go);  // two independent chains per trip
-                unit(line + kLineStep, xo + kConsumerWarps * 128, xso + kConsumerWarps * 32, go + gstep);
-                line += 2 * kLineStep;
-                xo += 2 * kConsumerWarps * 128;
-                xso += 2 * kConsumerWarps * 32;
-                go += 2 * gstep;
+            int line = line0;
+            for (int ul = warp; ul < nu; ul += kConsumerWarps) {
+                // one unit: TR rows x 64 codes against up to 8 columns of x
+                const uint32_t src = rowp + line * 128 + ((chunk0 ^ ((keyg + line) & 7)) << 4);
+                const uint4 x0 = lds_v4(xo), x1 = lds_v4(xo + 16);
+                const float2 xs = lds_f2(xso);
+#pragma unroll
+                for (int hp = 0; hp < NH / 2; ++hp) {  // one 16-row MMA tile: row groups 2hp, 2hp+1
+                    if (rows > 16 * hp) {              // warp-uniform: skip MMA tiles with no rows
+                        uint32_t ra[8], rb[8];
+                        decode16<BITS>(src + (2 * hp) * h_off, kmask, kmagic, ra);
+                        if (rows > 16 * hp + 8) {
+                            decode16<BITS>(src + (2 * hp + 1) * h_off, kmask, kmagic, rb);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) rb[i] = 0;
+                        }
+                        float c[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma_bf16_16x8x16(c, ra[0], rb[0], ra[1], rb[1], x0.x, x0.y);
+                        mma_bf16_16x8x16(c, ra[2], rb[2], ra[3], rb[3], x0.z, x0.w);
+                        mma_bf16_16x8x16(c, ra[4], rb[4], ra[5], rb[5], x1.x, x1.y);
+                        mma_bf16_16x8x16(c, ra[6], rb[6], ra[7], rb[7], x1.z, x1.w);
+                        const float2 lo = lds_f2(st_g + (2 * hp) * st_step + go);      // {scale, bias - 128 scale}
+                        const float2 hi = lds_f2(st_g + (2 * hp + 1) * st_step + go);
+                        // scale * (c - 128 sum(x)) + bias * sum(x) == scale * c + (bias - 128 scale) * sum(x)
+                        rs[4 * hp + 0] = fmaf(lo.x, c[0], fmaf(lo.y, xs.x, rs[4 * hp + 0]));
+                        rs[4 * hp + 1] = fmaf(lo.x, c[1], fmaf(lo.y, xs.y, rs[4 * hp + 1]));
+                        rs[4 * hp + 2] = fmaf(hi.x, c[2], fmaf(hi.y, xs.x, rs[4 * hp + 2]));
+                        rs[4 * hp + 3] = fmaf(hi.x, c[3], fmaf(hi.y, xs.y, rs[4 * hp + 3]));
+                    }
+                }
+                line += kLineStep;
+                xo += kConsumerWarps * 128;
+                xso += kConsumerWarps * 32;
+                go += gstep;
             }
-            if (ul < nu) unit(line, xo, xso, go);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);  // this warp is done reading the stage
             ubase += nu;
@@ -462,19 +482,22 @@ qmv_mma_kernel(const __grid_constant__ CUtensorMap map_a16, const __grid_constan
                 phase ^= 1;
             }
         }
-        // cross-warp reduction of the 16 x 8 tile
-        *reinterpret_cast<float4 *>(part + ((buf * kConsumerWarps + warp) * 32 + lane) * 4) =
-            make_float4(rs[0], rs[1], rs[2], rs[3]);
+        // cross-warp reduction of the TR x mc2 outputs: part[buf][warp][row][col]
+        if (part_writer) {
+            float *pw = part + ((buf * kConsumerWarps + warp) * TR + g) * p.mc2 + 2 * tig;
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+                *reinterpret_cast<float2 *>(pw + 8 * h * p.mc2) = make_float2(rs[2 * h], rs[2 * h + 1]);
+        }
         scales_landed();                 // raw scales of the next tile, requested a tile ago
         convert_scales(it + 1, buf ^ 1);
         consumer_sync();
         fetch_scales(it + 2);
-        if (tid < 128) {
+        for (int e = tid; e < TR * p.mc2; e += kConsumers) {
             float total = 0.f;
 #pragma unroll
-            for (int wi = 0; wi < kConsumerWarps; ++wi) total += part[(buf * kConsumerWarps + wi) * 128 + tid];
-            const int l = tid >> 2, i = tid & 3;
-            const int row = (l >> 2) + 8 * (i >> 1), col = 2 * (l & 3) + (i & 1);
+            for (int wi = 0; wi < kConsumerWarps; ++wi) total += part[(buf * kConsumerWarps + wi) * TR * p.mc2 + e];
+            const int row = e / p.mc2, col = e - row * p.mc2;
             if (row < rows && col < p.m)
                 p.y[static_cast<size_t>(col) * p.n + r0 + row] = static_cast<uint16_t>(f32_to_bf16_bits(total));
         }
@@ -560,34 +583,44 @@ static bool split_lines(int lines, int max_lines, int &l1, int &n1, int &l2) {
 }
 
 template <int BITS>
-static bool plan_mma(int64_t n, int64_t k, int group_size, int m, QmvParams &p, int &grid, int &smem) {
+static bool plan_mma(int64_t n, int64_t k, int group_size, int m, QmvParams &p, int &tr, int &grid, int &smem) {
     if (group_size != 64 && group_size != 128) return false;
     if (k % 64 != 0 || k % group_size != 0) return false;
     const int64_t row_bytes = k * BITS / 8;
     if (row_bytes % 128 != 0) return false;  // whole lines only
     const int lines = static_cast<int>(row_bytes / 128);
-    if (!split_lines<BITS>(lines, 14, p.l1, p.n1, p.l2)) return false;
     p.units = static_cast<int>(k / 64);
+    p.mc2 = (m + 1) & ~1;
     p.ushift = (group_size == 128) ? 1 : 0;
     p.s_chunk = (p.srow_bytes % 16 == 0) ? 16 : (p.srow_bytes % 8 == 0) ? 8 : (p.srow_bytes % 4 == 0) ? 4 : 0;
     // rows of staged x sit 16 bytes past a multiple of 128 so that the lanes of different columns
     // hit different banks
     p.xstride = static_cast<int>(((k * 2 + 127) / 128) * 128 + 16);
-    p.stage_bytes = kTileRows * std::max(p.l1, p.l2) * 128;
     const int sms = sm_count();
     const int smem_max = max_smem_optin();
-    // Two CTAs per SM when every CTA still gets a couple of full tiles; else one.
-    const int per_sm = (n / (2 * sms) >= 2 * kTileRows) ? 2 : 1;
+    // Two CTAs per SM when every CTA still gets more than a tile; else one.
+    const int per_sm = (n >= static_cast<int64_t>(2) * sms * 24) ? 2 : 1;
     for (int ps = per_sm; ps >= 1; --ps) {
-        const int budget = (ps == 2) ? smem_max / 2 - 1024 : smem_max;
-        for (int stages = kMaxStages; stages >= 2; --stages) {
-            if (stages > 4 && stages * p.stage_bytes > 96 * 1024) continue;  // deep rings only while small
-            const QmvSmemPlan sp = qmv_plan(p.units, m, p.xstride, p.srow_bytes, stages, p.stage_bytes);
-            if (sp.total <= budget) {
-                p.stages = stages;
-                smem = sp.total;
-                grid = static_cast<int>(std::min<int64_t>((n + kTileRows - 1) / kTileRows, static_cast<int64_t>(sms) * ps));
-                return true;
+        const int64_t ctas = std::min<int64_t>((n + 15) / 16, static_cast<int64_t>(sms) * ps);
+        const int64_t rows_per_cta = (n + ctas - 1) / ctas;
+        // 32-row tiles halve the per-unit bookkeeping; worth it once a CTA has more than 16 rows
+        for (int t : {32, 16}) {
+            if (t == 32 && rows_per_cta <= 16) continue;
+            const int budget = (ps == 2) ? smem_max / 2 - 1024 : smem_max;
+            // stages of at most ~28 KB so that a ring of three fits beside the rest
+            const int max_lines = std::max(2, std::min(14, (28 * 1024) / (t * 128)));
+            if (!split_lines<BITS>(lines, max_lines, p.l1, p.n1, p.l2)) continue;
+            p.stage_bytes = t * std::max(p.l1, p.l2) * 128;
+            for (int stages = kMaxStages; stages >= 2; --stages) {
+                if (stages > 4 && stages * p.stage_bytes > 96 * 1024) continue;  // deep rings only while small
+                const QmvSmemPlan sp = qmv_plan(t, p.units, m, p.mc2, p.xstride, p.srow_bytes, stages, p.stage_bytes);
+                if (sp.total <= budget) {
+                    p.stages = stages;
+                    smem = sp.total;
+                    tr = t;
+                    grid = static_cast<int>(ctas);
+                    return true;
+                }
             }
         }
     }
@@ -599,6 +632,15 @@ static int make_code_map(CUtensorMap *map, const void *w, int64_t n, int64_t row
     const uint64_t strides[2] = {128, static_cast<uint64_t>(row_bytes)};
     const uint32_t box[3] = {128, static_cast<uint32_t>(lines_box), static_cast<uint32_t>(rows_box)};
     return make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+template <int BITS, int TR>
+static int launch_mma(const cudaLaunchConfig_t &cfg, int smem, const QmvMaps &maps, const QmvParams &p) {
+    if (smem > 48 * 1024)
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_mma_kernel<BITS, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_mma_kernel<BITS, TR>, maps, p));
+    count_launch();
+    return LISA_OK;
 }
 
 template <int BITS>
@@ -620,17 +662,17 @@ static int qmv_dispatch(cudaStream_t stream, const void *x, int64_t m, int64_t k
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
 
-    CUtensorMap maps[4];
-    bool maps_ready = false;
+    QmvMaps maps;
+    int maps_l1 = -1, maps_l2 = -1;
     int64_t done = 0;
     while (done < m) {
         const int64_t left = m - done;
         int mc = static_cast<int>(std::min<int64_t>(left, 8));
-        int grid = 0, smem = 0;
+        int grid = 0, smem = 0, tr = 16;
         bool ok = false;
         if (!force_simple && k % 8 == 0) {
             for (; mc >= 1; mc = (mc > 1) ? (mc + 1) / 2 : 0) {
-                if (plan_mma<BITS>(n, k, group_size, mc, p, grid, smem)) {
+                if (plan_mma<BITS>(n, k, group_size, mc, p, tr, grid, smem)) {
                     ok = true;
                     break;
                 }
@@ -660,13 +702,17 @@ static int qmv_dispatch(cudaStream_t stream, const void *x, int64_t m, int64_t k
             count_launch();
             return LISA_OK;
         }
-        if (!maps_ready) {
-            int rc = make_code_map(&maps[0], w, n, row_bytes, p.l1, kTileRows);
-            if (rc == LISA_OK) rc = make_code_map(&maps[1], w, n, row_bytes, p.l1, 1);
-            if (rc == LISA_OK) rc = make_code_map(&maps[2], w, n, row_bytes, p.l2 > 0 ? p.l2 : p.l1, kTileRows);
-            if (rc == LISA_OK) rc = make_code_map(&maps[3], w, n, row_bytes, p.l2 > 0 ? p.l2 : p.l1, 1);
+        if (maps_l1 != p.l1 || maps_l2 != p.l2) {
+            const int lb = p.l2 > 0 ? p.l2 : p.l1;
+            int rc = make_code_map(&maps.a32, w, n, row_bytes, p.l1, 32);
+            if (rc == LISA_OK) rc = make_code_map(&maps.a16, w, n, row_bytes, p.l1, 16);
+            if (rc == LISA_OK) rc = make_code_map(&maps.a1, w, n, row_bytes, p.l1, 1);
+            if (rc == LISA_OK) rc = make_code_map(&maps.b32, w, n, row_bytes, lb, 32);
+            if (rc == LISA_OK) rc = make_code_map(&maps.b16, w, n, row_bytes, lb, 16);
+            if (rc == LISA_OK) rc = make_code_map(&maps.b1, w, n, row_bytes, lb, 1);
             if (rc != LISA_OK) return rc;
-            maps_ready = true;
+            maps_l1 = p.l1;
+            maps_l2 = p.l2;
         }
         p.x = xp + done * k;
         p.y = yp + done * n;
@@ -674,10 +720,8 @@ static int qmv_dispatch(cudaStream_t stream, const void *x, int64_t m, int64_t k
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(kQmvThreads);
         cfg.dynamicSmemBytes = smem;
-        if (smem > 48 * 1024)
-            LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_mma_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_mma_kernel<BITS>, maps[0], maps[1], maps[2], maps[3], p));
-        count_launch();
+        const int rc = (tr == 32) ? launch_mma<BITS, 32>(cfg, smem, maps, p) : launch_mma<BITS, 16>(cfg, smem, maps, p);
+        if (rc != LISA_OK) return rc;
         done += mc;
     }
     return LISA_OK;

@@ -80,9 +80,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)  // may sleep up to ~2 us before reporting "not yet"
+        : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
 }
@@ -92,6 +92,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
                                           uint32_t limit = 4000000u) {
     for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// The same for many waiting warps that are not on the critical path: sleep between polls, so that
+// their polling does not fill the shared-memory pipeline that the few latency-critical threads
+// (TMA producer, MMA issuer) of the CTA also go through.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t *bar, uint32_t parity, uint32_t sleep_ns = 64,
+                                                  uint32_t limit = 4000000u) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(sleep_ns);
+    }
     return false;
 }
 

@@ -10,16 +10,21 @@
 //
 // One CTA computes a 128 (weight rows) x BT (tokens, <= 256) output tile.  The dequantized
 // weight tile is the A operand (M = 128 of the MMA), the activation tile the B operand
-// (N = BT), so every dequantized weight is reused for BT tokens.  Warp roles:
-//   warp 0      TMA producer: activation tiles [BT x 64] bf16 (128-byte swizzle) and packed
-//               weight tiles [128 rows x 128 bytes] (128-byte swizzle), both tiled
-//               cp.async.bulk.tensor loads completing on mbarriers (no multicast);
-//   warp 1      allocates TMEM and issues tcgen05.mma (one thread), four K=16 steps per
-//               64-wide k-block, accumulating in TMEM;
-//   warps 2..9  dequantize: thread (row, half) turns 32 codes of its row into bf16 and stores
-//               them in the K-major 128-byte-swizzled layout the MMA descriptor expects, then
-//               fence.proxy.async + mbarrier arrive; after the main loop the same warps read
-//               the accumulator with tcgen05.ld and store bf16 rows.
+// (N = BT), so every dequantized weight is reused for BT tokens.  The A operand lives in
+// TENSOR MEMORY: the dequantize warps write bf16 pairs with tcgen05.st next to the accumulator,
+// and tcgen05.mma reads A from there.  Shared memory therefore carries only the TMA writes and
+// the B-operand reads: with A in shared memory as well (16 KiB stored and 16 KiB re-read per
+// k-block on top of 32 KiB of B reads and 36 KiB of TMA writes per 524 tensor-pipe clocks) the
+// 128 B/clk shared-memory port, not the tensor pipe, set the pace.  Warp roles:
+//   warp 0       TMA producer: activation tiles [BT x 64] bf16 (128-byte swizzle) and packed
+//                weight tiles [128 rows x 128 bytes] (128-byte swizzle), both tiled
+//                cp.async.bulk.tensor loads completing on mbarriers (no multicast);
+//   warp 1       allocates TMEM and issues tcgen05.mma (one thread), four K=16 steps per
+//                64-wide k-block, accumulating in TMEM;
+//   warps 2..17  dequantize: thread (row, part) turns 16 codes of its row into 8 bf16 pairs and
+//                stores them to its TMEM lane (row) with tcgen05.st.32x32b.x8, then
+//                tcgen05.wait::st + fence + mbarrier arrive; after the main loop the same warps
+//                read the accumulator with tcgen05.ld and store bf16 rows.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -39,12 +44,11 @@ int qmm_device_status() {
 
 constexpr int kBN = 128;        // weight rows per CTA (MMA M)
 constexpr int kBK = 64;         // k per MMA stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kXStages = 4;     // activation ring
-constexpr int kWpStages = 2;    // packed-weight ring
-constexpr int kWdStages = 3;    // dequantized-weight ring
-constexpr int kDequantWarps = 8;
+constexpr int kStages = 5;      // operand ring: stage s = activation tile in shared memory + A tile in tensor memory
+constexpr int kWpStages = 4;    // packed-weight ring: loads run a whole ring (12+ k-blocks) ahead of their use
+constexpr int kACols = kBK / 2; // one k-block of A: 64 bf16 per lane = 32 columns
+constexpr int kDequantWarps = 16;  // 4 threads per weight row, 16 codes each per k-block
 constexpr int kThreads = (2 + kDequantWarps) * 32;
-constexpr int kWdBytes = kBN * kBK * 2;   // 16 KiB
 constexpr int kWpBytes = kBN * 128;       // 16 KiB
 
 struct QmmParams {
@@ -53,10 +57,10 @@ struct QmmParams {
     uint16_t *y;
     int m, n, k;
     int groups;       // k / group_size
-    int gshift_kb;    // group index of (k-block kb, half h): see dequant
     int group_size;
     int bt;           // tokens per CTA tile, multiple of 16, <= 256
-    int tmem_cols;    // power of two >= 32, >= bt
+    int acc_cols;     // accumulator columns: power of two >= 32, >= bt; the A ring starts there
+    int tmem_cols;    // allocation: power of two >= acc_cols + kStages * 32
     int num_kb;       // k / 64 (rounded up)
 };
 
@@ -83,28 +87,33 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc]; bf16 operands, f32 accumulate.
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem descriptor {desc_lo, desc_hi}]; bf16 operands, f32 accumulate.
+// A: lane = row, two consecutive k per 32-bit column (low half = even k), 8 columns per K=16 step.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t desc_lo, uint32_t desc_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        ".reg .b64 d;\n\t"
+        "mov.b64 d, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d, %4, p;\n\t"
         "}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        "r"(tmem_a), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);  // start address
-    d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (unused for swizzled K-major)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset between 8-row groups
-    d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (Blackwell)
-    d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
-    return d;
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
 }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle, 8-row groups 1024 bytes apart, in two
+// halves: low = start address >> 4 (bits 0-13) | leading byte offset 1 (bit 16, unused for swizzled
+// K-major); high = stride byte offset 1024 >> 4 (bits 32-45) | version 1 (bit 46) | SWIZZLE_128B (2 << 61).
+// Advancing k by 16 bf16 inside the 128-byte row adds 32 bytes = 2 to the low half.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr) { return (smem_addr >> 4) | (1u << 16); }
+constexpr uint32_t kUmmaDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
 // Instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t umma_idesc_bf16(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
@@ -119,79 +128,73 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-__device__ __forceinline__ void qmm_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int code) {
-    if (*abort_flag) return;
-    if (!mbar_wait(bar, parity)) {
-        *abort_flag = 1;
-        atomicExch(&g_qmm_status, code);
-    }
+// Every wait is bounded; one that runs out records which wait it was, and the role that hit it leaves
+// its loop.  The other roles then run out at their own next wait, so the kernel always ends.
+__device__ __forceinline__ bool qmm_wait(uint64_t *bar, uint32_t parity, int code) {
+    if (mbar_wait(bar, parity)) return true;
+    atomicExch(&g_qmm_status, code);
+    return false;
+}
+// For the sixteen dequantize warps, which run several k-blocks ahead of the MMA issuer: polls spaced
+// by a short sleep keep the shared-memory pipeline free for the single MMA-issuing thread.
+__device__ __forceinline__ bool qmm_wait_relaxed(uint64_t *bar, uint32_t parity, int code) {
+    if (mbar_wait_relaxed(bar, parity)) return true;
+    atomicExch(&g_qmm_status, code);
+    return false;
 }
 
-// d = a + b on two packed f32 lanes.
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
-    unsigned long long ra, rb, rd;
-    ra = (static_cast<unsigned long long>(__float_as_uint(a.y)) << 32) | __float_as_uint(a.x);
-    rb = (static_cast<unsigned long long>(__float_as_uint(b.y)) << 32) | __float_as_uint(b.x);
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
-    return make_float2(__uint_as_float(static_cast<uint32_t>(rd)), __uint_as_float(static_cast<uint32_t>(rd >> 32)));
+// (a & b) | c in one LOP3 with all three operands in registers.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
 
-// Eight bf16 weights (one 16-byte chunk of the A tile) from codes of `word`.
+// Eight bf16 weights (four packed pairs, k ascending) from codes of `word`.
 // 4-bit: code j is masked in place (bits 4j..4j+3, j <= 3 after an optional >>16), turned into the
-// float 2^23 + q*16^j by OR-ing the exponent of 2^23, and q*16^j * (s/16^j) + b is evaluated with
+// float 2^23 + q*16^j by OR-ing the exponent of 2^23, and (f - 2^23) * (s/16^j) + b is evaluated with
 // one rounding: the same real number as q*s + b, hence the same f32 and the same bf16.
 template <int BITS>
 struct Dequant;
 
 template <>
 struct Dequant<4> {
-    static constexpr int kWordsPer32 = 4;  // words holding 32 codes
-    // sj[j] = s / 16^j, j = 0..3
-    __device__ __forceinline__ static uint4 chunk(uint32_t word, const float (&sj)[4], float b) {
+    // sj[j] = s / 16^j, j = 0..3; mk[j] = 0xF << 4j kept in registers
+    __device__ __forceinline__ static void chunk(uint32_t word, const float (&sj)[4], float b, const uint32_t (&mk)[4],
+                                                 uint32_t mbits, uint32_t *out) {
         const float magic = 8388608.0f;
-        const uint32_t mbits = 0x4b000000u;
         const uint32_t hi = word >> 16;
-        uint32_t out[4];
 #pragma unroll
         for (int p = 0; p < 4; ++p) {  // codes 2p, 2p+1
             const uint32_t src = (p < 2) ? word : hi;
             const int j0 = (2 * p) & 3, j1 = (2 * p + 1) & 3;
-            const float f0 = __uint_as_float((src & (0xfu << (4 * j0))) | mbits);
-            const float f1 = __uint_as_float((src & (0xfu << (4 * j1))) | mbits);
-            const float2 q = fadd2(make_float2(f0, f1), make_float2(-magic, -magic));
-            const float2 v = ffma2(q, make_float2(sj[j0], sj[j1]), make_float2(b, b));
-            out[p] = f32x2_to_bf16x2(v.x, v.y);
+            const float q0 = __uint_as_float(and_or(src, mk[j0], mbits)) - magic;
+            const float q1 = __uint_as_float(and_or(src, mk[j1], mbits)) - magic;
+            out[p] = f32x2_to_bf16x2(fmaf(q0, sj[j0], b), fmaf(q1, sj[j1], b));
         }
-        return make_uint4(out[0], out[1], out[2], out[3]);
     }
 };
 
 template <>
 struct Dequant<2> {
-    static constexpr int kWordsPer32 = 2;
-    // 2-bit: codes 0..7 of `half16` (a 16-bit half of a word); sj[j] = s / 4^j, j = 0..7
-    __device__ __forceinline__ static uint4 chunk(uint32_t half16, const float (&sj)[8], float b) {
+    // 2-bit: codes 0..7 of `half16` (a 16-bit half of a word); sj[j] = s / 4^j, mk[j] = 3 << 2j
+    __device__ __forceinline__ static void chunk(uint32_t half16, const float (&sj)[8], float b, const uint32_t (&mk)[8],
+                                                 uint32_t mbits, uint32_t *out) {
         const float magic = 8388608.0f;
-        const uint32_t mbits = 0x4b000000u;
-        uint32_t out[4];
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
-            const float f0 = __uint_as_float((half16 & (0x3u << (4 * p))) | mbits);
-            const float f1 = __uint_as_float((half16 & (0x3u << (4 * p + 2))) | mbits);
-            const float2 q = fadd2(make_float2(f0, f1), make_float2(-magic, -magic));
-            const float2 v = ffma2(q, make_float2(sj[2 * p], sj[2 * p + 1]), make_float2(b, b));
-            out[p] = f32x2_to_bf16x2(v.x, v.y);
+            const float q0 = __uint_as_float(and_or(half16, mk[2 * p], mbits)) - magic;
+            const float q1 = __uint_as_float(and_or(half16, mk[2 * p + 1], mbits)) - magic;
+            out[p] = f32x2_to_bf16x2(fmaf(q0, sj[2 * p], b), fmaf(q1, sj[2 * p + 1], b));
         }
-        return make_uint4(out[0], out[1], out[2], out[3]);
     }
 };
 
 struct QmmSmem {
     // byte offsets from the 1024-aligned base
-    static constexpr int kXs = 0;                                   // kXStages * bt * 128
-    __host__ __device__ static int wp(int bt) { return kXStages * bt * 128; }
-    __host__ __device__ static int wd(int bt) { return wp(bt) + kWpStages * kWpBytes; }
-    __host__ __device__ static int bars(int bt) { return wd(bt) + kWdStages * kWdBytes; }
+    static constexpr int kXs = 0;                                   // kStages * bt * 128
+    __host__ __device__ static int wp(int bt) { return kStages * bt * 128; }
+    __host__ __device__ static int bars(int bt) { return wp(bt) + kWpStages * kWpBytes; }
     __host__ __device__ static int total(int bt) { return bars(bt) + 256 + 1024; }  // + alignment slack
 };
 
@@ -203,14 +206,13 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *xs = smem + QmmSmem::kXs;
     uint8_t *wp = smem + QmmSmem::wp(p.bt);
-    uint8_t *wd = smem + QmmSmem::wd(p.bt);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + QmmSmem::bars(p.bt));
-    uint64_t *x_full = bars, *x_empty = bars + kXStages;
-    uint64_t *wp_full = bars + 2 * kXStages, *wp_empty = wp_full + kWpStages;
-    uint64_t *wd_full = wp_empty + kWpStages, *wd_empty = wd_full + kWdStages;
-    uint64_t *acc_full = wd_empty + kWdStages;
+    // full[s]: activation tile landed (1 arrival + bytes) and all sixteen dequantize warps stored their
+    // part of the A tile; empty[s]: the MMAs that read stage s completed (tcgen05.commit).
+    uint64_t *full = bars, *empty = bars + kStages;
+    uint64_t *wp_full = bars + 2 * kStages, *wp_empty = wp_full + kWpStages;
+    uint64_t *acc_full = wp_empty + kWpStages;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     constexpr int KBW = (128 * 8 / BITS) / kBK;  // k-blocks per packed-weight stage: 4 (4-bit), 8 (2-bit)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -219,20 +221,15 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int num_kb = p.num_kb;
 
     if (tid == 0) {
-        for (int i = 0; i < kXStages; ++i) {
-            mbar_init(&x_full[i], 1);
-            mbar_init(&x_empty[i], 1);
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&full[i], 1 + kDequantWarps);
+            mbar_init(&empty[i], 1);
         }
         for (int i = 0; i < kWpStages; ++i) {
             mbar_init(&wp_full[i], 1);
             mbar_init(&wp_empty[i], kDequantWarps);
         }
-        for (int i = 0; i < kWdStages; ++i) {
-            mbar_init(&wd_full[i], kDequantWarps);
-            mbar_init(&wd_empty[i], 1);
-        }
         mbar_init(acc_full, 1);
-        *abort_flag = 0;
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -243,61 +240,87 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a = tmem_base + static_cast<uint32_t>(p.acc_cols);
     pdl_launch_dependents();
     pdl_wait();
 
     if (warp == 0) {
         // ---------------- TMA producer
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % kXStages;
-                if (kb >= kXStages) qmm_wait(&x_empty[s], ((kb / kXStages) - 1) & 1, abort_flag, 1);
-                if (*abort_flag) break;
-                if (kb % KBW == 0) {
-                    const int wi = kb / KBW, ws = wi % kWpStages;
-                    if (wi >= kWpStages) qmm_wait(&wp_empty[ws], ((wi / kWpStages) - 1) & 1, abort_flag, 2);
-                    if (*abort_flag) break;
-                    mbar_arrive_expect_tx(&wp_full[ws], kWpBytes);
-                    tma_load_2d(wp + ws * kWpBytes, &map_w, wi * 128, n0, &wp_full[ws]);
-                }
-                mbar_arrive_expect_tx(&x_full[s], static_cast<uint32_t>(p.bt) * 128u);
-                tma_load_2d(xs + static_cast<size_t>(s) * p.bt * 128, &map_x, kb * kBK, t0, &x_full[s]);
+            const int num_wi = (num_kb + KBW - 1) / KBW;
+            const uint32_t x_bytes = static_cast<uint32_t>(p.bt) * 128u;
+            int next_wi = 0;
+            bool ok = true;
+            // Packed weights come from HBM: their loads are issued a whole ring ahead, independent of
+            // how far the operand ring has drained.
+            auto issue_w = [&]() {
+                const int ws = next_wi % kWpStages;
+                if (next_wi >= kWpStages) ok = qmm_wait(&wp_empty[ws], ((next_wi / kWpStages) - 1) & 1, 2);
+                if (!ok) return;
+                mbar_arrive_expect_tx(&wp_full[ws], kWpBytes);
+                tma_load_2d(wp + ws * kWpBytes, &map_w, next_wi * 128, n0, &wp_full[ws]);
+                ++next_wi;
+            };
+            for (int i = 0; i < kWpStages && next_wi < num_wi; ++i) issue_w();
+            int s = 0;
+            uint32_t ph = 1;  // parity of the lap before: the first lap does not wait
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                if (kb > 0 && kb % KBW == 0 && next_wi < num_wi) issue_w();
+                if (kb >= kStages && ok) ok = qmm_wait(&empty[s], ph, 1);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&full[s], x_bytes);
+                tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, kb * kBK, t0, &full[s]);
+                if (++s == kStages) { s = 0; ph ^= 1; }
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer
+        // ---------------- MMA issuer: one thread, and few instructions per k-block: a lone thread
+        // runs its dependent instructions one after the other, and four MMAs of N = 256 give it 512
+        // tensor-pipe clocks for one trip of this loop
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(p.bt);
+            const uint32_t b_lo0 = umma_desc_lo(smem_u32(xs));
+            const uint32_t b_step = static_cast<uint32_t>(p.bt) * 8u;  // one stage, in 16-byte units
+            int s = 0;
+            uint32_t ph = 0, acc = 0;
+            bool ok = true;
             for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % kXStages, b = kb % kWdStages;
-                qmm_wait(&x_full[s], (kb / kXStages) & 1, abort_flag, 3);
-                qmm_wait(&wd_full[b], (kb / kWdStages) & 1, abort_flag, 4);
-                if (*abort_flag) break;
+                ok = qmm_wait(&full[s], ph, 3);
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(wd + b * kWdBytes);
-                const uint32_t b_addr = smem_u32(xs + static_cast<size_t>(s) * p.bt * 128);
+                const uint32_t a_addr = tmem_a + static_cast<uint32_t>(s * kACols);
+                const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(s) * b_step;
 #pragma unroll
                 for (int ks = 0; ks < kBK / 16; ++ks) {
-                    umma_bf16(tmem_base, umma_desc_sw128(a_addr + ks * 32), umma_desc_sw128(b_addr + ks * 32), idesc,
-                              (kb > 0 || ks > 0) ? 1u : 0u);
+                    umma_bf16_ts(tmem_base, a_addr + ks * 8, b_lo + ks * 2, kUmmaDescHiSw128, idesc, acc);
+                    acc = 1;
                 }
-                umma_commit(&x_empty[s]);
-                umma_commit(&wd_empty[b]);
+                umma_commit(&empty[s]);
+                if (++s == kStages) { s = 0; ph ^= 1; }
             }
-            umma_commit(acc_full);
+            if (ok) umma_commit(acc_full);
         }
     } else {
         // ---------------- dequantize, then epilogue
-        const int dq = tid - 64;            // 0..255
-        const int row = dq & 127;           // weight row of the tile
-        const int half = dq >> 7;           // which 32 of the 64 k of a k-block
+        const int quad = warp & 3;           // this warp's TMEM lanes: 32*quad .. 32*quad+31
+        const int part = (warp - 2) >> 2;    // which 16 of the 64 k of a k-block
+        const int row = quad * 32 + lane;    // weight row of the tile = TMEM lane
         const int grow = n0 + row;
         const bool row_ok = grow < p.n;
         const int swz = row & 7;
         const uint16_t *srow = p.scales + static_cast<size_t>(row_ok ? grow : 0) * p.groups;
         const uint16_t *brow = p.biases + static_cast<size_t>(row_ok ? grow : 0) * p.groups;
-        // group of (kb, half): k = kb*64 + half*32
-        auto group_of = [&](int kb) { return (kb * kBK + half * 32) / p.group_size; };
+        // group of (kb, part): k = kb*64 + part*16; group sizes are powers of two
+        const int gshift = (p.group_size == 32) ? 5 : (p.group_size == 64) ? 6 : 7;
+        auto group_of = [&](int kb) { return (kb * kBK + part * 16) >> gshift; };
+        // masks and the exponent of 2^23, pinned in registers so that every extraction is one LOP3
+        uint32_t mk[8], mbits;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            asm volatile("mov.u32 %0, %1;" : "=r"(mk[j]) : "r"(BITS == 4 ? (0xfu << (4 * (j & 3))) : (0x3u << (2 * j))));
+        asm volatile("mov.u32 %0, %1;" : "=r"(mbits) : "r"(0x4b000000u));
+        const uint32_t wp32 = smem_u32(wp) + row * 128;
+        const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(part * 8);
         float s_next = 0.f, b_next = 0.f;
         {
             const int g = group_of(0);
@@ -306,8 +329,11 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 b_next = bf16_bits_to_f32(__ldg(brow + g));
             }
         }
+        int a = 0;
+        uint32_t aph = 1;  // parity of the lap before: the first lap over the ring does not wait
+        bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
-            const int wi = kb / KBW, ws = wi % kWpStages, sub = kb % KBW, b = kb % kWdStages;
+            const int wi = kb / KBW, ws = wi % kWpStages, sub = kb % KBW;
             const float sc = s_next, bi = b_next;
             if (kb + 1 < num_kb) {
                 const int g = group_of(kb + 1);
@@ -319,33 +345,30 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     b_next = 0.f;
                 }
             }
-            if (sub == 0) qmm_wait(&wp_full[ws], (wi / kWpStages) & 1, abort_flag, 5);
-            // packed codes of (row, k-block, half): 32 codes
-            const uint8_t *prow = wp + ws * kWpBytes + row * 128;
-            uint32_t words[4];
+            if (sub == 0) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wi / kWpStages) & 1, 5));
+            if (!ok) break;
+            // packed codes of (row, k-block, part): 16 codes
+            uint32_t w0, w1;
             if (BITS == 4) {
-                const int c = sub * 2 + half;  // 16-byte chunk of the 128-byte packed row
-                const uint4 v = *reinterpret_cast<const uint4 *>(prow + ((c ^ swz) << 4));
-                words[0] = v.x; words[1] = v.y; words[2] = v.z; words[3] = v.w;
+                const int c = sub * 2 + (part >> 1);  // 16-byte chunk of the 128-byte packed row
+                asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1)
+                             : "r"(wp32 + ws * kWpBytes + ((c ^ swz) << 4) + (part & 1) * 8));
             } else {
-                const int c = sub;
-                const uint2 v = *reinterpret_cast<const uint2 *>(prow + ((c ^ swz) << 4) + half * 8);
-                words[0] = v.x; words[1] = v.y; words[2] = 0; words[3] = 0;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(wp32 + ws * kWpBytes + ((sub ^ swz) << 4) + part * 4));
+                w1 = w0 >> 16;
+                w0 &= 0xffffu;
             }
             if (sub == KBW - 1 || kb == num_kb - 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&wp_empty[ws]);
             }
-            if (kb >= kWdStages) qmm_wait(&wd_empty[b], ((kb / kWdStages) - 1) & 1, abort_flag, 6);
-            uint8_t *drow = wd + b * kWdBytes + (row >> 3) * 1024 + swz * 128;
+            uint32_t o[8];
             if (BITS == 4) {
                 float sj[4];
                 sj[0] = sc; sj[1] = sc * 0.0625f; sj[2] = sc * 0.00390625f; sj[3] = sc * 0.000244140625f;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 o = Dequant<4>::chunk(words[j], sj, bi);
-                    *reinterpret_cast<uint4 *>(drow + (((half * 4 + j) ^ swz) << 4)) = o;
-                }
+                const uint32_t m4[4] = {mk[0], mk[1], mk[2], mk[3]};
+                Dequant<4>::chunk(w0, sj, bi, m4, mbits, o);
+                Dequant<4>::chunk(w1, sj, bi, m4, mbits, o + 4);
             } else {
                 float sj[8];
                 float f = sc;
@@ -354,30 +377,34 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     sj[j] = f;
                     f *= 0.25f;
                 }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t h16 = (j & 1) ? (words[j >> 1] >> 16) : (words[j >> 1] & 0xffffu);
-                    const uint4 o = Dequant<2>::chunk(h16, sj, bi);
-                    *reinterpret_cast<uint4 *>(drow + (((half * 4 + j) ^ swz) << 4)) = o;
-                }
+                Dequant<2>::chunk(w0, sj, bi, mk, mbits, o);
+                Dequant<2>::chunk(w1, sj, bi, mk, mbits, o + 4);
             }
-            fence_proxy_async_smem();
+            // the MMAs that read this stage of the A ring a lap ago must have completed
+            if (kb >= kStages) {
+                ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&empty[a], aph, 6));  // warp-uniform: tcgen05.st is warp-wide
+                if (!ok) break;
+                tc_fence_after();
+            }
+            tmem_st8(a_lane + static_cast<uint32_t>(a * kACols), o);
+            tmem_st_wait();
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&wd_full[b]);
+            if (lane == 0) mbar_arrive(&full[a]);
+            if (++a == kStages) { a = 0; aph ^= 1; }
         }
 
         // ---------------- epilogue: TMEM -> registers -> bf16 rows of y
-        qmm_wait(acc_full, 0, abort_flag, 7);
+        if (ok) ok = qmm_wait_relaxed(acc_full, 0, 7);
+        ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-wide
         tc_fence_after();
-        const int quad = warp & 3;                 // TMEM lanes 32*quad .. 32*quad+31
-        const int egroup = (warp - 2) >> 2;        // two warps share a quadrant: interleave column chunks
-        const int out_row = n0 + quad * 32 + lane;
+        const int out_row = n0 + row;
         const int chunks = p.bt / 16;
-        for (int ci = egroup; ci < chunks; ci += 2) {
+        for (int ci = part; ci < chunks && ok; ci += kDequantWarps / 4) {
             uint32_t r[16];
             tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
             tmem_ld_wait();
-            if (out_row < p.n && !*abort_flag) {
+            if (out_row < p.n) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int tok = t0 + ci * 16 + j;
@@ -430,8 +457,11 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
     p.group_size = group_size;
     int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
     p.bt = bt;
+    int acc = 32;
+    while (acc < bt) acc <<= 1;
+    p.acc_cols = acc;
     int cols = 32;
-    while (cols < bt) cols <<= 1;
+    while (cols < acc + kStages * kACols) cols <<= 1;
     p.tmem_cols = cols;
     p.num_kb = static_cast<int>((k + kBK - 1) / kBK);
 

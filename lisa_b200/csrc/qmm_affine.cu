@@ -21,8 +21,9 @@
 //                cp.async.bulk.tensor loads completing on mbarriers (no multicast);
 //   warp 1       allocates TMEM and issues tcgen05.mma (one thread), four K=16 steps per
 //                64-wide k-block, accumulating in TMEM;
-//   warps 2..17  dequantize: thread (row, part) turns 16 codes of its row into 8 bf16 pairs and
-//                stores them to its TMEM lane (row) with tcgen05.st.32x32b.x8, then
+//   warps 2..17  dequantize: warps 2..9 take the even k-blocks, warps 10..17 the odd ones; thread
+//                (row, half) turns 32 codes of its row into 16 bf16 pairs (packed f32x2 arithmetic)
+//                and stores them to its TMEM lane (row) with tcgen05.st.32x32b.x16, then
 //                tcgen05.wait::st + fence + mbarrier arrive; after the main loop the same warps
 //                read the accumulator with tcgen05.ld and store bf16 rows.
 #include <cuda.h>
@@ -47,7 +48,8 @@ constexpr int kBK = 64;         // k per MMA stage: 64 bf16 = one 128-byte swizz
 constexpr int kStages = 5;      // operand ring: stage s = activation tile in shared memory + A tile in tensor memory
 constexpr int kWpStages = 4;    // packed-weight ring: loads run a whole ring (12+ k-blocks) ahead of their use
 constexpr int kACols = kBK / 2; // one k-block of A: 64 bf16 per lane = 32 columns
-constexpr int kDequantWarps = 16;  // 4 threads per weight row, 16 codes each per k-block
+constexpr int kDequantWarps = 16;  // two sets of 8 warps (even / odd k-blocks); 2 threads per weight row, 32 codes each
+constexpr int kWarpsPerKb = kDequantWarps / 2;
 constexpr int kThreads = (2 + kDequantWarps) * 32;
 constexpr int kWpBytes = kBN * 128;       // 16 KiB
 
@@ -107,6 +109,14 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8])
                  "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                  : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::
+            "r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle, 8-row groups 1024 bytes apart, in two
 // halves: low = start address >> 4 (bits 0-13) | leading byte offset 1 (bit 16, unused for swizzled
@@ -150,45 +160,35 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     return d;
 }
 
-// Eight bf16 weights (four packed pairs, k ascending) from codes of `word`.
-// 4-bit: code j is masked in place (bits 4j..4j+3, j <= 3 after an optional >>16), turned into the
-// float 2^23 + q*16^j by OR-ing the exponent of 2^23, and (f - 2^23) * (s/16^j) + b is evaluated with
-// one rounding: the same real number as q*s + b, hence the same f32 and the same bf16.
-template <int BITS>
-struct Dequant;
-
-template <>
-struct Dequant<4> {
-    // sj[j] = s / 16^j, j = 0..3; mk[j] = 0xF << 4j kept in registers
-    __device__ __forceinline__ static void chunk(uint32_t word, const float (&sj)[4], float b, const uint32_t (&mk)[4],
-                                                 uint32_t mbits, uint32_t *out) {
-        const float magic = 8388608.0f;
-        const uint32_t hi = word >> 16;
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {  // codes 2p, 2p+1
-            const uint32_t src = (p < 2) ? word : hi;
-            const int j0 = (2 * p) & 3, j1 = (2 * p + 1) & 3;
-            const float q0 = __uint_as_float(and_or(src, mk[j0], mbits)) - magic;
-            const float q1 = __uint_as_float(and_or(src, mk[j1], mbits)) - magic;
-            out[p] = f32x2_to_bf16x2(fmaf(q0, sj[j0], b), fmaf(q1, sj[j1], b));
-        }
-    }
-};
-
-template <>
-struct Dequant<2> {
-    // 2-bit: codes 0..7 of `half16` (a 16-bit half of a word); sj[j] = s / 4^j, mk[j] = 3 << 2j
-    __device__ __forceinline__ static void chunk(uint32_t half16, const float (&sj)[8], float b, const uint32_t (&mk)[8],
-                                                 uint32_t mbits, uint32_t *out) {
-        const float magic = 8388608.0f;
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const float q0 = __uint_as_float(and_or(half16, mk[2 * p], mbits)) - magic;
-            const float q1 = __uint_as_float(and_or(half16, mk[2 * p + 1], mbits)) - magic;
-            out[p] = f32x2_to_bf16x2(fmaf(q0, sj[2 * p], b), fmaf(q1, sj[2 * p + 1], b));
-        }
-    }
-};
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+// Two codes of `src` -> one word of two bf16 weights.  Code j sits at bit offset BITS*j of `src` and
+// is masked in place (m0, m1), turned into the float 2^23 + q * 2^(BITS*j) by OR-ing the exponent of
+// 2^23 (one LOP3 each), then both lanes at once: f - 2^23 (exact), (f - 2^23) * (s / 2^(BITS*j)) + b
+// with one rounding -- the same real number as q * s + b, hence the same f32 and the same bf16.
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t src, uint32_t m0, uint32_t m1, uint32_t mbits,
+                                                 unsigned long long neg_magic2, unsigned long long s2,
+                                                 unsigned long long b2) {
+    uint32_t out;
+    asm("{\n\t"
+        ".reg .b32 q0, q1;\n\t"
+        ".reg .f32 f0, f1;\n\t"
+        ".reg .b64 t;\n\t"
+        "lop3.b32 q0, %1, %2, %4, 0xEA;\n\t"
+        "lop3.b32 q1, %1, %3, %4, 0xEA;\n\t"
+        "mov.b64 t, {q0, q1};\n\t"
+        "add.rn.f32x2 t, t, %5;\n\t"
+        "fma.rn.f32x2 t, t, %6, %7;\n\t"
+        "mov.b64 {f0, f1}, t;\n\t"
+        "cvt.rn.bf16x2.f32 %0, f1, f0;\n\t"
+        "}\n"
+        : "=r"(out)
+        : "r"(src), "r"(m0), "r"(m1), "r"(mbits), "l"(neg_magic2), "l"(s2), "l"(b2));
+    return out;
+}
 
 struct QmmSmem {
     // byte offsets from the 1024-aligned base
@@ -207,8 +207,8 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint8_t *xs = smem + QmmSmem::kXs;
     uint8_t *wp = smem + QmmSmem::wp(p.bt);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + QmmSmem::bars(p.bt));
-    // full[s]: activation tile landed (1 arrival + bytes) and all sixteen dequantize warps stored their
-    // part of the A tile; empty[s]: the MMAs that read stage s completed (tcgen05.commit).
+    // full[s]: activation tile landed (1 arrival + bytes) and the eight dequantize warps of the k-block
+    // stored their parts of the A tile; empty[s]: the MMAs that read stage s completed (tcgen05.commit).
     uint64_t *full = bars, *empty = bars + kStages;
     uint64_t *wp_full = bars + 2 * kStages, *wp_empty = wp_full + kWpStages;
     uint64_t *acc_full = wp_empty + kWpStages;
@@ -222,7 +222,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(&full[i], 1 + kDequantWarps);
+            mbar_init(&full[i], 1 + kWarpsPerKb);
             mbar_init(&empty[i], 1);
         }
         for (int i = 0; i < kWpStages; ++i) {
@@ -302,83 +302,94 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
     } else {
         // ---------------- dequantize, then epilogue
+        const int dw = warp - 2;             // 0..15
         const int quad = warp & 3;           // this warp's TMEM lanes: 32*quad .. 32*quad+31
-        const int part = (warp - 2) >> 2;    // which 16 of the 64 k of a k-block
+        const int half = (dw >> 2) & 1;      // which 32 of the 64 k of a k-block
+        const int kpar = dw >> 3;            // this warp's k-blocks: kpar, kpar + 2, ...
         const int row = quad * 32 + lane;    // weight row of the tile = TMEM lane
         const int grow = n0 + row;
-        const bool row_ok = grow < p.n;
         const int swz = row & 7;
-        const uint16_t *srow = p.scales + static_cast<size_t>(row_ok ? grow : 0) * p.groups;
-        const uint16_t *brow = p.biases + static_cast<size_t>(row_ok ? grow : 0) * p.groups;
-        // group of (kb, part): k = kb*64 + part*16; group sizes are powers of two
+        // scale and bias of (k-block, half): group (kb*64 + half*32) >> log2(group_size); rows past n and
+        // groups past k read a valid element instead: their products meet zero activations or unused rows
         const int gshift = (p.group_size == 32) ? 5 : (p.group_size == 64) ? 6 : 7;
-        auto group_of = [&](int kb) { return (kb * kBK + part * 16) >> gshift; };
+        const size_t srow_off = static_cast<size_t>(grow < p.n ? grow : 0) * p.groups;
+        const uint16_t *srow = p.scales + srow_off;
+        const uint16_t *brow = p.biases + srow_off;
+        const int g_last = p.groups - 1;
         // masks and the exponent of 2^23, pinned in registers so that every extraction is one LOP3
         uint32_t mk[8], mbits;
 #pragma unroll
         for (int j = 0; j < 8; ++j)
             asm volatile("mov.u32 %0, %1;" : "=r"(mk[j]) : "r"(BITS == 4 ? (0xfu << (4 * (j & 3))) : (0x3u << (2 * j))));
         asm volatile("mov.u32 %0, %1;" : "=r"(mbits) : "r"(0x4b000000u));
+        const unsigned long long neg_magic2 = pack_f32x2(-8388608.0f, -8388608.0f);
         const uint32_t wp32 = smem_u32(wp) + row * 128;
-        const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(part * 8);
-        float s_next = 0.f, b_next = 0.f;
-        {
-            const int g = group_of(0);
-            if (row_ok && g < p.groups) {
-                s_next = bf16_bits_to_f32(__ldg(srow + g));
-                b_next = bf16_bits_to_f32(__ldg(brow + g));
-            }
-        }
-        int a = 0;
+        const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(half * 16);
+        auto load_sb = [&](int kb, uint32_t &sb, uint32_t &bb) {
+            int g = (kb * kBK + half * 32) >> gshift;
+            g = g < g_last ? g : g_last;
+            sb = __ldg(srow + g);
+            bb = __ldg(brow + g);
+        };
+        uint32_t s_next = 0, b_next = 0;
+        if (kpar < num_kb) load_sb(kpar, s_next, b_next);
+        int a = kpar;
         uint32_t aph = 1;  // parity of the lap before: the first lap over the ring does not wait
         bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kpar; kb < num_kb; kb += 2) {
             const int wi = kb / KBW, ws = wi % kWpStages, sub = kb % KBW;
-            const float sc = s_next, bi = b_next;
-            if (kb + 1 < num_kb) {
-                const int g = group_of(kb + 1);
-                if (row_ok && g < p.groups) {
-                    s_next = bf16_bits_to_f32(__ldg(srow + g));
-                    b_next = bf16_bits_to_f32(__ldg(brow + g));
-                } else {
-                    s_next = 0.f;
-                    b_next = 0.f;
-                }
-            }
-            if (sub == 0) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wi / kWpStages) & 1, 5));
+            const float sc = bf16_bits_to_f32(s_next), bi = bf16_bits_to_f32(b_next);
+            if (kb + 2 < num_kb) load_sb(kb + 2, s_next, b_next);
+            // first visit of this packed-weight stage
+            if (sub < 2) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wi / kWpStages) & 1, 5));
             if (!ok) break;
-            // packed codes of (row, k-block, part): 16 codes
-            uint32_t w0, w1;
+            // packed codes of (row, k-block, half): 32 codes
+            uint32_t w[4];
             if (BITS == 4) {
-                const int c = sub * 2 + (part >> 1);  // 16-byte chunk of the 128-byte packed row
-                asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1)
-                             : "r"(wp32 + ws * kWpBytes + ((c ^ swz) << 4) + (part & 1) * 8));
+                const int c = sub * 2 + half;  // 16-byte chunk of the 128-byte packed row
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                             : "r"(wp32 + ws * kWpBytes + ((c ^ swz) << 4)));
             } else {
-                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(wp32 + ws * kWpBytes + ((sub ^ swz) << 4) + part * 4));
-                w1 = w0 >> 16;
-                w0 &= 0xffffu;
+                uint32_t v0, v1;
+                asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v0), "=r"(v1)
+                             : "r"(wp32 + ws * kWpBytes + ((sub ^ swz) << 4) + half * 8));
+                w[0] = v0;        // 2-bit: each 16-bit half holds 8 codes; the masks reach bits 0..15 only
+                w[1] = v0 >> 16;
+                w[2] = v1;
+                w[3] = v1 >> 16;
             }
-            if (sub == KBW - 1 || kb == num_kb - 1) {
+            // last visit of the stage: hand it back to the producer
+            if (sub >= KBW - 2 || kb + 2 >= num_kb) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&wp_empty[ws]);
             }
-            uint32_t o[8];
+            uint32_t o[16];
+            const unsigned long long b2 = pack_f32x2(bi, bi);
             if (BITS == 4) {
-                float sj[4];
-                sj[0] = sc; sj[1] = sc * 0.0625f; sj[2] = sc * 0.00390625f; sj[3] = sc * 0.000244140625f;
-                const uint32_t m4[4] = {mk[0], mk[1], mk[2], mk[3]};
-                Dequant<4>::chunk(w0, sj, bi, m4, mbits, o);
-                Dequant<4>::chunk(w1, sj, bi, m4, mbits, o + 4);
+                const unsigned long long s01 = pack_f32x2(sc, sc * 0.0625f);
+                const unsigned long long s23 = pack_f32x2(sc * 0.00390625f, sc * 0.000244140625f);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t lo = w[i], hi = w[i] >> 16;
+                    o[4 * i + 0] = dequant_pair(lo, mk[0], mk[1], mbits, neg_magic2, s01, b2);
+                    o[4 * i + 1] = dequant_pair(lo, mk[2], mk[3], mbits, neg_magic2, s23, b2);
+                    o[4 * i + 2] = dequant_pair(hi, mk[0], mk[1], mbits, neg_magic2, s01, b2);
+                    o[4 * i + 3] = dequant_pair(hi, mk[2], mk[3], mbits, neg_magic2, s23, b2);
+                }
             } else {
-                float sj[8];
+                unsigned long long s2[4];
                 float f = sc;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    sj[j] = f;
-                    f *= 0.25f;
+                for (int j = 0; j < 4; ++j) {
+                    s2[j] = pack_f32x2(f, f * 0.25f);
+                    f *= 0.0625f;
                 }
-                Dequant<2>::chunk(w0, sj, bi, mk, mbits, o);
-                Dequant<2>::chunk(w1, sj, bi, mk, mbits, o + 4);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        o[4 * i + j] = dequant_pair(w[i], mk[2 * j], mk[2 * j + 1], mbits, neg_magic2, s2[j], b2);
+                }
             }
             // the MMAs that read this stage of the A ring a lap ago must have completed
             if (kb >= kStages) {
@@ -386,12 +397,13 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (!ok) break;
                 tc_fence_after();
             }
-            tmem_st8(a_lane + static_cast<uint32_t>(a * kACols), o);
+            tmem_st16(a_lane + static_cast<uint32_t>(a * kACols), o);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[a]);
-            if (++a == kStages) { a = 0; aph ^= 1; }
+            a += 2;
+            if (a >= kStages) { a -= kStages; aph ^= 1; }
         }
 
         // ---------------- epilogue: TMEM -> registers -> bf16 rows of y
@@ -400,7 +412,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         tc_fence_after();
         const int out_row = n0 + row;
         const int chunks = p.bt / 16;
-        for (int ci = part; ci < chunks && ok; ci += kDequantWarps / 4) {
+        for (int ci = dw >> 2; ci < chunks && ok; ci += kDequantWarps / 4) {
             uint32_t r[16];
             tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
             tmem_ld_wait();

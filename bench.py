@@ -9,7 +9,11 @@ Every linear is one call of the C ABI (`lisa_cuda_quantized_matmul_ex`), 252 lau
 token, replayed from a CUDA graph.  The weights of a token (2.04 GB) are far larger than
 L2, so no flush is needed between steps.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--mode decode|prefill]
+
+`--mode prefill` makes the second half of the same config the headline: the same stack at
+M=2048 through the tcgen05 GEMM, metric bf16 TFLOP/s against the measured dense bf16 peak.  The
+default (decode) line carries a short prefill measurement as well, under "qmm".
 
 One JSON line on stdout (rank 0).  With N > 1 (torchrun) each rank decodes its own token
 stream through its own replica ("replicas only": this config has no exchange step), value is
@@ -58,6 +62,23 @@ def peaks():
         d = json.load(open(path))
         return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def tensor_peak():
+    """Dense bf16 TFLOP/s for a kernel timed inside a long step (the sustained figure)."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops_sustained)"
+    return 1400.0, "fallback (1.4 PFLOP/s sustained, earlier measurement on this pool)"
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launches, from the
+# ncu captures summarised in profiles/ (qmv_mma_kernel on 4 layers of the decode stack; qmm_affine_kernel
+# on 2 layers of the prefill stack).  Traffic grows in proportion to the units processed, so the ratio
+# carries over to a full launch.
+DRAM_TRAFFIC_RATIO = {"decode": None, "prefill": None}
+PREFILL_M = 2048
 
 
 class ClockSampler:
@@ -244,6 +265,49 @@ class DecodeStack:
         else:
             self.token()
 
+    # ---- prefill: the same weights at M = PREFILL_M through the tensor-core GEMM
+    def prefill_setup(self, m: int = PREFILL_M):
+        torch = self.torch
+        g = torch.Generator(device=self.dev)
+        g.manual_seed(1234)
+        self.pm = m
+        self.pin = {"h": torch.randn((m, HIDDEN), device=self.dev, generator=g).to(torch.bfloat16),
+                    "a": torch.randn((m, Q_OUT), device=self.dev, generator=g).to(torch.bfloat16),
+                    "i": torch.randn((m, INTER), device=self.dev, generator=g).to(torch.bfloat16)}
+        self.pout = {n: torch.empty((m, n), dtype=torch.bfloat16, device=self.dev) for n in (Q_OUT, KV_OUT, HIDDEN, INTER)}
+
+    def prefill(self):
+        from lisa_b200 import _cabi
+
+        lib = _cabi.lib()
+        stream = self.torch.cuda.current_stream().cuda_stream
+        for per in self.weights:
+            for w, s, b, _, k, n, src in per:
+                rc = lib.lisa_cuda_quantized_matmul_ex(stream, self.pin[src].data_ptr(), self.pm, k, w.data_ptr(),
+                                                       s.data_ptr(), b.data_ptr(), n, 1, GROUP, BITS, 0,
+                                                       self.pout[n].data_ptr(), 0)
+                _cabi.check(rc)
+
+    def prefill_flops(self) -> float:
+        return 2.0 * self.pm * token_weights(self.layers)
+
+    def prefill_bytes(self) -> int:
+        return self.layers * sum(linear_bytes(k, n, self.pm) for _, k, n, _ in LINEARS)
+
+
+def time_prefill(torch, stack, steps: int, warmup: int):
+    """ms per prefill pass of the stack (CUDA events on the launching stream)."""
+    for _ in range(warmup):
+        stack.prefill()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        stack.prefill()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -253,6 +317,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures only")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
+                    help="decode: M=1 GEMV stack, HBM GB/s (headline); prefill: M=2048 GEMM stack, bf16 TFLOP/s")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -281,6 +347,9 @@ def main():
 
     warmup = max(args.warmup, 3)
     stack = DecodeStack(dev, seed=rank, layers=args.layers)
+    if args.mode == "prefill":
+        prefill_main(args, torch, dist, stack, rank, local_rank, world, warmup)
+        return
     before = ops.launch_count()
     stack.capture()
     launches_per_token = (ops.launch_count() - before) // (2 if stack.graph is not None else 1)
@@ -351,7 +420,9 @@ def main():
             "tokens_per_s": world * args.steps / (total_ms * 1e-3),
             "ms_per_step_median": statistics.median(step_ms),
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "traffic": None, "kernel": "qmv_stream_kernel<4,*,1>", "peak_source": peak_src,
+                         "traffic": (DRAM_TRAFFIC_RATIO["decode"] * bytes_token / max(launches_per_token, 1)
+                                     if DRAM_TRAFFIC_RATIO["decode"] else None),
+                         "kernel": "qmv_mma_kernel<4,*>", "peak_source": peak_src,
                          "bytes_per_launch_avg": bytes_token / max(launches_per_token, 1),
                          "us_per_launch_avg": 1e3 * total_ms / args.steps / max(launches_per_token, 1)},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -360,6 +431,14 @@ def main():
             "clocks": clocks, "device_status": status,
             "launch": {"graph": stack.graph is not None, "pdl": bool(stack.flags & 8), "layers": args.layers},
         }
+        # the prefill half of the same config, briefly (full stack, M = 2048)
+        stack.prefill_setup()
+        pms = time_prefill(torch, stack, steps=3, warmup=2)
+        tpeak, tsrc = tensor_peak()
+        tf = stack.prefill_flops() / (pms * 1e-3) / 1e12
+        line["qmm"] = {"metric": "qmm bf16 TFLOP/s", "value": tf, "m": PREFILL_M, "ms_per_pass": pms,
+                       "frac_of_bf16_peak": tf / tpeak, "peak": tpeak, "peak_source": tsrc,
+                       "launches_per_pass": args.layers * 7, "kernel": "qmm_affine_kernel<4>"}
         if not args.skip_cpu:
             layers = cpu_sample_layers()
             gbs, dt, cores = run_cpu_baseline(0, layers)
@@ -367,6 +446,74 @@ def main():
                 "value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                 "sample": f"{layers} of {LAYERS} layers (7 linears each), M=1, seed 0, {dt:.2f} s; "
                           "restatement of the reference's Rust dequant + scalar f32 matmul"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def prefill_main(args, torch, dist, stack, rank, local_rank, world, warmup):
+    """Headline = the prefill half of the config: M=2048 through qmm_affine_kernel, TFLOP/s."""
+    from lisa_b200 import ops
+
+    stack.prefill_setup()
+    before = ops.launch_count()
+    stack.prefill()
+    launches = ops.launch_count() - before
+    for _ in range(warmup - 1):
+        stack.prefill()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = time_prefill(torch, stack, steps=args.steps, warmup=0)
+    # end to end: activations from pinned host memory in, last output back, every pass
+    pinned_in = {k: v.cpu().pin_memory() for k, v in stack.pin.items()}
+    out = stack.pout[HIDDEN]
+    pinned_out = torch.empty_like(out, device="cpu").pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in pinned_in.values())
+    d2h = pinned_out.numel() * pinned_out.element_size()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        for k, v in pinned_in.items():
+            stack.pin[k].copy_(v, non_blocking=True)
+        stack.prefill()
+        pinned_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=torch.device("cuda", local_rank))
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        flops = stack.prefill_flops()
+        per_gpu = flops / (ms * 1e-3) / 1e12
+        peak, src = tensor_peak()
+        ratio = DRAM_TRAFFIC_RATIO["prefill"]
+        cfg = workload_config(world)
+        cfg["workload"] = ("configs[1] prefill: Qwen3-4B-shaped 4-bit gs64 linear stack, "
+                           f"{args.layers} layers x 7 linears, M={PREFILL_M}")
+        cfg["launches_per_pass"] = launches
+        cfg["l2"] = "inputs larger than L2 (2.04 GB of weights per pass)"
+        line = {
+            "metric": "qmm bf16 TFLOP/s", "value": world * per_gpu, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
+                         "frac": per_gpu / peak,
+                         "traffic": ratio * stack.prefill_bytes() / launches if ratio else None,
+                         "kernel": "qmm_affine_kernel<4>", "peak_source": src},
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": launches * args.steps, "clocks": clocks, "device_status": ops.device_status(),
+        }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -77,7 +77,7 @@ def tensor_peak():
 # ncu captures summarised in profiles/ (qmv_mma_kernel on 4 layers of the decode stack; qmm_affine_kernel
 # on 2 layers of the prefill stack).  Traffic grows in proportion to the units processed, so the ratio
 # carries over to a full launch.
-DRAM_TRAFFIC_RATIO = {"decode": None, "prefill": None}
+DRAM_TRAFFIC_RATIO = {"decode": 1.004, "prefill": 0.577}
 PREFILL_M = 2048
 
 

@@ -67,17 +67,102 @@ __global__ void __launch_bounds__(256) gather_qmv_kernel(const GatherParams p, i
     if (lane == 0) p.y[row * p.n + col] = static_cast<uint16_t>(f32_to_bf16_bits(result));
 }
 
+// ---------------------------------------------------------------------------------------
+// Tile table of the grouped GEMM, built on the device from the sorted ids (no host read-back):
+// tile = {expert, row_begin, row_end, 0}, at most `bt` rows, never spanning two experts -- the layout
+// of the reference's prefill tile table (crates/lisa-engine/src/models/qwen4/prefill_indirect.rs:103-133)
+// with the expert added.  Rows whose id is outside [0, experts) get zeros here and no tile.
+__device__ __forceinline__ int lower_bound_ids(const int32_t *ids, int rows, int value) {
+    int lo = 0, hi = rows;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(ids + mid) < value) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+constexpr int kTableThreads = 1024;
+
+__global__ void __launch_bounds__(kTableThreads) gather_tile_table_kernel(const int32_t *ids, int rows, int experts, int bt,
+                                                                          int n, int32_t *tiles, int32_t *tile_count,
+                                                                          uint16_t *y) {
+    __shared__ int scan[kTableThreads];
+    __shared__ int running;
+    const int tid = threadIdx.x;
+    if (tid == 0) running = 0;
+    __syncthreads();
+    for (int base = 0; base < experts; base += kTableThreads) {
+        const int e = base + tid;
+        int begin = 0, end = 0;
+        if (e < experts) {
+            begin = lower_bound_ids(ids, rows, e);
+            end = lower_bound_ids(ids, rows, e + 1);
+        }
+        const int mine = (end - begin + bt - 1) / bt;
+        scan[tid] = mine;
+        __syncthreads();
+        for (int off = 1; off < kTableThreads; off <<= 1) {  // inclusive Hillis-Steele scan
+            const int v = (tid >= off) ? scan[tid - off] : 0;
+            __syncthreads();
+            scan[tid] += v;
+            __syncthreads();
+        }
+        int at = running + scan[tid] - mine;
+        for (int r = begin; r < end; r += bt, ++at)
+            reinterpret_cast<int4 *>(tiles)[at] = make_int4(e, r, min(r + bt, end), 0);
+        __syncthreads();
+        if (tid == kTableThreads - 1) running += scan[tid];
+        __syncthreads();
+    }
+    if (tid == 0) *tile_count = running;
+    // rows with ids outside the table: zeros (sorted ids: negatives first, ids >= experts last)
+    const int first_ok = lower_bound_ids(ids, rows, 0);
+    const int first_bad = lower_bound_ids(ids, rows, experts);
+    const int64_t head = static_cast<int64_t>(first_ok) * n;
+    for (int64_t i = tid; i < head; i += kTableThreads) y[i] = 0;
+    const int64_t tail0 = static_cast<int64_t>(first_bad) * n, tail1 = static_cast<int64_t>(rows) * n;
+    for (int64_t i = tail0 + tid; i < tail1; i += kTableThreads) y[i] = 0;
+}
+
+// Rows per tile of the grouped GEMM: a CTA costs about the same for any tile up to 256 rows, so the
+// tile is as tall as the average expert run allows.
+static int grouped_tile_rows(int64_t rows, int64_t experts) {
+    const int64_t avg = rows / (experts > 0 ? experts : 1);
+    if (avg >= 96) return 256;
+    if (avg >= 40) return 128;
+    if (avg >= 12) return 64;
+    if (avg >= 4) return 32;
+    return 16;
+}
+
 size_t gather_qmm_workspace_bytes(int64_t rows, int64_t experts) {
-    // Tile table of the grouped GEMM: (ceil(rows/128) + experts) tiles of 4 int32, plus a counter block.
-    const int64_t tiles = (rows + 127) / 128 + experts;
+    // Tile table of the grouped GEMM: at most ceil(rows/16) + experts tiles of 4 int32, plus a counter block.
+    const int64_t tiles = (rows + 15) / 16 + experts;
     return static_cast<size_t>(tiles * 16 + 256);
 }
 
 int gather_qmm_affine(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
                       const void *scales, const void *biases, const int32_t *ids, int64_t experts, int64_t n,
                       int group_size, int bits, void *y, void *workspace, size_t workspace_bytes) {
-    (void)workspace;
-    (void)workspace_bytes;
+    // Grouped tensor-core GEMM once there are enough rows to fill 16-row tiles; below that the
+    // problem is weight streaming and the warp-per-output kernel is used.
+    if (workspace && workspace_bytes >= gather_qmm_workspace_bytes(rows, experts) && rows >= 32 && rows < (1ll << 30) &&
+        qmm_affine_supported(rows, k, n, group_size, bits)) {
+        const int bt = grouped_tile_rows(rows, experts);
+        const int64_t max_tiles = (rows + bt - 1) / bt + experts;
+        if (max_tiles <= 65535) {
+            int32_t *tile_count = reinterpret_cast<int32_t *>(workspace);
+            int32_t *tiles = tile_count + 64;  // 256 bytes further: 16-byte aligned int4 entries
+            gather_tile_table_kernel<<<1, kTableThreads, 0, stream>>>(ids, static_cast<int>(rows), static_cast<int>(experts),
+                                                                     bt, static_cast<int>(n), tiles, tile_count,
+                                                                     reinterpret_cast<uint16_t *>(y));
+            LISA_CUDA_TRY(cudaGetLastError());
+            count_launch();
+            return qmm_affine_grouped(stream, x, rows, k, w, scales, biases, experts, n, group_size, bits, y, bt, tiles,
+                                      tile_count, max_tiles);
+        }
+    }
     GatherParams p{};
     p.w = w;
     p.scales = reinterpret_cast<const uint16_t *>(scales);

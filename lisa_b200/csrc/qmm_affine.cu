@@ -64,6 +64,10 @@ struct QmmParams {
     int acc_cols;     // accumulator columns: power of two >= 32, >= bt; the A ring starts there
     int tmem_cols;    // allocation: power of two >= acc_cols + kStages * 32
     int num_kb;       // k / 64 (rounded up)
+    // Grouped (MoE) form: tile blockIdx.y is {expert, row_begin, row_end, -} of the rows sorted by expert;
+    // the weights of expert e are rows [e*n, (e+1)*n) of the packed matrix.  Null for the dense GEMM.
+    const int32_t *tiles;
+    const int32_t *tile_count;
 };
 
 // ---- tcgen05 / TMA wrappers ----
@@ -217,7 +221,14 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     constexpr int KBW = (128 * 8 / BITS) / kBK;  // k-blocks per packed-weight stage: 4 (4-bit), 8 (2-bit)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n0 = blockIdx.x * kBN;
-    const int t0 = blockIdx.y * p.bt;
+    int t0 = blockIdx.y * p.bt, t_end = p.m, wrow0 = n0;
+    if (p.tiles) {
+        if (static_cast<int>(blockIdx.y) >= __ldg(p.tile_count)) return;  // whole CTA, before any barrier
+        const int4 tile = __ldg(reinterpret_cast<const int4 *>(p.tiles) + blockIdx.y);
+        wrow0 = tile.x * p.n + n0;
+        t0 = tile.y;
+        t_end = tile.z;
+    }
     const int num_kb = p.num_kb;
 
     if (tid == 0) {
@@ -258,7 +269,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (next_wi >= kWpStages) ok = qmm_wait(&wp_empty[ws], ((next_wi / kWpStages) - 1) & 1, 2);
                 if (!ok) return;
                 mbar_arrive_expect_tx(&wp_full[ws], kWpBytes);
-                tma_load_2d(wp + ws * kWpBytes, &map_w, next_wi * 128, n0, &wp_full[ws]);
+                tma_load_2d(wp + ws * kWpBytes, &map_w, next_wi * 128, wrow0, &wp_full[ws]);
                 ++next_wi;
             };
             for (int i = 0; i < kWpStages && next_wi < num_wi; ++i) issue_w();
@@ -312,7 +323,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // scale and bias of (k-block, half): group (kb*64 + half*32) >> log2(group_size); rows past n and
         // groups past k read a valid element instead: their products meet zero activations or unused rows
         const int gshift = (p.group_size == 32) ? 5 : (p.group_size == 64) ? 6 : 7;
-        const size_t srow_off = static_cast<size_t>(grow < p.n ? grow : 0) * p.groups;
+        const size_t srow_off = static_cast<size_t>(wrow0 - n0 + (grow < p.n ? grow : 0)) * p.groups;
         const uint16_t *srow = p.scales + srow_off;
         const uint16_t *brow = p.biases + srow_off;
         const int g_last = p.groups - 1;
@@ -420,7 +431,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int tok = t0 + ci * 16 + j;
-                    if (tok < p.m)
+                    if (tok < t_end)
                         p.y[static_cast<size_t>(tok) * p.n + out_row] =
                             static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
                 }
@@ -456,8 +467,9 @@ bool qmm_affine_supported(int64_t m, int64_t k, int64_t n, int group_size, int b
     return true;
 }
 
-int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
-               const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
+static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                      const void *biases, int64_t n, int64_t experts, int group_size, int bits, void *y, unsigned flags,
+                      int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles) {
     QmmParams p{};
     p.scales = reinterpret_cast<const uint16_t *>(scales);
     p.biases = reinterpret_cast<const uint16_t *>(biases);
@@ -467,7 +479,6 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
     p.k = static_cast<int>(k);
     p.groups = static_cast<int>(k / group_size);
     p.group_size = group_size;
-    int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
     p.bt = bt;
     int acc = 32;
     while (acc < bt) acc <<= 1;
@@ -476,19 +487,22 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
     while (cols < acc + kStages * kACols) cols <<= 1;
     p.tmem_cols = cols;
     p.num_kb = static_cast<int>((k + kBK - 1) / kBK);
+    p.tiles = tiles;
+    p.tile_count = tile_count;
 
     CUtensorMap map_x, map_w;
     int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, static_cast<uint64_t>(k),
                          static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBK, static_cast<uint32_t>(bt));
     if (rc != LISA_OK) return rc;
     const uint64_t wrow_bytes = static_cast<uint64_t>(k) * bits / 8;
-    rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, wrow_bytes, static_cast<uint64_t>(n), wrow_bytes, 128,
-                     kBN);
+    rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, wrow_bytes, static_cast<uint64_t>(n * experts), wrow_bytes,
+                     128, kBN);
     if (rc != LISA_OK) return rc;
 
     const size_t smem = static_cast<size_t>(QmmSmem::total(bt));
-    dim3 grid(static_cast<unsigned>((n + kBN - 1) / kBN), static_cast<unsigned>((m + bt - 1) / bt));
-    if (grid.y > 65535) return fail(LISA_ERR_LIMIT, "qmm: too many row tiles");
+    const int64_t ytiles = tiles ? max_tiles : (m + bt - 1) / bt;
+    if (ytiles > 65535) return fail(LISA_ERR_LIMIT, "qmm: too many row tiles");
+    dim3 grid(static_cast<unsigned>((n + kBN - 1) / kBN), static_cast<unsigned>(ytiles));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kThreads);
@@ -508,6 +522,21 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
     }
     count_launch();
     return LISA_OK;
+}
+
+int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+               const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
+    const int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
+    return qmm_launch(stream, x, m, k, w, scales, biases, n, 1, group_size, bits, y, flags, bt, nullptr, nullptr, 0);
+}
+
+// Grouped GEMM over a tile table: rows of x sorted by expert, tile i = {expert, row_begin, row_end} with
+// row_end - row_begin <= bt; tiles[max_tiles][4] and *tile_count live in device memory.
+int qmm_affine_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
+                       const void *scales, const void *biases, int64_t experts, int64_t n, int group_size, int bits,
+                       void *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles) {
+    return qmm_launch(stream, x, rows, k, w, scales, biases, n, experts, group_size, bits, y, 0, bt, tiles, tile_count,
+                      max_tiles);
 }
 
 }  // namespace lisa

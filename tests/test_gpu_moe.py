@@ -52,20 +52,48 @@ def test_swiglu_and_combine_bit_exact(cuda):
 
 @pytest.mark.parametrize("bits", [4, 2])
 @pytest.mark.parametrize("n,k", [(768, 2048), (2048, 768)])
-def test_gather_qmm_matches_oracle(cuda, bits, n, k):
-    rng = np.random.default_rng(2)
+@pytest.mark.parametrize("rows", [12, 40, 300])
+def test_gather_qmm_matches_oracle(cuda, bits, n, k, rows):
+    """Few rows: the weight-streaming kernel (GEMV law, f32 weights); 32 rows and more: the grouped
+    tensor-core GEMM over the device-built tile table (tile-loader law, weights rounded to bf16)."""
+    rng = np.random.default_rng(2 + rows)
     experts = 6
     w, s, b = util.affine_weights(rng, n, k, bits, 64, experts=experts)
-    ids = np.sort(rng.integers(0, experts, size=40)).astype(np.int32)
-    ids[-1] = experts  # out of range: zeros, no weight access
+    ids = np.sort(rng.integers(0, experts, size=rows)).astype(np.int32)
+    ids[ids == 2] = 3   # an expert with no rows
+    ids[0] = -1         # ids outside the table, at both ends of the sorted order: zeros, no weight access
+    ids[-1] = experts
     x = util.activations(rng, ids.size, k)
     y = ops.gather_qmm(dev_bf16(x, cuda).reshape(ids.size, 1, k), dev_u32(w, cuda), dev_bf16(s, cuda),
                        dev_bf16(b, cuda), None, dev_i32(ids, cuda), True, 64, bits, True)
     assert y.shape == (ids.size, 1, n)
     got = O.bf16_to_f32(host_bf16_bits(y).reshape(ids.size, n))
-    ref = O.bf16_to_f32(O.gather_qmm(x, w, s, b, ids, 64, bits, round_weight_bf16=False))
+    ref = O.bf16_to_f32(O.gather_qmm(x, w, s, b, ids, 64, bits, round_weight_bf16=rows >= 32))
     assert util.parity(got, ref)[0] <= 1e-2
-    assert np.all(got[-1] == 0)
+    assert np.all(got[-1] == 0) and np.all(got[0] == 0)
+
+
+def test_grouped_gather_qmm_equals_dense_gemm_per_expert(cuda):
+    """BASELINE config 4 at full size (128 experts, 4096 tokens x top-8 = 32768 sorted rows, 2048 -> 768):
+    every expert run of the grouped GEMM must equal, bit for bit, the dense tensor-core GEMM on that
+    expert's rows and weights (same kernel, same accumulation order)."""
+    from lisa_b200 import _cabi
+
+    rng = np.random.default_rng(7)
+    experts, n, k, rows = 128, 768, 2048, 32768
+    g = torch.Generator(device=cuda)
+    g.manual_seed(5)
+    w = torch.randint(-2 ** 31, 2 ** 31 - 1, (experts, n, k // 8), dtype=torch.int32, device=cuda, generator=g)
+    s = (torch.randn((experts, n, k // 64), device=cuda, generator=g) * 0.02).abs().to(torch.bfloat16)
+    b = (torch.randn((experts, n, k // 64), device=cuda, generator=g) * 0.01).to(torch.bfloat16)
+    x = torch.randn((rows, k), device=cuda, generator=g).to(torch.bfloat16)
+    ids = np.sort(rng.integers(0, experts, size=rows)).astype(np.int32)
+    y = ops.gather_qmm(x.reshape(rows, 1, k), w, s, b, None, dev_i32(ids, cuda), True, 64, 4, True).reshape(rows, n)
+    for e in (0, 1, 17, 64, 127):
+        sel = np.nonzero(ids == e)[0]
+        lo, hi = int(sel[0]), int(sel[-1]) + 1
+        dense = ops.quantized_matmul(x[lo:hi].contiguous(), w[e], s[e], b[e], True, 64, 4, flags=_cabi.FLAG_FORCE_QMM)
+        assert torch.equal(dense, y[lo:hi]), e
 
 
 @pytest.mark.parametrize("tokens", [1, 64])

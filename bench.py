@@ -317,8 +317,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures only")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
-                    help="decode: M=1 GEMV stack, HBM GB/s (headline); prefill: M=2048 GEMM stack, bf16 TFLOP/s")
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "shard", "moe"],
+                    help="decode: M=1 GEMV stack, HBM GB/s (headline); prefill: M=2048 GEMM stack, bf16 TFLOP/s; "
+                         "shard: configs[2] 2-bit MLP stack, N-sharded over the ranks with an all-gather; "
+                         "moe: configs[3] routed experts, expert-parallel over the ranks with all-to-all")
+    ap.add_argument("--m", type=int, default=1, help="rows of x for --mode shard (1, 8 or 512)")
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens per rank for --mode moe (1, 64 or 4096)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -346,6 +350,9 @@ def main():
     from lisa_b200 import ops
 
     warmup = max(args.warmup, 3)
+    if args.mode in ("shard", "moe"):
+        sharded_main(args, torch, dist, dev, rank, world, warmup)
+        return
     stack = DecodeStack(dev, seed=rank, layers=args.layers)
     if args.mode == "prefill":
         prefill_main(args, torch, dist, stack, rank, local_rank, world, warmup)
@@ -514,6 +521,128 @@ def prefill_main(args, torch, dist, stack, rank, local_rank, world, warmup):
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gpu_launches": launches * args.steps, "clocks": clocks, "device_status": ops.device_status(),
         }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def sharded_main(args, torch, dist, dev, rank, world, warmup):
+    """configs[2] (N-sharded 2-bit MLP stack + all-gather) and configs[3] (expert-parallel routed experts +
+    all-to-all).  With one rank the same code runs unsharded and no collective is issued."""
+    from lisa_b200 import ops, parallel
+    from lisa_b200.quant import QuantizedLinear, SwitchGlu
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+
+    def affine(lead, n, k, bits):
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, lead + (n, k * bits // 32), dtype=torch.int32, device=dev, generator=g)
+        s = (torch.randn(lead + (n, k // GROUP), device=dev, generator=g) * 0.02).abs().to(torch.bfloat16)
+        b = (torch.randn(lead + (n, k // GROUP), device=dev, generator=g) * 0.01).to(torch.bfloat16)
+        return w, s, b
+
+    if args.mode == "shard":
+        hidden, inter, bits, m = 5120, 17408, 2, args.m
+        layers = args.layers if args.layers != LAYERS else 64
+        shapes = [(hidden, inter), (hidden, inter), (inter, hidden)]  # gate, up, down (K, N)
+        lins = []
+        for _ in range(layers):
+            per = []
+            for k, n in shapes:
+                n0, n1 = parallel.shard_rows(n, world, rank)
+                w, s, b = affine((), n1 - n0, k, bits)  # this rank's rows only: full matrices never exist
+                per.append(parallel.ShardedQuantizedLinear(w, s, b, n, n0, n1, GROUP, bits))
+            lins.append(per)
+        xs = {hidden: torch.randn((m, hidden), device=dev, generator=g).to(torch.bfloat16),
+              inter: torch.randn((m, inter), device=dev, generator=g).to(torch.bfloat16)}
+
+        def step():
+            for per in lins:
+                for lin, (k, n) in zip(per, shapes):
+                    if world > 1:
+                        lin.forward(xs[k])
+                    else:
+                        ops.quantized_matmul(xs[k], lin.weight, lin.scales, lin.biases, True, GROUP, bits)
+
+        weights = layers * sum(k * n for k, n in shapes)
+        work_bytes = layers * sum(n * k * bits // 8 + 2 * n * (k // GROUP) * 2 + m * k * 2 + m * n * 2 for k, n in shapes)
+        flops = 2.0 * m * weights
+        name = f"configs[2]: 27B-class 2-bit gs64 MLP stack, {layers} layers x (gate, up, down), M={m}"
+        par = f"N-sharded over {world} ranks, NCCL all-gather of every output" if world > 1 else "single GPU"
+        scaling = "strong"
+    else:
+        experts, top_k, hidden, inter, tokens = 128, 8, 2048, 768, args.tokens
+        e0, e1 = parallel.expert_range(experts, world, rank)
+        mk = lambda n, k: QuantizedLinear(*affine((e1 - e0,), n, k, 4), GROUP, 4)
+        block = SwitchGlu(mk(inter, hidden), mk(inter, hidden), mk(hidden, inter), top_k)
+        x = torch.randn((tokens, hidden), device=dev, generator=g).to(torch.bfloat16)
+        lg = torch.Generator(device=dev)
+        lg.manual_seed(100 + rank)
+        logits = torch.randn((tokens, experts), device=dev, generator=lg)
+
+        def local_experts(rows, local_ids):
+            order = torch.sort(local_ids, stable=True).indices
+            xr, ids = rows[order].contiguous(), local_ids[order].contiguous()
+            r = rows.shape[0]
+            gg = ops.gather_qmm(xr.reshape(r, 1, hidden), block.gate.weight, block.gate.scales, block.gate.biases, None,
+                                ids, True, GROUP, 4, True).reshape(r, inter)
+            uu = ops.gather_qmm(xr.reshape(r, 1, hidden), block.up.weight, block.up.scales, block.up.biases, None, ids,
+                                True, GROUP, 4, True).reshape(r, inter)
+            dd = ops.gather_qmm(ops.swiglu(gg, uu).reshape(r, 1, inter), block.down.weight, block.down.scales,
+                                block.down.biases, None, ids, True, GROUP, 4, True).reshape(r, hidden)
+            res = torch.empty_like(dd)
+            res[order] = dd
+            return res
+
+        def step():
+            if world > 1:
+                idx, wts = ops.moe_route(logits, top_k)
+                parallel.ep_moe_forward(x, idx, wts, experts, local_experts)
+            else:
+                block.forward(x, logits)
+
+        flops = 2.0 * tokens * top_k * 3 * inter * hidden  # per rank: its own tokens
+        work_bytes = 0
+        name = f"configs[3]: routed experts 128 x top-8, hidden 2048, intermediate 768, 4-bit gs64, {tokens} tokens per rank"
+        par = f"expert-parallel, {(e1 - e0)} experts per rank, NCCL all-to-all dispatch and combine" if world > 1 else "single GPU"
+        scaling = "weak"
+
+    for _ in range(warmup):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    before = ops.launch_count()
+    e0_.record()
+    for _ in range(args.steps):
+        step()
+    e1_.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = ops.launch_count() - before
+    ms = e0_.elapsed_time(e1_) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    if rank == 0:
+        total_flops = flops * (world if args.mode == "moe" else 1)
+        line = {"metric": "qmm bf16 TFLOP/s" if (args.mode == "moe" or args.m > 8) else "2-bit qmv HBM GB/s",
+                "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": name, "parallelism": par}, "gpu_launches": launches, "clocks": clocks,
+                "device_status": ops.device_status()}
+        if line["metric"].startswith("qmm"):
+            line.update(value=total_flops / (ms * 1e-3) / 1e12, unit="TFLOP/s")
+        else:
+            line.update(value=work_bytes / (ms * 1e-3) / 1e9, unit="GB/s")  # whole job: all ranks' weight bytes
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -68,10 +68,14 @@ static int check_affine(const char *op, const void *x, int64_t m, int64_t k, con
     return LISA_OK;
 }
 
-// Row count from which the tensor-core GEMM takes over from the CUDA-core streaming kernel.
-// The reference switches at qmv_batch_limit (crates/lisa-mlx/src/jit/matmul.rs:1873-1881);
-// here the CUDA-core kernel keeps up with HBM only while the per-weight FMA work stays small.
-static const int64_t kQmvMaxRows = 4;
+// Row count from which the tensor-core GEMM takes over from the weight-streaming kernel.
+// The reference switches at qmv_batch_limit (crates/lisa-mlx/src/jit/matmul.rs:1873-1881).  Here the
+// streaming kernel takes up to 8 rows in one pass over the weights while their activations fit its
+// shared-memory staging (m * k <= 8 * 9728, measured crossover); a GEMM CTA costs the same for any
+// tile of up to 256 rows, so it wins as soon as the streaming kernel would need a second pass.
+static const int64_t kQmvMaxRows = 8;
+static const int64_t kQmvMaxStaged = 8 * 9728;
+static bool prefer_qmv(int64_t m, int64_t k) { return m <= kQmvMaxRows && (m <= 4 || m * k <= kQmvMaxStaged); }
 
 static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
                                  const void *scales, const void *biases, int64_t n, int transpose, int group_size,
@@ -84,7 +88,7 @@ static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, 
     if (force_qmv && force_qmm) return fail(LISA_ERR_BAD_ARG, "quantized_matmul: contradictory flags");
     const bool qmm_ok = qmm_affine_supported(m, k, n, group_size, bits);
     if (force_qmm && !qmm_ok) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the GEMM kernel");
-    if (force_qmm || (!force_qmv && m > kQmvMaxRows && qmm_ok))
+    if (force_qmm || (!force_qmv && !prefer_qmv(m, k) && qmm_ok))
         return qmm_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
     return qmv_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
 }

@@ -321,7 +321,7 @@ def main():
                     help="decode: M=1 GEMV stack, HBM GB/s (headline); prefill: M=2048 GEMM stack, bf16 TFLOP/s; "
                          "shard: configs[2] 2-bit MLP stack, N-sharded over the ranks with an all-gather; "
                          "moe: configs[3] routed experts, expert-parallel over the ranks with all-to-all")
-    ap.add_argument("--m", type=int, default=1, help="rows of x for --mode shard (1, 8 or 512)")
+    ap.add_argument("--rows", dest="m", type=int, default=1, help="rows of x for --mode shard (1, 8 or 512)")
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per rank for --mode moe (1, 64 or 4096)")
     args = ap.parse_args()
 

@@ -230,6 +230,8 @@ class DecodeStack:
         self.flags = _cabi.FLAG_PDL if os.environ.get("LISA_BENCH_PDL", "1") != "0" else 0
         if os.environ.get("LISA_BENCH_SIMPLE", "0") == "1":
             self.flags |= _cabi.FLAG_FORCE_QMV_SIMPLE
+        if os.environ.get("LISA_BENCH_TC", "0") == "1":
+            self.flags |= _cabi.FLAG_FORCE_QMV_TC
         self.graph = None
 
     def token(self):

@@ -53,9 +53,11 @@ enum {
     LISA_FLAG_FORCE_QMV = 1 << 0,     /* CUDA-core streaming kernel (staged ring) */
     LISA_FLAG_FORCE_QMV_SIMPLE = 1 << 1, /* CUDA-core generic kernel (direct loads) */
     LISA_FLAG_FORCE_QMM = 1 << 2,     /* tcgen05 tensor-core kernel */
-    LISA_FLAG_PDL = 1 << 3            /* launch with programmatic stream serialization: the
+    LISA_FLAG_PDL = 1 << 3,           /* launch with programmatic stream serialization: the
                                          kernel prefetches weights before waiting on the
                                          previous kernel in the stream */
+    LISA_FLAG_FORCE_QMV_TC = 1 << 4   /* streaming kernel with the unpacked weights in tensor memory
+                                         (tcgen05); group size 64 only */
 };
 
 const char *lisa_cuda_last_error_string(void);

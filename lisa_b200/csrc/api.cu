@@ -83,13 +83,19 @@ static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, 
     if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: only transpose=true supported");
     int rc = check_affine("quantized_matmul", x, m, k, w, scales, biases, n, group_size, bits, dtype, y);
     if (rc != LISA_OK) return rc;
-    const bool force_qmv = (flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) != 0;
+    const bool force_tc = (flags & LISA_FLAG_FORCE_QMV_TC) != 0;
+    const bool force_qmv = (flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) != 0 || force_tc;
     const bool force_qmm = (flags & LISA_FLAG_FORCE_QMM) != 0;
     if (force_qmv && force_qmm) return fail(LISA_ERR_BAD_ARG, "quantized_matmul: contradictory flags");
     const bool qmm_ok = qmm_affine_supported(m, k, n, group_size, bits);
     if (force_qmm && !qmm_ok) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the GEMM kernel");
     if (force_qmm || (!force_qmv && !prefer_qmv(m, k) && qmm_ok))
         return qmm_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
+    if (force_tc) {
+        if (!qmv_tc_supported(m, k, n, group_size, bits))
+            return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the tensor-memory GEMV");
+        return qmv_tc(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
+    }
     return qmv_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
 }
 
@@ -107,8 +113,9 @@ int lisa_cuda_device_status(void) {
     // Non-zero after a kernel gave up on a bounded wait.  Synchronises the device.
     const int a = qmv_device_status();
     const int b = qmm_device_status();
-    if (a < 0 || b < 0) return -1;
-    return a | (b << 8);
+    const int c = qmv_tc_device_status();
+    if (a < 0 || b < 0 || c < 0) return -1;
+    return a | (b << 8) | (c << 16);
 }
 
 int lisa_cuda_quantized_matmul(lisa_stream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,

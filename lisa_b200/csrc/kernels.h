@@ -13,6 +13,12 @@ int qmv_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
                const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
 int qmv_device_status();
 
+// qmv_tc.cu: the same GEMV with the unpacked weights in tensor memory (tcgen05), group size 64, m <= 8 per pass
+bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);
+int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
+int qmv_tc_device_status();
+
 // qmm_affine.cu
 bool qmm_affine_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);
 int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,

@@ -369,11 +369,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 w[2] = v1;
                 w[3] = v1 >> 16;
             }
-            // last visit of the stage: hand it back to the producer
-            if (sub >= KBW - 2 || kb + 2 >= num_kb) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&wp_empty[ws]);
-            }
+            const bool last_visit = sub >= KBW - 2 || kb + 2 >= num_kb;
             uint32_t o[16];
             const unsigned long long b2 = pack_f32x2(bi, bi);
             if (BITS == 4) {
@@ -412,7 +408,12 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full[a]);
+            if (lane == 0) {
+                mbar_arrive(&full[a]);
+                // last visit of the packed stage: hand it back to the producer only now that its words
+                // have been consumed (an arrival placed right after the loads let the refill overtake them)
+                if (last_visit) mbar_arrive(&wp_empty[ws]);
+            }
             a += 2;
             if (a >= kStages) { a -= kStages; aph ^= 1; }
         }

@@ -1,0 +1,568 @@
+// Decode GEMV for MLX affine 2-/4-bit weights through tcgen05 with the weights in tensor memory:
+//   y[m, n] = sum_k x[m, k] * (scale * q + bias),  m <= 8 rows of x per launch, group size 64.
+//
+// Same operator as qmv_affine.cu (replaces affine_qmv_fast / affine_qmv_wide,
+// crates/lisa-mlx/src/shaders/common/matmul/quantized.metal:762-1088) and the same factorisation as the
+// reference's qdot (quantized.metal:196-295): per 64 codes  scale * sum(q*x) + bias * sum(x)  in f32.
+//
+// Why a second GEMV kernel.  The mma.sync kernel spends about 0.12 warp-instructions per code: the
+// fragment loads, the per-lane shifts and the four MMAs of every 16 rows x 64 codes are issued by the
+// same warps that unpack, and a 4-bit stream at HBM speed (45 codes per clock per SM) would need 5.5
+// warp-instructions per clock of the 4 an SM has.  Here the unpacked weights never pass through MMA
+// fragments: one LOP3 lifts TWO codes into a bf16 pair (mask 0x000F000F, OR 0x43004300: each half is
+// 128 + q exactly), thread (row) writes its 32 pair-words of a 64-code k-block straight to its lane of
+// tensor memory with tcgen05.st, and one thread issues tcgen05.mma with A = that tile (128 rows x 64 k,
+// in TMEM), B = the activations (16 padded rows x 64 k, in shared memory), D = a 128 x 16 f32 tile in
+// TMEM -- one D per 64-code group, so that scale and bias are applied by the epilogue warps:
+//   y += scale * D + (bias - 128 * scale) * sum(x_group).
+// About 0.04 warp-instructions per code.
+//
+// Work split: CTA = (128-row tile, k-slice); the k-slices of a tile form a thread-block cluster and are
+// summed through distributed shared memory by the cluster's rank 0.  CTAs use under half an SM, and the
+// weights do not depend on the previous kernel in the stream: launched with programmatic stream
+// serialization, kernel i+1 fills its ring and unpacks while kernel i still computes.
+//
+// Warp roles (14 warps):
+//   warp 0        TMA producer: packed tiles [128 rows x 128 bytes], 128-byte swizzle, no multicast;
+//   warp 1        TMEM allocation; one thread issues the MMAs, one commit per k-block;
+//   warps 2..9    unpack: warps 2..5 the even k-blocks, 6..9 the odd ones;
+//   warps 10..13  stage scales and biases, then (after griddepcontrol.wait) the activations in the
+//                 permuted K order of the pair words; epilogue per k-block; final reduction and store.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "tensor_map.h"
+
+namespace lisa {
+
+static __device__ int g_qmv_tc_status = 0;
+
+int qmv_tc_device_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_qmv_tc_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+namespace {
+
+constexpr int kRows = 128;            // weight rows per CTA = MMA M = TMEM lanes
+constexpr int kNA = 4;                // A ring (tensor memory), 32 columns per k-block
+constexpr int kND = 8;                // D ring (tensor memory), 16 columns per k-block
+constexpr int kACols = 32, kDCols = 16;
+constexpr int kTmemCols = 256;        // kNA * 32 + kND * 16
+constexpr int kMaxWStages = 6;        // packed-weight ring (shared memory), 16 KiB per stage
+constexpr int kWBytes = kRows * 128;
+constexpr int kUnpackWarps = 8, kEpilogueWarps = 4;
+constexpr int kThreads = (2 + kUnpackWarps + kEpilogueWarps) * 32;
+constexpr int kXTile = 1024;          // 8 token rows x 128 bytes of one k-block (rows 8..15: the zero block)
+
+struct TcParams {
+    const uint16_t *scales;
+    const uint16_t *biases;
+    const uint16_t *x;
+    uint16_t *y;
+    int n, k, m;
+    int groups;      // k / 64
+    int num_kb;      // k / 64
+    int splits;      // cluster size: k-slices per row tile
+    int wstages;     // stages of the packed ring
+    int max_l;       // k-blocks of the longest slice (sizes the shared-memory plan)
+};
+
+// Shared-memory plan, bytes from the 1024-aligned base.
+struct TcPlan {
+    int ring, xb, zero, xsum, sc, part, bars, total;
+};
+__host__ __device__ inline TcPlan tc_plan(int wstages, int max_l) {
+    TcPlan p;
+    int off = 0;
+    p.ring = off;
+    off += wstages * kWBytes;
+    p.xb = off;                       // max_l activation tiles of 1 KiB (8 rows x 128 bytes, swizzled)
+    off += max_l * kXTile;
+    p.zero = off;                     // rows 8..15 of every tile
+    off += kXTile;
+    p.xsum = off;                     // [max_l][8] f32
+    off += max_l * 8 * 4;
+    p.sc = off;                       // [max_l][128] words {scale bf16 | bias bf16 << 16}
+    off += max_l * kRows * 4;
+    p.part = off;                     // [128][8] f32 partial sums of this k-slice
+    off += kRows * 8 * 4;
+    p.bars = off;                     // 33 mbarriers and the TMEM address
+    off += 512;
+    p.total = off + 1024;
+    return p;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor {lo, hi}], bf16 operands, f32 accumulate.
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t desc_lo, uint32_t desc_hi,
+                                        uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 d;\n\t"
+        "mov.b64 d, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d, %4, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::
+            "r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int code) {
+    if (mbar_wait(bar, parity)) return true;
+    atomicExch(&g_qmv_tc_status, code);
+    return false;
+}
+// The producer and the unpack warps run ahead of griddepcontrol.wait, so their waits can last as long as
+// the previous kernel in the stream: polls spaced by a short sleep, and a limit of a few seconds.
+__device__ __forceinline__ bool tc_wait_relaxed(uint64_t *bar, uint32_t parity, int code) {
+    if (mbar_wait_relaxed(bar, parity, 32, 1u << 26)) return true;
+    atomicExch(&g_qmv_tc_status, code);
+    return false;
+}
+
+// K order of the pair words.  4-bit: word j of a k-block (8 codes) gives pair i = codes (8j+i, 8j+i+4),
+// i < 4.  2-bit: word j (16 codes) gives pair i = codes (16j+i, 16j+i+8), i < 8.  The activations are
+// stored in the same order.
+template <int BITS>
+__global__ void __launch_bounds__(kThreads, 2)
+qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
+    constexpr int CPW = 32 / BITS;             // codes per word
+    constexpr int KBW = (128 * 8 / BITS) / 64;  // k-blocks per packed stage: 4 / 8
+    constexpr int KB_BYTES = 64 * BITS / 8;    // packed bytes of one row of a k-block: 32 / 16
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const TcPlan plan = tc_plan(p.wstages, p.max_l);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + plan.bars);
+    uint64_t *wp_full = bars;                      // [kMaxWStages]
+    uint64_t *wp_empty = wp_full + kMaxWStages;    // [kMaxWStages], 8 unpack warps
+    uint64_t *a_full = wp_empty + kMaxWStages;     // [kNA], 4 unpack warps of the k-block's set
+    uint64_t *done = a_full + kNA;                 // [kND], tcgen05.commit of k-block kb: A stage free, D ready
+    uint64_t *d_empty = done + kND;                // [kND], 4 epilogue warps
+    uint64_t *x_ready = d_empty + kND;             // 4 epilogue warps
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(x_ready + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t rank = (p.splits > 1) ? cluster_ctarank() : 0u;
+    const int tile = blockIdx.x / p.splits;
+    const int n0 = tile * kRows;
+    // this CTA's k-slice, in packed stages and in k-blocks
+    const int total_ws = (p.num_kb + KBW - 1) / KBW;
+    const int ws0 = static_cast<int>((static_cast<int64_t>(rank) * total_ws) / p.splits);
+    const int ws1 = static_cast<int>((static_cast<int64_t>(rank + 1) * total_ws) / p.splits);
+    const int kb0 = ws0 * KBW;
+    const int L = min(ws1 * KBW, p.num_kb) - kb0;  // k-blocks of this slice (>= 0)
+
+    pdl_launch_dependents();
+    if (tid == 0) {
+        for (int i = 0; i < kMaxWStages; ++i) {
+            mbar_init(&wp_full[i], 1);
+            mbar_init(&wp_empty[i], kUnpackWarps);
+        }
+        for (int i = 0; i < kNA; ++i) mbar_init(&a_full[i], kUnpackWarps / 2);
+        for (int i = 0; i < kND; ++i) {
+            mbar_init(&done[i], 1);
+            mbar_init(&d_empty[i], kEpilogueWarps);
+        }
+        mbar_init(x_ready, kEpilogueWarps);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + kNA * kACols;
+    const uint32_t ring32 = smem_u32(smem + plan.ring);
+    const uint32_t xb32 = smem_u32(smem + plan.xb);
+    float *xsum = reinterpret_cast<float *>(smem + plan.xsum);
+    uint32_t *sc = reinterpret_cast<uint32_t *>(smem + plan.sc);
+    float *part = reinterpret_cast<float *>(smem + plan.part);
+
+    if (warp == 0) {
+        // ---------------- producer: packed codes do not depend on the previous kernel in the stream
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 1;
+            for (int wi = ws0; wi < ws1; ++wi) {
+                if (wi - ws0 >= p.wstages && !tc_wait_relaxed(&wp_empty[s], ph, 1)) break;
+                mbar_arrive_expect_tx(&wp_full[s], kWBytes);
+                tma_load_2d(ring32 + s * kWBytes, &map_w, wi * 128, n0, &wp_full[s]);
+                if (++s == p.wstages) { s = 0; ph ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0 && L > 0) {
+            // instruction descriptor: D f32, A and B bf16, K-major, M = 128, N = 16
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            pdl_wait();  // the bounded waits below start counting once the previous kernel is done
+            bool ok = tc_wait(x_ready, 0, 2);
+            int a = 0, d = 0;
+            uint32_t aph = 0;
+            const uint32_t zero32 = smem_u32(smem + plan.zero);
+            for (int kbl = 0; kbl < L && ok; ++kbl) {
+                ok = tc_wait(&a_full[a], aph, 3);
+                if (!ok) break;
+                tc_fence_after();
+                // B tile of this k-block: rows 0..7 at xt, rows 8..15 = the zero block: the stride between
+                // the two 8-row groups is whatever leads from this tile to the zero block
+                const uint32_t xt = xb32 + kbl * kXTile;
+                const uint32_t desc_hi = ((zero32 - xt) >> 4) | (1u << 14) | (2u << 29);
+                const uint32_t desc_lo = (xt >> 4) | (1u << 16);
+                const uint32_t a_addr = tmem_a + a * kACols, d_addr = tmem_d + d * kDCols;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) umma_ts(d_addr, a_addr + ks * 8, desc_lo + ks * 2, desc_hi, idesc, ks > 0);
+                umma_commit(&done[d]);
+                if (++a == kNA) { a = 0; aph ^= 1; }
+                if (++d == kND) d = 0;
+            }
+        }
+    } else if (warp < 2 + kUnpackWarps) {
+        // ---------------- unpack: thread = weight row = TMEM lane; one 64-code k-block per trip
+        const int uw = warp - 2;
+        const int set = uw >> 2;       // k-blocks set, set + 2, ...
+        const int quad = warp & 3;     // TMEM lanes 32*quad .. +31
+        const int row = quad * 32 + lane;
+        const int swz = row & 7;
+        uint32_t kmask, kmagic;
+        asm volatile("mov.u32 %0, %1;" : "=r"(kmask) : "r"(BITS == 4 ? 0x000f000fu : 0x00030003u));
+        asm volatile("mov.u32 %0, %1;" : "=r"(kmagic) : "r"(0x43004300u));
+        const uint32_t row32 = ring32 + row * 128;
+        const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16);
+        bool ok = true;
+        for (int kbl = set; kbl < L; kbl += 2) {
+            const int wsl = kbl / KBW, sub = kbl - wsl * KBW;  // stage of the slice, k-block inside it
+            const int s = wsl % p.wstages;
+            if (sub < 2) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], (wsl / p.wstages) & 1, 4));
+            if (!ok) break;
+            uint32_t o[32];
+            if (BITS == 4) {
+                const uint32_t base = row32 + s * kWBytes;
+                uint32_t w[8];
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                             : "r"(base + (((2 * sub) ^ swz) << 4)));
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                             : "r"(base + (((2 * sub + 1) ^ swz) << 4)));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    o[4 * j + 0] = lop_and_or(w[j], kmask, kmagic);
+                    o[4 * j + 1] = lop_and_or(w[j] >> 4, kmask, kmagic);
+                    o[4 * j + 2] = lop_and_or(w[j] >> 8, kmask, kmagic);
+                    o[4 * j + 3] = lop_and_or(w[j] >> 12, kmask, kmagic);
+                }
+            } else {
+                uint32_t w[4];
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                             : "r"(row32 + s * kWBytes + ((sub ^ swz) << 4)));
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[8 * j + i] = lop_and_or(w[j] >> (2 * i), kmask, kmagic);
+            }
+            const bool last_visit = sub >= KBW - 2 || kbl + 2 >= L;
+            // the A stage is free once the MMAs of k-block kbl - kNA completed; the D buffer of this
+            // k-block once the epilogue has read k-block kbl - kND
+            if (kbl >= kNA) ok = tc_wait_relaxed(&done[(kbl - kNA) % kND], ((kbl - kNA) / kND) & 1, 5);
+            if (ok && kbl >= kND) ok = tc_wait_relaxed(&d_empty[kbl % kND], ((kbl / kND) - 1) & 1, 6);
+            ok = __all_sync(0xffffffffu, ok);  // tcgen05.st is warp-wide
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t dst = a_lane + static_cast<uint32_t>((kbl % kNA) * kACols);
+            tmem_st16(dst, o);
+            tmem_st16(dst + 16, o + 16);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&a_full[kbl % kNA]);
+                // last visit of the packed stage: hand it back to the producer only now that its words are
+                // in TMEM (an arrival placed right after the loads let the refill overtake them)
+                if (last_visit) mbar_arrive(&wp_empty[s]);
+            }
+        }
+        (void)KB_BYTES;
+    } else {
+        // ---------------- staging, epilogue, reduction
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int et = tid - (2 + kUnpackWarps) * 32;  // 0..127
+        const int grow = min(n0 + row, p.n - 1);
+        // scales and biases of (row, group) of the slice: weights, no dependency on the previous kernel
+        {
+            const uint16_t *sr = p.scales + static_cast<size_t>(grow) * p.groups + kb0;
+            const uint16_t *br = p.biases + static_cast<size_t>(grow) * p.groups + kb0;
+            for (int g = 0; g < L; ++g) sc[g * kRows + row] = static_cast<uint32_t>(__ldg(sr + g)) | (static_cast<uint32_t>(__ldg(br + g)) << 16);
+        }
+        // activation tiles: zero everything (rows >= m and the zero block stay zero)
+        {
+            uint4 *z = reinterpret_cast<uint4 *>(smem + plan.xb);
+            const int n16 = (L + 1) * kXTile / 16;  // the zero block follows tile max_l-1; cover both ends
+            for (int i = et; i < n16; i += kEpilogueWarps * 32) z[i] = make_uint4(0, 0, 0, 0);
+            uint4 *zb = reinterpret_cast<uint4 *>(smem + plan.zero);
+            for (int i = et; i < kXTile / 16; i += kEpilogueWarps * 32) zb[i] = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+        pdl_wait();  // activations come from the previous kernel
+        {
+            // one item = one word's worth of codes (CPW activations) of one token: loaded, permuted into
+            // pair order, stored swizzled; the items of a (token, k-block) are adjacent lanes
+            constexpr int IPK = 64 / CPW;  // items per k-block: 8 / 4
+            const int items = p.m * L * IPK;
+            for (int base = 0; base < items; base += kEpilogueWarps * 32) {
+                const int item = base + et;
+                const bool in = item < items;
+                const int u = in ? item % (L * IPK) : 0, t = in ? item / (L * IPK) : 0;
+                const int kbl = u / IPK, j = u - kbl * IPK;
+                float s = 0.f;
+                if (in) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(t) * p.k + (kb0 + kbl) * 64 + j * CPW);
+                    const uint32_t dstrow = xb32 + kbl * kXTile + t * 128;
+                    if (BITS == 4) {
+                        const uint4 v = __ldg(src);
+                        const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) s += bf16_bits_to_f32(r[i] & 0xffffu) + __uint_as_float(r[i] & 0xffff0000u);
+                        const uint32_t o0 = __byte_perm(r[0], r[2], 0x5410), o1 = __byte_perm(r[0], r[2], 0x7632);
+                        const uint32_t o2 = __byte_perm(r[1], r[3], 0x5410), o3 = __byte_perm(r[1], r[3], 0x7632);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dstrow + ((j ^ t) << 4)), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+                    } else {
+                        const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+                        const uint32_t r[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) s += bf16_bits_to_f32(r[i] & 0xffffu) + __uint_as_float(r[i] & 0xffff0000u);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            o[2 * i] = __byte_perm(r[i], r[4 + i], 0x5410);
+                            o[2 * i + 1] = __byte_perm(r[i], r[4 + i], 0x7632);
+                        }
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dstrow + (((2 * j) ^ t) << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dstrow + (((2 * j + 1) ^ t) << 4)), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+                    }
+                }
+#pragma unroll
+                for (int off = 1; off < IPK; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+                if (in && j == 0) xsum[kbl * 8 + t] = s;
+            }
+        }
+        fence_proxy_async_smem();  // the MMA reads the tiles through the async proxy
+        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+        if (lane == 0) mbar_arrive(x_ready);
+
+        float rs[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) rs[t] = 0.f;
+        const uint32_t d_lane = tmem_d + (static_cast<uint32_t>(quad * 32) << 16);
+        bool ok = true;
+        for (int kbl = 0; kbl < L; ++kbl) {
+            const int d = kbl % kND;
+            ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[d], (kbl / kND) & 1, 7));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t c[8];
+            tmem_ld8(d_lane + d * kDCols, c);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&d_empty[d]);
+            const uint32_t sb = sc[kbl * kRows + row];
+            const float sv = bf16_bits_to_f32(sb & 0xffffu), bv = __uint_as_float(sb & 0xffff0000u);
+            const float bb = fmaf(-128.f, sv, bv);
+            const float4 xs0 = *reinterpret_cast<const float4 *>(xsum + kbl * 8);
+            const float4 xs1 = *reinterpret_cast<const float4 *>(xsum + kbl * 8 + 4);
+            const float xs[8] = {xs0.x, xs0.y, xs0.z, xs0.w, xs1.x, xs1.y, xs1.z, xs1.w};
+#pragma unroll
+            for (int t = 0; t < 8; ++t) rs[t] = fmaf(sv, __uint_as_float(c[t]), fmaf(bb, xs[t], rs[t]));
+        }
+        // this slice's partial sums; rows of x beyond m read zero tiles and give zero
+#pragma unroll
+        for (int t = 0; t < 8; ++t) part[row * 8 + t] = rs[t];
+    }
+
+    // ---------------- sum of the k-slices (cluster rank 0), store
+    tc_fence_before();
+    __syncthreads();
+    if (p.splits > 1) cluster_sync_all();
+    if (rank == 0 && warp >= 2 + kUnpackWarps) {
+        const int row = (warp & 3) * 32 + lane;
+        const uint32_t mine = smem_u32(part + row * 8);
+        float tot[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) tot[t] = part[row * 8 + t];
+        for (int r = 1; r < p.splits; ++r)
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                if (t < p.m) tot[t] += ld_cluster_f32(mine + 4 * t, static_cast<uint32_t>(r));
+        if (n0 + row < p.n) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                if (t < p.m) p.y[static_cast<size_t>(t) * p.n + n0 + row] = static_cast<uint16_t>(f32_to_bf16_bits(tot[t]));
+        }
+    }
+    if (p.splits > 1) cluster_sync_all();  // peers keep their shared memory until rank 0 has read it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+}  // namespace
+
+// Shapes the kernel takes: group size 64, m <= 8, packed rows addressable by a tensor map, and a k-slice
+// whose staging fits half an SM's shared memory.
+static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, TcParams &p, int &smem, int &grid) {
+    if (bits != 2 && bits != 4) return false;
+    if (group_size != 64 || k % 64 != 0 || m < 1 || m > 8) return false;
+    if ((k * bits / 8) % 16 != 0 || (k * 2) % 16 != 0) return false;
+    const int kbw = (128 * 8 / bits) / 64;
+    const int num_kb = static_cast<int>(k / 64);
+    const int total_ws = (num_kb + kbw - 1) / kbw;
+    const int64_t tiles = (n + kRows - 1) / kRows;
+    const int budget = max_smem_optin() / 2 - 2048;  // two CTAs (of consecutive kernels) per SM
+    // as many k-slices as keep the grid near one CTA per SM; more when the slice would not fit
+    int splits = 1;
+    while (splits < 8 && tiles * (splits * 2) <= sm_count() + 20 && splits * 2 <= total_ws) splits *= 2;
+    for (; splits <= 8; splits *= 2) {
+        if (splits > total_ws) break;
+        const int max_ws = (total_ws + splits - 1) / splits;
+        const int max_l = std::min(max_ws * kbw, num_kb);
+        for (int ws = std::min(kMaxWStages, max_ws); ws >= std::min(2, max_ws); --ws) {
+            const TcPlan plan = tc_plan(ws, max_l);
+            if (plan.total <= budget) {
+                p.splits = splits;
+                p.wstages = ws;
+                p.max_l = max_l;
+                p.num_kb = num_kb;
+                p.groups = num_kb;
+                smem = plan.total;
+                grid = static_cast<int>(tiles * splits);
+                return true;
+            }
+        }
+    }
+    return false;
+}
+
+bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits) {
+    TcParams p{};
+    int smem = 0, grid = 0;
+    if (n < 1 || n > (1 << 24)) return false;
+    return tc_make_plan(n, k, group_size, bits, static_cast<int>(std::min<int64_t>(m, 8)), p, smem, grid);
+}
+
+int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
+    const uint16_t *xp = reinterpret_cast<const uint16_t *>(x);
+    uint16_t *yp = reinterpret_cast<uint16_t *>(y);
+    CUtensorMap map_w;
+    {
+        const uint64_t row_bytes = static_cast<uint64_t>(k) * bits / 8;
+        const uint64_t dims[2] = {row_bytes, static_cast<uint64_t>(n)};
+        const uint64_t strides[1] = {row_bytes};
+        const uint32_t box[2] = {128, kRows};
+        const int rc = make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != LISA_OK) return rc;
+    }
+    for (int64_t done = 0; done < m; done += 8) {
+        const int mc = static_cast<int>(std::min<int64_t>(m - done, 8));
+        TcParams p{};
+        int smem = 0, grid = 0;
+        if (!tc_make_plan(n, k, group_size, bits, mc, p, smem, grid))
+            return fail(LISA_ERR_UNSUPPORTED, "qmv_tc: shape not supported");
+        p.scales = reinterpret_cast<const uint16_t *>(scales);
+        p.biases = reinterpret_cast<const uint16_t *>(biases);
+        p.x = xp + done * k;
+        p.y = yp + done * n;
+        p.n = static_cast<int>(n);
+        p.k = static_cast<int>(k);
+        p.m = mc;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int na = 0;
+        if (p.splits > 1) {
+            attr[na].id = cudaLaunchAttributeClusterDimension;
+            attr[na].val.clusterDim.x = p.splits;
+            attr[na].val.clusterDim.y = 1;
+            attr[na].val.clusterDim.z = 1;
+            ++na;
+        }
+        if (flags & LISA_FLAG_PDL) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
+        cfg.attrs = attr;
+        cfg.numAttrs = na;
+        if (bits == 4) {
+            LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4>, map_w, p));
+        } else {
+            LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2>, map_w, p));
+        }
+        count_launch();
+    }
+    return LISA_OK;
+}
+
+}  // namespace lisa

@@ -1,0 +1,73 @@
+"""GPU parity of the tensor-memory GEMV (qmv_tc.cu) against the oracle's qmv law, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from lisa_b200 import _cabi, ops
+from oracle import oracle as O
+from tests import util
+from tests.gpu_util import dev_bf16, dev_u32, host_bf16_bits
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _run(cuda, n, k, m, bits, seed=0, flags=_cabi.FLAG_FORCE_QMV_TC):
+    rng = np.random.default_rng(seed + n + k + m)
+    w, s, b = util.affine_weights(rng, n, k, bits, 64)
+    x = util.activations(rng, m, k)
+    y = ops.quantized_matmul(dev_bf16(x, cuda), dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda), True, 64, bits,
+                             flags=flags)
+    got = O.bf16_to_f32(host_bf16_bits(y))
+    truth = O.affine_matmul(x, w, s, b, 64, bits, round_weight_bf16=False, f64=True)
+    return got, truth
+
+
+# config shapes (some with a cluster of k-slices and a packed ring that wraps), ragged n, short k, m up to 8 and beyond
+@pytest.mark.parametrize("n,k,m,bits", [
+    (128, 256, 1, 4), (256, 512, 3, 4), (1024, 2560, 1, 4), (9728, 2560, 1, 4), (2560, 9728, 4, 4), (4096, 2560, 8, 4),
+    (2560, 4096, 2, 4), (200, 320, 2, 4), (8, 64, 1, 4), (768, 2048, 1, 4), (2048, 768, 11, 4),
+    (128, 512, 1, 2), (17408, 5120, 1, 2), (5120, 17408, 2, 2), (136, 1088, 5, 2)])
+def test_matches_oracle(cuda, n, k, m, bits):
+    got, truth = _run(cuda, n, k, m, bits)
+    err, l2 = util.parity(got, truth)
+    assert err <= TOL, (err, l2)
+    assert ops.device_status() == 0
+
+
+def test_repeated_cold_launches_are_stable(cuda):
+    """A ring that wraps, two CTAs per SM, weights that are not in L2: twelve different matrices in turn."""
+    g = torch.Generator(device=cuda)
+    g.manual_seed(0)
+    n, k = 2560, 9728
+    x = torch.randn((1, k), device=cuda, generator=g).to(torch.bfloat16)
+    for _ in range(12):
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), dtype=torch.int32, device=cuda, generator=g)
+        s = (torch.randn((n, k // 64), device=cuda, generator=g) * 0.02).abs().to(torch.bfloat16)
+        b = (torch.randn((n, k // 64), device=cuda, generator=g) * 0.01).to(torch.bfloat16)
+        ref = ops.quantized_matmul(x, w, s, b, True, 64, 4, flags=_cabi.FLAG_FORCE_QMV).float()
+        y = ops.quantized_matmul(x, w, s, b, True, 64, 4, flags=_cabi.FLAG_FORCE_QMV_TC).float()
+        assert (y - ref).abs().max() <= 0.02 * ref.abs().max()
+
+
+def test_rows_do_not_depend_on_m(cuda):
+    """Row r of an m-row call equals the m=1 call on that row, bit for bit (array_ops.rs:500-555 contract)."""
+    rng = np.random.default_rng(5)
+    n, k, m = 1024, 2560, 6
+    w, s, b = util.affine_weights(rng, n, k, 4, 64)
+    x = util.activations(rng, m, k)
+    tw, ts, tb = dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda)
+    full = host_bf16_bits(ops.quantized_matmul(dev_bf16(x, cuda), tw, ts, tb, True, 64, 4, flags=_cabi.FLAG_FORCE_QMV_TC))
+    for r in (0, 3, 5):
+        one = host_bf16_bits(ops.quantized_matmul(dev_bf16(x[r:r + 1], cuda), tw, ts, tb, True, 64, 4,
+                                                  flags=_cabi.FLAG_FORCE_QMV_TC))
+        assert np.array_equal(one[0], full[r])
+
+
+def test_unsupported_group_size_is_refused(cuda):
+    rng = np.random.default_rng(1)
+    w, s, b = util.affine_weights(rng, 128, 256, 4, 128)
+    x = util.activations(rng, 1, 256)
+    with pytest.raises(_cabi.LisaError):
+        ops.quantized_matmul(dev_bf16(x, cuda), dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda), True, 128, 4,
+                             flags=_cabi.FLAG_FORCE_QMV_TC)

@@ -107,6 +107,15 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t *bar, uint32_t parity
     return false;
 }
 
+// One lane of a converged warp (elect.sync).  The single-thread roles (TMA producer, MMA issuer) run
+// their loops with the whole warp -- waits, counters and addresses stay warp-uniform -- and only the
+// instruction that must be issued once sits behind this predicate.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- bulk async copy global -> shared (TMA, untiled), completes on an mbarrier ----
 // dst, src 16-byte aligned; bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {

@@ -77,7 +77,7 @@ struct TcParams {
 struct TcPlan {
     int ring, xb, zero, xsum, sc, part, bars, total;
 };
-__host__ __device__ inline TcPlan tc_plan(int wstages, int max_l) {
+__host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, int m) {
     TcPlan p;
     int off = 0;
     p.ring = off;
@@ -90,8 +90,9 @@ __host__ __device__ inline TcPlan tc_plan(int wstages, int max_l) {
     off += max_l * 8 * 4;
     p.sc = off;                       // [max_l][128] words {scale bf16 | bias bf16 << 16}
     off += max_l * kRows * 4;
-    p.part = off;                     // [128][8] f32 partial sums of this k-slice
-    off += kRows * 8 * 4;
+    p.part = off;                     // rank 0 of the cluster: [splits][128][m] f32 partial sums of all k-slices
+    off += splits * kRows * m * 4;
+    off = (off + 15) & ~15;
     p.bars = off;                     // 33 mbarriers and the TMEM address
     off += 512;
     p.total = off + 1024;
@@ -147,15 +148,13 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// Store into the shared memory of CTA `rank` of the cluster, at the address `local_addr` has there.
+__device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t rank, float v) {
     uint32_t remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 __device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int code) {
@@ -182,7 +181,7 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
     constexpr int KB_BYTES = 64 * BITS / 8;    // packed bytes of one row of a k-block: 32 / 16
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const TcPlan plan = tc_plan(p.wstages, p.max_l);
+    const TcPlan plan = tc_plan(p.wstages, p.max_l, p.splits, p.m);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + plan.bars);
     uint64_t *wp_full = bars;                      // [kMaxWStages]
     uint64_t *wp_empty = wp_full + kMaxWStages;    // [kMaxWStages], 8 unpack warps
@@ -192,7 +191,8 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
     uint64_t *x_ready = d_empty + kND;             // 4 epilogue warps
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(x_ready + 1);
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler too
     const uint32_t rank = (p.splits > 1) ? cluster_ctarank() : 0u;
     const int tile = blockIdx.x / p.splits;
     const int n0 = tile * kRows;
@@ -226,6 +226,9 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // first cluster phase: every CTA of the cluster is running (its shared memory exists) before any
+    // partial sum is sent to rank 0; arrived here, waited for just before the stores
+    if (p.splits > 1) cluster_arrive();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + kNA * kACols;
     const uint32_t ring32 = smem_u32(smem + plan.ring);
@@ -247,8 +250,9 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer
-        if (lane == 0 && L > 0) {
+        // ---------------- MMA issuer: the whole warp runs the loop (uniform waits and addresses), one
+        // elected lane issues the four MMAs and the commit of a k-block
+        if (L > 0) {
             // instruction descriptor: D f32, A and B bf16, K-major, M = 128, N = 16
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             pdl_wait();  // the bounded waits below start counting once the previous kernel is done
@@ -256,21 +260,44 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             int a = 0, d = 0;
             uint32_t aph = 0;
             const uint32_t zero32 = smem_u32(smem + plan.zero);
-            for (int kbl = 0; kbl < L && ok; ++kbl) {
-                ok = tc_wait(&a_full[a], aph, 3);
+            // Two k-blocks per trip, their MMAs interleaved: the four K=16 steps of a k-block accumulate
+            // into the same D and would run one after the other at the latency of the tensor pipe (about
+            // 100 clocks each at N = 16); steps of different k-blocks overlap.
+            for (int kbl = 0; kbl < L; kbl += 2) {
+                const bool two = kbl + 1 < L;
+                const int a1 = a + 1, d1 = (d + 1 == kND) ? 0 : d + 1;  // kNA is even: the pair never wraps the A ring
+                ok = ok && tc_wait(&a_full[a], aph, 3);
+                if (two) ok = ok && tc_wait(&a_full[a1], aph, 3);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                // B tile of this k-block: rows 0..7 at xt, rows 8..15 = the zero block: the stride between
-                // the two 8-row groups is whatever leads from this tile to the zero block
-                const uint32_t xt = xb32 + kbl * kXTile;
-                const uint32_t desc_hi = ((zero32 - xt) >> 4) | (1u << 14) | (2u << 29);
-                const uint32_t desc_lo = (xt >> 4) | (1u << 16);
-                const uint32_t a_addr = tmem_a + a * kACols, d_addr = tmem_d + d * kDCols;
+                // B tile of a k-block: rows 0..7 at xt, rows 8..15 = the zero block: the stride between the
+                // two 8-row groups is whatever leads from this tile to the zero block
+                const uint32_t xt0 = xb32 + kbl * kXTile, xt1 = xt0 + kXTile;
+                const uint32_t hi0 = ((zero32 - xt0) >> 4) | (1u << 14) | (2u << 29);
+                const uint32_t hi1 = ((zero32 - xt1) >> 4) | (1u << 14) | (2u << 29);
+                const uint32_t lo0 = (xt0 >> 4) | (1u << 16), lo1 = (xt1 >> 4) | (1u << 16);
+                const uint32_t a0_addr = tmem_a + a * kACols, a1_addr = tmem_a + a1 * kACols;
+                const uint32_t d0_addr = tmem_d + d * kDCols, d1_addr = tmem_d + d1 * kDCols;
+                if (elect_one()) {
+                    if (two) {
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) umma_ts(d_addr, a_addr + ks * 8, desc_lo + ks * 2, desc_hi, idesc, ks > 0);
-                umma_commit(&done[d]);
-                if (++a == kNA) { a = 0; aph ^= 1; }
-                if (++d == kND) d = 0;
+                        for (int ks = 0; ks < 4; ++ks) {
+                            umma_ts(d0_addr, a0_addr + ks * 8, lo0 + ks * 2, hi0, idesc, ks > 0);
+                            umma_ts(d1_addr, a1_addr + ks * 8, lo1 + ks * 2, hi1, idesc, ks > 0);
+                        }
+                        umma_commit(&done[d]);
+                        umma_commit(&done[d1]);
+                    } else {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) umma_ts(d0_addr, a0_addr + ks * 8, lo0 + ks * 2, hi0, idesc, ks > 0);
+                        umma_commit(&done[d]);
+                    }
+                }
+                __syncwarp();
+                a += 2;
+                if (a == kNA) { a = 0; aph ^= 1; }
+                d = (d1 + 1 == kND) ? 0 : d1 + 1;
             }
         }
     } else if (warp < 2 + kUnpackWarps) {
@@ -286,6 +313,23 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         const uint32_t row32 = ring32 + row * 128;
         const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
+        // The TMEM store of one k-block completes while the next one is loaded and unpacked: its
+        // completion wait, the hand-over to the MMA warp and the release of the packed stage are deferred
+        // to the next trip (`pend_*`).
+        bool pending = false, pend_last = false;
+        int pend_a = 0, pend_s = 0;
+        auto finish_pending = [&]() {
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&a_full[pend_a]);
+                // last visit of the packed stage: hand it back to the producer only now that its words are
+                // in TMEM (an arrival placed right after the loads let the refill overtake them)
+                if (pend_last) mbar_arrive(&wp_empty[pend_s]);
+            }
+            pending = false;
+        };
         for (int kbl = set; kbl < L; kbl += 2) {
             const int wsl = kbl / KBW, sub = kbl - wsl * KBW;  // stage of the slice, k-block inside it
             const int s = wsl % p.wstages;
@@ -315,7 +359,7 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) o[8 * j + i] = lop_and_or(w[j] >> (2 * i), kmask, kmagic);
             }
-            const bool last_visit = sub >= KBW - 2 || kbl + 2 >= L;
+            if (pending) finish_pending();
             // the A stage is free once the MMAs of k-block kbl - kNA completed; the D buffer of this
             // k-block once the epilogue has read k-block kbl - kND
             if (kbl >= kNA) ok = tc_wait_relaxed(&done[(kbl - kNA) % kND], ((kbl - kNA) / kND) & 1, 5);
@@ -326,16 +370,12 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             const uint32_t dst = a_lane + static_cast<uint32_t>((kbl % kNA) * kACols);
             tmem_st16(dst, o);
             tmem_st16(dst + 16, o + 16);
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&a_full[kbl % kNA]);
-                // last visit of the packed stage: hand it back to the producer only now that its words are
-                // in TMEM (an arrival placed right after the loads let the refill overtake them)
-                if (last_visit) mbar_arrive(&wp_empty[s]);
-            }
+            pending = true;
+            pend_a = kbl % kNA;
+            pend_s = s;
+            pend_last = sub >= KBW - 2 || kbl + 2 >= L;
         }
+        if (pending) finish_pending();
         (void)KB_BYTES;
     } else {
         // ---------------- staging, epilogue, reduction
@@ -347,7 +387,26 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         {
             const uint16_t *sr = p.scales + static_cast<size_t>(grow) * p.groups + kb0;
             const uint16_t *br = p.biases + static_cast<size_t>(grow) * p.groups + kb0;
-            for (int g = 0; g < L; ++g) sc[g * kRows + row] = static_cast<uint32_t>(__ldg(sr + g)) | (static_cast<uint32_t>(__ldg(br + g)) << 16);
+            if ((p.groups & 3) == 0 && (kb0 & 3) == 0) {
+                // four groups per 8-byte load; a row holds a multiple of four groups, so the last load
+                // of a short slice stays inside the row
+                const uint2 *s4 = reinterpret_cast<const uint2 *>(sr), *b4 = reinterpret_cast<const uint2 *>(br);
+#pragma unroll 6
+                for (int g4 = 0; g4 < (L + 3) / 4; ++g4) {
+                    const uint2 sv = __ldg(s4 + g4), bv = __ldg(b4 + g4);
+                    const uint32_t w0 = (sv.x & 0xffffu) | (bv.x << 16), w1 = (sv.x >> 16) | (bv.x & 0xffff0000u);
+                    const uint32_t w2 = (sv.y & 0xffffu) | (bv.y << 16), w3 = (sv.y >> 16) | (bv.y & 0xffff0000u);
+                    const int g = 4 * g4;
+                    sc[g * kRows + row] = w0;
+                    if (g + 1 < L) sc[(g + 1) * kRows + row] = w1;
+                    if (g + 2 < L) sc[(g + 2) * kRows + row] = w2;
+                    if (g + 3 < L) sc[(g + 3) * kRows + row] = w3;
+                }
+            } else {
+#pragma unroll 4
+                for (int g = 0; g < L; ++g)
+                    sc[g * kRows + row] = static_cast<uint32_t>(__ldg(sr + g)) | (static_cast<uint32_t>(__ldg(br + g)) << 16);
+            }
         }
         // activation tiles: zero everything (rows >= m and the zero block stay zero)
         {
@@ -361,29 +420,36 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         pdl_wait();  // activations come from the previous kernel
         {
             // one item = one word's worth of codes (CPW activations) of one token: loaded, permuted into
-            // pair order, stored swizzled; the items of a (token, k-block) are adjacent lanes
+            // pair order, stored swizzled; the items of a (token, k-block) are adjacent lanes.  Two rounds
+            // of loads are in flight at a time: this runs after griddepcontrol.wait, on the critical path.
             constexpr int IPK = 64 / CPW;  // items per k-block: 8 / 4
+            constexpr int NV = CPW / 8;    // 16-byte vectors per item: 1 / 2
             const int items = p.m * L * IPK;
-            for (int base = 0; base < items; base += kEpilogueWarps * 32) {
-                const int item = base + et;
+            const int per_token = L * IPK;
+            auto load_item = [&](int item, uint4 (&v)[NV]) {
+                if (item < items) {
+                    const int t = item / per_token, u = item - t * per_token;
+                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(t) * p.k + kb0 * 64 + u * CPW);
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) v[i] = __ldg(src + i);
+                }
+            };
+            auto store_item = [&](int item, const uint4 (&v)[NV]) {
                 const bool in = item < items;
-                const int u = in ? item % (L * IPK) : 0, t = in ? item / (L * IPK) : 0;
+                const int t = in ? item / per_token : 0, u = in ? item - t * per_token : 0;
                 const int kbl = u / IPK, j = u - kbl * IPK;
                 float s = 0.f;
                 if (in) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(t) * p.k + (kb0 + kbl) * 64 + j * CPW);
                     const uint32_t dstrow = xb32 + kbl * kXTile + t * 128;
                     if (BITS == 4) {
-                        const uint4 v = __ldg(src);
-                        const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+                        const uint32_t r[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
 #pragma unroll
                         for (int i = 0; i < 4; ++i) s += bf16_bits_to_f32(r[i] & 0xffffu) + __uint_as_float(r[i] & 0xffff0000u);
                         const uint32_t o0 = __byte_perm(r[0], r[2], 0x5410), o1 = __byte_perm(r[0], r[2], 0x7632);
                         const uint32_t o2 = __byte_perm(r[1], r[3], 0x5410), o3 = __byte_perm(r[1], r[3], 0x7632);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dstrow + ((j ^ t) << 4)), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
                     } else {
-                        const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
-                        const uint32_t r[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                        const uint32_t r[8] = {v[0].x, v[0].y, v[0].z, v[0].w, v[NV - 1].x, v[NV - 1].y, v[NV - 1].z, v[NV - 1].w};
                         uint32_t o[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) s += bf16_bits_to_f32(r[i] & 0xffffu) + __uint_as_float(r[i] & 0xffff0000u);
@@ -399,6 +465,14 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
 #pragma unroll
                 for (int off = 1; off < IPK; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
                 if (in && j == 0) xsum[kbl * 8 + t] = s;
+            };
+            constexpr int kStep = kEpilogueWarps * 32;
+            for (int base = 0; base < items; base += 2 * kStep) {
+                uint4 va[NV], vb[NV];
+                load_item(base + et, va);
+                load_item(base + kStep + et, vb);
+                store_item(base + et, va);
+                if (base + kStep < items) store_item(base + kStep + et, vb);
             }
         }
         fence_proxy_async_smem();  // the MMA reads the tiles through the async proxy
@@ -410,52 +484,72 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         for (int t = 0; t < 8; ++t) rs[t] = 0.f;
         const uint32_t d_lane = tmem_d + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
-        for (int kbl = 0; kbl < L; ++kbl) {
-            const int d = kbl % kND;
-            ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[d], (kbl / kND) & 1, 7));
+        for (int kbl = 0; kbl < L; kbl += 2) {
+            // two k-blocks per trip: the commit of the second one covers the first (MMAs complete in order)
+            const bool two = kbl + 1 < L;
+            const int last = two ? kbl + 1 : kbl;
+            const int d0 = kbl % kND, d1 = last % kND;
+            ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[d1], (last / kND) & 1, 7));
             if (!ok) break;
             tc_fence_after();
-            uint32_t c[8];
-            tmem_ld8(d_lane + d * kDCols, c);
+            uint32_t c0[8], c1[8];
+            tmem_ld8(d_lane + d0 * kDCols, c0);
+            tmem_ld8(d_lane + d1 * kDCols, c1);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&d_empty[d]);
-            const uint32_t sb = sc[kbl * kRows + row];
-            const float sv = bf16_bits_to_f32(sb & 0xffffu), bv = __uint_as_float(sb & 0xffff0000u);
-            const float bb = fmaf(-128.f, sv, bv);
-            const float4 xs0 = *reinterpret_cast<const float4 *>(xsum + kbl * 8);
-            const float4 xs1 = *reinterpret_cast<const float4 *>(xsum + kbl * 8 + 4);
-            const float xs[8] = {xs0.x, xs0.y, xs0.z, xs0.w, xs1.x, xs1.y, xs1.z, xs1.w};
+            if (lane == 0) {
+                mbar_arrive(&d_empty[d0]);
+                if (two) mbar_arrive(&d_empty[d1]);
+            }
 #pragma unroll
-            for (int t = 0; t < 8; ++t) rs[t] = fmaf(sv, __uint_as_float(c[t]), fmaf(bb, xs[t], rs[t]));
+            for (int h = 0; h < 2; ++h) {
+                if (h == 1 && !two) break;
+                const int kk = kbl + h;
+                const uint32_t sb = sc[kk * kRows + row];
+                const float sv = bf16_bits_to_f32(sb & 0xffffu), bv = __uint_as_float(sb & 0xffff0000u);
+                const float bb = fmaf(-128.f, sv, bv);
+                const float4 xs0 = *reinterpret_cast<const float4 *>(xsum + kk * 8);
+                const float4 xs1 = *reinterpret_cast<const float4 *>(xsum + kk * 8 + 4);
+                const float xs[8] = {xs0.x, xs0.y, xs0.z, xs0.w, xs1.x, xs1.y, xs1.z, xs1.w};
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+                    rs[t] = fmaf(sv, __uint_as_float(h ? c1[t] : c0[t]), fmaf(bb, xs[t], rs[t]));
+            }
         }
-        // this slice's partial sums; rows of x beyond m read zero tiles and give zero
+        // this slice's partial sums go to rank 0 of the cluster (slot [rank][row][t] of its `part`)
+        if (p.splits > 1) cluster_wait();  // first phase: rank 0 is running
+        const uint32_t slot = smem_u32(part) + ((rank * kRows + row) * p.m) * 4;
 #pragma unroll
-        for (int t = 0; t < 8; ++t) part[row * 8 + t] = rs[t];
+        for (int t = 0; t < 8; ++t) {
+            if (t < p.m) {
+                if (p.splits > 1) st_cluster_f32(slot + 4 * t, 0u, rs[t]);
+                else part[row * p.m + t] = rs[t];
+            }
+        }
     }
+    if (p.splits > 1 && warp < 2 + kUnpackWarps) cluster_wait();  // the other warps close the first phase too
 
-    // ---------------- sum of the k-slices (cluster rank 0), store
+    // ---------------- sum of the k-slices in rank order (cluster rank 0), store
     tc_fence_before();
     __syncthreads();
-    if (p.splits > 1) cluster_sync_all();
+    if (p.splits > 1) {
+        cluster_arrive();            // second phase: this CTA's partial sums are on their way (release)
+        if (rank == 0) cluster_wait();  // rank 0 alone waits for all of them; the others may leave
+    }
     if (rank == 0 && warp >= 2 + kUnpackWarps) {
         const int row = (warp & 3) * 32 + lane;
-        const uint32_t mine = smem_u32(part + row * 8);
-        float tot[8];
-#pragma unroll
-        for (int t = 0; t < 8; ++t) tot[t] = part[row * 8 + t];
-        for (int r = 1; r < p.splits; ++r)
-#pragma unroll
-            for (int t = 0; t < 8; ++t)
-                if (t < p.m) tot[t] += ld_cluster_f32(mine + 4 * t, static_cast<uint32_t>(r));
         if (n0 + row < p.n) {
 #pragma unroll
-            for (int t = 0; t < 8; ++t)
-                if (t < p.m) p.y[static_cast<size_t>(t) * p.n + n0 + row] = static_cast<uint16_t>(f32_to_bf16_bits(tot[t]));
+            for (int t = 0; t < 8; ++t) {
+                if (t < p.m) {
+                    float tot = 0.f;
+                    for (int r = 0; r < p.splits; ++r) tot += part[(r * kRows + row) * p.m + t];
+                    p.y[static_cast<size_t>(t) * p.n + n0 + row] = static_cast<uint16_t>(f32_to_bf16_bits(tot));
+                }
+            }
         }
     }
-    if (p.splits > 1) cluster_sync_all();  // peers keep their shared memory until rank 0 has read it
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -483,7 +577,7 @@ static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, 
         const int max_ws = (total_ws + splits - 1) / splits;
         const int max_l = std::min(max_ws * kbw, num_kb);
         for (int ws = std::min(kMaxWStages, max_ws); ws >= std::min(2, max_ws); --ws) {
-            const TcPlan plan = tc_plan(ws, max_l);
+            const TcPlan plan = tc_plan(ws, max_l, splits, m);
             if (plan.total <= budget) {
                 p.splits = splits;
                 p.wstages = ws;

@@ -219,7 +219,8 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
 
     constexpr int KBW = (128 * 8 / BITS) / kBK;  // k-blocks per packed-weight stage: 4 (4-bit), 8 (2-bit)
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler too
     const int n0 = blockIdx.x * kBN;
     int t0 = blockIdx.y * p.bt, t_end = p.m, wrow0 = n0;
     if (p.tiles) {
@@ -285,10 +286,11 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer: one thread, and few instructions per k-block: a lone thread
-        // runs its dependent instructions one after the other, and four MMAs of N = 256 give it 512
-        // tensor-pipe clocks for one trip of this loop
-        if (lane == 0) {
+        // ---------------- MMA issuer: the whole warp runs the loop, so that waits, counters and operand
+        // addresses stay warp-uniform, and one elected lane issues the four MMAs and the commit of a
+        // k-block.  (Issued from inside an `if (lane == 0)` the same loop took ~450 of the 512 clocks
+        // that four N = 256 MMAs last.)
+        {
             const uint32_t idesc = umma_idesc_bf16(p.bt);
             const uint32_t b_lo0 = umma_desc_lo(smem_u32(xs));
             const uint32_t b_step = static_cast<uint32_t>(p.bt) * 8u;  // one stage, in 16-byte units
@@ -296,20 +298,24 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             uint32_t ph = 0, acc = 0;
             bool ok = true;
             for (int kb = 0; kb < num_kb; ++kb) {
-                ok = qmm_wait(&full[s], ph, 3);
+                ok = __all_sync(0xffffffffu, qmm_wait(&full[s], ph, 3));
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_addr = tmem_a + static_cast<uint32_t>(s * kACols);
                 const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(s) * b_step;
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < kBK / 16; ++ks) {
-                    umma_bf16_ts(tmem_base, a_addr + ks * 8, b_lo + ks * 2, kUmmaDescHiSw128, idesc, acc);
-                    acc = 1;
+                    for (int ks = 0; ks < kBK / 16; ++ks) {
+                        umma_bf16_ts(tmem_base, a_addr + ks * 8, b_lo + ks * 2, kUmmaDescHiSw128, idesc, acc);
+                        acc = 1;
+                    }
+                    umma_commit(&empty[s]);
                 }
-                umma_commit(&empty[s]);
+                acc = 1;
+                __syncwarp();
                 if (++s == kStages) { s = 0; ph ^= 1; }
             }
-            if (ok) umma_commit(acc_full);
+            if (ok && elect_one()) umma_commit(acc_full);
         }
     } else {
         // ---------------- dequantize, then epilogue

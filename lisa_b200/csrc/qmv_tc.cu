@@ -8,26 +8,34 @@
 // Why a second GEMV kernel.  The mma.sync kernel spends about 0.12 warp-instructions per code: the
 // fragment loads, the per-lane shifts and the four MMAs of every 16 rows x 64 codes are issued by the
 // same warps that unpack, and a 4-bit stream at HBM speed (45 codes per clock per SM) would need 5.5
-// warp-instructions per clock of the 4 an SM has.  Here the unpacked weights never pass through MMA
-// fragments: one LOP3 lifts TWO codes into a bf16 pair (mask 0x000F000F, OR 0x43004300: each half is
-// 128 + q exactly), thread (row) writes its 32 pair-words of a 64-code k-block straight to its lane of
-// tensor memory with tcgen05.st, and one thread issues tcgen05.mma with A = that tile (128 rows x 64 k,
-// in TMEM), B = the activations (16 padded rows x 64 k, in shared memory), D = a 128 x 16 f32 tile in
-// TMEM -- one D per 64-code group, so that scale and bias are applied by the epilogue warps:
-//   y += scale * D + (bias - 128 * scale) * sum(x_group).
-// About 0.04 warp-instructions per code.
+// warp-instructions per clock of the 4 an SM has.  Here the codes go to the tensor core as what they
+// are, unsigned 8-bit integers: two instructions spread the eight nibbles of a word over two words of
+// bytes (w & 0x0F0F0F0F, (w >> 4) & 0x0F0F0F0F), thread (row) writes the 16 words of a 64-code k-block
+// straight to its lane of tensor memory with tcgen05.st, and tcgen05.mma.kind::i8 multiplies A = that
+// tile (128 rows x 64 k, u8, in TMEM) with B = the activations (in shared memory), D = a 128 x 16 s32
+// tile in TMEM -- one D per 64-code group, so that scale and bias are applied by the epilogue warps.
 //
-// Work split: CTA = (128-row tile, k-slice); the k-slices of a tile form a thread-block cluster and are
-// summed through distributed shared memory by the cluster's rank 0.  CTAs use under half an SM, and the
-// weights do not depend on the previous kernel in the stream: launched with programmatic stream
-// serialization, kernel i+1 fills its ring and unpacks while kernel i still computes.
+// The activations become integers per (token, 64-k group): with E the exponent of the group's largest
+// magnitude, x * 2^(13-E) is rounded to an integer below 2^14 and split into two signed bytes,
+// x_int = 256 * hi + lo; rows 0..7 of the B tile hold the hi bytes of up to 8 tokens, rows 8..15 the lo
+// bytes.  A bf16 value has 8 significant bits, so every element within 2^-6 of the group maximum is
+// represented exactly and the rest to 2^-14 of that maximum; products and sums are exact in s32:
+//   sum(q*x) = 2^(E-13) * (256 * D[:, t] + D[:, 8+t]),   y += scale * sum(q*x) + bias * sum(x)
+// with sum(x) the f32 sum of the bf16 activations.  About 0.03 warp-instructions per code.
+//
+// Work split: CTA = (128-row tile, k-slice); the k-slices of a tile form a thread-block cluster and their
+// partial sums are written into the shared memory of the cluster's rank 0, which adds them in rank
+// order.  CTAs use under half an SM, and the weights do not depend on the previous kernel in the
+// stream: launched with programmatic stream serialization, kernel i+1 fills its ring and unpacks while
+// kernel i still computes.
 //
 // Warp roles (14 warps):
 //   warp 0        TMA producer: packed tiles [128 rows x 128 bytes], 128-byte swizzle, no multicast;
-//   warp 1        TMEM allocation; one thread issues the MMAs, one commit per k-block;
+//   warp 1        TMEM allocation; runs the MMA loop warp-uniformly, an elected lane issues the MMAs of
+//                 two k-blocks and their commits;
 //   warps 2..9    unpack: warps 2..5 the even k-blocks, 6..9 the odd ones;
-//   warps 10..13  stage scales and biases, then (after griddepcontrol.wait) the activations in the
-//                 permuted K order of the pair words; epilogue per k-block; final reduction and store.
+//   warps 10..13  stage scales and biases, then (after griddepcontrol.wait) the activations as byte
+//                 pairs in the K order of the unpacked words; epilogue per pair of k-blocks; final store.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -50,15 +58,15 @@ int qmv_tc_device_status() {
 namespace {
 
 constexpr int kRows = 128;            // weight rows per CTA = MMA M = TMEM lanes
-constexpr int kNA = 4;                // A ring (tensor memory), 32 columns per k-block
-constexpr int kND = 8;                // D ring (tensor memory), 16 columns per k-block
-constexpr int kACols = 32, kDCols = 16;
-constexpr int kTmemCols = 256;        // kNA * 32 + kND * 16
+constexpr int kNA = 8;                // A ring (tensor memory), 16 columns (64 bytes per row) per k-block
+constexpr int kND = 8;                // D ring (tensor memory), 16 s32 columns per k-block
+constexpr int kACols = 16, kDCols = 16;
+constexpr int kTmemCols = 256;        // kNA * 16 + kND * 16
 constexpr int kMaxWStages = 6;        // packed-weight ring (shared memory), 16 KiB per stage
 constexpr int kWBytes = kRows * 128;
 constexpr int kUnpackWarps = 8, kEpilogueWarps = 4;
 constexpr int kThreads = (2 + kUnpackWarps + kEpilogueWarps) * 32;
-constexpr int kXTile = 1024;          // 8 token rows x 128 bytes of one k-block (rows 8..15: the zero block)
+constexpr int kXTile = 2048;          // B tile of TWO k-blocks: 16 rows (8 hi, 8 lo) x 128 bytes (2 x 64 k)
 
 struct TcParams {
     const uint16_t *scales;
@@ -82,12 +90,11 @@ __host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, in
     int off = 0;
     p.ring = off;
     off += wstages * kWBytes;
-    p.xb = off;                       // max_l activation tiles of 1 KiB (8 rows x 128 bytes, swizzled)
-    off += max_l * kXTile;
-    p.zero = off;                     // rows 8..15 of every tile
-    off += kXTile;
-    p.xsum = off;                     // [max_l][8] f32
-    off += max_l * 8 * 4;
+    p.xb = off;                       // one B tile per pair of k-blocks (swizzled)
+    off += ((max_l + 1) / 2) * kXTile;
+    p.zero = off;                     // (unused)
+    p.xsum = off;                     // [max_l][8] f32 sum(x), then [max_l][8] f32 2^(E-13)
+    off += 2 * max_l * 8 * 4;
     p.sc = off;                       // [max_l][128] words {scale bf16 | bias bf16 << 16}
     off += max_l * kRows * 4;
     p.part = off;                     // rank 0 of the cluster: [splits][128][m] f32 partial sums of all k-slices
@@ -111,7 +118,7 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem descriptor {lo, hi}], bf16 operands, f32 accumulate.
+// D[tmem] (+)= A[tmem] * B[smem descriptor {lo, hi}], u8 x s8 operands, s32 accumulate, K = 32.
 __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t desc_lo, uint32_t desc_hi,
                                         uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -120,7 +127,7 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32
         ".reg .b64 d;\n\t"
         "mov.b64 d, {%2, %3};\n\t"
         "setp.ne.b32 p, %5, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d, %4, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], d, %4, p;\n\t"
         "}\n" ::"r"(tmem_d),
         "r"(tmem_a), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
@@ -133,15 +140,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
         "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr));
-}
-__device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
 }
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -170,9 +174,9 @@ __device__ __forceinline__ bool tc_wait_relaxed(uint64_t *bar, uint32_t parity, 
     return false;
 }
 
-// K order of the pair words.  4-bit: word j of a k-block (8 codes) gives pair i = codes (8j+i, 8j+i+4),
-// i < 4.  2-bit: word j (16 codes) gives pair i = codes (16j+i, 16j+i+8), i < 8.  The activations are
-// stored in the same order.
+// K order of the unpacked bytes.  4-bit: word j of a k-block (8 codes) becomes the words
+// (c0, c2, c4, c6) and (c1, c3, c5, c7).  2-bit: word j (16 codes) becomes four words, word i holding
+// (c_i, c_{4+i}, c_{8+i}, c_{12+i}).  The activation bytes are stored in the same order.
 template <int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
 qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
@@ -234,6 +238,7 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
     const uint32_t ring32 = smem_u32(smem + plan.ring);
     const uint32_t xb32 = smem_u32(smem + plan.xb);
     float *xsum = reinterpret_cast<float *>(smem + plan.xsum);
+    float *xscale = xsum + p.max_l * 8;
     uint32_t *sc = reinterpret_cast<uint32_t *>(smem + plan.sc);
     float *part = reinterpret_cast<float *>(smem + plan.part);
 
@@ -253,51 +258,47 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         // ---------------- MMA issuer: the whole warp runs the loop (uniform waits and addresses), one
         // elected lane issues the four MMAs and the commit of a k-block
         if (L > 0) {
-            // instruction descriptor: D f32, A and B bf16, K-major, M = 128, N = 16
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            // instruction descriptor: D s32 (2 << 4), A u8 (0 << 7), B s8 (1 << 10), K-major, M = 128, N = 16
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            // B descriptor, K-major, 128-byte swizzle: rows 0..7 (hi bytes) and rows 8..15 (lo bytes) are 1024 apart
+            const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
             pdl_wait();  // the bounded waits below start counting once the previous kernel is done
             bool ok = tc_wait(x_ready, 0, 2);
             int a = 0, d = 0;
             uint32_t aph = 0;
-            const uint32_t zero32 = smem_u32(smem + plan.zero);
-            // Two k-blocks per trip, their MMAs interleaved: the four K=16 steps of a k-block accumulate
-            // into the same D and would run one after the other at the latency of the tensor pipe (about
-            // 100 clocks each at N = 16); steps of different k-blocks overlap.
+            // Two k-blocks per trip (they share a B tile), their MMAs interleaved: the two K=32 steps of a
+            // k-block accumulate into the same D; steps of different k-blocks can overlap.
             for (int kbl = 0; kbl < L; kbl += 2) {
                 const bool two = kbl + 1 < L;
-                const int a1 = a + 1, d1 = (d + 1 == kND) ? 0 : d + 1;  // kNA is even: the pair never wraps the A ring
+                const int a1 = a + 1, d1 = d + 1;  // kNA and kND are even: a pair never wraps a ring
                 ok = ok && tc_wait(&a_full[a], aph, 3);
                 if (two) ok = ok && tc_wait(&a_full[a1], aph, 3);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                // B tile of a k-block: rows 0..7 at xt, rows 8..15 = the zero block: the stride between the
-                // two 8-row groups is whatever leads from this tile to the zero block
-                const uint32_t xt0 = xb32 + kbl * kXTile, xt1 = xt0 + kXTile;
-                const uint32_t hi0 = ((zero32 - xt0) >> 4) | (1u << 14) | (2u << 29);
-                const uint32_t hi1 = ((zero32 - xt1) >> 4) | (1u << 14) | (2u << 29);
-                const uint32_t lo0 = (xt0 >> 4) | (1u << 16), lo1 = (xt1 >> 4) | (1u << 16);
+                const uint32_t lo0 = ((xb32 + (kbl >> 1) * kXTile) >> 4) | (1u << 16), lo1 = lo0 + 4;  // +64 bytes: second k-block
                 const uint32_t a0_addr = tmem_a + a * kACols, a1_addr = tmem_a + a1 * kACols;
                 const uint32_t d0_addr = tmem_d + d * kDCols, d1_addr = tmem_d + d1 * kDCols;
                 if (elect_one()) {
                     if (two) {
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) {
-                            umma_ts(d0_addr, a0_addr + ks * 8, lo0 + ks * 2, hi0, idesc, ks > 0);
-                            umma_ts(d1_addr, a1_addr + ks * 8, lo1 + ks * 2, hi1, idesc, ks > 0);
+                        for (int ks = 0; ks < 2; ++ks) {
+                            umma_ts(d0_addr, a0_addr + ks * 8, lo0 + ks * 2, desc_hi, idesc, ks > 0);
+                            umma_ts(d1_addr, a1_addr + ks * 8, lo1 + ks * 2, desc_hi, idesc, ks > 0);
                         }
                         umma_commit(&done[d]);
                         umma_commit(&done[d1]);
                     } else {
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) umma_ts(d0_addr, a0_addr + ks * 8, lo0 + ks * 2, hi0, idesc, ks > 0);
+                        for (int ks = 0; ks < 2; ++ks) umma_ts(d0_addr, a0_addr + ks * 8, lo0 + ks * 2, desc_hi, idesc, ks > 0);
                         umma_commit(&done[d]);
                     }
                 }
                 __syncwarp();
                 a += 2;
                 if (a == kNA) { a = 0; aph ^= 1; }
-                d = (d1 + 1 == kND) ? 0 : d1 + 1;
+                d += 2;
+                if (d == kND) d = 0;
             }
         }
     } else if (warp < 2 + kUnpackWarps) {
@@ -307,9 +308,8 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         const int quad = warp & 3;     // TMEM lanes 32*quad .. +31
         const int row = quad * 32 + lane;
         const int swz = row & 7;
-        uint32_t kmask, kmagic;
-        asm volatile("mov.u32 %0, %1;" : "=r"(kmask) : "r"(BITS == 4 ? 0x000f000fu : 0x00030003u));
-        asm volatile("mov.u32 %0, %1;" : "=r"(kmagic) : "r"(0x43004300u));
+        uint32_t kmask;
+        asm volatile("mov.u32 %0, %1;" : "=r"(kmask) : "r"(BITS == 4 ? 0x0f0f0f0fu : 0x03030303u));
         const uint32_t row32 = ring32 + row * 128;
         const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
@@ -335,7 +335,7 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             const int s = wsl % p.wstages;
             if (sub < 2) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], (wsl / p.wstages) & 1, 4));
             if (!ok) break;
-            uint32_t o[32];
+            uint32_t o[16];
             if (BITS == 4) {
                 const uint32_t base = row32 + s * kWBytes;
                 uint32_t w[8];
@@ -345,10 +345,8 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                              : "r"(base + (((2 * sub + 1) ^ swz) << 4)));
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    o[4 * j + 0] = lop_and_or(w[j], kmask, kmagic);
-                    o[4 * j + 1] = lop_and_or(w[j] >> 4, kmask, kmagic);
-                    o[4 * j + 2] = lop_and_or(w[j] >> 8, kmask, kmagic);
-                    o[4 * j + 3] = lop_and_or(w[j] >> 12, kmask, kmagic);
+                    o[2 * j + 0] = w[j] & kmask;         // codes 0, 2, 4, 6 of the word, one per byte
+                    o[2 * j + 1] = (w[j] >> 4) & kmask;  // codes 1, 3, 5, 7
                 }
             } else {
                 uint32_t w[4];
@@ -357,7 +355,7 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) o[8 * j + i] = lop_and_or(w[j] >> (2 * i), kmask, kmagic);
+                    for (int i = 0; i < 4; ++i) o[4 * j + i] = (w[j] >> (2 * i)) & kmask;  // codes i, 4+i, 8+i, 12+i
             }
             if (pending) finish_pending();
             // the A stage is free once the MMAs of k-block kbl - kNA completed; the D buffer of this
@@ -369,7 +367,6 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             tc_fence_after();
             const uint32_t dst = a_lane + static_cast<uint32_t>((kbl % kNA) * kACols);
             tmem_st16(dst, o);
-            tmem_st16(dst + 16, o + 16);
             pending = true;
             pend_a = kbl % kNA;
             pend_s = s;
@@ -408,20 +405,20 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                     sc[g * kRows + row] = static_cast<uint32_t>(__ldg(sr + g)) | (static_cast<uint32_t>(__ldg(br + g)) << 16);
             }
         }
-        // activation tiles: zero everything (rows >= m and the zero block stay zero)
+        // activation tiles: zero everything (rows of tokens >= m and the half of an odd last tile stay zero)
         {
             uint4 *z = reinterpret_cast<uint4 *>(smem + plan.xb);
-            const int n16 = (L + 1) * kXTile / 16;  // the zero block follows tile max_l-1; cover both ends
+            const int n16 = ((L + 1) / 2) * kXTile / 16;
             for (int i = et; i < n16; i += kEpilogueWarps * 32) z[i] = make_uint4(0, 0, 0, 0);
-            uint4 *zb = reinterpret_cast<uint4 *>(smem + plan.zero);
-            for (int i = et; i < kXTile / 16; i += kEpilogueWarps * 32) zb[i] = make_uint4(0, 0, 0, 0);
         }
         asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
         pdl_wait();  // activations come from the previous kernel
         {
-            // one item = one word's worth of codes (CPW activations) of one token: loaded, permuted into
-            // pair order, stored swizzled; the items of a (token, k-block) are adjacent lanes.  Two rounds
-            // of loads are in flight at a time: this runs after griddepcontrol.wait, on the critical path.
+            // one item = one word's worth of codes (CPW activations) of one token: loaded, turned into
+            // integer byte pairs in the K order of the unpacked words, stored swizzled; the items of a
+            // (token, k-block) are adjacent lanes and share the group's exponent and sum through
+            // shuffles.  Two rounds of loads are in flight at a time: this runs after
+            // griddepcontrol.wait, on the critical path.
             constexpr int IPK = 64 / CPW;  // items per k-block: 8 / 4
             constexpr int NV = CPW / 8;    // 16-byte vectors per item: 1 / 2
             const int items = p.m * L * IPK;
@@ -438,33 +435,64 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                 const bool in = item < items;
                 const int t = in ? item / per_token : 0, u = in ? item - t * per_token : 0;
                 const int kbl = u / IPK, j = u - kbl * IPK;
+                uint32_t r[CPW / 2];
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    r[4 * i + 0] = in ? v[i].x : 0u;
+                    r[4 * i + 1] = in ? v[i].y : 0u;
+                    r[4 * i + 2] = in ? v[i].z : 0u;
+                    r[4 * i + 3] = in ? v[i].w : 0u;
+                }
+                float xf[CPW];
                 float s = 0.f;
-                if (in) {
-                    const uint32_t dstrow = xb32 + kbl * kXTile + t * 128;
-                    if (BITS == 4) {
-                        const uint32_t r[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+                uint32_t amax = 0;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) s += bf16_bits_to_f32(r[i] & 0xffffu) + __uint_as_float(r[i] & 0xffff0000u);
-                        const uint32_t o0 = __byte_perm(r[0], r[2], 0x5410), o1 = __byte_perm(r[0], r[2], 0x7632);
-                        const uint32_t o2 = __byte_perm(r[1], r[3], 0x5410), o3 = __byte_perm(r[1], r[3], 0x7632);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dstrow + ((j ^ t) << 4)), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
-                    } else {
-                        const uint32_t r[8] = {v[0].x, v[0].y, v[0].z, v[0].w, v[NV - 1].x, v[NV - 1].y, v[NV - 1].z, v[NV - 1].w};
-                        uint32_t o[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) s += bf16_bits_to_f32(r[i] & 0xffffu) + __uint_as_float(r[i] & 0xffff0000u);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            o[2 * i] = __byte_perm(r[i], r[4 + i], 0x5410);
-                            o[2 * i + 1] = __byte_perm(r[i], r[4 + i], 0x7632);
-                        }
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dstrow + (((2 * j) ^ t) << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dstrow + (((2 * j + 1) ^ t) << 4)), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
-                    }
+                for (int i = 0; i < CPW / 2; ++i) {
+                    xf[2 * i] = bf16_bits_to_f32(r[i] & 0xffffu);
+                    xf[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u);
+                    s += xf[2 * i] + xf[2 * i + 1];
+                    amax = max(amax, max(r[i] & 0x7fffu, (r[i] >> 16) & 0x7fffu));
                 }
 #pragma unroll
-                for (int off = 1; off < IPK; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-                if (in && j == 0) xsum[kbl * 8 + t] = s;
+                for (int off = 1; off < IPK; off <<= 1) {
+                    s += __shfl_xor_sync(0xffffffffu, s, off);
+                    amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                }
+                // E: biased exponent of the group's largest magnitude.  Groups below 2^-113 count as zero;
+                // an infinity or NaN makes the group's factor NaN.
+                const uint32_t e = amax >> 7;
+                const bool live = e >= 14u && e < 255u;
+                const float up = __uint_as_float((267u - e) << 23);  // 2^(13 - (E - 127))
+                uint32_t hi[CPW / 4], lo[CPW / 4];
+#pragma unroll
+                for (int i = 0; i < CPW / 4; ++i) hi[i] = lo[i] = 0;
+#pragma unroll
+                for (int i = 0; i < CPW; ++i) {
+                    const int xi = live ? __float2int_rn(xf[i] * up) : 0;  // |xi| < 2^14
+                    const int h = (xi + 128) >> 8, l = xi - (h << 8);      // xi = 256 h + l, both signed bytes
+                    // byte position of element i in the unpacked order
+                    const int pos = (BITS == 4) ? ((i & 1) * 4 + (i >> 1)) : ((i & 3) * 4 + (i >> 2));
+                    hi[pos >> 2] |= (static_cast<uint32_t>(h) & 0xffu) << (8 * (pos & 3));
+                    lo[pos >> 2] |= (static_cast<uint32_t>(l) & 0xffu) << (8 * (pos & 3));
+                }
+                if (in) {
+                    const uint32_t rowaddr = xb32 + (kbl >> 1) * kXTile + t * 128;
+                    const int par = kbl & 1;
+                    if (BITS == 4) {
+                        const uint32_t at = rowaddr + (((par * 4 + (j >> 1)) ^ t) << 4) + (j & 1) * 8;
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(at), "r"(hi[0]), "r"(hi[1]) : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(at + 1024), "r"(lo[0]), "r"(lo[1]) : "memory");
+                    } else {
+                        const uint32_t at = rowaddr + (((par * 4 + j) ^ t) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(hi[0]), "r"(hi[1]), "r"(hi[CPW / 4 - 2]), "r"(hi[CPW / 4 - 1]) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at + 1024), "r"(lo[0]), "r"(lo[1]), "r"(lo[CPW / 4 - 2]), "r"(lo[CPW / 4 - 1]) : "memory");
+                    }
+                    if (j == 0) {
+                        xsum[kbl * 8 + t] = s;
+                        xscale[kbl * 8 + t] = live ? __uint_as_float((e - 13u) << 23)  // 2^(E - 127 - 13)
+                                                   : (e == 255u ? __uint_as_float(0x7fc00000u) : 0.f);
+                    }
+                }
             };
             constexpr int kStep = kEpilogueWarps * 32;
             for (int base = 0; base < items; base += 2 * kStep) {
@@ -492,9 +520,9 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[d1], (last / kND) & 1, 7));
             if (!ok) break;
             tc_fence_after();
-            uint32_t c0[8], c1[8];
-            tmem_ld8(d_lane + d0 * kDCols, c0);
-            tmem_ld8(d_lane + d1 * kDCols, c1);
+            uint32_t c0[16], c1[16];
+            tmem_ld16(d_lane + d0 * kDCols, c0);
+            tmem_ld16(d_lane + d1 * kDCols, c1);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
@@ -508,13 +536,18 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                 const int kk = kbl + h;
                 const uint32_t sb = sc[kk * kRows + row];
                 const float sv = bf16_bits_to_f32(sb & 0xffffu), bv = __uint_as_float(sb & 0xffff0000u);
-                const float bb = fmaf(-128.f, sv, bv);
                 const float4 xs0 = *reinterpret_cast<const float4 *>(xsum + kk * 8);
                 const float4 xs1 = *reinterpret_cast<const float4 *>(xsum + kk * 8 + 4);
+                const float4 xe0 = *reinterpret_cast<const float4 *>(xscale + kk * 8);
+                const float4 xe1 = *reinterpret_cast<const float4 *>(xscale + kk * 8 + 4);
                 const float xs[8] = {xs0.x, xs0.y, xs0.z, xs0.w, xs1.x, xs1.y, xs1.z, xs1.w};
+                const float xe[8] = {xe0.x, xe0.y, xe0.z, xe0.w, xe1.x, xe1.y, xe1.z, xe1.w};
 #pragma unroll
-                for (int t = 0; t < 8; ++t)
-                    rs[t] = fmaf(sv, __uint_as_float(h ? c1[t] : c0[t]), fmaf(bb, xs[t], rs[t]));
+                for (int t = 0; t < 8; ++t) {
+                    // sum(q * x_int) = 256 * (hi column) + (lo column), below 2^24: exact as a float
+                    const int qx = static_cast<int>(h ? c1[t] : c0[t]) * 256 + static_cast<int>(h ? c1[8 + t] : c0[8 + t]);
+                    rs[t] = fmaf(sv * xe[t], static_cast<float>(qx), fmaf(bv, xs[t], rs[t]));
+                }
             }
         }
         // this slice's partial sums go to rank 0 of the cluster (slot [rank][row][t] of its `part`)

@@ -230,8 +230,8 @@ class DecodeStack:
         self.flags = _cabi.FLAG_PDL if os.environ.get("LISA_BENCH_PDL", "1") != "0" else 0
         if os.environ.get("LISA_BENCH_SIMPLE", "0") == "1":
             self.flags |= _cabi.FLAG_FORCE_QMV_SIMPLE
-        if os.environ.get("LISA_BENCH_TC", "0") == "1":
-            self.flags |= _cabi.FLAG_FORCE_QMV_TC
+        if os.environ.get("LISA_BENCH_TC", "1") == "0":  # the mma.sync kernel instead of the tensor-memory one
+            self.flags |= _cabi.FLAG_FORCE_QMV
         self.graph = None
 
     def token(self):
@@ -431,7 +431,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "traffic": (DRAM_TRAFFIC_RATIO["decode"] * bytes_token / max(launches_per_token, 1)
                                      if DRAM_TRAFFIC_RATIO["decode"] else None),
-                         "kernel": "qmv_mma_kernel<4,*>", "peak_source": peak_src,
+                         "kernel": "qmv_tc_kernel<4>", "peak_source": peak_src,
                          "bytes_per_launch_avg": bytes_token / max(launches_per_token, 1),
                          "us_per_launch_avg": 1e3 * total_ms / args.steps / max(launches_per_token, 1)},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

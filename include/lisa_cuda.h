@@ -50,14 +50,15 @@ typedef enum lisa_gguf_format { LISA_GGUF_Q2_K = 10, LISA_GGUF_Q4_K = 12 } lisa_
 /* Dispatch overrides for lisa_cuda_quantized_matmul_ex. */
 enum {
     LISA_FLAG_NONE = 0,
-    LISA_FLAG_FORCE_QMV = 1 << 0,     /* CUDA-core streaming kernel (staged ring) */
+    LISA_FLAG_FORCE_QMV = 1 << 0,     /* mma.sync streaming kernel (staged ring) */
     LISA_FLAG_FORCE_QMV_SIMPLE = 1 << 1, /* CUDA-core generic kernel (direct loads) */
     LISA_FLAG_FORCE_QMM = 1 << 2,     /* tcgen05 tensor-core kernel */
     LISA_FLAG_PDL = 1 << 3,           /* launch with programmatic stream serialization: the
                                          kernel prefetches weights before waiting on the
                                          previous kernel in the stream */
     LISA_FLAG_FORCE_QMV_TC = 1 << 4   /* streaming kernel with the unpacked weights in tensor memory
-                                         (tcgen05); group size 64 only */
+                                         (tcgen05, the default for group size 64): fail instead of
+                                         falling back when the shape is not supported */
 };
 
 const char *lisa_cuda_last_error_string(void);

@@ -91,11 +91,13 @@ static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, 
     if (force_qmm && !qmm_ok) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the GEMM kernel");
     if (force_qmm || (!force_qmv && !prefer_qmv(m, k) && qmm_ok))
         return qmm_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
-    if (force_tc) {
-        if (!qmv_tc_supported(m, k, n, group_size, bits))
-            return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the tensor-memory GEMV");
-        return qmv_tc(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
-    }
+    const bool tc_ok = qmv_tc_supported(m, k, n, group_size, bits);
+    if (force_tc && !tc_ok)
+        return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the tensor-memory GEMV");
+    // The tensor-memory GEMV is the default wherever it applies (group size 64); LISA_FLAG_FORCE_QMV and
+    // LISA_FLAG_FORCE_QMV_SIMPLE select the mma.sync and the generic kernel.
+    const bool plain_forced = (flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) != 0;
+    if (force_tc || (tc_ok && !plain_forced)) return qmv_tc(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
     return qmv_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
 }
 

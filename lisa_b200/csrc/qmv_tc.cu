@@ -58,10 +58,10 @@ int qmv_tc_device_status() {
 namespace {
 
 constexpr int kRows = 128;            // weight rows per CTA = MMA M = TMEM lanes
-constexpr int kNA = 8;                // A ring (tensor memory), 16 columns (64 bytes per row) per k-block
-constexpr int kND = 8;                // D ring (tensor memory), 16 s32 columns per k-block
+// Everything downstream of the packed ring moves in PAIRS of k-blocks (one B tile, one hand-over):
+constexpr int kNP = 4;                // ring of pair stages: A (tensor memory, 2 x 16 columns) and D (2 x 16 s32 columns)
 constexpr int kACols = 16, kDCols = 16;
-constexpr int kTmemCols = 256;        // kNA * 16 + kND * 16
+constexpr int kTmemCols = 256;        // kNP * 32 + kNP * 32
 constexpr int kMaxWStages = 6;        // packed-weight ring (shared memory), 16 KiB per stage
 constexpr int kWBytes = kRows * 128;
 constexpr int kUnpackWarps = 8, kEpilogueWarps = 4;
@@ -140,13 +140,33 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
         "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
+// tcgen05.ld.32x32b of N consecutive columns of the warp's 32 lanes (N = 1, 2, 4, 8).
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t *r);
+template <>
+__device__ __forceinline__ void tmem_ld<1>(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r[0]) : "r"(taddr));
 }
+template <>
+__device__ __forceinline__ void tmem_ld<2>(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr));
+}
+template <>
+__device__ __forceinline__ void tmem_ld<4>(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr));
+}
+template <>
+__device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+template <int N>
+struct IntC {
+    static constexpr int value = N;
+};
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -189,10 +209,10 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + plan.bars);
     uint64_t *wp_full = bars;                      // [kMaxWStages]
     uint64_t *wp_empty = wp_full + kMaxWStages;    // [kMaxWStages], 8 unpack warps
-    uint64_t *a_full = wp_empty + kMaxWStages;     // [kNA], 4 unpack warps of the k-block's set
-    uint64_t *done = a_full + kNA;                 // [kND], tcgen05.commit of k-block kb: A stage free, D ready
-    uint64_t *d_empty = done + kND;                // [kND], 4 epilogue warps
-    uint64_t *x_ready = d_empty + kND;             // 4 epilogue warps
+    uint64_t *a_full = wp_empty + kMaxWStages;     // [kNP], 4 unpack warps of the pair's set
+    uint64_t *done = a_full + kNP;                 // [kNP], tcgen05.commit of the pair's MMAs: D ready
+    uint64_t *d_empty = done + kNP;                // [kNP], 4 epilogue warps: D read, hence A stage and D buffer free
+    uint64_t *x_ready = d_empty + kNP;             // 4 epilogue warps
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(x_ready + 1);
 
     const int tid = threadIdx.x, lane = tid & 31;
@@ -213,8 +233,8 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             mbar_init(&wp_full[i], 1);
             mbar_init(&wp_empty[i], kUnpackWarps);
         }
-        for (int i = 0; i < kNA; ++i) mbar_init(&a_full[i], kUnpackWarps / 2);
-        for (int i = 0; i < kND; ++i) {
+        for (int i = 0; i < kNP; ++i) {
+            mbar_init(&a_full[i], kUnpackWarps / 2);
             mbar_init(&done[i], 1);
             mbar_init(&d_empty[i], kEpilogueWarps);
         }
@@ -234,7 +254,8 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
     // partial sum is sent to rank 0; arrived here, waited for just before the stores
     if (p.splits > 1) cluster_arrive();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + kNA * kACols;
+    const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + kNP * 2 * kACols;
+    const int P = (L + 1) / 2;  // pairs of k-blocks of this slice
     const uint32_t ring32 = smem_u32(smem + plan.ring);
     const uint32_t xb32 = smem_u32(smem + plan.xb);
     float *xsum = reinterpret_cast<float *>(smem + plan.xsum);
@@ -264,21 +285,18 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
             pdl_wait();  // the bounded waits below start counting once the previous kernel is done
             bool ok = tc_wait(x_ready, 0, 2);
-            int a = 0, d = 0;
-            uint32_t aph = 0;
-            // Two k-blocks per trip (they share a B tile), their MMAs interleaved: the two K=32 steps of a
-            // k-block accumulate into the same D; steps of different k-blocks can overlap.
-            for (int kbl = 0; kbl < L; kbl += 2) {
-                const bool two = kbl + 1 < L;
-                const int a1 = a + 1, d1 = d + 1;  // kNA and kND are even: a pair never wraps a ring
-                ok = ok && tc_wait(&a_full[a], aph, 3);
-                if (two) ok = ok && tc_wait(&a_full[a1], aph, 3);
-                ok = __all_sync(0xffffffffu, ok);
+            int st = 0;
+            uint32_t ph = 0;
+            // One pair of k-blocks per trip (they share a B tile), their MMAs interleaved: the two K=32 steps
+            // of a k-block accumulate into the same D; steps of different k-blocks can overlap.
+            for (int pr = 0; pr < P; ++pr) {
+                const bool two = 2 * pr + 1 < L;
+                ok = __all_sync(0xffffffffu, ok && tc_wait(&a_full[st], ph, 3));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t lo0 = ((xb32 + (kbl >> 1) * kXTile) >> 4) | (1u << 16), lo1 = lo0 + 4;  // +64 bytes: second k-block
-                const uint32_t a0_addr = tmem_a + a * kACols, a1_addr = tmem_a + a1 * kACols;
-                const uint32_t d0_addr = tmem_d + d * kDCols, d1_addr = tmem_d + d1 * kDCols;
+                const uint32_t lo0 = ((xb32 + pr * kXTile) >> 4) | (1u << 16), lo1 = lo0 + 4;  // +64 bytes: second k-block
+                const uint32_t a0_addr = tmem_a + st * 2 * kACols, a1_addr = a0_addr + kACols;
+                const uint32_t d0_addr = tmem_d + st * 2 * kDCols, d1_addr = d0_addr + kDCols;
                 if (elect_one()) {
                     if (two) {
 #pragma unroll
@@ -286,25 +304,20 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                             umma_ts(d0_addr, a0_addr + ks * 8, lo0 + ks * 2, desc_hi, idesc, ks > 0);
                             umma_ts(d1_addr, a1_addr + ks * 8, lo1 + ks * 2, desc_hi, idesc, ks > 0);
                         }
-                        umma_commit(&done[d]);
-                        umma_commit(&done[d1]);
                     } else {
 #pragma unroll
                         for (int ks = 0; ks < 2; ++ks) umma_ts(d0_addr, a0_addr + ks * 8, lo0 + ks * 2, desc_hi, idesc, ks > 0);
-                        umma_commit(&done[d]);
                     }
+                    umma_commit(&done[st]);
                 }
                 __syncwarp();
-                a += 2;
-                if (a == kNA) { a = 0; aph ^= 1; }
-                d += 2;
-                if (d == kND) d = 0;
+                if (++st == kNP) { st = 0; ph ^= 1; }
             }
         }
     } else if (warp < 2 + kUnpackWarps) {
-        // ---------------- unpack: thread = weight row = TMEM lane; one 64-code k-block per trip
+        // ---------------- unpack: thread = weight row = TMEM lane; one pair of k-blocks (128 codes) per trip
         const int uw = warp - 2;
-        const int set = uw >> 2;       // k-blocks set, set + 2, ...
+        const int set = uw >> 2;       // pairs set, set + 2, ...
         const int quad = warp & 3;     // TMEM lanes 32*quad .. +31
         const int row = quad * 32 + lane;
         const int swz = row & 7;
@@ -313,67 +326,69 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         const uint32_t row32 = ring32 + row * 128;
         const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
-        // The TMEM store of one k-block completes while the next one is loaded and unpacked: its
+        // The TMEM stores of one pair complete while the next one is loaded and unpacked: their
         // completion wait, the hand-over to the MMA warp and the release of the packed stage are deferred
         // to the next trip (`pend_*`).
         bool pending = false, pend_last = false;
-        int pend_a = 0, pend_s = 0;
+        int pend_st = 0, pend_s = 0;
         auto finish_pending = [&]() {
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&a_full[pend_a]);
+                mbar_arrive(&a_full[pend_st]);
                 // last visit of the packed stage: hand it back to the producer only now that its words are
                 // in TMEM (an arrival placed right after the loads let the refill overtake them)
                 if (pend_last) mbar_arrive(&wp_empty[pend_s]);
             }
             pending = false;
         };
-        for (int kbl = set; kbl < L; kbl += 2) {
-            const int wsl = kbl / KBW, sub = kbl - wsl * KBW;  // stage of the slice, k-block inside it
+        constexpr int kChunksPerKb = KB_BYTES / 16;  // 16-byte chunks of one row of a k-block: 2 / 1
+        for (int pr = set; pr < P; pr += 2) {
+            const int kbl = 2 * pr;
+            const bool two = kbl + 1 < L;
+            const int wsl = kbl / KBW, sub = kbl - wsl * KBW;  // stage of the slice, first k-block inside it (even)
             const int s = wsl % p.wstages;
-            if (sub < 2) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], (wsl / p.wstages) & 1, 4));
+            if (sub < 4) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], (wsl / p.wstages) & 1, 4));
             if (!ok) break;
-            uint32_t o[16];
-            if (BITS == 4) {
+            uint32_t o[32];
+            {
                 const uint32_t base = row32 + s * kWBytes;
-                uint32_t w[8];
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                             : "r"(base + (((2 * sub) ^ swz) << 4)));
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
-                             : "r"(base + (((2 * sub + 1) ^ swz) << 4)));
+                uint32_t w[8 * kChunksPerKb];  // 16 (4-bit) / 8 (2-bit) words of the pair
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    o[2 * j + 0] = w[j] & kmask;         // codes 0, 2, 4, 6 of the word, one per byte
-                    o[2 * j + 1] = (w[j] >> 4) & kmask;  // codes 1, 3, 5, 7
+                for (int c = 0; c < 2 * kChunksPerKb; ++c)
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
+                                 : "r"(base + (((sub * kChunksPerKb + c) ^ swz) << 4)));
+                if (BITS == 4) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        o[2 * j + 0] = w[j] & kmask;         // codes 0, 2, 4, 6 of the word, one per byte
+                        o[2 * j + 1] = (w[j] >> 4) & kmask;  // codes 1, 3, 5, 7
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) o[4 * j + i] = (w[j] >> (2 * i)) & kmask;  // codes i, 4+i, 8+i, 12+i
                 }
-            } else {
-                uint32_t w[4];
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                             : "r"(row32 + s * kWBytes + ((sub ^ swz) << 4)));
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) o[4 * j + i] = (w[j] >> (2 * i)) & kmask;  // codes i, 4+i, 8+i, 12+i
             }
             if (pending) finish_pending();
-            // the A stage is free once the MMAs of k-block kbl - kNA completed; the D buffer of this
-            // k-block once the epilogue has read k-block kbl - kND
-            if (kbl >= kNA) ok = tc_wait_relaxed(&done[(kbl - kNA) % kND], ((kbl - kNA) / kND) & 1, 5);
-            if (ok && kbl >= kND) ok = tc_wait_relaxed(&d_empty[kbl % kND], ((kbl / kND) - 1) & 1, 6);
+            // A stage and D buffer of this pair are free once the epilogue has read pair pr - kNP
+            const int stg = pr % kNP;
+            if (pr >= kNP) ok = tc_wait_relaxed(&d_empty[stg], ((pr / kNP) - 1) & 1, 6);
             ok = __all_sync(0xffffffffu, ok);  // tcgen05.st is warp-wide
             if (!ok) break;
             tc_fence_after();
-            const uint32_t dst = a_lane + static_cast<uint32_t>((kbl % kNA) * kACols);
+            const uint32_t dst = a_lane + static_cast<uint32_t>(stg * 2 * kACols);
             tmem_st16(dst, o);
+            if (two) tmem_st16(dst + kACols, o + 16);
             pending = true;
-            pend_a = kbl % kNA;
+            pend_st = stg;
             pend_s = s;
-            pend_last = sub >= KBW - 2 || kbl + 2 >= L;
+            pend_last = sub >= KBW - 4 || pr + 2 >= P;
         }
         if (pending) finish_pending();
-        (void)KB_BYTES;
     } else {
         // ---------------- staging, epilogue, reduction
         const int quad = warp & 3;
@@ -512,44 +527,47 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         for (int t = 0; t < 8; ++t) rs[t] = 0.f;
         const uint32_t d_lane = tmem_d + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
-        for (int kbl = 0; kbl < L; kbl += 2) {
-            // two k-blocks per trip: the commit of the second one covers the first (MMAs complete in order)
-            const bool two = kbl + 1 < L;
-            const int last = two ? kbl + 1 : kbl;
-            const int d0 = kbl % kND, d1 = last % kND;
-            ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[d1], (last / kND) & 1, 7));
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t c0[16], c1[16];
-            tmem_ld16(d_lane + d0 * kDCols, c0);
-            tmem_ld16(d_lane + d1 * kDCols, c1);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&d_empty[d0]);
-                if (two) mbar_arrive(&d_empty[d1]);
-            }
+        // One pair of k-blocks per trip; only the columns of the tokens that exist are read (MT = m rounded
+        // up to a power of two): hi bytes in columns [0, MT), lo bytes in columns [8, 8 + MT) of each D.
+        auto run = [&](auto mt) {
+            constexpr int MT = decltype(mt)::value;
+            int st = 0;
+            uint32_t ph = 0;
+            for (int pr = 0; pr < P; ++pr) {
+                const bool two = 2 * pr + 1 < L;
+                ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[st], ph, 7));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t c[2][2][MT];  // [k-block of the pair][hi, lo][token]
+                const uint32_t dp = d_lane + st * 2 * kDCols;
+                tmem_ld<MT>(dp, c[0][0]);
+                tmem_ld<MT>(dp + 8, c[0][1]);
+                tmem_ld<MT>(dp + kDCols, c[1][0]);
+                tmem_ld<MT>(dp + kDCols + 8, c[1][1]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&d_empty[st]);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (h == 1 && !two) break;
-                const int kk = kbl + h;
-                const uint32_t sb = sc[kk * kRows + row];
-                const float sv = bf16_bits_to_f32(sb & 0xffffu), bv = __uint_as_float(sb & 0xffff0000u);
-                const float4 xs0 = *reinterpret_cast<const float4 *>(xsum + kk * 8);
-                const float4 xs1 = *reinterpret_cast<const float4 *>(xsum + kk * 8 + 4);
-                const float4 xe0 = *reinterpret_cast<const float4 *>(xscale + kk * 8);
-                const float4 xe1 = *reinterpret_cast<const float4 *>(xscale + kk * 8 + 4);
-                const float xs[8] = {xs0.x, xs0.y, xs0.z, xs0.w, xs1.x, xs1.y, xs1.z, xs1.w};
-                const float xe[8] = {xe0.x, xe0.y, xe0.z, xe0.w, xe1.x, xe1.y, xe1.z, xe1.w};
+                for (int h = 0; h < 2; ++h) {
+                    if (h == 1 && !two) break;
+                    const int kk = 2 * pr + h;
+                    const uint32_t sb = sc[kk * kRows + row];
+                    const float sv = bf16_bits_to_f32(sb & 0xffffu), bv = __uint_as_float(sb & 0xffff0000u);
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
-                    // sum(q * x_int) = 256 * (hi column) + (lo column), below 2^24: exact as a float
-                    const int qx = static_cast<int>(h ? c1[t] : c0[t]) * 256 + static_cast<int>(h ? c1[8 + t] : c0[8 + t]);
-                    rs[t] = fmaf(sv * xe[t], static_cast<float>(qx), fmaf(bv, xs[t], rs[t]));
+                    for (int t = 0; t < MT; ++t) {
+                        // sum(q * x_int) = 256 * (hi column) + (lo column), below 2^24: exact as a float
+                        const int qx = static_cast<int>(c[h][0][t]) * 256 + static_cast<int>(c[h][1][t]);
+                        rs[t] = fmaf(sv * xscale[kk * 8 + t], static_cast<float>(qx), fmaf(bv, xsum[kk * 8 + t], rs[t]));
+                    }
                 }
+                if (++st == kNP) { st = 0; ph ^= 1; }
             }
-        }
+        };
+        if (p.m == 1) run(IntC<1>{});
+        else if (p.m == 2) run(IntC<2>{});
+        else if (p.m <= 4) run(IntC<4>{});
+        else run(IntC<8>{});
         // this slice's partial sums go to rank 0 of the cluster (slot [rank][row][t] of its `part`)
         if (p.splits > 1) cluster_wait();  // first phase: rank 0 is running
         const uint32_t slot = smem_u32(part) + ((rank * kRows + row) * p.m) * 4;

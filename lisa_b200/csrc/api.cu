@@ -144,8 +144,11 @@ int lisa_cuda_quantized_matmul_serial_rows(lisa_stream_t stream, const void *x, 
                                      group_size, bits, dtype, y, LISA_FLAG_NONE);
     int rc = check_affine("quantized_matmul_serial_rows", x, rows, k, w, scales, biases, n, group_size, bits, dtype, y);
     if (rc != LISA_OK) return rc;
-    // The streaming kernel accumulates every input row in the same order whatever the row
-    // count, so each row equals its own m=1 call bit for bit.
+    // Both streaming kernels accumulate every input row in the same order whatever the row count, so
+    // each row equals its own m=1 call bit for bit -- as long as it is the kernel an m=1 call takes.
+    if (qmv_tc_supported(1, k, n, group_size, bits))
+        return qmv_tc(static_cast<cudaStream_t>(stream), x, rows, k, w, scales, biases, n, group_size, bits, y,
+                      LISA_FLAG_NONE);
     return qmv_affine(static_cast<cudaStream_t>(stream), x, rows, k, w, scales, biases, n, group_size, bits, y,
                       LISA_FLAG_NONE);
 }

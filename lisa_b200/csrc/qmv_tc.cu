@@ -609,11 +609,11 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
 
 }  // namespace
 
-// Shapes the kernel takes: group size 64, m <= 8, packed rows addressable by a tensor map, and a k-slice
-// whose staging fits half an SM's shared memory.
-static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, TcParams &p, int &smem, int &grid) {
+// Shapes the kernel takes: group size 64, packed rows addressable by a tensor map, and a k-slice whose
+// staging fits half an SM's shared memory.  `m` rows are wanted; `mc` (<= 8) is how many one launch takes.
+static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, TcParams &p, int &smem, int &grid, int &mc) {
     if (bits != 2 && bits != 4) return false;
-    if (group_size != 64 || k % 64 != 0 || m < 1 || m > 8) return false;
+    if (group_size != 64 || k % 64 != 0 || m < 1) return false;
     if ((k * bits / 8) % 16 != 0 || (k * 2) % 16 != 0) return false;
     const int kbw = (128 * 8 / bits) / 64;
     const int num_kb = static_cast<int>(k / 64);
@@ -623,12 +623,20 @@ static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, 
     // as many k-slices as keep the grid near one CTA per SM; more when the slice would not fit
     int splits = 1;
     while (splits < 8 && tiles * (splits * 2) <= sm_count() + 20 && splits * 2 <= total_ws) splits *= 2;
+    // The number of k-slices must not depend on m (a row's result is the sum of its slices in rank order,
+    // and a row of an m-row call has to equal its own m = 1 call bit for bit): it is the first one whose
+    // shallowest ring fits beside the staging of ONE token; a call with more rows than fit beside that
+    // runs as several launches of fewer rows, each with the same slices.
     for (; splits <= 8; splits *= 2) {
         if (splits > total_ws) break;
         const int max_ws = (total_ws + splits - 1) / splits;
         const int max_l = std::min(max_ws * kbw, num_kb);
-        for (int ws = std::min(kMaxWStages, max_ws); ws >= std::min(2, max_ws); --ws) {
-            const TcPlan plan = tc_plan(ws, max_l, splits, m);
+        const int ws_min = std::min(2, max_ws);
+        if (tc_plan(ws_min, max_l, splits, 1).total > budget) continue;
+        mc = std::min(m, 8);
+        while (mc > 1 && tc_plan(ws_min, max_l, splits, mc).total > budget) mc = (mc + 1) / 2;
+        for (int ws = std::min(kMaxWStages, max_ws); ws >= ws_min; --ws) {
+            const TcPlan plan = tc_plan(ws, max_l, splits, mc);
             if (plan.total <= budget) {
                 p.splits = splits;
                 p.wstages = ws;
@@ -640,15 +648,16 @@ static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, 
                 return true;
             }
         }
+        return false;
     }
     return false;
 }
 
 bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits) {
     TcParams p{};
-    int smem = 0, grid = 0;
-    if (n < 1 || n > (1 << 24)) return false;
-    return tc_make_plan(n, k, group_size, bits, static_cast<int>(std::min<int64_t>(m, 8)), p, smem, grid);
+    int smem = 0, grid = 0, mc = 0;
+    if (n < 1 || n > (1 << 24) || m < 1) return false;
+    return tc_make_plan(n, k, group_size, bits, static_cast<int>(std::min<int64_t>(m, 8)), p, smem, grid, mc);
 }
 
 int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
@@ -664,11 +673,11 @@ int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint3
         const int rc = make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != LISA_OK) return rc;
     }
-    for (int64_t done = 0; done < m; done += 8) {
-        const int mc = static_cast<int>(std::min<int64_t>(m - done, 8));
+    int mc = 0;
+    for (int64_t done = 0; done < m; done += mc) {
         TcParams p{};
         int smem = 0, grid = 0;
-        if (!tc_make_plan(n, k, group_size, bits, mc, p, smem, grid))
+        if (!tc_make_plan(n, k, group_size, bits, static_cast<int>(std::min<int64_t>(m - done, 8)), p, smem, grid, mc))
             return fail(LISA_ERR_UNSUPPORTED, "qmv_tc: shape not supported");
         p.scales = reinterpret_cast<const uint16_t *>(scales);
         p.biases = reinterpret_cast<const uint16_t *>(biases);

@@ -612,6 +612,23 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
 
     for _ in range(warmup):
         step()
+    torch.cuda.synchronize()
+    graphed = False
+    if world == 1 and os.environ.get("LISA_BENCH_GRAPH", "1") != "0":
+        # one GPU: no collective inside the step, so it replays from a CUDA graph like the decode stack
+        # (eager launches through the Python mirror are host-bound at small sizes)
+        eager = step
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                eager()
+        torch.cuda.current_stream().wait_stream(side)
+        step = graph.replay
+        graphed = True
+        for _ in range(2):
+            step()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -628,6 +645,11 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         dist.barrier()
     torch.cuda.synchronize()
     launches = ops.launch_count() - before
+    if graphed:  # replays do not pass through the library's launch counter
+        before = ops.launch_count()
+        eager()
+        torch.cuda.synchronize()
+        launches = (ops.launch_count() - before) * args.steps
     ms = e0_.elapsed_time(e1_) / args.steps
     clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -639,7 +661,8 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         line = {"metric": "qmm bf16 TFLOP/s" if (args.mode == "moe" or args.m > 8) else "2-bit qmv HBM GB/s",
                 "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
                 "scaling": scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": name, "parallelism": par}, "gpu_launches": launches, "clocks": clocks,
+                "config": {"workload": name, "parallelism": par, "graph": graphed}, "gpu_launches": launches,
+                "clocks": clocks,
                 "device_status": ops.device_status()}
         if line["metric"].startswith("qmm"):
             line.update(value=total_flops / (ms * 1e-3) / 1e12, unit="TFLOP/s")

@@ -75,7 +75,11 @@ static int check_affine(const char *op, const void *x, int64_t m, int64_t k, con
 // tile of up to 256 rows, so it wins as soon as the streaming kernel would need a second pass.
 static const int64_t kQmvMaxRows = 8;
 static const int64_t kQmvMaxStaged = 8 * 9728;
-static bool prefer_qmv(int64_t m, int64_t k) { return m <= kQmvMaxRows && (m <= 4 || m * k <= kQmvMaxStaged); }
+static bool prefer_qmv(int64_t m, int64_t k, bool tc_ok) {
+    // the tensor-memory GEMV takes up to 8 rows for about the cost of one
+    if (tc_ok) return m <= kQmvMaxRows;
+    return m <= kQmvMaxRows && (m <= 4 || m * k <= kQmvMaxStaged);
+}
 
 static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
                                  const void *scales, const void *biases, int64_t n, int transpose, int group_size,
@@ -89,9 +93,9 @@ static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, 
     if (force_qmv && force_qmm) return fail(LISA_ERR_BAD_ARG, "quantized_matmul: contradictory flags");
     const bool qmm_ok = qmm_affine_supported(m, k, n, group_size, bits);
     if (force_qmm && !qmm_ok) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the GEMM kernel");
-    if (force_qmm || (!force_qmv && !prefer_qmv(m, k) && qmm_ok))
-        return qmm_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
     const bool tc_ok = qmv_tc_supported(m, k, n, group_size, bits);
+    if (force_qmm || (!force_qmv && !prefer_qmv(m, k, tc_ok) && qmm_ok))
+        return qmm_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
     if (force_tc && !tc_ok)
         return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the tensor-memory GEMV");
     // The tensor-memory GEMV is the default wherever it applies (group size 64); LISA_FLAG_FORCE_QMV and

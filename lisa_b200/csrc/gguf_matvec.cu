@@ -38,6 +38,8 @@ __device__ __forceinline__ void q4k_row(const uint8_t *__restrict__ wrow, const 
                                         int lane, float (&acc)[TT]) {
     const int pg = lane >> 3;          // pair of sub-blocks: low nibbles -> 2*pg, high -> 2*pg+1
     const int l0 = (lane & 7) * 4;     // element offset within the sub-block
+    // several blocks of the row in flight per warp: the loads of a block do not depend on the previous one
+#pragma unroll(TT == 1 ? 4 : 2)
     for (int ib = 0; ib < nblocks; ++ib) {
         const uint8_t *blk = wrow + static_cast<size_t>(ib) * 144;
         const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
@@ -78,6 +80,7 @@ __device__ __forceinline__ void q2k_row(const uint8_t *__restrict__ wrow, const 
                                         int lane, float (&acc)[TT]) {
     const int sub = lane >> 4, t16 = lane & 15;
     const int half = t16 >> 3, group = (t16 & 7) >> 2, pos = (t16 & 7) * 4;
+#pragma unroll(TT == 1 ? 4 : 2)
     for (int ib = sub; ib < nblocks; ib += 2) {
         const uint8_t *blk = wrow + static_cast<size_t>(ib) * 84;
         const uint32_t qs = __ldg(reinterpret_cast<const uint32_t *>(blk + 16) + t16);

@@ -74,10 +74,10 @@ def tensor_peak():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launches, from the
-# ncu captures summarised in profiles/ (qmv_mma_kernel on 4 layers of the decode stack; qmm_affine_kernel
+# ncu captures summarised in profiles/ (qmv_tc_kernel on 4 layers of the decode stack; qmm_affine_kernel
 # on 2 layers of the prefill stack).  Traffic grows in proportion to the units processed, so the ratio
 # carries over to a full launch.
-DRAM_TRAFFIC_RATIO = {"decode": 1.004, "prefill": 0.577}
+DRAM_TRAFFIC_RATIO = {"decode": 1.008, "prefill": 0.576}
 PREFILL_M = 2048
 
 

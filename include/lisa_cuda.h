@@ -122,6 +122,18 @@ int lisa_cuda_gather_qmm(lisa_stream_t stream, const void *x, int64_t rows, int6
 int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows,
                                  int64_t row_bytes, const float *x, int64_t tokens, float *y);
 
+/* The same operator for many tokens (prefill, target-verify: the reference runs these rows as
+ * independent matvecs, deepseek41.rs:165-171) with a device workspace from the caller's pool
+ * (lisa_cuda_gguf_packed_matmul_workspace_bytes, 16-byte aligned).  With a workspace, 32 tokens or
+ * more and a Q4_K matrix the product runs on the tensor cores: activations and decoded weights each
+ * enter as two bf16 planes (value = hi + lo, 16 significant bits), f32 accumulate, f32 out; results
+ * agree with the matvec to ~5e-5 max-relative, not bit for bit.  Any other case is the matvec above,
+ * exactly. */
+size_t lisa_cuda_gguf_packed_matmul_workspace_bytes(int64_t tokens, int64_t row_bytes, int format);
+int lisa_cuda_gguf_packed_matmul(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows,
+                                 int64_t row_bytes, const float *x, int64_t tokens, float *y,
+                                 void *workspace, size_t workspace_bytes);
+
 /* deepseek41::expert_matvec(format, weights, input, ids), deepseek41.rs:204-283.
  * w uint8 [experts, rows, row_bytes]; x f32 [tokens, slots, K], slots in {1, top_k};
  * ids int32 [tokens, top_k], top_k <= 32; y f32 [tokens, top_k, rows].

@@ -221,6 +221,32 @@ int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t
     return gguf_matvec(static_cast<cudaStream_t>(stream), format, w, 1, rows, row_bytes, x, tokens, 1, nullptr, 1, y);
 }
 
+size_t lisa_cuda_gguf_packed_matmul_workspace_bytes(int64_t tokens, int64_t row_bytes, int format) {
+    const int block = (format == LISA_GGUF_Q2_K) ? 84 : 144;
+    if (tokens < 1 || row_bytes < block) return 0;
+    return qmm_gguf_workspace_bytes(tokens, row_bytes / block * 256);
+}
+
+// Tokens from which the tensor-core product replaces the per-token matvecs.
+static const int64_t kGgufGemmMinTokens = 32;
+
+int lisa_cuda_gguf_packed_matmul(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes,
+                                 const float *x, int64_t tokens, float *y, void *workspace, size_t workspace_bytes) {
+    int block = 0;
+    int rc = gguf_geometry("packed_matmul", format, rows, row_bytes, &block);
+    if (rc != LISA_OK) return rc;
+    const bool gemm = workspace && tokens >= kGgufGemmMinTokens && qmm_gguf_supported(format, tokens, rows, row_bytes) &&
+                      aligned16(w) && row_bytes % 16 == 0;
+    if (!gemm) return lisa_cuda_gguf_packed_matvec(stream, format, w, rows, row_bytes, x, tokens, y);
+    if (!w || !x || !y) return fail(LISA_ERR_BAD_ARG, "packed_matmul: null pointer");
+    if (tokens > 65535) return fail(LISA_ERR_BAD_ARG, "invalid GGUF matvec input rows");
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 3u) != 0 || !aligned16(workspace))
+        return fail(LISA_ERR_MISALIGNED, "packed_matmul: x and workspace must be 16-byte and y 4-byte aligned");
+    if (workspace_bytes < lisa_cuda_gguf_packed_matmul_workspace_bytes(tokens, row_bytes, format))
+        return fail(LISA_ERR_WORKSPACE, "packed_matmul: workspace too small");
+    return qmm_gguf(static_cast<cudaStream_t>(stream), format, w, rows, row_bytes, x, tokens, y, workspace);
+}
+
 int lisa_cuda_gguf_expert_matvec(lisa_stream_t stream, int format, const uint8_t *w, int64_t experts, int64_t rows,
                                  int64_t row_bytes, const float *x, int64_t tokens, int64_t slots, const int32_t *ids,
                                  int64_t top_k, float *y) {

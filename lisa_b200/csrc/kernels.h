@@ -27,6 +27,11 @@ int qmm_affine_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t
                        const void *scales, const void *biases, int64_t experts, int64_t n, int group_size, int bits,
                        void *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles);
 int qmm_device_status();
+// GGUF Q4_K GEMM on the same kernel (bf16 operands: the caller opts in by giving a workspace)
+bool qmm_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes);
+size_t qmm_gguf_workspace_bytes(int64_t tokens, int64_t k);
+int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
+             int64_t tokens, float *y, void *workspace);
 
 // dequantize.cu
 int dequantize_affine(cudaStream_t stream, const uint32_t *w, const void *scales, const void *biases, int64_t rows,

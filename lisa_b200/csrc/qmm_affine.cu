@@ -47,6 +47,7 @@ constexpr int kBN = 128;        // weight rows per CTA (MMA M)
 constexpr int kBK = 64;         // k per MMA stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kStages = 5;      // operand ring: stage s = activation tile in shared memory + A tile in tensor memory
 constexpr int kWpStages = 4;    // packed-weight ring: loads run a whole ring (12+ k-blocks) ahead of their use
+constexpr int kQ4kBlock = 144;  // GGUF Q4_K: bytes of a 256-element block = one packed stage row (4 k-blocks)
 constexpr int kACols = kBK / 2; // one k-block of A: 64 bf16 per lane = 32 columns
 constexpr int kDequantWarps = 16;  // two sets of 8 warps (even / odd k-blocks); 2 threads per weight row, 32 codes each
 constexpr int kWarpsPerKb = kDequantWarps / 2;
@@ -68,6 +69,7 @@ struct QmmParams {
     // the weights of expert e are rows [e*n, (e+1)*n) of the packed matrix.  Null for the dense GEMM.
     const int32_t *tiles;
     const int32_t *tile_count;
+    float *yf;        // GGUF form: f32 output [m, n]
 };
 
 // ---- tcgen05 / TMA wrappers ----
@@ -194,28 +196,73 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t src, uint32_t m0, uint
     return out;
 }
 
+// The same two weights as dequant_pair, as a bf16 pair `hi` and the bf16 pair `lo` of what the rounding to
+// bf16 left over: hi + lo carries 16 significant bits of each f32 weight.
+__device__ __forceinline__ void dequant_pair_split(uint32_t src, uint32_t m0, uint32_t m1, uint32_t mbits,
+                                                   unsigned long long neg_magic2, unsigned long long s2,
+                                                   unsigned long long b2, uint32_t &hi, uint32_t &lo) {
+    asm("{\n\t"
+        ".reg .b32 q0, q1, h0, h1;\n\t"
+        ".reg .f32 f0, f1;\n\t"
+        ".reg .b64 t;\n\t"
+        "lop3.b32 q0, %2, %3, %5, 0xEA;\n\t"
+        "lop3.b32 q1, %2, %4, %5, 0xEA;\n\t"
+        "mov.b64 t, {q0, q1};\n\t"
+        "add.rn.f32x2 t, t, %6;\n\t"
+        "fma.rn.f32x2 t, t, %7, %8;\n\t"
+        "mov.b64 {f0, f1}, t;\n\t"
+        "cvt.rn.bf16x2.f32 %0, f1, f0;\n\t"
+        "shl.b32 h0, %0, 16;\n\t"
+        "and.b32 h1, %0, 0xffff0000;\n\t"
+        "sub.rn.f32 f0, f0, h0;\n\t"
+        "sub.rn.f32 f1, f1, h1;\n\t"
+        "cvt.rn.bf16x2.f32 %1, f1, f0;\n\t"
+        "}\n"
+        : "=r"(hi), "=r"(lo)
+        : "r"(src), "r"(m0), "r"(m1), "r"(mbits), "l"(neg_magic2), "l"(s2), "l"(b2));
+}
+
 struct QmmSmem {
     // byte offsets from the 1024-aligned base
     static constexpr int kXs = 0;                                   // kStages * bt * 128
-    __host__ __device__ static int wp(int bt) { return kStages * bt * 128; }
-    __host__ __device__ static int bars(int bt) { return wp(bt) + kWpStages * kWpBytes; }
-    __host__ __device__ static int total(int bt) { return bars(bt) + 256 + 1024; }  // + alignment slack
+    __host__ __device__ static int wp(int bt, int xplanes = 1) { return kStages * xplanes * bt * 128; }
+    __host__ __device__ static int bars(int bt, int wstages = kWpStages, int wbytes = kWpBytes, int xplanes = 1) {
+        return wp(bt, xplanes) + wstages * wbytes;
+    }
+    __host__ __device__ static int total(int bt, int wstages = kWpStages, int wbytes = kWpBytes, int xplanes = 1) {
+        return bars(bt, wstages, wbytes, xplanes) + 256 + 1024;  // + alignment slack
+    }
 };
 
-template <int BITS>
+// GGUF = true (with BITS = 4): the packed rows are GGUF Q4_K blocks (crates/lisa-gguf/src/quant.rs:82-101):
+// a stage row is one 144-byte block {f16 d, f16 dmin, 12 bytes of 6-bit scales and mins, 128 nibble bytes},
+// a (k-block, half) is one 32-element sub-block g = 2*sub + half -- nibble `half` of bytes 32*sub .. +31 --
+// i.e. an affine group with scale = d*sc_g and bias = -dmin*m_g, taken from the block header in shared
+// memory; the output is f32.
+template <int BITS, bool GGUF = false>
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   const QmmParams p) {
+    constexpr int WS = GGUF ? 3 : kWpStages;              // packed ring stages
+    constexpr int ROWB = GGUF ? kQ4kBlock : 128;          // bytes of a packed stage row
+    constexpr int WPB = kBN * ROWB;                       // bytes of a packed stage
+    // GGUF activations are f32: they come as two bf16 planes, x = hi + lo (rows [0, m) and [m, 2m) of the
+    // activation tensor map), both multiplied with the same A tile into the same accumulator, so that only
+    // the rounding of the decoded weights is left
+    constexpr int XP = GGUF ? 2 : 1;
+    // ... and the decoded weights as two bf16 planes as well (hi in columns 0..31 of an A stage, lo in
+    // 32..63); the products hi*hi, hi*lo and lo*hi go into the same accumulator
+    constexpr int ACOLS = GGUF ? 2 * kACols : kACols;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *xs = smem + QmmSmem::kXs;
-    uint8_t *wp = smem + QmmSmem::wp(p.bt);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + QmmSmem::bars(p.bt));
+    uint8_t *wp = smem + QmmSmem::wp(p.bt, XP);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + QmmSmem::bars(p.bt, WS, WPB, XP));
     // full[s]: activation tile landed (1 arrival + bytes) and the eight dequantize warps of the k-block
     // stored their parts of the A tile; empty[s]: the MMAs that read stage s completed (tcgen05.commit).
     uint64_t *full = bars, *empty = bars + kStages;
-    uint64_t *wp_full = bars + 2 * kStages, *wp_empty = wp_full + kWpStages;
-    uint64_t *acc_full = wp_empty + kWpStages;
+    uint64_t *wp_full = bars + 2 * kStages, *wp_empty = wp_full + WS;
+    uint64_t *acc_full = wp_empty + WS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
 
     constexpr int KBW = (128 * 8 / BITS) / kBK;  // k-blocks per packed-weight stage: 4 (4-bit), 8 (2-bit)
@@ -237,7 +284,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             mbar_init(&full[i], 1 + kWarpsPerKb);
             mbar_init(&empty[i], 1);
         }
-        for (int i = 0; i < kWpStages; ++i) {
+        for (int i = 0; i < WS; ++i) {
             mbar_init(&wp_full[i], 1);
             mbar_init(&wp_empty[i], kDequantWarps);
         }
@@ -260,20 +307,20 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // ---------------- TMA producer
         if (lane == 0) {
             const int num_wi = (num_kb + KBW - 1) / KBW;
-            const uint32_t x_bytes = static_cast<uint32_t>(p.bt) * 128u;
+            const uint32_t x_bytes = static_cast<uint32_t>(p.bt) * 128u * XP;
             int next_wi = 0;
             bool ok = true;
             // Packed weights come from HBM: their loads are issued a whole ring ahead, independent of
             // how far the operand ring has drained.
             auto issue_w = [&]() {
-                const int ws = next_wi % kWpStages;
-                if (next_wi >= kWpStages) ok = qmm_wait(&wp_empty[ws], ((next_wi / kWpStages) - 1) & 1, 2);
+                const int ws = next_wi % WS;
+                if (next_wi >= WS) ok = qmm_wait(&wp_empty[ws], ((next_wi / WS) - 1) & 1, 2);
                 if (!ok) return;
-                mbar_arrive_expect_tx(&wp_full[ws], kWpBytes);
-                tma_load_2d(wp + ws * kWpBytes, &map_w, next_wi * 128, wrow0, &wp_full[ws]);
+                mbar_arrive_expect_tx(&wp_full[ws], WPB);
+                tma_load_2d(wp + ws * WPB, &map_w, next_wi * ROWB, wrow0, &wp_full[ws]);
                 ++next_wi;
             };
-            for (int i = 0; i < kWpStages && next_wi < num_wi; ++i) issue_w();
+            for (int i = 0; i < WS && next_wi < num_wi; ++i) issue_w();
             int s = 0;
             uint32_t ph = 1;  // parity of the lap before: the first lap does not wait
             for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -282,6 +329,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (!ok) break;
                 mbar_arrive_expect_tx(&full[s], x_bytes);
                 tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, kb * kBK, t0, &full[s]);
+                if (GGUF) tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + x_bytes / 2, &map_x, kb * kBK, p.m + t0, &full[s]);
                 if (++s == kStages) { s = 0; ph ^= 1; }
             }
         }
@@ -293,7 +341,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         {
             const uint32_t idesc = umma_idesc_bf16(p.bt);
             const uint32_t b_lo0 = umma_desc_lo(smem_u32(xs));
-            const uint32_t b_step = static_cast<uint32_t>(p.bt) * 8u;  // one stage, in 16-byte units
+            const uint32_t b_step = static_cast<uint32_t>(p.bt) * 8u * XP;  // one stage, in 16-byte units
             int s = 0;
             uint32_t ph = 0, acc = 0;
             bool ok = true;
@@ -301,13 +349,18 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 ok = __all_sync(0xffffffffu, qmm_wait(&full[s], ph, 3));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = tmem_a + static_cast<uint32_t>(s * kACols);
+                const uint32_t a_addr = tmem_a + static_cast<uint32_t>(s * ACOLS);
                 const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(s) * b_step;
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks) {
                         umma_bf16_ts(tmem_base, a_addr + ks * 8, b_lo + ks * 2, kUmmaDescHiSw128, idesc, acc);
                         acc = 1;
+                        if (GGUF) {
+                            // x_lo (half a stage further) with w_hi, then x_hi with w_lo
+                            umma_bf16_ts(tmem_base, a_addr + ks * 8, b_lo + b_step / 2 + ks * 2, kUmmaDescHiSw128, idesc, 1u);
+                            umma_bf16_ts(tmem_base, a_addr + kACols + ks * 8, b_lo + ks * 2, kUmmaDescHiSw128, idesc, 1u);
+                        }
                     }
                     umma_commit(&empty[s]);
                 }
@@ -340,7 +393,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             asm volatile("mov.u32 %0, %1;" : "=r"(mk[j]) : "r"(BITS == 4 ? (0xfu << (4 * (j & 3))) : (0x3u << (2 * j))));
         asm volatile("mov.u32 %0, %1;" : "=r"(mbits) : "r"(0x4b000000u));
         const unsigned long long neg_magic2 = pack_f32x2(-8388608.0f, -8388608.0f);
-        const uint32_t wp32 = smem_u32(wp) + row * 128;
+        const uint32_t wp32 = smem_u32(wp) + row * ROWB;
         const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(half * 16);
         auto load_sb = [&](int kb, uint32_t &sb, uint32_t &bb) {
             int g = (kb * kBK + half * 32) >> gshift;
@@ -349,27 +402,46 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             bb = __ldg(brow + g);
         };
         uint32_t s_next = 0, b_next = 0;
-        if (kpar < num_kb) load_sb(kpar, s_next, b_next);
+        if (!GGUF && kpar < num_kb) load_sb(kpar, s_next, b_next);
         int a = kpar;
         uint32_t aph = 1;  // parity of the lap before: the first lap over the ring does not wait
         bool ok = true;
         for (int kb = kpar; kb < num_kb; kb += 2) {
-            const int wi = kb / KBW, ws = wi % kWpStages, sub = kb % KBW;
-            const float sc = bf16_bits_to_f32(s_next), bi = bf16_bits_to_f32(b_next);
-            if (kb + 2 < num_kb) load_sb(kb + 2, s_next, b_next);
+            const int wi = kb / KBW, ws = wi % WS, sub = kb % KBW;
+            float sc = bf16_bits_to_f32(s_next), bi = bf16_bits_to_f32(b_next);
+            if (!GGUF && kb + 2 < num_kb) load_sb(kb + 2, s_next, b_next);
             // first visit of this packed-weight stage
-            if (sub < 2) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wi / kWpStages) & 1, 5));
+            if (sub < 2) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wi / WS) & 1, 5));
             if (!ok) break;
             // packed codes of (row, k-block, half): 32 codes
             uint32_t w[4];
-            if (BITS == 4) {
+            uint32_t wq[8];  // GGUF: the 32 bytes whose nibble `half` are this thread's codes
+            if (GGUF) {
+                const uint32_t blk = wp32 + ws * WPB;
+                uint32_t h0, h1, h2, h3;
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(blk));
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(wq[0]), "=r"(wq[1]), "=r"(wq[2]), "=r"(wq[3])
+                             : "r"(blk + 16 + sub * 32));
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(wq[4]), "=r"(wq[5]), "=r"(wq[6]), "=r"(wq[7])
+                             : "r"(blk + 32 + sub * 32));
+                // 6-bit scale and min of sub-block g (quant.rs:88-96)
+                const int g = 2 * sub + half, sh = 8 * (g & 3);
+                const uint32_t b0 = (h1 >> sh) & 255u, b1 = (h2 >> sh) & 255u, b2 = (h3 >> sh) & 255u;
+                const uint32_t sq = (g < 4) ? (b0 & 63u) : ((b2 & 15u) | ((b0 >> 6) << 4));
+                const uint32_t mq = (g < 4) ? (b1 & 63u) : ((b2 >> 4) | ((b1 >> 6) << 4));
+                float d, dmin;
+                asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %2; cvt.f32.f16 %0, lo; cvt.f32.f16 %1, hi; }" : "=f"(d), "=f"(dmin) : "r"(h0));
+                sc = d * static_cast<float>(sq);            // exact: 11 x 6 significant bits
+                bi = -(dmin * static_cast<float>(mq));
+                w[0] = w[1] = w[2] = w[3] = 0;
+            } else if (BITS == 4) {
                 const int c = sub * 2 + half;  // 16-byte chunk of the 128-byte packed row
                 asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                             : "r"(wp32 + ws * kWpBytes + ((c ^ swz) << 4)));
+                             : "r"(wp32 + ws * WPB + ((c ^ swz) << 4)));
             } else {
                 uint32_t v0, v1;
                 asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v0), "=r"(v1)
-                             : "r"(wp32 + ws * kWpBytes + ((sub ^ swz) << 4) + half * 8));
+                             : "r"(wp32 + ws * WPB + ((sub ^ swz) << 4) + half * 8));
                 w[0] = v0;        // 2-bit: each 16-bit half holds 8 codes; the masks reach bits 0..15 only
                 w[1] = v0 >> 16;
                 w[2] = v1;
@@ -377,8 +449,20 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             }
             const bool last_visit = sub >= KBW - 2 || kb + 2 >= num_kb;
             uint32_t o[16];
+            uint32_t olo[16];  // GGUF only
             const unsigned long long b2 = pack_f32x2(bi, bi);
-            if (BITS == 4) {
+            if (GGUF) {
+                // element 4i + b of the sub-block is nibble `half` of byte b of word i: bit offsets 4*half and
+                // 4*half + 8 of each 16-bit half of the word
+                const unsigned long long sg = half ? pack_f32x2(sc * 0.0625f, sc * 0.000244140625f)
+                                                   : pack_f32x2(sc, sc * 0.00390625f);
+                const uint32_t m0 = half ? mk[1] : mk[0], m1 = half ? mk[3] : mk[2];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    dequant_pair_split(wq[i], m0, m1, mbits, neg_magic2, sg, b2, o[2 * i + 0], olo[2 * i + 0]);
+                    dequant_pair_split(wq[i] >> 16, m0, m1, mbits, neg_magic2, sg, b2, o[2 * i + 1], olo[2 * i + 1]);
+                }
+            } else if (BITS == 4) {
                 const unsigned long long s01 = pack_f32x2(sc, sc * 0.0625f);
                 const unsigned long long s23 = pack_f32x2(sc * 0.00390625f, sc * 0.000244140625f);
 #pragma unroll
@@ -410,7 +494,8 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (!ok) break;
                 tc_fence_after();
             }
-            tmem_st16(a_lane + static_cast<uint32_t>(a * kACols), o);
+            tmem_st16(a_lane + static_cast<uint32_t>(a * ACOLS), o);
+            if (GGUF) tmem_st16(a_lane + static_cast<uint32_t>(a * ACOLS + kACols), olo);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -438,9 +523,11 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int tok = t0 + ci * 16 + j;
-                    if (tok < t_end)
-                        p.y[static_cast<size_t>(tok) * p.n + out_row] =
-                            static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
+                    if (tok < t_end) {
+                        if (GGUF) p.yf[static_cast<size_t>(tok) * p.n + out_row] = __uint_as_float(r[j]);
+                        else p.y[static_cast<size_t>(tok) * p.n + out_row] =
+                                 static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
+                    }
                 }
             }
         }
@@ -527,6 +614,85 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<2>, map_x, map_w, p));
     }
+    count_launch();
+    return LISA_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// GGUF Q4_K GEMM: f32 activations are first rounded to bf16 into the caller's workspace, then the same
+// tensor-core kernel runs with the Q4_K block decoder; f32 output.
+// x (f32) -> hi = bf16(x), lo = bf16(x - hi): hi + lo carries 16 significant bits of x.
+__global__ void __launch_bounds__(256) f32_to_bf16_planes_kernel(const float4 *__restrict__ src, uint2 *__restrict__ hi,
+                                                                 uint2 *__restrict__ lo, int64_t n4) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n4) {
+        const float4 v = __ldg(src + i);
+        const uint32_t h0 = f32x2_to_bf16x2(v.x, v.y), h1 = f32x2_to_bf16x2(v.z, v.w);
+        const float rx = v.x - bf16_bits_to_f32(h0 & 0xffffu), ry = v.y - __uint_as_float(h0 & 0xffff0000u);
+        const float rz = v.z - bf16_bits_to_f32(h1 & 0xffffu), rw = v.w - __uint_as_float(h1 & 0xffff0000u);
+        hi[i] = make_uint2(h0, h1);
+        lo[i] = make_uint2(f32x2_to_bf16x2(rx, ry), f32x2_to_bf16x2(rz, rw));
+    }
+}
+
+bool qmm_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes) {
+    if (format != LISA_GGUF_Q4_K) return false;
+    if (tokens < 1 || rows < 1 || row_bytes % kQ4kBlock != 0) return false;
+    return tokens * (row_bytes / kQ4kBlock) * 256 < (1ll << 40);
+}
+
+size_t qmm_gguf_workspace_bytes(int64_t tokens, int64_t k) { return static_cast<size_t>(2 * tokens * k * 2 + 256); }
+
+int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
+             int64_t tokens, float *y, void *workspace) {
+    (void)format;
+    const int64_t k = row_bytes / kQ4kBlock * 256;
+    uint16_t *xb = reinterpret_cast<uint16_t *>(workspace);
+    const int64_t n4 = tokens * k / 4;
+    f32_to_bf16_planes_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const float4 *>(x), reinterpret_cast<uint2 *>(xb), reinterpret_cast<uint2 *>(xb + tokens * k), n4);
+    LISA_CUDA_TRY(cudaGetLastError());
+    count_launch();
+
+    QmmParams p{};
+    p.yf = y;
+    p.m = static_cast<int>(tokens);
+    p.n = static_cast<int>(rows);
+    p.k = static_cast<int>(k);
+    p.groups = 1;
+    p.group_size = 32;
+    // two activation planes per stage: token tiles of at most 128
+    const int bt = static_cast<int>(tokens >= 128 ? 128 : ((tokens + 15) / 16) * 16);
+    p.bt = bt;
+    int acc = 32;
+    while (acc < bt) acc <<= 1;
+    p.acc_cols = acc;
+    int cols = 32;
+    while (cols < acc + kStages * 2 * kACols) cols <<= 1;  // two weight planes per A stage
+    p.tmem_cols = cols;
+    p.num_kb = static_cast<int>(k / kBK);
+
+    CUtensorMap map_x, map_w;
+    int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, xb, static_cast<uint64_t>(k), static_cast<uint64_t>(2 * tokens),
+                         static_cast<uint64_t>(k) * 2, kBK, static_cast<uint32_t>(bt));
+    if (rc != LISA_OK) return rc;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(row_bytes), static_cast<uint64_t>(rows)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(row_bytes)};
+        const uint32_t box[2] = {kQ4kBlock, kBN};
+        rc = make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != LISA_OK) return rc;
+    }
+    const int smem = QmmSmem::total(bt, 3, kBN * kQ4kBlock, 2);
+    const int64_t ytiles = (tokens + bt - 1) / bt;
+    if (ytiles > 65535) return fail(LISA_ERR_LIMIT, "gguf matmul: too many row tiles");
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>((rows + kBN - 1) / kBN), static_cast<unsigned>(ytiles));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4, true>, map_x, map_w, p));
     count_launch();
     return LISA_OK;
 }

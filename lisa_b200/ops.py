@@ -162,6 +162,31 @@ def packed_matvec(fmt, weights: torch.Tensor, input: torch.Tensor, *, stream=Non
     return y
 
 
+def packed_matmul(fmt, weights: torch.Tensor, input: torch.Tensor, *, workspace: Optional[torch.Tensor] = None,
+                  stream=None) -> torch.Tensor:
+    """``packed_matvec`` for many tokens with a workspace: Q4_K products of 32 tokens or more run on the
+    tensor cores (operands as hi + lo bf16 planes, f32 accumulate and output, ~5e-5 of the matvec);
+    everything else is the exact matvec."""
+    _need_cuda(weights, input)
+    code = _format_code(fmt)
+    if weights.dim() != 2 or weights.dtype != torch.uint8 or not weights.is_contiguous():
+        raise LisaError(_cabi.ERR_BAD_ARG, "unsupported GGUF quantized matvec layout")
+    if input.dim() != 2 or input.dtype != torch.float32:
+        raise LisaError(_cabi.ERR_BAD_ARG, "invalid GGUF matvec input rows")
+    rows, row_bytes = weights.shape
+    tokens = input.shape[0]
+    need = lib().lisa_cuda_gguf_packed_matmul_workspace_bytes(tokens, row_bytes, code)
+    if workspace is None and need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=input.device)
+    y = torch.empty((tokens, rows), dtype=torch.float32, device=input.device)
+    rc = lib().lisa_cuda_gguf_packed_matmul(_stream(stream), code, weights.data_ptr(), rows, row_bytes,
+                                            input.contiguous().data_ptr(), tokens, y.data_ptr(),
+                                            workspace.data_ptr() if workspace is not None else None,
+                                            workspace.numel() if workspace is not None else 0)
+    check(rc)
+    return y
+
+
 def expert_matvec(fmt, weights: torch.Tensor, input: torch.Tensor, ids: torch.Tensor, *,
                   stream=None) -> torch.Tensor:
     """``deepseek41::expert_matvec`` (deepseek41.rs:204-283): weights uint8 [E, rows, row_bytes],

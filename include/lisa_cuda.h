@@ -124,11 +124,11 @@ int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t
 
 /* The same operator for many tokens (prefill, target-verify: the reference runs these rows as
  * independent matvecs, deepseek41.rs:165-171) with a device workspace from the caller's pool
- * (lisa_cuda_gguf_packed_matmul_workspace_bytes, 16-byte aligned).  With a workspace, 32 tokens or
- * more and a Q4_K matrix the product runs on the tensor cores: activations and decoded weights each
- * enter as two bf16 planes (value = hi + lo, 16 significant bits), f32 accumulate, f32 out; results
- * agree with the matvec to ~5e-5 max-relative, not bit for bit.  Any other case is the matvec above,
- * exactly. */
+ * (lisa_cuda_gguf_packed_matmul_workspace_bytes, 16-byte aligned).  With a workspace and 32 tokens
+ * or more (Q2_K: row_bytes a multiple of 336) the product runs on the tensor cores: activations and
+ * decoded weights each enter as two bf16 planes (value = hi + lo, 16 significant bits), f32
+ * accumulate, f32 out; results agree with the matvec to ~1e-4 max-relative, not bit for bit (on
+ * the reference's dyadic test inputs they are exact).  Any other case is the matvec above, exactly. */
 size_t lisa_cuda_gguf_packed_matmul_workspace_bytes(int64_t tokens, int64_t row_bytes, int format);
 int lisa_cuda_gguf_packed_matmul(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows,
                                  int64_t row_bytes, const float *x, int64_t tokens, float *y,

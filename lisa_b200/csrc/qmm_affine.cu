@@ -48,6 +48,7 @@ constexpr int kBK = 64;         // k per MMA stage: 64 bf16 = one 128-byte swizz
 constexpr int kStages = 5;      // operand ring: stage s = activation tile in shared memory + A tile in tensor memory
 constexpr int kWpStages = 4;    // packed-weight ring: loads run a whole ring (12+ k-blocks) ahead of their use
 constexpr int kQ4kBlock = 144;  // GGUF Q4_K: bytes of a 256-element block = one packed stage row (4 k-blocks)
+constexpr int kQ2kBlock = 84;   // GGUF Q2_K: bytes of a block; a packed stage row is four of them (16 k-blocks)
 constexpr int kACols = kBK / 2; // one k-block of A: 64 bf16 per lane = 32 columns
 constexpr int kDequantWarps = 16;  // two sets of 8 warps (even / odd k-blocks); 2 threads per weight row, 32 codes each
 constexpr int kWarpsPerKb = kDequantWarps / 2;
@@ -225,26 +226,32 @@ __device__ __forceinline__ void dequant_pair_split(uint32_t src, uint32_t m0, ui
 struct QmmSmem {
     // byte offsets from the 1024-aligned base
     static constexpr int kXs = 0;                                   // kStages * bt * 128
-    __host__ __device__ static int wp(int bt, int xplanes = 1) { return kStages * xplanes * bt * 128; }
-    __host__ __device__ static int bars(int bt, int wstages = kWpStages, int wbytes = kWpBytes, int xplanes = 1) {
-        return wp(bt, xplanes) + wstages * wbytes;
+    __host__ __device__ static int wp(int bt, int xplanes = 1, int stages = kStages) { return stages * xplanes * bt * 128; }
+    __host__ __device__ static int bars(int bt, int wstages = kWpStages, int wbytes = kWpBytes, int xplanes = 1,
+                                        int stages = kStages) {
+        return wp(bt, xplanes, stages) + wstages * wbytes;
     }
-    __host__ __device__ static int total(int bt, int wstages = kWpStages, int wbytes = kWpBytes, int xplanes = 1) {
-        return bars(bt, wstages, wbytes, xplanes) + 256 + 1024;  // + alignment slack
+    __host__ __device__ static int total(int bt, int wstages = kWpStages, int wbytes = kWpBytes, int xplanes = 1,
+                                         int stages = kStages) {
+        return bars(bt, wstages, wbytes, xplanes, stages) + 256 + 1024;  // + alignment slack
     }
 };
 
-// GGUF = true (with BITS = 4): the packed rows are GGUF Q4_K blocks (crates/lisa-gguf/src/quant.rs:82-101):
+// GGUF = 4 (with BITS = 4): the packed rows are GGUF Q4_K blocks (crates/lisa-gguf/src/quant.rs:82-101):
 // a stage row is one 144-byte block {f16 d, f16 dmin, 12 bytes of 6-bit scales and mins, 128 nibble bytes},
 // a (k-block, half) is one 32-element sub-block g = 2*sub + half -- nibble `half` of bytes 32*sub .. +31 --
 // i.e. an affine group with scale = d*sc_g and bias = -dmin*m_g, taken from the block header in shared
-// memory; the output is f32.
-template <int BITS, bool GGUF = false>
+// memory.  GGUF = 2 (with BITS = 2): Q2_K blocks (quant.rs:64-80), four 84-byte blocks {16 scale/min
+// bytes, 64 code bytes, f16 d, f16 dmin} per stage row; the 32 elements of (k-block, half) are the 2-bit
+// fields at bit offset 2*shift of bytes 32*(kb4/2) .. +31, shift = 2*(kb4&1) + half, the first 16 under scale
+// byte [half_of_block*8 + shift*2], the last 16 under the next one.  The output is f32.
+template <int BITS, int GGUF = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   const QmmParams p) {
-    constexpr int WS = GGUF ? 3 : kWpStages;              // packed ring stages
-    constexpr int ROWB = GGUF ? kQ4kBlock : 128;          // bytes of a packed stage row
+    constexpr int ST = (GGUF == 2) ? 3 : kStages;                      // operand ring stages
+    constexpr int WS = (GGUF == 4) ? 3 : (GGUF == 2) ? 2 : kWpStages;  // packed ring stages
+    constexpr int ROWB = (GGUF == 4) ? kQ4kBlock : (GGUF == 2) ? 4 * kQ2kBlock : 128;  // bytes of a packed stage row
     constexpr int WPB = kBN * ROWB;                       // bytes of a packed stage
     // GGUF activations are f32: they come as two bf16 planes, x = hi + lo (rows [0, m) and [m, 2m) of the
     // activation tensor map), both multiplied with the same A tile into the same accumulator, so that only
@@ -256,16 +263,16 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *xs = smem + QmmSmem::kXs;
-    uint8_t *wp = smem + QmmSmem::wp(p.bt, XP);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + QmmSmem::bars(p.bt, WS, WPB, XP));
+    uint8_t *wp = smem + QmmSmem::wp(p.bt, XP, ST);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + QmmSmem::bars(p.bt, WS, WPB, XP, ST));
     // full[s]: activation tile landed (1 arrival + bytes) and the eight dequantize warps of the k-block
     // stored their parts of the A tile; empty[s]: the MMAs that read stage s completed (tcgen05.commit).
-    uint64_t *full = bars, *empty = bars + kStages;
-    uint64_t *wp_full = bars + 2 * kStages, *wp_empty = wp_full + WS;
+    uint64_t *full = bars, *empty = bars + ST;
+    uint64_t *wp_full = bars + 2 * ST, *wp_empty = wp_full + WS;
     uint64_t *acc_full = wp_empty + WS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
 
-    constexpr int KBW = (128 * 8 / BITS) / kBK;  // k-blocks per packed-weight stage: 4 (4-bit), 8 (2-bit)
+    constexpr int KBW = (GGUF == 2) ? 16 : (128 * 8 / BITS) / kBK;  // k-blocks per packed-weight stage: 4 (4-bit), 8 (2-bit), 16 (Q2_K)
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler too
     const int n0 = blockIdx.x * kBN;
@@ -280,7 +287,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int num_kb = p.num_kb;
 
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) {
+        for (int i = 0; i < ST; ++i) {
             mbar_init(&full[i], 1 + kWarpsPerKb);
             mbar_init(&empty[i], 1);
         }
@@ -317,7 +324,8 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (next_wi >= WS) ok = qmm_wait(&wp_empty[ws], ((next_wi / WS) - 1) & 1, 2);
                 if (!ok) return;
                 mbar_arrive_expect_tx(&wp_full[ws], WPB);
-                tma_load_2d(wp + ws * WPB, &map_w, next_wi * ROWB, wrow0, &wp_full[ws]);
+                // x coordinate in elements of the map: bytes, or 32-bit words for Q2_K
+                tma_load_2d(wp + ws * WPB, &map_w, next_wi * (GGUF == 2 ? ROWB / 4 : ROWB), wrow0, &wp_full[ws]);
                 ++next_wi;
             };
             for (int i = 0; i < WS && next_wi < num_wi; ++i) issue_w();
@@ -325,12 +333,12 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             uint32_t ph = 1;  // parity of the lap before: the first lap does not wait
             for (int kb = 0; kb < num_kb && ok; ++kb) {
                 if (kb > 0 && kb % KBW == 0 && next_wi < num_wi) issue_w();
-                if (kb >= kStages && ok) ok = qmm_wait(&empty[s], ph, 1);
+                if (kb >= ST && ok) ok = qmm_wait(&empty[s], ph, 1);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&full[s], x_bytes);
                 tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, kb * kBK, t0, &full[s]);
                 if (GGUF) tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + x_bytes / 2, &map_x, kb * kBK, p.m + t0, &full[s]);
-                if (++s == kStages) { s = 0; ph ^= 1; }
+                if (++s == ST) { s = 0; ph ^= 1; }
             }
         }
     } else if (warp == 1) {
@@ -366,7 +374,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 }
                 acc = 1;
                 __syncwarp();
-                if (++s == kStages) { s = 0; ph ^= 1; }
+                if (++s == ST) { s = 0; ph ^= 1; }
             }
             if (ok && elect_one()) umma_commit(acc_full);
         }
@@ -409,6 +417,8 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         for (int kb = kpar; kb < num_kb; kb += 2) {
             const int wi = kb / KBW, ws = wi % WS, sub = kb % KBW;
             float sc = bf16_bits_to_f32(s_next), bi = bf16_bits_to_f32(b_next);
+            float sc1 = 0.f, bi1 = 0.f;  // Q2_K: scale and bias of the second 16 elements
+            int qshift = 0;              // Q2_K: which 2-bit field of every byte
             if (!GGUF && kb + 2 < num_kb) load_sb(kb + 2, s_next, b_next);
             // first visit of this packed-weight stage
             if (sub < 2) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wi / WS) & 1, 5));
@@ -416,7 +426,27 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             // packed codes of (row, k-block, half): 32 codes
             uint32_t w[4];
             uint32_t wq[8];  // GGUF: the 32 bytes whose nibble `half` are this thread's codes
-            if (GGUF) {
+            if (GGUF == 2) {
+                const int bq = sub >> 2, kb4 = sub & 3;  // block of the stage row, k-block of the block
+                const uint32_t blk = wp32 + ws * WPB + bq * kQ2kBlock;  // 4-byte aligned only
+                const int hb = kb4 >> 1, shift = 2 * (kb4 & 1) + half;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(wq[i]) : "r"(blk + 16 + hb * 32 + 4 * i));
+                uint32_t sw, dd;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sw) : "r"(blk + hb * 8 + (shift >> 1) * 4));
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(dd) : "r"(blk + 80));
+                // scale bytes [hb*8 + shift*2 + group], group 0 / 1 = first / last 16 elements
+                const uint32_t sb0 = (sw >> (16 * (shift & 1))) & 255u, sb1 = (sw >> (16 * (shift & 1) + 8)) & 255u;
+                float d, dmin;
+                asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %2; cvt.f32.f16 %0, lo; cvt.f32.f16 %1, hi; }" : "=f"(d), "=f"(dmin) : "r"(dd));
+                sc = d * static_cast<float>(sb0 & 15u);
+                bi = -(dmin * static_cast<float>(sb0 >> 4));
+                sc1 = d * static_cast<float>(sb1 & 15u);
+                bi1 = -(dmin * static_cast<float>(sb1 >> 4));
+                qshift = shift;
+                w[0] = w[1] = w[2] = w[3] = 0;
+            } else if (GGUF == 4) {
                 const uint32_t blk = wp32 + ws * WPB;
                 uint32_t h0, h1, h2, h3;
                 asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(blk));
@@ -451,7 +481,23 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             uint32_t o[16];
             uint32_t olo[16];  // GGUF only
             const unsigned long long b2 = pack_f32x2(bi, bi);
-            if (GGUF) {
+            if (GGUF == 2) {
+                // element 4i + b is the field at bit offset 2*shift of byte b of word i: offsets 2*shift and
+                // 2*shift + 8 of each 16-bit half; mk[j] = 3 << 2j
+                const float down = __uint_as_float((127u - 2u * qshift) << 23);  // 2^(-2*shift)
+                const unsigned long long sg0 = pack_f32x2(sc * down, sc * down * 0.00390625f);
+                const unsigned long long sg1 = pack_f32x2(sc1 * down, sc1 * down * 0.00390625f);
+                const unsigned long long b21 = pack_f32x2(bi1, bi1);
+                uint32_t m0 = mk[0], m1 = mk[4];
+                if (qshift == 1) { m0 = mk[1]; m1 = mk[5]; }
+                if (qshift == 2) { m0 = mk[2]; m1 = mk[6]; }
+                if (qshift == 3) { m0 = mk[3]; m1 = mk[7]; }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    dequant_pair_split(wq[i], m0, m1, mbits, neg_magic2, i < 4 ? sg0 : sg1, i < 4 ? b2 : b21, o[2 * i + 0], olo[2 * i + 0]);
+                    dequant_pair_split(wq[i] >> 16, m0, m1, mbits, neg_magic2, i < 4 ? sg0 : sg1, i < 4 ? b2 : b21, o[2 * i + 1], olo[2 * i + 1]);
+                }
+            } else if (GGUF == 4) {
                 // element 4i + b of the sub-block is nibble `half` of byte b of word i: bit offsets 4*half and
                 // 4*half + 8 of each 16-bit half of the word
                 const unsigned long long sg = half ? pack_f32x2(sc * 0.0625f, sc * 0.000244140625f)
@@ -489,7 +535,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 }
             }
             // the MMAs that read this stage of the A ring a lap ago must have completed
-            if (kb >= kStages) {
+            if (kb >= ST) {
                 ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&empty[a], aph, 6));  // warp-uniform: tcgen05.st is warp-wide
                 if (!ok) break;
                 tc_fence_after();
@@ -506,7 +552,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (last_visit) mbar_arrive(&wp_empty[ws]);
             }
             a += 2;
-            if (a >= kStages) { a -= kStages; aph ^= 1; }
+            if (a >= ST) { a -= ST; aph ^= 1; }
         }
 
         // ---------------- epilogue: TMEM -> registers -> bf16 rows of y
@@ -636,17 +682,24 @@ __global__ void __launch_bounds__(256) f32_to_bf16_planes_kernel(const float4 *_
 }
 
 bool qmm_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes) {
-    if (format != LISA_GGUF_Q4_K) return false;
-    if (tokens < 1 || rows < 1 || row_bytes % kQ4kBlock != 0) return false;
-    return tokens * (row_bytes / kQ4kBlock) * 256 < (1ll << 40);
+    if (tokens < 1 || rows < 1) return false;
+    if (format == LISA_GGUF_Q4_K) {
+        if (row_bytes % kQ4kBlock != 0) return false;
+    } else if (format == LISA_GGUF_Q2_K) {
+        if (row_bytes % (4 * kQ2kBlock) != 0) return false;  // whole stage rows of four blocks; 16-byte row pitch
+    } else {
+        return false;
+    }
+    const int64_t k = row_bytes / (format == LISA_GGUF_Q4_K ? kQ4kBlock : kQ2kBlock) * 256;
+    return tokens * k < (1ll << 40);
 }
 
 size_t qmm_gguf_workspace_bytes(int64_t tokens, int64_t k) { return static_cast<size_t>(2 * tokens * k * 2 + 256); }
 
 int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
              int64_t tokens, float *y, void *workspace) {
-    (void)format;
-    const int64_t k = row_bytes / kQ4kBlock * 256;
+    const bool q4 = format == LISA_GGUF_Q4_K;
+    const int64_t k = row_bytes / (q4 ? kQ4kBlock : kQ2kBlock) * 256;
     uint16_t *xb = reinterpret_cast<uint16_t *>(workspace);
     const int64_t n4 = tokens * k / 4;
     f32_to_bf16_planes_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, stream>>>(
@@ -654,6 +707,8 @@ int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, in
     LISA_CUDA_TRY(cudaGetLastError());
     count_launch();
 
+    const int stages = q4 ? kStages : 3, wstages = q4 ? 3 : 2;
+    const int row_stage_bytes = q4 ? kQ4kBlock : 4 * kQ2kBlock;
     QmmParams p{};
     p.yf = y;
     p.m = static_cast<int>(tokens);
@@ -668,7 +723,7 @@ int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, in
     while (acc < bt) acc <<= 1;
     p.acc_cols = acc;
     int cols = 32;
-    while (cols < acc + kStages * 2 * kACols) cols <<= 1;  // two weight planes per A stage
+    while (cols < acc + stages * 2 * kACols) cols <<= 1;  // two weight planes per A stage
     p.tmem_cols = cols;
     p.num_kb = static_cast<int>(k / kBK);
 
@@ -677,13 +732,15 @@ int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, in
                          static_cast<uint64_t>(k) * 2, kBK, static_cast<uint32_t>(bt));
     if (rc != LISA_OK) return rc;
     {
-        const uint64_t dims[2] = {static_cast<uint64_t>(row_bytes), static_cast<uint64_t>(rows)};
+        // Q4_K: bytes, one block per box row; Q2_K: 32-bit words (a 336-byte box row is over the 256-element limit in bytes)
+        const uint64_t dims[2] = {static_cast<uint64_t>(q4 ? row_bytes : row_bytes / 4), static_cast<uint64_t>(rows)};
         const uint64_t strides[1] = {static_cast<uint64_t>(row_bytes)};
-        const uint32_t box[2] = {kQ4kBlock, kBN};
-        rc = make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        const uint32_t box[2] = {static_cast<uint32_t>(q4 ? kQ4kBlock : kQ2kBlock), kBN};
+        rc = make_tensor_map(&map_w, q4 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w, dims, strides,
+                             box, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc != LISA_OK) return rc;
     }
-    const int smem = QmmSmem::total(bt, 3, kBN * kQ4kBlock, 2);
+    const int smem = QmmSmem::total(bt, wstages, kBN * row_stage_bytes, 2, stages);
     const int64_t ytiles = (tokens + bt - 1) / bt;
     if (ytiles > 65535) return fail(LISA_ERR_LIMIT, "gguf matmul: too many row tiles");
     cudaLaunchConfig_t cfg{};
@@ -691,8 +748,13 @@ int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, in
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4, true>, map_x, map_w, p));
+    if (q4) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4, 4>, map_x, map_w, p));
+    } else {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<2, 2>, map_x, map_w, p));
+    }
     count_launch();
     return LISA_OK;
 }

@@ -164,8 +164,8 @@ def packed_matvec(fmt, weights: torch.Tensor, input: torch.Tensor, *, stream=Non
 
 def packed_matmul(fmt, weights: torch.Tensor, input: torch.Tensor, *, workspace: Optional[torch.Tensor] = None,
                   stream=None) -> torch.Tensor:
-    """``packed_matvec`` for many tokens with a workspace: Q4_K products of 32 tokens or more run on the
-    tensor cores (operands as hi + lo bf16 planes, f32 accumulate and output, ~5e-5 of the matvec);
+    """``packed_matvec`` for many tokens with a workspace: products of 32 tokens or more run on the
+    tensor cores (operands as hi + lo bf16 planes, f32 accumulate and output, ~1e-4 of the matvec);
     everything else is the exact matvec."""
     _need_cuda(weights, input)
     code = _format_code(fmt)

@@ -83,26 +83,41 @@ def test_layout_rejections(cuda):
         ops.packed_matvec("Q2K", w, x)
 
 
-@pytest.mark.parametrize("rows,k,tokens", [(128, 1024, 32), (200, 2304, 77), (1024, 7168, 512), (256, 256, 40)])
-def test_q4k_tensor_core_matmul_within_tolerance(cuda, rows, k, tokens):
-    """packed_matmul with a workspace: Q4_K, 32 tokens or more -> tcgen05 GEMM; activations and decoded
-    weights each enter as two bf16 planes (hi + lo), so the result is held to the matvec's own bar
-    (1e-4 max-relative against the f64 product of the decoded blocks), far inside the 1e-2 of the path."""
+@pytest.mark.parametrize("name,fmt", FORMATS)
+@pytest.mark.parametrize("rows,k,tokens", [(128, 1024, 32), (200, 2048, 77), (1024, 7168, 512), (256, 1024, 40)])
+def test_tensor_core_matmul_within_tolerance(cuda, name, fmt, rows, k, tokens):
+    """packed_matmul with a workspace and 32 tokens or more -> tcgen05 GEMM; activations and decoded
+    weights each enter as two bf16 planes (hi + lo, 16 significant bits): 5e-4 max-relative and 1e-4
+    relative L2 against the f64 product of the decoded blocks (observed 2e-5 .. 1.1e-4 and 5e-6 .. 2.5e-5),
+    far inside the 1e-2 of the path."""
     rng = np.random.default_rng(rows + k + tokens)
-    w = util.gguf_weights(rng, O.Q4_K, rows, k)
+    w = util.gguf_weights(rng, fmt, rows, k)
     x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
-    y = ops.packed_matmul("Q4K", dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
-    dec = O.gguf_decode(O.Q4_K, w).reshape(rows, k).astype(np.float64)
+    y = ops.packed_matmul(name, dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
+    dec = O.gguf_decode(fmt, w).reshape(rows, k).astype(np.float64)
     truth = x.astype(np.float64) @ dec.T
     err, l2 = util.parity(y, truth)
-    assert err <= 1e-4 and l2 <= 2e-5, (err, l2)
+    assert err <= 5e-4 and l2 <= 1e-4, (err, l2)
     assert ops.device_status() == 0
 
 
 @pytest.mark.parametrize("name,fmt", FORMATS)
-def test_packed_matmul_small_or_q2k_is_the_exact_matvec(cuda, name, fmt):
+def test_tensor_core_matmul_on_dyadic_inputs_is_exact(cuda, name, fmt):
+    """The reference's dyadic construction (kernel_tests.rs:178-210) through the GEMM: weights and
+    activations are exact in bf16 hi + lo planes, so the product equals the f64 dot."""
+    rows, width, tokens = 128, 1024, 48
+    blocks = O.gguf_dyadic_blocks(fmt, width * rows // 256)
+    w = blocks.reshape(rows, -1)
+    x = O.gguf_dyadic_inputs(tokens * width).reshape(tokens, width)
+    y = ops.packed_matmul(name, dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
+    dec = O.gguf_decode(fmt, blocks).reshape(rows, width).astype(np.float64)
+    assert np.array_equal(y.astype(np.float64), x.astype(np.float64) @ dec.T)
+
+
+@pytest.mark.parametrize("name,fmt", FORMATS)
+def test_packed_matmul_small_is_the_exact_matvec(cuda, name, fmt):
     rng = np.random.default_rng(3)
-    rows, k, tokens = 64, 512, 40 if fmt == O.Q2_K else 8
+    rows, k, tokens = 64, 1024, 8
     w = util.gguf_weights(rng, fmt, rows, k)
     x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
     a = ops.packed_matmul(name, dev_u8(w, cuda), dev_f32(x, cuda))

@@ -319,10 +319,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures only")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "shard", "moe"],
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "shard", "moe", "gguf"],
                     help="decode: M=1 GEMV stack, HBM GB/s (headline); prefill: M=2048 GEMM stack, bf16 TFLOP/s; "
                          "shard: configs[2] 2-bit MLP stack, N-sharded over the ranks with an all-gather; "
-                         "moe: configs[3] routed experts, expert-parallel over the ranks with all-to-all")
+                         "moe: configs[3] routed experts, expert-parallel over the ranks with all-to-all; "
+                         "gguf: configs[4] Q2_K / Q4_K matvec (M=1) and tensor-core matmul (M=512), one GPU")
     ap.add_argument("--rows", dest="m", type=int, default=1, help="rows of x for --mode shard (1, 8 or 512)")
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per rank for --mode moe (1, 64 or 4096)")
     args = ap.parse_args()
@@ -354,6 +355,9 @@ def main():
     warmup = max(args.warmup, 3)
     if args.mode in ("shard", "moe"):
         sharded_main(args, torch, dist, dev, rank, world, warmup)
+        return
+    if args.mode == "gguf":
+        gguf_main(args, torch, dev, rank, warmup)
         return
     stack = DecodeStack(dev, seed=rank, layers=args.layers)
     if args.mode == "prefill":
@@ -527,6 +531,50 @@ def prefill_main(args, torch, dist, stack, rank, local_rank, world, warmup):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def gguf_main(args, torch, dev, rank, warmup):
+    """configs[4]: GGUF Q2_K / Q4_K, K=7168 N=18432 and K=18432 N=7168, M=1 (matvec, HBM GB/s on the block
+    bytes) and M=512 (tensor-core matmul with a workspace, TFLOP/s).  Uniform random code and scale bytes,
+    d, dmin ~ |N(0, 0.01)| as f16, activations ~ N(0, 1)."""
+    if rank != 0:
+        return
+    from lisa_b200 import _cabi, ops
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    results = []
+    for fmt, block, code, d_at in (("Q4K", 144, _cabi.GGUF_Q4_K, 0), ("Q2K", 84, _cabi.GGUF_Q2_K, 80)):
+        for k, n in ((7168, 18432), (18432, 7168)):
+            nb = k // 256
+            w = torch.randint(0, 256, (n, nb, block), dtype=torch.uint8, device=dev, generator=g)
+            dd = (torch.randn((n, nb, 2), device=dev, generator=g) * 0.01).abs().to(torch.float16).view(torch.uint8)
+            w[:, :, d_at:d_at + 4] = dd.reshape(n, nb, 4)
+            w = w.reshape(n, nb * block).contiguous()
+            for m in (1, 512):
+                x = torch.randn((m, k), device=dev, generator=g)
+                ws = torch.empty(_cabi.lib().lisa_cuda_gguf_packed_matmul_workspace_bytes(m, nb * block, code),
+                                 dtype=torch.uint8, device=dev)
+                fn = (lambda: ops.packed_matmul(fmt, w, x, workspace=ws)) if m > 1 else (lambda: ops.packed_matvec(fmt, w, x))
+                for _ in range(warmup):
+                    fn()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.steps):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) / args.steps * 1e3
+                results.append({"format": fmt, "k": k, "n": n, "m": m, "us": us,
+                                "GB/s": w.numel() / us / 1e3 if m == 1 else None,
+                                "TFLOP/s": 2.0 * m * n * k / us / 1e6 if m > 1 else None})
+    best = max(r["TFLOP/s"] for r in results if r["TFLOP/s"])
+    print(json.dumps({"metric": "GGUF K-quant matmul TFLOP/s (M=512, best of the four)", "value": best, "unit": "TFLOP/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "configs[4]: GGUF Q2_K/Q4_K, K=7168 N=18432 and K=18432 N=7168, M in {1, 512}"},
+                      "results": results, "device_status": ops.device_status()}), flush=True)
 
 
 def sharded_main(args, torch, dist, dev, rank, world, warmup):

@@ -607,6 +607,12 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         xs = {hidden: torch.randn((m, hidden), device=dev, generator=g).to(torch.bfloat16),
               inter: torch.randn((m, inter), device=dev, generator=g).to(torch.bfloat16)}
 
+        # m <= 8: the GEMV whose epilogue stores into every rank's buffer + peer barrier (no NCCL on the data
+        # path); LISA_BENCH_FUSED=0 or more rows: local GEMM + NCCL all-gather
+        fused = world > 1 and m <= 8 and os.environ.get("LISA_BENCH_FUSED", "1") != "0"
+        if fused:
+            lins = [[parallel.FusedShardedLinear(lin, max_rows=m) for lin in per] for per in lins]
+
         def step():
             for per in lins:
                 for lin, (k, n) in zip(per, shapes):
@@ -619,7 +625,9 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         work_bytes = layers * sum(n * k * bits // 8 + 2 * n * (k // GROUP) * 2 + m * k * 2 + m * n * 2 for k, n in shapes)
         flops = 2.0 * m * weights
         name = f"configs[2]: 27B-class 2-bit gs64 MLP stack, {layers} layers x (gate, up, down), M={m}"
-        par = f"N-sharded over {world} ranks, NCCL all-gather of every output" if world > 1 else "single GPU"
+        par = ("single GPU" if world == 1 else
+               f"N-sharded over {world} ranks, all-gather fused into the GEMV epilogue (peer stores) + peer barrier" if fused
+               else f"N-sharded over {world} ranks, NCCL all-gather of every output")
         scaling = "strong"
     else:
         experts, top_k, hidden, inter, tokens = 128, 8, 2048, 768, args.tokens
@@ -662,9 +670,13 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         step()
     torch.cuda.synchronize()
     graphed = False
-    if world == 1 and os.environ.get("LISA_BENCH_GRAPH", "1") != "0":
-        # one GPU: no collective inside the step, so it replays from a CUDA graph like the decode stack
-        # (eager launches through the Python mirror are host-bound at small sizes)
+    fused_mode = args.mode == "shard" and world > 1 and args.m <= 8 and os.environ.get("LISA_BENCH_FUSED", "1") != "0"
+    if (world == 1 or fused_mode) and os.environ.get("LISA_BENCH_GRAPH", "1") != "0":
+        # no collective library inside the step (one GPU, or the fused GEMV + peer barrier form), so it
+        # replays from a CUDA graph like the decode stack (eager launches through the Python mirror are
+        # host-bound at small sizes)
+        if world > 1:
+            dist.barrier()
         eager = step
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()

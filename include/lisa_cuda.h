@@ -93,6 +93,27 @@ int lisa_cuda_quantized_matmul_serial_rows(lisa_stream_t stream, const void *x, 
                                            const void *biases, int64_t n, int transpose,
                                            int group_size, int bits, int dtype, void *y);
 
+/* N-sharded decode linear fused with its all-gather (one node, up to 8 GPUs, one process per GPU).
+ * No counterpart in the reference, which runs on one device: this is the multi-GPU form of
+ * ops::quantized_matmul for m <= 8 rows and group size 64.  The caller holds rows
+ * [col0, col0 + n_local) of an n_total-row linear; y_all[r] is rank r's [m, n_total] output buffer as
+ * seen from this GPU (its own buffer and peer mappings of the others', e.g. CUDA IPC or
+ * cuMemMap'd symmetric memory with peer access enabled).  The kernel's epilogue stores this rank's
+ * column block into all of them with plain stores; no collective library is involved.
+ * lisa_cuda_peer_barrier, enqueued after it on every rank, makes the blocks of all ranks visible:
+ * flag_arrays[r] is rank r's array of 16 uint64 (zero-initialised, peer-mapped like the outputs;
+ * slots 0..7 are written by the peers, slot 8 counts this rank's barriers), `epoch` a number that
+ * grows with every barrier, or 0 to use the count in slot 8 (the same launch can then be replayed
+ * from a CUDA graph).  Its wait is bounded (about a second), after which
+ * lisa_cuda_device_status() reports the failure. */
+int lisa_cuda_quantized_matmul_allgather(lisa_stream_t stream, const void *x, int64_t m, int64_t k,
+                                         const uint32_t *w, const void *scales, const void *biases,
+                                         int64_t n_local, int transpose, int group_size, int bits, int dtype,
+                                         void *const *y_all, int world, int64_t n_total, int64_t col0,
+                                         unsigned flags);
+int lisa_cuda_peer_barrier(lisa_stream_t stream, int rank, int world, void *const *flag_arrays,
+                           uint64_t epoch);
+
 /* ops::dequantize(w, scales, biases, group_size, bits), array_ops.rs:37-84 and
  * jit::affine_dequantize, crates/lisa-mlx/src/jit/matmul.rs:1316-1402.
  * out[r, c] = dtype( f32(q) * f32(scale) + f32(bias) ): the host law of

@@ -120,8 +120,9 @@ int lisa_cuda_device_status(void) {
     const int a = qmv_device_status();
     const int b = qmm_device_status();
     const int c = qmv_tc_device_status();
-    if (a < 0 || b < 0 || c < 0) return -1;
-    return a | (b << 8) | (c << 16);
+    const int d = peer_device_status();
+    if (a < 0 || b < 0 || c < 0 || d < 0) return -1;
+    return a | (b << 8) | (c << 16) | (d << 24);
 }
 
 int lisa_cuda_quantized_matmul(lisa_stream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
@@ -155,6 +156,32 @@ int lisa_cuda_quantized_matmul_serial_rows(lisa_stream_t stream, const void *x, 
                       LISA_FLAG_NONE);
     return qmv_affine(static_cast<cudaStream_t>(stream), x, rows, k, w, scales, biases, n, group_size, bits, y,
                       LISA_FLAG_NONE);
+}
+
+int lisa_cuda_quantized_matmul_allgather(lisa_stream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
+                                         const void *scales, const void *biases, int64_t n_local, int transpose,
+                                         int group_size, int bits, int dtype, void *const *y_all, int world,
+                                         int64_t n_total, int64_t col0, unsigned flags) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_allgather: only transpose=true supported");
+    if (!y_all || world < 1 || world > 8) return fail(LISA_ERR_BAD_ARG, "quantized_matmul_allgather: 1 to 8 output buffers");
+    for (int r = 0; r < world; ++r)
+        if (!y_all[r] || (reinterpret_cast<uintptr_t>(y_all[r]) & 1u)) return fail(LISA_ERR_BAD_ARG, "quantized_matmul_allgather: null or misaligned output buffer");
+    int rc = check_affine("quantized_matmul_allgather", x, m, k, w, scales, biases, n_local, group_size, bits, dtype, y_all[0]);
+    if (rc != LISA_OK) return rc;
+    if (col0 < 0 || n_total < 1 || col0 + n_local > n_total || n_total > (1ll << 30))
+        return fail(LISA_ERR_BAD_ARG, "quantized_matmul_allgather: column block outside the output");
+    if (m > 8 || !qmv_tc_supported(m, k, n_local, group_size, bits))
+        return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_allgather: needs m <= 8 and a shape the tensor-memory GEMV takes");
+    return qmv_tc_allgather(static_cast<cudaStream_t>(stream), x, m, k, w, scales, biases, n_local, group_size, bits, y_all,
+                            world, n_total, col0, flags);
+}
+
+int lisa_cuda_peer_barrier(lisa_stream_t stream, int rank, int world, void *const *flag_arrays, uint64_t epoch) {
+    if (!flag_arrays || world < 1 || world > 8 || rank < 0 || rank >= world)
+        return fail(LISA_ERR_BAD_ARG, "peer_barrier: bad rank or world");
+    for (int r = 0; r < world; ++r)
+        if (!flag_arrays[r] || (reinterpret_cast<uintptr_t>(flag_arrays[r]) & 7u)) return fail(LISA_ERR_BAD_ARG, "peer_barrier: null or misaligned flag array");
+    return peer_barrier(static_cast<cudaStream_t>(stream), rank, world, flag_arrays, epoch);
 }
 
 int lisa_cuda_dequantize(lisa_stream_t stream, const uint32_t *w, const void *scales, const void *biases,

@@ -18,6 +18,11 @@ bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits)
 int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
            const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
 int qmv_tc_device_status();
+int qmv_tc_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                     const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
+                     int64_t n_total, int64_t col0, unsigned flags);
+int peer_barrier(cudaStream_t stream, int rank, int world, void *const *flag_arrays, unsigned long long epoch);
+int peer_device_status();
 
 // qmm_affine.cu
 bool qmm_affine_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);

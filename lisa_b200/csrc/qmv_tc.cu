@@ -72,13 +72,17 @@ struct TcParams {
     const uint16_t *scales;
     const uint16_t *biases;
     const uint16_t *x;
-    uint16_t *y;
     int n, k, m;
     int groups;      // k / 64
     int num_kb;      // k / 64
     int splits;      // cluster size: k-slices per row tile
     int wstages;     // stages of the packed ring
     int max_l;       // k-blocks of the longest slice (sizes the shared-memory plan)
+    // Output: row r of this matrix is column col0 + r of every buffer in `out` (leading dimension ldy).
+    // One buffer (the caller's y, col0 = 0, ldy = n) for the plain GEMV; for the N-sharded form the
+    // buffers of all ranks, this rank's own among them: the all-gather is the epilogue's stores.
+    uint16_t *out[8];
+    int nout, ldy, col0;
 };
 
 // Shared-memory plan, bytes from the 1024-aligned base.
@@ -596,7 +600,9 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                 if (t < p.m) {
                     float tot = 0.f;
                     for (int r = 0; r < p.splits; ++r) tot += part[(r * kRows + row) * p.m + t];
-                    p.y[static_cast<size_t>(t) * p.n + n0 + row] = static_cast<uint16_t>(f32_to_bf16_bits(tot));
+                    const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(tot));
+                    const size_t at = static_cast<size_t>(t) * p.ldy + p.col0 + n0 + row;
+                    for (int o = 0; o < p.nout; ++o) p.out[o][at] = v;  // plain stores, peers' memory included
                 }
             }
         }
@@ -660,10 +666,10 @@ bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits)
     return tc_make_plan(n, k, group_size, bits, static_cast<int>(std::min<int64_t>(m, 8)), p, smem, grid, mc);
 }
 
-int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
-           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
+static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                         const void *biases, int64_t n, int group_size, int bits, void *const *outs, int nout, int64_t ldy,
+                         int64_t col0, unsigned flags) {
     const uint16_t *xp = reinterpret_cast<const uint16_t *>(x);
-    uint16_t *yp = reinterpret_cast<uint16_t *>(y);
     CUtensorMap map_w;
     {
         const uint64_t row_bytes = static_cast<uint64_t>(k) * bits / 8;
@@ -682,7 +688,10 @@ int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint3
         p.scales = reinterpret_cast<const uint16_t *>(scales);
         p.biases = reinterpret_cast<const uint16_t *>(biases);
         p.x = xp + done * k;
-        p.y = yp + done * n;
+        p.nout = nout;
+        p.ldy = static_cast<int>(ldy);
+        p.col0 = static_cast<int>(col0);
+        for (int o = 0; o < nout; ++o) p.out[o] = reinterpret_cast<uint16_t *>(outs[o]) + done * ldy;
         p.n = static_cast<int>(n);
         p.k = static_cast<int>(k);
         p.m = mc;
@@ -716,6 +725,78 @@ int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint3
         }
         count_launch();
     }
+    return LISA_OK;
+}
+
+int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
+    void *outs[1] = {y};
+    return qmv_tc_launch(stream, x, m, k, w, scales, biases, n, group_size, bits, outs, 1, n, 0, flags);
+}
+
+// N-sharded GEMV fused with its all-gather: this rank's rows [col0, col0 + n) of an n_total-row linear,
+// stored as columns of every rank's [m, n_total] output (outs[0 .. world), peer pointers included).
+int qmv_tc_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                     const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
+                     int64_t n_total, int64_t col0, unsigned flags) {
+    return qmv_tc_launch(stream, x, m, k, w, scales, biases, n, group_size, bits, outs, world, n_total, col0, flags);
+}
+
+// ---------------------------------------------------------------------------------------
+// Barrier between the GPUs of one node over peer memory, one launch per rank: every rank writes `epoch`
+// into its slot of every rank's flag array (plain system-scope stores after a system fence; the stores of
+// the kernels before it in the stream have completed by stream order), then waits until all slots of its
+// own array have reached `epoch`.  The wait is bounded: after about a second it records an error status
+// and returns, so a rank that never arrives costs an error, not a hung GPU.
+static __device__ int g_peer_status = 0;
+
+int peer_device_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_peer_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+struct PeerBarrierParams {
+    unsigned long long *slots[8];  // slots[p]: the flag array of rank p (peer pointer), this rank writes [rank]
+    const unsigned long long *mine;  // this rank's own flag array
+    int rank, world;
+    unsigned long long epoch;
+};
+
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerBarrierParams p) {
+    const int lane = threadIdx.x;
+    // epoch 0: count the barriers in slot 8 of this rank's own array (every rank runs the same sequence
+    // of barriers, so the counts agree); the launch can then be replayed from a CUDA graph
+    unsigned long long epoch = p.epoch;
+    if (epoch == 0) {
+        unsigned long long *counter = const_cast<unsigned long long *>(p.mine) + 8;
+        if (lane == 0) epoch = atomicAdd(counter, 1ull) + 1ull;
+        epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    }
+    if (lane < p.world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.slots[lane] + p.rank), "l"(epoch) : "memory");
+        bool ok = false;
+        for (int i = 0; i < 4000000 && !ok; ++i) {
+            unsigned long long v;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p.mine + lane) : "memory");
+            ok = v >= epoch;
+            if (!ok) __nanosleep(200);
+        }
+        if (!ok) atomicExch(&g_peer_status, 1 + lane);
+    }
+}
+
+int peer_barrier(cudaStream_t stream, int rank, int world, void *const *flag_arrays, unsigned long long epoch) {
+    PeerBarrierParams p{};
+    for (int i = 0; i < world; ++i) p.slots[i] = reinterpret_cast<unsigned long long *>(flag_arrays[i]);
+    p.mine = reinterpret_cast<const unsigned long long *>(flag_arrays[rank]);
+    p.rank = rank;
+    p.world = world;
+    p.epoch = epoch;
+    peer_barrier_kernel<<<1, 32, 0, stream>>>(p);
+    LISA_CUDA_TRY(cudaGetLastError());
+    count_launch();
     return LISA_OK;
 }
 

@@ -136,3 +136,131 @@ def ep_moe_forward(x: torch.Tensor, idx: torch.Tensor, weights: torch.Tensor, ex
         from . import ops
         combine = ops.moe_combine
     return combine(back, weights.reshape(t, top_k), inverse.to(torch.int32), top_k)
+
+
+# ---------------------------------------------------------------- fused GEMV + all-gather over peer memory
+def _enable_peer_access(me: int, peer: int) -> None:
+    """Makes memory of GPU `peer` addressable from kernels on GPU `me` (both directions are needed by the
+    two ranks involved; each rank enables its own).  Raises when the pair has no peer path."""
+    from cuda.bindings import runtime as rt
+
+    (err, can) = rt.cudaDeviceCanAccessPeer(me, peer)
+    if int(err) != 0 or not can:
+        raise RuntimeError(f"GPU {me} cannot access GPU {peer} as a peer")
+    torch.cuda.set_device(me)
+    (err,) = rt.cudaDeviceEnablePeerAccess(peer, 0)
+    if int(err) not in (0, int(rt.cudaError_t.cudaErrorPeerAccessAlreadyEnabled)):
+        raise RuntimeError(f"cudaDeviceEnablePeerAccess({peer}) failed: {err}")
+    rt.cudaGetLastError()  # clear the sticky "already enabled"
+
+
+class _DevicePtr:
+    """Wraps a raw device allocation for ``torch.as_tensor`` (CUDA array interface, zero copy)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"data": (ptr, False), "shape": tuple(shape), "typestr": typestr, "version": 3,
+                                         "strides": None}
+
+
+_TYPESTR = {torch.bfloat16: "<u2", torch.int64: "<i8", torch.float32: "<f4", torch.int32: "<i4"}
+
+
+class PeerBuffers:
+    """A same-shaped device buffer on every rank of one node, with every rank holding pointers to all of
+    them: its own ``cudaMalloc`` block and CUDA IPC mappings of the others', opened with this rank's GPU
+    current and peer access enabled.  `ptrs()` is the pointer table
+    `lisa_cuda_quantized_matmul_allgather` / `lisa_cuda_peer_barrier` take; `local` is a tensor view of
+    this rank's block.  Every mapping is read once through ``cudaMemcpy`` before it is handed to a
+    kernel, so that a pair without a working peer path fails here with an error code."""
+
+    def __init__(self, shape, dtype, group=None):
+        import ctypes as C
+
+        from cuda.bindings import runtime as rt
+
+        def ok(res, what):
+            err = res[0]
+            if int(err) != 0:
+                raise RuntimeError(f"{what} failed: {err}")
+            return res[1] if len(res) > 1 else None
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.cuda.current_device()
+        torch.cuda.set_device(self.device)
+        elem = torch.empty((), dtype=dtype).element_size()
+        count = 1
+        for d in shape:
+            count *= int(d)
+        self.nbytes = max(count * elem, 256)
+        self._rt = rt
+        self._ptr = int(ok(rt.cudaMalloc(self.nbytes), "cudaMalloc"))
+        ok(rt.cudaMemset(self._ptr, 0, self.nbytes), "cudaMemset")
+        ok(rt.cudaDeviceSynchronize(), "cudaDeviceSynchronize")
+        handle = ok(rt.cudaIpcGetMemHandle(self._ptr), "cudaIpcGetMemHandle")
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, (bytes(handle.reserved), self.device), group=group)
+        self._peer_ptrs = []
+        scratch = ok(rt.cudaMalloc(256), "cudaMalloc")
+        for r, (raw, dev_r) in enumerate(gathered):
+            if r == self.rank:
+                self._peer_ptrs.append(self._ptr)
+                continue
+            if dev_r != self.device:
+                _enable_peer_access(self.device, dev_r)
+            h = rt.cudaIpcMemHandle_t()
+            h.reserved = raw
+            ptr = int(ok(rt.cudaIpcOpenMemHandle(h, rt.cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle"))
+            ok(rt.cudaMemcpy(scratch, ptr, min(self.nbytes, 256), rt.cudaMemcpyKind.cudaMemcpyDefault), "read of the peer mapping")
+            self._peer_ptrs.append(ptr)
+        ok(rt.cudaFree(scratch), "cudaFree")
+        self.local = torch.as_tensor(_DevicePtr(self._ptr, shape, _TYPESTR[dtype]), device=torch.device("cuda", self.device))
+        if dtype == torch.bfloat16:
+            self.local = self.local.view(torch.bfloat16)
+        self._table = (C.c_void_p * self.world)(*self._peer_ptrs)
+        dist.barrier(group=group)
+
+    def ptrs(self):
+        return self._table
+
+    def close(self):
+        """Unmaps the peers' blocks and frees this rank's (after a barrier: nobody may still write to it)."""
+        if self._ptr is None:
+            return
+        dist.barrier(group=self.group)
+        for r, ptr in enumerate(self._peer_ptrs):
+            if r != self.rank:
+                self._rt.cudaIpcCloseMemHandle(ptr)
+        dist.barrier(group=self.group)
+        self.local = None
+        self._rt.cudaFree(self._ptr)
+        self._ptr = None
+
+
+class FusedShardedLinear:
+    """`ShardedQuantizedLinear` for m <= 8 without a collective library: the GEMV's epilogue stores this
+    rank's column block into every rank's output buffer, and `lisa_cuda_peer_barrier` orders the ranks."""
+
+    def __init__(self, shard: ShardedQuantizedLinear, max_rows: int = 8, group=None):
+        self.shard = shard
+        self.out = PeerBuffers((max_rows, shard.n_total), torch.bfloat16, group)
+        self.flags = PeerBuffers((16,), torch.int64, group)
+
+    def close(self):
+        self.out.close()
+        self.flags.close()
+
+    def forward(self, x: torch.Tensor, stream=None) -> torch.Tensor:
+        from . import _cabi
+
+        sh = self.shard
+        m, k = x.shape
+        st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        lib = _cabi.lib()
+        _cabi.check(lib.lisa_cuda_quantized_matmul_allgather(
+            st, x.data_ptr(), m, k, sh.weight.data_ptr(), sh.scales.data_ptr(), sh.biases.data_ptr(), sh.n1 - sh.n0, 1,
+            sh.group_size, sh.bits, _cabi.BF16, self.out.ptrs(), self.out.world, sh.n_total, sh.n0, _cabi.FLAG_PDL))
+        # epoch 0: the barrier counts itself on the device, so the pair of launches replays from a CUDA graph
+        _cabi.check(lib.lisa_cuda_peer_barrier(st, self.out.rank, self.out.world, self.flags.ptrs(), 0))
+        return self.out.local[:m]

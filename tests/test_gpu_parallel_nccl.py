@@ -47,6 +47,17 @@ def _worker(rank, world, port, out):
         # the shard's kernel plan (tile height, k segments) may differ from the full matrix's, so the
         # f32 summation order may too: a bf16 ulp, not equality
         ok[f"linear_m{m}"] = bool((y.float() - full.float()).abs().max() <= 1e-2 * full.float().abs().max())
+    # ---- the same linear without NCCL: GEMV epilogue stores into every rank's buffer + peer barrier
+    fused = parallel.FusedShardedLinear(lin)
+    for m in (1, 8):
+        x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
+        full = ops.quantized_matmul(x, w, s, b, True, 64, bits)
+        for rep in range(3):  # the buffers are reused: the barrier epochs must keep the ranks in step
+            y = fused.forward(x)
+            torch.cuda.synchronize()
+            ok[f"fused_m{m}_{rep}"] = bool((y.float() - full.float()).abs().max() <= 1e-2 * full.float().abs().max())
+            dist.barrier()  # nobody overwrites a buffer another rank is still comparing
+    ok["device_status"] = ops.device_status() == 0
     # ---- expert-parallel routed experts (config 4 geometry with 16 experts), tokens data-parallel
     experts, hidden, inter, top_k, tokens = 16, 2048, 768, 8, 64
     gate, up, down = (_affine(g, dev, (experts,), inter, hidden, 4), _affine(g, dev, (experts,), inter, hidden, 4),

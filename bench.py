@@ -428,7 +428,7 @@ def main():
         line = {
             "metric": "4-bit qmv HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world),
+            "vs_baseline": None, "dtype": "u8*s8->s32, f32 epilogue", "data": "synthetic", "config": workload_config(world),
             "pct_of_8TBps": 100.0 * per_gpu / 8000.0,
             "tokens_per_s": world * args.steps / (total_ms * 1e-3),
             "ms_per_step_median": statistics.median(step_ms),

@@ -90,6 +90,33 @@ def test_gguf_rejections(lib):
     assert g(None, 12, 16, 4, 8, 144, 16, 2, 1, 16, 33, 16) == _cabi.ERR_BAD_ARG  # top_k > 32
 
 
+def test_allgather_and_peer_barrier_rejections(lib):
+    import ctypes as C
+
+    ag, pb = lib.lisa_cuda_quantized_matmul_allgather, lib.lisa_cuda_peer_barrier
+    table = (C.c_void_p * 8)(*([0x1000] * 8))  # never dereferenced: every call below is refused on the host
+    def call(world=2, n_local=128, n_total=256, col0=0, m=1, gs=64, tr=1, tbl=table):
+        return ag(None, 0x1000, m, 256, 0x1000, 0x1000, 0x1000, n_local, tr, gs, 4, _cabi.BF16, tbl, world, n_total, col0, 0)
+    assert call(world=0) == _cabi.ERR_BAD_ARG and call(world=9) == _cabi.ERR_BAD_ARG
+    assert call(tbl=None) == _cabi.ERR_BAD_ARG
+    assert call(tr=0) == _cabi.ERR_UNSUPPORTED
+    assert call(col0=200) == _cabi.ERR_BAD_ARG          # block past the end of the output
+    assert call(m=9) == _cabi.ERR_UNSUPPORTED            # more rows than the GEMV takes
+    assert call(gs=128) == _cabi.ERR_UNSUPPORTED         # the tensor-memory GEMV is group size 64
+    assert pb(None, 2, 2, table, 1) == _cabi.ERR_BAD_ARG  # rank outside the world
+    assert pb(None, 0, 0, table, 1) == _cabi.ERR_BAD_ARG
+    assert pb(None, 0, 2, None, 1) == _cabi.ERR_BAD_ARG
+
+
+def test_gguf_matmul_workspace_and_rejections(lib):
+    ws = lib.lisa_cuda_gguf_packed_matmul_workspace_bytes
+    assert ws(512, 28 * 144, _cabi.GGUF_Q4_K) >= 2 * 512 * 7168 * 2
+    assert ws(0, 144, _cabi.GGUF_Q4_K) == 0
+    f = lib.lisa_cuda_gguf_packed_matmul
+    assert f(None, 12, 16, 12, 144, 16, 64, 16, None, 0) == _cabi.ERR_BAD_ARG      # rows % 8
+    assert f(None, 11, 16, 16, 144, 16, 64, 16, None, 0) == _cabi.ERR_UNSUPPORTED  # Q3_K is not on the path
+
+
 def test_product_package_never_imports_the_oracle():
     pkg = os.path.join(ROOT, "lisa_b200")
     for dirpath, _, files in os.walk(pkg):

@@ -245,6 +245,9 @@ int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t
     if ((reinterpret_cast<uintptr_t>(w) & 1u) != 0) return fail(LISA_ERR_MISALIGNED, "packed_matvec: weights must be 2-byte aligned");
     if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 3u) != 0)
         return fail(LISA_ERR_MISALIGNED, "packed_matvec: x must be 16-byte and y 4-byte aligned");
+    // one or two tokens of a Q4_K matrix: the tensor-memory kernel (exact on dyadic inputs like the warp-per-row one)
+    if (aligned16(w) && row_bytes % 16 == 0 && qmv_tc_gguf_supported(format, tokens, rows, row_bytes))
+        return qmv_tc_gguf(static_cast<cudaStream_t>(stream), format, w, rows, row_bytes, x, tokens, y);
     return gguf_matvec(static_cast<cudaStream_t>(stream), format, w, 1, rows, row_bytes, x, tokens, 1, nullptr, 1, y);
 }
 

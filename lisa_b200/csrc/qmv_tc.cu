@@ -83,17 +83,23 @@ struct TcParams {
     // buffers of all ranks, this rank's own among them: the all-gather is the epilogue's stores.
     uint16_t *out[8];
     int nout, ldy, col0;
+    int wbytes;      // bytes of a packed stage: 128 rows x 128 (affine) or x 144 (Q4_K blocks)
+    // GGUF form (f32 in, f32 out; the packed rows are Q4_K blocks, row pitch row_bytes)
+    const float *xf;
+    float *yf;
+    const uint8_t *wg;
+    long long row_bytes;
 };
 
 // Shared-memory plan, bytes from the 1024-aligned base.
 struct TcPlan {
     int ring, xb, zero, xsum, sc, part, bars, total;
 };
-__host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, int m) {
+__host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, int m, int wbytes = kWBytes) {
     TcPlan p;
     int off = 0;
     p.ring = off;
-    off += wstages * kWBytes;
+    off += wstages * wbytes;
     p.xb = off;                       // one B tile per pair of k-blocks (swizzled)
     off += ((max_l + 1) / 2) * kXTile;
     p.zero = off;                     // (unused)
@@ -201,15 +207,27 @@ __device__ __forceinline__ bool tc_wait_relaxed(uint64_t *bar, uint32_t parity, 
 // K order of the unpacked bytes.  4-bit: word j of a k-block (8 codes) becomes the words
 // (c0, c2, c4, c6) and (c1, c3, c5, c7).  2-bit: word j (16 codes) becomes four words, word i holding
 // (c_i, c_{4+i}, c_{8+i}, c_{12+i}).  The activation bytes are stored in the same order.
-template <int BITS>
+//
+// GG = 4 (with BITS = 4): GGUF Q4_K matvec, f32 activations and output, one or two tokens
+// (replaces lisa_gguf_q4_K_mv, crates/lisa-mlx/src/shaders/deepseek41/iq.metal:1239-1363; block layout
+// crates/lisa-gguf/src/quant.rs:82-101).  A packed stage row is one 144-byte block = 4 k-blocks; the low
+// nibbles of code bytes 32j .. 32j+31 are sub-block 2j, the high nibbles sub-block 2j+1, so the unpacked
+// bytes are already in K order.  Each 32-element sub-block has its own scale and min: the two K=32 MMAs
+// of a k-block accumulate into ONE D whose columns 0..7 see only sub-block 0 and columns 8..15 only
+// sub-block 1, because the B tile is block diagonal (rows 0..7 hold activation bytes for k 0..31 and
+// zeros for k 32..63, rows 8..15 the reverse).  An activation is three signed bytes,
+// x_int = rn(x * 2^(21-E)) = 65536 p0 + 256 p1 + p2 (22 bits; exact on the reference's dyadic inputs),
+// row 3t + q of a half holding piece q of token t.
+template <int BITS, int GG = 0>
 __global__ void __launch_bounds__(kThreads, 2)
 qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
+    constexpr int ROWB = GG ? 144 : 128;  // bytes of a packed stage row
     constexpr int CPW = 32 / BITS;             // codes per word
     constexpr int KBW = (128 * 8 / BITS) / 64;  // k-blocks per packed stage: 4 / 8
     constexpr int KB_BYTES = 64 * BITS / 8;    // packed bytes of one row of a k-block: 32 / 16
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const TcPlan plan = tc_plan(p.wstages, p.max_l, p.splits, p.m);
+    const TcPlan plan = tc_plan(p.wstages, p.max_l, p.splits, p.m, p.wbytes);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + plan.bars);
     uint64_t *wp_full = bars;                      // [kMaxWStages]
     uint64_t *wp_empty = wp_full + kMaxWStages;    // [kMaxWStages], 8 unpack warps
@@ -274,8 +292,8 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             uint32_t ph = 1;
             for (int wi = ws0; wi < ws1; ++wi) {
                 if (wi - ws0 >= p.wstages && !tc_wait_relaxed(&wp_empty[s], ph, 1)) break;
-                mbar_arrive_expect_tx(&wp_full[s], kWBytes);
-                tma_load_2d(ring32 + s * kWBytes, &map_w, wi * 128, n0, &wp_full[s]);
+                mbar_arrive_expect_tx(&wp_full[s], kRows * ROWB);
+                tma_load_2d(ring32 + s * (kRows * ROWB), &map_w, wi * ROWB, n0, &wp_full[s]);
                 if (++s == p.wstages) { s = 0; ph ^= 1; }
             }
         }
@@ -327,7 +345,7 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         const int swz = row & 7;
         uint32_t kmask;
         asm volatile("mov.u32 %0, %1;" : "=r"(kmask) : "r"(BITS == 4 ? 0x0f0f0f0fu : 0x03030303u));
-        const uint32_t row32 = ring32 + row * 128;
+        const uint32_t row32 = ring32 + row * ROWB;
         const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
         // The TMEM stores of one pair complete while the next one is loaded and unpacked: their
@@ -357,14 +375,25 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             if (!ok) break;
             uint32_t o[32];
             {
-                const uint32_t base = row32 + s * kWBytes;
+                const uint32_t base = row32 + s * (kRows * ROWB);
                 uint32_t w[8 * kChunksPerKb];  // 16 (4-bit) / 8 (2-bit) words of the pair
 #pragma unroll
                 for (int c = 0; c < 2 * kChunksPerKb; ++c)
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                                  : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3])
-                                 : "r"(base + (((sub * kChunksPerKb + c) ^ swz) << 4)));
-                if (BITS == 4) {
+                                 : "r"(GG ? base + 16 + (sub * kChunksPerKb + c) * 16  // Q4_K: code bytes follow the 16-byte header, no swizzle
+                                          : base + (((sub * kChunksPerKb + c) ^ swz) << 4)));
+                if (GG == 4) {
+                    // k-block h of the pair = code bytes 32h .. 32h+31 = words 8h .. 8h+7: low nibbles are its
+                    // first 32 elements, high nibbles its last 32
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            o[16 * h + i] = w[8 * h + i] & kmask;
+                            o[16 * h + 8 + i] = (w[8 * h + i] >> 4) & kmask;
+                        }
+                } else if (BITS == 4) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         o[2 * j + 0] = w[j] & kmask;         // codes 0, 2, 4, 6 of the word, one per byte
@@ -400,7 +429,13 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         const int et = tid - (2 + kUnpackWarps) * 32;  // 0..127
         const int grow = min(n0 + row, p.n - 1);
         // scales and biases of (row, group) of the slice: weights, no dependency on the previous kernel
-        {
+        if (GG) {
+            // the 16-byte headers {d, dmin, 6-bit scales and mins} of this row's blocks: [block][row] uint4 in `sc`
+            const uint8_t *wr = p.wg + static_cast<size_t>(grow) * p.row_bytes + static_cast<size_t>(kb0 / 4) * 144;
+            uint4 *hdr = reinterpret_cast<uint4 *>(sc);
+#pragma unroll 4
+            for (int bq = 0; bq < (L + 3) / 4; ++bq) hdr[bq * kRows + row] = __ldg(reinterpret_cast<const uint4 *>(wr + bq * 144));
+        } else {
             const uint16_t *sr = p.scales + static_cast<size_t>(grow) * p.groups + kb0;
             const uint16_t *br = p.biases + static_cast<size_t>(grow) * p.groups + kb0;
             if ((p.groups & 3) == 0 && (kb0 & 3) == 0) {
@@ -432,7 +467,7 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         }
         asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
         pdl_wait();  // activations come from the previous kernel
-        {
+        if (!GG) {
             // one item = one word's worth of codes (CPW activations) of one token: loaded, turned into
             // integer byte pairs in the K order of the unpacked words, stored swizzled; the items of a
             // (token, k-block) are adjacent lanes and share the group's exponent and sum through
@@ -522,6 +557,73 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                 if (base + kStep < items) store_item(base + kStep + et, vb);
             }
         }
+        if (GG) {
+            // one item = 8 consecutive f32 activations of one token; the four items of a 32-element
+            // sub-block are adjacent lanes and share its exponent and sum through shuffles
+            const int items = p.m * L * 8;
+            const int per_token = L * 8;
+            constexpr int kStep = kEpilogueWarps * 32;
+            for (int base = 0; base < items; base += kStep) {
+                const int item = base + et;
+                const bool in = item < items;
+                const int t = in ? item / per_token : 0, u = in ? item - t * per_token : 0;
+                const int kbl = u >> 3, j = u & 7;  // k-block, 8-element run of it
+                float xv[8];
+                if (in) {
+                    const float4 *src = reinterpret_cast<const float4 *>(p.xf + static_cast<size_t>(t) * p.k + (kb0 + kbl) * 64 + j * 8);
+                    const float4 v0 = __ldg(src), v1 = __ldg(src + 1);
+                    xv[0] = v0.x; xv[1] = v0.y; xv[2] = v0.z; xv[3] = v0.w;
+                    xv[4] = v1.x; xv[5] = v1.y; xv[6] = v1.z; xv[7] = v1.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) xv[i] = 0.f;
+                }
+                float sum = 0.f;
+                uint32_t amax = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    sum += xv[i];
+                    amax = max(amax, __float_as_uint(xv[i]) & 0x7fffffffu);
+                }
+#pragma unroll
+                for (int off = 1; off < 4; off <<= 1) {
+                    sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                    amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                }
+                // E: biased exponent of the sub-block's largest magnitude; below 2^-105 the sub-block counts
+                // as zero, an infinity or NaN makes its factor NaN
+                const uint32_t e = amax >> 23;
+                const bool live = e >= 22u && e < 255u;
+                const float up = __uint_as_float((275u - e) << 23);  // 2^(21 - (E - 127))
+                uint32_t pc[3][2] = {{0, 0}, {0, 0}, {0, 0}};        // piece q, bytes of the 8 elements
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int xi = live ? __float2int_rn(xv[i] * up) : 0;  // |xi| < 2^22
+                    const int r1 = (xi + 128) >> 8, p2 = xi - (r1 << 8);   // xi = 256 r1 + p2
+                    const int p0 = (r1 + 128) >> 8, p1 = r1 - (p0 << 8);   // r1 = 256 p0 + p1
+                    pc[0][i >> 2] |= (static_cast<uint32_t>(p0) & 0xffu) << (8 * (i & 3));
+                    pc[1][i >> 2] |= (static_cast<uint32_t>(p1) & 0xffu) << (8 * (i & 3));
+                    pc[2][i >> 2] |= (static_cast<uint32_t>(p2) & 0xffu) << (8 * (i & 3));
+                }
+                if (in) {
+                    const int h = j >> 2;                       // sub-block of the k-block
+                    const int par = kbl & 1;                    // k-block of the pair (64-byte half of a B row)
+                    const int chunk = par * 4 + 2 * h + ((j & 3) >> 1), off8 = (j & 1) * 8;
+                    const uint32_t tile = xb32 + (kbl >> 1) * kXTile + h * 1024;  // rows 8h .. 8h+7
+#pragma unroll
+                    for (int q = 0; q < 3; ++q) {
+                        const int r = 3 * t + q;                // row within the 8-row group
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(tile + r * 128 + ((chunk ^ r) << 4) + off8),
+                                     "r"(pc[q][0]), "r"(pc[q][1]) : "memory");
+                    }
+                    if ((j & 3) == 0) {
+                        xsum[kbl * 8 + h * 4 + t] = sum;
+                        xscale[kbl * 8 + h * 4 + t] = live ? __uint_as_float((e - 21u) << 23)  // 2^(E - 127 - 21)
+                                                             : (e == 255u ? __uint_as_float(0x7fc00000u) : 0.f);
+                    }
+                }
+            }
+        }
         fence_proxy_async_smem();  // the MMA reads the tiles through the async proxy
         asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
         if (lane == 0) mbar_arrive(x_ready);
@@ -568,7 +670,59 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                 if (++st == kNP) { st = 0; ph ^= 1; }
             }
         };
-        if (p.m == 1) run(IntC<1>{});
+        // Q4_K: columns 3t + q of each half of a D are the pieces of token t against one sub-block; its scale
+        // d * sc_g and min dmin * m_g come from the staged block header (quant.rs:88-96)
+        auto run_gguf = [&](auto mt) {
+            constexpr int MT = decltype(mt)::value;  // columns read per half: 4 (one token) or 8 (two)
+            const uint4 *hdr = reinterpret_cast<const uint4 *>(sc);
+            int st = 0;
+            uint32_t ph = 0;
+            for (int pr = 0; pr < P; ++pr) {
+                const bool two = 2 * pr + 1 < L;
+                ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[st], ph, 7));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t c[2][2][MT];  // [k-block of the pair][sub-block][piece columns]
+                const uint32_t dp = d_lane + st * 2 * kDCols;
+                tmem_ld<MT>(dp, c[0][0]);
+                tmem_ld<MT>(dp + 8, c[0][1]);
+                tmem_ld<MT>(dp + kDCols, c[1][0]);
+                tmem_ld<MT>(dp + kDCols + 8, c[1][1]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&d_empty[st]);
+                const uint4 hd = hdr[((2 * pr) >> 2) * kRows + row];  // both k-blocks of a pair sit in one block
+                float d, dmin;
+                asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %2; cvt.f32.f16 %0, lo; cvt.f32.f16 %1, hi; }" : "=f"(d), "=f"(dmin) : "r"(hd.x));
+#pragma unroll
+                for (int hk = 0; hk < 2; ++hk) {
+                    if (hk == 1 && !two) break;
+                    const int kk = 2 * pr + hk;
+#pragma unroll
+                    for (int hs = 0; hs < 2; ++hs) {
+                        const int g = 2 * (kk & 3) + hs, sh = 8 * (g & 3);
+                        const uint32_t b0 = (hd.y >> sh) & 255u, b1 = (hd.z >> sh) & 255u, b2 = (hd.w >> sh) & 255u;
+                        const uint32_t sq = (g < 4) ? (b0 & 63u) : ((b2 & 15u) | ((b0 >> 6) << 4));
+                        const uint32_t mq = (g < 4) ? (b1 & 63u) : ((b2 >> 4) | ((b1 >> 6) << 4));
+                        const float ds = d * static_cast<float>(sq), dm = dmin * static_cast<float>(mq);
+#pragma unroll
+                        for (int t = 0; t < MT / 4; ++t) {  // MT = 4: one token, MT = 8: two
+                            // sum(q * x_int) = 65536 c0 + 256 c1 + c2
+                            const float val = static_cast<float>(static_cast<int>(c[hk][hs][3 * t])) * 65536.f +
+                                              static_cast<float>(static_cast<int>(c[hk][hs][3 * t + 1]) * 256 +
+                                                                 static_cast<int>(c[hk][hs][3 * t + 2]));
+                            rs[t] += ds * (val * xscale[kk * 8 + hs * 4 + t]) - dm * xsum[kk * 8 + hs * 4 + t];
+                        }
+                    }
+                }
+                if (++st == kNP) { st = 0; ph ^= 1; }
+            }
+        };
+        if (GG) {
+            if (p.m == 1) run_gguf(IntC<4>{});
+            else run_gguf(IntC<8>{});
+        } else if (p.m == 1) run(IntC<1>{});
         else if (p.m == 2) run(IntC<2>{});
         else if (p.m <= 4) run(IntC<4>{});
         else run(IntC<8>{});
@@ -600,9 +754,13 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                 if (t < p.m) {
                     float tot = 0.f;
                     for (int r = 0; r < p.splits; ++r) tot += part[(r * kRows + row) * p.m + t];
-                    const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(tot));
                     const size_t at = static_cast<size_t>(t) * p.ldy + p.col0 + n0 + row;
-                    for (int o = 0; o < p.nout; ++o) p.out[o][at] = v;  // plain stores, peers' memory included
+                    if (GG) {
+                        p.yf[at] = tot;
+                    } else {
+                        const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(tot));
+                        for (int o = 0; o < p.nout; ++o) p.out[o][at] = v;  // plain stores, peers' memory included
+                    }
                 }
             }
         }
@@ -617,7 +775,8 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
 
 // Shapes the kernel takes: group size 64, packed rows addressable by a tensor map, and a k-slice whose
 // staging fits half an SM's shared memory.  `m` rows are wanted; `mc` (<= 8) is how many one launch takes.
-static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, TcParams &p, int &smem, int &grid, int &mc) {
+static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, TcParams &p, int &smem, int &grid, int &mc,
+                         int wbytes = kWBytes) {
     if (bits != 2 && bits != 4) return false;
     if (group_size != 64 || k % 64 != 0 || m < 1) return false;
     if ((k * bits / 8) % 16 != 0 || (k * 2) % 16 != 0) return false;
@@ -638,17 +797,18 @@ static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, 
         const int max_ws = (total_ws + splits - 1) / splits;
         const int max_l = std::min(max_ws * kbw, num_kb);
         const int ws_min = std::min(2, max_ws);
-        if (tc_plan(ws_min, max_l, splits, 1).total > budget) continue;
+        if (tc_plan(ws_min, max_l, splits, 1, wbytes).total > budget) continue;
         mc = std::min(m, 8);
-        while (mc > 1 && tc_plan(ws_min, max_l, splits, mc).total > budget) mc = (mc + 1) / 2;
+        while (mc > 1 && tc_plan(ws_min, max_l, splits, mc, wbytes).total > budget) mc = (mc + 1) / 2;
         for (int ws = std::min(kMaxWStages, max_ws); ws >= ws_min; --ws) {
-            const TcPlan plan = tc_plan(ws, max_l, splits, mc);
+            const TcPlan plan = tc_plan(ws, max_l, splits, mc, wbytes);
             if (plan.total <= budget) {
                 p.splits = splits;
                 p.wstages = ws;
                 p.max_l = max_l;
                 p.num_kb = num_kb;
                 p.groups = num_kb;
+                p.wbytes = wbytes;
                 smem = plan.total;
                 grid = static_cast<int>(tiles * splits);
                 return true;
@@ -740,6 +900,64 @@ int qmv_tc_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, c
                      const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
                      int64_t n_total, int64_t col0, unsigned flags) {
     return qmv_tc_launch(stream, x, m, k, w, scales, biases, n, group_size, bits, outs, world, n_total, col0, flags);
+}
+
+// GGUF Q4_K matvec for one or two tokens through the same kernel (f32 in, f32 out).
+bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes) {
+    if (format != LISA_GGUF_Q4_K || tokens < 1 || tokens > 2 || rows < 1 || rows > (1 << 24)) return false;
+    if (row_bytes % 144 != 0) return false;
+    TcParams p{};
+    int smem = 0, grid = 0, mc = 0;
+    if (!tc_make_plan(rows, row_bytes / 144 * 256, 64, 4, static_cast<int>(tokens), p, smem, grid, mc, kRows * 144)) return false;
+    return mc == tokens;
+}
+
+int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
+                int64_t tokens, float *y) {
+    (void)format;
+    const int64_t k = row_bytes / 144 * 256;
+    TcParams p{};
+    int smem = 0, grid = 0, mc = 0;
+    if (!tc_make_plan(rows, k, 64, 4, static_cast<int>(tokens), p, smem, grid, mc, kRows * 144) || mc != tokens)
+        return fail(LISA_ERR_UNSUPPORTED, "gguf matvec: shape not supported by the tensor-memory kernel");
+    CUtensorMap map_w;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(row_bytes), static_cast<uint64_t>(rows)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(row_bytes)};
+        const uint32_t box[2] = {144, kRows};
+        const int rc = make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != LISA_OK) return rc;
+    }
+    p.xf = x;
+    p.yf = y;
+    p.wg = w;
+    p.row_bytes = row_bytes;
+    p.n = static_cast<int>(rows);
+    p.k = static_cast<int>(k);
+    p.m = mc;
+    p.nout = 0;
+    p.ldy = static_cast<int>(rows);
+    p.col0 = 0;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (p.splits > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = p.splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4, 4>, map_w, p));
+    count_launch();
+    return LISA_OK;
 }
 
 // ---------------------------------------------------------------------------------------

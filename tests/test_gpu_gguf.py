@@ -73,7 +73,12 @@ def test_full_size_row_slices_config5(cuda, name, fmt):
     ref = O.gguf_matvec(fmt, np.ascontiguousarray(w[pick]), x)
     assert util.parity(y[:, pick], ref)[0] <= 1e-4
     sub = ops.packed_matvec(name, dev_u8(np.ascontiguousarray(w[1024:1024 + 64]), cuda), tx).cpu().numpy()
-    assert np.array_equal(sub, y[:, 1024:1024 + 64])
+    if fmt == O.Q2_K:
+        assert np.array_equal(sub, y[:, 1024:1024 + 64])  # warp-per-row kernel: the same sum, bit for bit
+    else:
+        # Q4_K at one token takes the tensor-memory kernel, whose number of k-slices follows the row count
+        # (64 rows: 8 slices, 18432 rows: 1): the same products in another f32 summation order
+        assert util.parity(sub, y[:, 1024:1024 + 64])[0] <= 1e-5
 
 
 def test_layout_rejections(cuda):
@@ -123,3 +128,31 @@ def test_packed_matmul_small_is_the_exact_matvec(cuda, name, fmt):
     a = ops.packed_matmul(name, dev_u8(w, cuda), dev_f32(x, cuda))
     b = ops.packed_matvec(name, dev_u8(w, cuda), dev_f32(x, cuda))
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("tokens", [1, 2])
+@pytest.mark.parametrize("rows,width", [(16, 256), (128, 1280), (200, 5120), (1024, 8192)])
+def test_q4k_one_or_two_tokens_tensor_memory_kernel_is_exact_on_dyadic_inputs(cuda, tokens, rows, width):
+    """One or two tokens of a Q4_K matrix take the tensor-memory kernel (activations as three signed
+    bytes, tcgen05.mma.kind::i8): the reference's dyadic construction must still come out exactly."""
+    blocks = O.gguf_dyadic_blocks(O.Q4_K, width * rows // 256)
+    w = blocks.reshape(rows, -1)
+    x = O.gguf_dyadic_inputs(tokens * width).reshape(tokens, width)
+    y = ops.packed_matvec("Q4K", dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
+    assert np.array_equal(y, O.gguf_matvec(O.Q4_K, w, x))
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("rows,k,tokens", [(18432, 7168, 1), (7168, 18432, 2), (136, 2048, 1)])
+def test_q4k_one_or_two_tokens_random_blocks(cuda, rows, k, tokens):
+    """BASELINE config 5 shapes at M=1 (and 2) through the tensor-memory kernel: the matvec bar."""
+    rng = np.random.default_rng(rows + k + tokens)
+    w = util.gguf_weights(rng, O.Q4_K, rows, k)
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    x[0, 5] = 300.0   # an outlier: the exponent is per 32-element sub-block
+    x[0, 40:72] = 0.0  # and an all-zero sub-block
+    y = ops.packed_matvec("Q4K", dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
+    dec = O.gguf_decode(O.Q4_K, w).reshape(rows, k).astype(np.float64)
+    truth = x.astype(np.float64) @ dec.T
+    err, l2 = util.parity(y, truth)
+    assert err <= 1e-4 and l2 <= 1e-5, (err, l2)

@@ -41,6 +41,8 @@ GROUP, BITS = 64, 4
 LINEARS = [("q", HIDDEN, Q_OUT, "h"), ("k", HIDDEN, KV_OUT, "h"), ("v", HIDDEN, KV_OUT, "h"),
            ("o", Q_OUT, HIDDEN, "a"), ("gate", HIDDEN, INTER, "h"), ("up", HIDDEN, INTER, "h"),
            ("down", INTER, HIDDEN, "i")]
+# linears of a layer that read the same activations: one launch each group in the sibling form
+SIBLINGS = [(0, 1, 2), (3,), (4, 5), (6,)]
 
 
 def linear_bytes(k: int, n: int, m: int = 1) -> int:
@@ -233,12 +235,31 @@ class DecodeStack:
         if os.environ.get("LISA_BENCH_TC", "1") == "0":  # the mma.sync kernel instead of the tensor-memory one
             self.flags |= _cabi.FLAG_FORCE_QMV
         self.graph = None
+        self.siblings = os.environ.get("LISA_BENCH_SIBLINGS", "0") == "1"
+        self.calls = []  # sibling form: one argument pack per launch
+        import ctypes as C
+        for per in self.weights:
+            for group in SIBLINGS:
+                c = len(group)
+                wp, sp, bp, yp, ns = (C.c_void_p * c)(), (C.c_void_p * c)(), (C.c_void_p * c)(), (C.c_void_p * c)(), (C.c_int64 * c)()
+                for j, i in enumerate(group):
+                    w, s, b, y, k, n, src = per[i]
+                    wp[j], sp[j], bp[j], yp[j], ns[j] = w.data_ptr(), s.data_ptr(), b.data_ptr(), y.data_ptr(), n
+                self.calls.append((self.inputs[src].data_ptr(), k, c, wp, sp, bp, ns, yp))
+
+    def launches_per_token(self) -> int:
+        return len(self.calls) if self.siblings else self.layers * len(LINEARS)
 
     def token(self):
         from lisa_b200 import _cabi
 
         lib = _cabi.lib()
         stream = self.torch.cuda.current_stream().cuda_stream
+        if self.siblings:
+            for x, k, c, wp, sp, bp, ns, yp in self.calls:
+                _cabi.check(lib.lisa_cuda_quantized_matmul_siblings(stream, x, 1, k, c, wp, sp, bp, ns, 1, GROUP, BITS, 0, yp,
+                                                                    self.flags))
+            return
         for per in self.weights:
             for w, s, b, y, k, n, src in per:
                 rc = lib.lisa_cuda_quantized_matmul_ex(stream, self.inputs[src].data_ptr(), 1, k, w.data_ptr(),

@@ -93,6 +93,20 @@ int lisa_cuda_quantized_matmul_serial_rows(lisa_stream_t stream, const void *x, 
                                            const void *biases, int64_t n, int transpose,
                                            int group_size, int bits, int dtype, void *y);
 
+/* Sibling linears: `count` (1..3) quantized linears with the same k, group size, bit width and dtype
+ * applied to the SAME x -- q_proj | k_proj | v_proj of an attention block
+ * (crates/lisa-engine/src/models/qwen4/attention.rs:111-128 calls the three `forward(x)` one after
+ * another) or gate_proj | up_proj of an MLP.  Linear i is (w[i], scales[i], biases[i]) with n[i]
+ * output rows and writes its own [m, n[i]] output y[i]; results are those of `count` calls of
+ * lisa_cuda_quantized_matmul within the f32 summation order.  For m <= 8 and shapes the
+ * tensor-memory GEMV takes this is ONE launch (a decode launch costs microseconds whatever its size);
+ * otherwise the linears run one after another through the dispatch of lisa_cuda_quantized_matmul. */
+int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int64_t m, int64_t k,
+                                        int count, const uint32_t *const *w,
+                                        const void *const *scales, const void *const *biases,
+                                        const int64_t *n, int transpose, int group_size, int bits,
+                                        int dtype, void *const *y, unsigned flags);
+
 /* N-sharded decode linear fused with its all-gather (one node, up to 8 GPUs, one process per GPU).
  * No counterpart in the reference, which runs on one device: this is the multi-GPU form of
  * ops::quantized_matmul for m <= 8 rows and group size 64.  The caller holds rows

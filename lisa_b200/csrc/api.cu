@@ -176,6 +176,30 @@ int lisa_cuda_quantized_matmul_allgather(lisa_stream_t stream, const void *x, in
                             world, n_total, col0, flags);
 }
 
+int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int64_t m, int64_t k, int count,
+                                        const uint32_t *const *w, const void *const *scales,
+                                        const void *const *biases, const int64_t *n, int transpose, int group_size,
+                                        int bits, int dtype, void *const *y, unsigned flags) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_siblings: only transpose=true supported");
+    if (count < 1 || count > 3 || !w || !scales || !biases || !n || !y)
+        return fail(LISA_ERR_BAD_ARG, "quantized_matmul_siblings: one to three linears, non-null tables");
+    for (int i = 0; i < count; ++i) {
+        const int rc = check_affine("quantized_matmul_siblings", x, m, k, w[i], scales[i], biases[i], n[i], group_size, bits, dtype, y[i]);
+        if (rc != LISA_OK) return rc;
+    }
+    // one launch when the tensor-memory GEMV takes the rows; otherwise the linears one after another,
+    // each through the dispatch of quantized_matmul
+    if (count >= 2 && m <= 8 && !(flags & (LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) &&
+        qmv_tc_multi_supported(m, k, count, n, group_size, bits))
+        return qmv_tc_multi(static_cast<cudaStream_t>(stream), x, m, k, count, w, scales, biases, n, group_size, bits, y, flags);
+    for (int i = 0; i < count; ++i) {
+        const int rc = quantized_matmul_impl(static_cast<cudaStream_t>(stream), x, m, k, w[i], scales[i], biases[i], n[i],
+                                             transpose, group_size, bits, dtype, y[i], flags);
+        if (rc != LISA_OK) return rc;
+    }
+    return LISA_OK;
+}
+
 int lisa_cuda_peer_barrier(lisa_stream_t stream, int rank, int world, void *const *flag_arrays, uint64_t epoch) {
     if (!flag_arrays || world < 1 || world > 8 || rank < 0 || rank >= world)
         return fail(LISA_ERR_BAD_ARG, "peer_barrier: bad rank or world");

@@ -21,6 +21,10 @@ int qmv_tc_device_status();
 int qmv_tc_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                      const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
                      int64_t n_total, int64_t col0, unsigned flags);
+bool qmv_tc_multi_supported(int64_t m, int64_t k, int count, const int64_t *n, int group_size, int bits);
+int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
+                 const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
+                 void *const *y, unsigned flags);
 bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes);
 int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
                 int64_t tokens, float *y);

@@ -66,6 +66,7 @@ constexpr int kMaxWStages = 6;        // packed-weight ring (shared memory), 16 
 constexpr int kWBytes = kRows * 128;
 constexpr int kUnpackWarps = 8, kEpilogueWarps = 4;
 constexpr int kThreads = (2 + kUnpackWarps + kEpilogueWarps) * 32;
+constexpr int kMaxSeg = 3;            // linears of one launch in the sibling form (q|k|v, gate|up)
 constexpr int kXTile = 2048;          // B tile of TWO k-blocks: 16 rows (8 hi, 8 lo) x 128 bytes (2 x 64 k)
 
 struct TcParams {
@@ -89,6 +90,18 @@ struct TcParams {
     float *yf;
     const uint8_t *wg;
     long long row_bytes;
+    // sibling form: up to kMaxSeg linears that share x, m, k in one launch; segment s owns row tiles
+    // [seg_tile[s], seg_tile[s + 1]) and has its own packed rows (tensor map s), scales, biases and output
+    int nseg;
+    int seg_tile[kMaxSeg];
+    int seg_n[kMaxSeg];
+    const uint16_t *seg_scales[kMaxSeg];
+    const uint16_t *seg_biases[kMaxSeg];
+    uint16_t *seg_out[kMaxSeg];
+    const uint8_t *seg_w[kMaxSeg];   // packed rows of segment s (affine form), for the L2 prefetch
+};
+struct TcMaps {
+    CUtensorMap m[kMaxSeg];
 };
 
 // Shared-memory plan, bytes from the 1024-aligned base.
@@ -105,8 +118,9 @@ __host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, in
     p.zero = off;                     // (unused)
     p.xsum = off;                     // [max_l][8] f32 sum(x), then [max_l][8] f32 2^(E-13)
     off += 2 * max_l * 8 * 4;
-    p.sc = off;                       // [max_l][128] words {scale bf16 | bias bf16 << 16}
+    p.sc = off;                       // [max_l][128] words {scale bf16 | bias bf16 << 16}; GGUF: block headers
     off += max_l * kRows * 4;
+    if (wbytes == kRows * 336) off += (max_l / 4 + 1) * kRows * 4;  // Q2_K: {d, dmin} of every block, after the scale bytes
     p.part = off;                     // rank 0 of the cluster: [splits][128][m] f32 partial sums of all k-slices
     off += splits * kRows * m * 4;
     off = (off + 15) & ~15;
@@ -218,12 +232,18 @@ __device__ __forceinline__ bool tc_wait_relaxed(uint64_t *bar, uint32_t parity, 
 // zeros for k 32..63, rows 8..15 the reverse).  An activation is three signed bytes,
 // x_int = rn(x * 2^(21-E)) = 65536 p0 + 256 p1 + p2 (22 bits; exact on the reference's dyadic inputs),
 // row 3t + q of a half holding piece q of token t.
+//
+// GG = 2 (with BITS = 2): GGUF Q2_K matvec, one token (replaces lisa_gguf_q2_K_mv, iq.metal:1130-1237; block
+// layout quant.rs:64-80).  A packed stage row is four 84-byte blocks (16 k-blocks); the 64 elements of
+// k-block kb4 of a block are the 2-bit fields at shifts 2*(kb4&1) and 2*(kb4&1)+1 of code bytes
+// 32*(kb4/2) .. +31, so a pair of k-blocks is the four fields of the same 32 bytes.  Sub-blocks are 16
+// elements: four per k-block, D columns 4*g + q (piece q), B rows 4*g + q non-zero only for k 16g .. 16g+15.
 template <int BITS, int GG = 0>
 __global__ void __launch_bounds__(kThreads, 2)
-qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
-    constexpr int ROWB = GG ? 144 : 128;  // bytes of a packed stage row
+qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
+    constexpr int ROWB = (GG == 4) ? 144 : (GG == 2) ? 336 : 128;  // bytes of a packed stage row
     constexpr int CPW = 32 / BITS;             // codes per word
-    constexpr int KBW = (128 * 8 / BITS) / 64;  // k-blocks per packed stage: 4 / 8
+    constexpr int KBW = (GG == 2) ? 16 : (128 * 8 / BITS) / 64;  // k-blocks per packed stage: 4 / 8 (affine), 4 (Q4_K), 16 (Q2_K)
     constexpr int KB_BYTES = 64 * BITS / 8;    // packed bytes of one row of a k-block: 32 / 16
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -240,7 +260,16 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler too
     const uint32_t rank = (p.splits > 1) ? cluster_ctarank() : 0u;
-    const int tile = blockIdx.x / p.splits;
+    int tile = blockIdx.x / p.splits;
+    // the linear this row tile belongs to (one, unless the launch is the sibling form)
+    int seg = 0;
+    if (!GG && p.nseg > 1) {
+        seg = (tile >= p.seg_tile[1]) ? 1 : 0;
+        if (p.nseg > 2 && tile >= p.seg_tile[2]) seg = 2;
+        tile -= (seg == 0) ? 0 : (seg == 1) ? p.seg_tile[1] : p.seg_tile[2];
+    }
+    const CUtensorMap *map_w = &maps.m[seg];
+    const int seg_n = (seg == 0) ? p.n : (seg == 1) ? p.seg_n[1] : p.seg_n[2];
     const int n0 = tile * kRows;
     // this CTA's k-slice, in packed stages and in k-blocks
     const int total_ws = (p.num_kb + KBW - 1) / KBW;
@@ -287,14 +316,39 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
 
     if (warp == 0) {
         // ---------------- producer: packed codes do not depend on the previous kernel in the stream
+        int s = 0;
+        uint32_t ph = 1;
+        auto issue = [&](int wi) {
+            mbar_arrive_expect_tx(&wp_full[s], kRows * ROWB);
+            // x coordinate in elements of the map: bytes, or 32-bit words for Q2_K
+            tma_load_2d(ring32 + s * (kRows * ROWB), map_w, wi * (GG == 2 ? ROWB / 4 : ROWB), n0, &wp_full[s]);
+            if (++s == p.wstages) { s = 0; ph ^= 1; }
+        };
+        const int ws_ring = min(ws1, ws0 + p.wstages);
+        if (lane == 0)
+            for (int wi = ws0; wi < ws_ring; ++wi) issue(wi);
+        // The ring holds a few stages; a load from cold DRAM takes microseconds, so the ring alone keeps too
+        // few bytes in flight per SM.  The rest of this CTA's slice -- for every row one contiguous run of
+        // the packed row -- is asked into L2 now (while the previous kernel in the stream still runs, when
+        // launched as a dependent), and the ring then refills at L2 latency.
+        if (ws_ring < ws1) {
+            const uint8_t *wb = GG ? p.wg : (seg == 0) ? p.seg_w[0] : (seg == 1) ? p.seg_w[1] : p.seg_w[2];
+            const long long rb = GG ? p.row_bytes : static_cast<long long>(p.k) * BITS / 8;
+            const long long off = static_cast<long long>(ws_ring) * ROWB;
+            const long long len = min(static_cast<long long>(ws1 - ws_ring) * ROWB, rb - off);
+            if (len > 0) {
+                for (int r = lane; r < kRows; r += 32) {
+                    if (n0 + r < seg_n)
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wb + static_cast<long long>(n0 + r) * rb + off),
+                                     "r"(static_cast<uint32_t>(len))
+                                     : "memory");
+                }
+            }
+        }
         if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 1;
-            for (int wi = ws0; wi < ws1; ++wi) {
-                if (wi - ws0 >= p.wstages && !tc_wait_relaxed(&wp_empty[s], ph, 1)) break;
-                mbar_arrive_expect_tx(&wp_full[s], kRows * ROWB);
-                tma_load_2d(ring32 + s * (kRows * ROWB), &map_w, wi * ROWB, n0, &wp_full[s]);
-                if (++s == p.wstages) { s = 0; ph ^= 1; }
+            for (int wi = ws_ring; wi < ws1; ++wi) {
+                if (!tc_wait_relaxed(&wp_empty[s], ph, 1)) break;
+                issue(wi);
             }
         }
     } else if (warp == 1) {
@@ -374,7 +428,17 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
             if (sub < 4) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], (wsl / p.wstages) & 1, 4));
             if (!ok) break;
             uint32_t o[32];
-            {
+            if (GG == 2) {
+                // the pair's 128 elements are the four 2-bit fields of 32 code bytes of one block
+                const uint32_t blk = row32 + s * (kRows * ROWB) + (sub >> 2) * 84 + 16 + ((sub & 3) >> 1) * 32;
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[i]) : "r"(blk + 4 * i));
+#pragma unroll
+                for (int f = 0; f < 4; ++f)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[8 * f + i] = (w[i] >> (2 * f)) & kmask;
+            } else {
                 const uint32_t base = row32 + s * (kRows * ROWB);
                 uint32_t w[8 * kChunksPerKb];  // 16 (4-bit) / 8 (2-bit) words of the pair
 #pragma unroll
@@ -427,17 +491,30 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int et = tid - (2 + kUnpackWarps) * 32;  // 0..127
-        const int grow = min(n0 + row, p.n - 1);
+        const int grow = min(n0 + row, seg_n - 1);
         // scales and biases of (row, group) of the slice: weights, no dependency on the previous kernel
-        if (GG) {
+        if (GG == 2) {
+            // per block of this row: the 16 scale/min bytes ([block][row] uint4 in `sc`) and {d, dmin} (a word each, after them)
+            const uint8_t *wr = p.wg + static_cast<size_t>(grow) * p.row_bytes + static_cast<size_t>(kb0 / 4) * 84;
+            uint4 *hdr = reinterpret_cast<uint4 *>(sc);
+            uint32_t *dd = sc + p.max_l * kRows;
+#pragma unroll 2
+            for (int bq = 0; bq < (L + 3) / 4; ++bq) {
+                const uint32_t *bp = reinterpret_cast<const uint32_t *>(wr + bq * 84);  // 4-byte aligned
+                hdr[bq * kRows + row] = make_uint4(__ldg(bp), __ldg(bp + 1), __ldg(bp + 2), __ldg(bp + 3));
+                dd[bq * kRows + row] = __ldg(bp + 20);
+            }
+        } else if (GG) {
             // the 16-byte headers {d, dmin, 6-bit scales and mins} of this row's blocks: [block][row] uint4 in `sc`
             const uint8_t *wr = p.wg + static_cast<size_t>(grow) * p.row_bytes + static_cast<size_t>(kb0 / 4) * 144;
             uint4 *hdr = reinterpret_cast<uint4 *>(sc);
 #pragma unroll 4
             for (int bq = 0; bq < (L + 3) / 4; ++bq) hdr[bq * kRows + row] = __ldg(reinterpret_cast<const uint4 *>(wr + bq * 144));
         } else {
-            const uint16_t *sr = p.scales + static_cast<size_t>(grow) * p.groups + kb0;
-            const uint16_t *br = p.biases + static_cast<size_t>(grow) * p.groups + kb0;
+            const uint16_t *sbase = (seg == 0) ? p.scales : (seg == 1) ? p.seg_scales[1] : p.seg_scales[2];
+            const uint16_t *bbase = (seg == 0) ? p.biases : (seg == 1) ? p.seg_biases[1] : p.seg_biases[2];
+            const uint16_t *sr = sbase + static_cast<size_t>(grow) * p.groups + kb0;
+            const uint16_t *br = bbase + static_cast<size_t>(grow) * p.groups + kb0;
             if ((p.groups & 3) == 0 && (kb0 & 3) == 0) {
                 // four groups per 8-byte load; a row holds a multiple of four groups, so the last load
                 // of a short slice stays inside the row
@@ -586,7 +663,7 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                     amax = max(amax, __float_as_uint(xv[i]) & 0x7fffffffu);
                 }
 #pragma unroll
-                for (int off = 1; off < 4; off <<= 1) {
+                for (int off = 1; off < (GG == 2 ? 2 : 4); off <<= 1) {  // items per sub-block: 2 (Q2_K) / 4 (Q4_K)
                     sum += __shfl_xor_sync(0xffffffffu, sum, off);
                     amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, off));
                 }
@@ -605,7 +682,23 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                     pc[1][i >> 2] |= (static_cast<uint32_t>(p1) & 0xffu) << (8 * (i & 3));
                     pc[2][i >> 2] |= (static_cast<uint32_t>(p2) & 0xffu) << (8 * (i & 3));
                 }
-                if (in) {
+                if (in && GG == 2) {
+                    const int g4 = j >> 1;                      // 16-element sub-block of the k-block
+                    const int par = kbl & 1;
+                    const int chunk = par * 4 + g4, off8 = (j & 1) * 8;  // a sub-block is one 16-byte chunk
+                    const uint32_t tile = xb32 + (kbl >> 1) * kXTile + (g4 >> 1) * 1024;  // rows 4*g4 + q
+#pragma unroll
+                    for (int q = 0; q < 3; ++q) {
+                        const int r = 4 * (g4 & 1) + q;         // row within the 8-row group
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(tile + r * 128 + ((chunk ^ r) << 4) + off8),
+                                     "r"(pc[q][0]), "r"(pc[q][1]) : "memory");
+                    }
+                    if ((j & 1) == 0) {
+                        xsum[kbl * 8 + g4] = sum;
+                        xscale[kbl * 8 + g4] = live ? __uint_as_float((e - 21u) << 23)
+                                                    : (e == 255u ? __uint_as_float(0x7fc00000u) : 0.f);
+                    }
+                } else if (in) {
                     const int h = j >> 2;                       // sub-block of the k-block
                     const int par = kbl & 1;                    // k-block of the pair (64-byte half of a B row)
                     const int chunk = par * 4 + 2 * h + ((j & 3) >> 1), off8 = (j & 1) * 8;
@@ -719,7 +812,55 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
                 if (++st == kNP) { st = 0; ph ^= 1; }
             }
         };
-        if (GG) {
+        // Q2_K, one token: columns 4*g + q of a D are piece q against sub-block g (16 elements) of the k-block
+        auto run_q2k = [&]() {
+            const uint4 *hdr = reinterpret_cast<const uint4 *>(sc);
+            const uint32_t *dd = sc + p.max_l * kRows;
+            int st = 0;
+            uint32_t ph = 0;
+            for (int pr = 0; pr < P; ++pr) {
+                const bool two = 2 * pr + 1 < L;
+                ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[st], ph, 7));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t c[2][2][8];  // [k-block of the pair][rows 0..7 / 8..15][columns]
+                const uint32_t dp = d_lane + st * 2 * kDCols;
+                tmem_ld<8>(dp, c[0][0]);
+                tmem_ld<8>(dp + 8, c[0][1]);
+                tmem_ld<8>(dp + kDCols, c[1][0]);
+                tmem_ld<8>(dp + kDCols + 8, c[1][1]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&d_empty[st]);
+                const int blk = (2 * pr) >> 2;
+                const uint4 sb16 = hdr[blk * kRows + row];
+                float d, dmin;
+                asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %2; cvt.f32.f16 %0, lo; cvt.f32.f16 %1, hi; }" : "=f"(d), "=f"(dmin) : "r"(dd[blk * kRows + row]));
+#pragma unroll
+                for (int hk = 0; hk < 2; ++hk) {
+                    if (hk == 1 && !two) break;
+                    const int kk = 2 * pr + hk, kb4 = kk & 3;
+#pragma unroll
+                    for (int g4 = 0; g4 < 4; ++g4) {
+                        // scale byte [half*8 + shift*2 + group], shift = 2*(kb4&1) + g4/2, group = g4&1
+                        const int si = (kb4 >> 1) * 8 + (2 * (kb4 & 1) + (g4 >> 1)) * 2 + (g4 & 1);
+                        const int wi4 = si >> 2;  // selects instead of a dynamically indexed array
+                        const uint32_t sword = wi4 == 0 ? sb16.x : wi4 == 1 ? sb16.y : wi4 == 2 ? sb16.z : sb16.w;
+                        const uint32_t sbyte = (sword >> (8 * (si & 3))) & 255u;
+                        const float ds = d * static_cast<float>(sbyte & 15u), dm = dmin * static_cast<float>(sbyte >> 4);
+                        const uint32_t *cc = c[hk][g4 >> 1] + 4 * (g4 & 1);
+                        const float val = static_cast<float>(static_cast<int>(cc[0])) * 65536.f +
+                                          static_cast<float>(static_cast<int>(cc[1]) * 256 + static_cast<int>(cc[2]));
+                        rs[0] += ds * (val * xscale[kk * 8 + g4]) - dm * xsum[kk * 8 + g4];
+                    }
+                }
+                if (++st == kNP) { st = 0; ph ^= 1; }
+            }
+        };
+        if (GG == 2) {
+            run_q2k();
+        } else if (GG) {
             if (p.m == 1) run_gguf(IntC<4>{});
             else run_gguf(IntC<8>{});
         } else if (p.m == 1) run(IntC<1>{});
@@ -748,18 +889,22 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
     }
     if (rank == 0 && warp >= 2 + kUnpackWarps) {
         const int row = (warp & 3) * 32 + lane;
-        if (n0 + row < p.n) {
+        if (n0 + row < seg_n) {
+            // sibling form: the segment's own [m, n] output; else outs[0 .. nout) with pitch ldy
+            uint16_t *out0 = (seg == 0) ? p.out[0] : (seg == 1) ? p.seg_out[1] : p.seg_out[2];
+            const int ldy = (p.nseg > 1) ? seg_n : p.ldy;
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
                 if (t < p.m) {
                     float tot = 0.f;
                     for (int r = 0; r < p.splits; ++r) tot += part[(r * kRows + row) * p.m + t];
-                    const size_t at = static_cast<size_t>(t) * p.ldy + p.col0 + n0 + row;
+                    const size_t at = static_cast<size_t>(t) * ldy + p.col0 + n0 + row;
                     if (GG) {
                         p.yf[at] = tot;
                     } else {
                         const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(tot));
-                        for (int o = 0; o < p.nout; ++o) p.out[o][at] = v;  // plain stores, peers' memory included
+                        out0[at] = v;
+                        for (int o = 1; o < p.nout; ++o) p.out[o][at] = v;  // plain stores, peers' memory included
                     }
                 }
             }
@@ -776,15 +921,16 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcParams p) {
 // Shapes the kernel takes: group size 64, packed rows addressable by a tensor map, and a k-slice whose
 // staging fits half an SM's shared memory.  `m` rows are wanted; `mc` (<= 8) is how many one launch takes.
 static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, TcParams &p, int &smem, int &grid, int &mc,
-                         int wbytes = kWBytes) {
+                         int wbytes = kWBytes, int kbw_stage = 0, int64_t tiles_all = 0) {
     if (bits != 2 && bits != 4) return false;
     if (group_size != 64 || k % 64 != 0 || m < 1) return false;
     if ((k * bits / 8) % 16 != 0 || (k * 2) % 16 != 0) return false;
-    const int kbw = (128 * 8 / bits) / 64;
+    const int kbw = kbw_stage ? kbw_stage : (128 * 8 / bits) / 64;  // k-blocks per packed stage
     const int num_kb = static_cast<int>(k / 64);
     const int total_ws = (num_kb + kbw - 1) / kbw;
-    const int64_t tiles = (n + kRows - 1) / kRows;
-    const int budget = max_smem_optin() / 2 - 2048;  // two CTAs (of consecutive kernels) per SM
+    const int64_t tiles = tiles_all ? tiles_all : (n + kRows - 1) / kRows;  // row tiles of the launch
+    int budget = max_smem_optin() / 2 - 2048;  // two CTAs (of consecutive kernels) per SM
+    if (wbytes == kRows * 336) budget = max_smem_optin() - 2048;  // Q2_K stages are 42 KB: one CTA per SM, two stages or more
     // as many k-slices as keep the grid near one CTA per SM; more when the slice would not fit
     int splits = 1;
     while (splits < 8 && tiles * (splits * 2) <= sm_count() + 20 && splits * 2 <= total_ws) splits *= 2;
@@ -826,17 +972,54 @@ bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits)
     return tc_make_plan(n, k, group_size, bits, static_cast<int>(std::min<int64_t>(m, 8)), p, smem, grid, mc);
 }
 
+static int affine_tensor_map(CUtensorMap *map, const uint32_t *w, int64_t n, int64_t k, int bits) {
+    const uint64_t row_bytes = static_cast<uint64_t>(k) * bits / 8;
+    const uint64_t dims[2] = {row_bytes, static_cast<uint64_t>(n)};
+    const uint64_t strides[1] = {row_bytes};
+    const uint32_t box[2] = {128, kRows};
+    return make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+static int tc_launch_kernel(cudaStream_t stream, int bits, const TcMaps &maps, const TcParams &p, int grid, int smem, unsigned flags) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (p.splits > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = p.splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (flags & LISA_FLAG_PDL) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    if (bits == 4) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4>, maps, p));
+    } else {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2>, maps, p));
+    }
+    count_launch();
+    return LISA_OK;
+}
+
 static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                          const void *biases, int64_t n, int group_size, int bits, void *const *outs, int nout, int64_t ldy,
                          int64_t col0, unsigned flags) {
     const uint16_t *xp = reinterpret_cast<const uint16_t *>(x);
-    CUtensorMap map_w;
+    TcMaps maps{};
     {
-        const uint64_t row_bytes = static_cast<uint64_t>(k) * bits / 8;
-        const uint64_t dims[2] = {row_bytes, static_cast<uint64_t>(n)};
-        const uint64_t strides[1] = {row_bytes};
-        const uint32_t box[2] = {128, kRows};
-        const int rc = make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        const int rc = affine_tensor_map(&maps.m[0], w, n, k, bits);
         if (rc != LISA_OK) return rc;
     }
     int mc = 0;
@@ -847,6 +1030,7 @@ static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t 
             return fail(LISA_ERR_UNSUPPORTED, "qmv_tc: shape not supported");
         p.scales = reinterpret_cast<const uint16_t *>(scales);
         p.biases = reinterpret_cast<const uint16_t *>(biases);
+        p.seg_w[0] = reinterpret_cast<const uint8_t *>(w);
         p.x = xp + done * k;
         p.nout = nout;
         p.ldy = static_cast<int>(ldy);
@@ -855,35 +1039,8 @@ static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t 
         p.n = static_cast<int>(n);
         p.k = static_cast<int>(k);
         p.m = mc;
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
-        int na = 0;
-        if (p.splits > 1) {
-            attr[na].id = cudaLaunchAttributeClusterDimension;
-            attr[na].val.clusterDim.x = p.splits;
-            attr[na].val.clusterDim.y = 1;
-            attr[na].val.clusterDim.z = 1;
-            ++na;
-        }
-        if (flags & LISA_FLAG_PDL) {
-            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[na].val.programmaticStreamSerializationAllowed = 1;
-            ++na;
-        }
-        cfg.attrs = attr;
-        cfg.numAttrs = na;
-        if (bits == 4) {
-            LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4>, map_w, p));
-        } else {
-            LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2>, map_w, p));
-        }
-        count_launch();
+        const int rc = tc_launch_kernel(stream, bits, maps, p, grid, smem, flags);
+        if (rc != LISA_OK) return rc;
     }
     return LISA_OK;
 }
@@ -902,30 +1059,104 @@ int qmv_tc_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, c
     return qmv_tc_launch(stream, x, m, k, w, scales, biases, n, group_size, bits, outs, world, n_total, col0, flags);
 }
 
-// GGUF Q4_K matvec for one or two tokens through the same kernel (f32 in, f32 out).
-bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes) {
-    if (format != LISA_GGUF_Q4_K || tokens < 1 || tokens > 2 || rows < 1 || rows > (1 << 24)) return false;
-    if (row_bytes % 144 != 0) return false;
+// Sibling linears: `count` (2 or 3) weight matrices with the same k, group size and bit width applied to the
+// same x in ONE launch (q|k|v, gate|up of a decoder layer); linear i writes its own [m, n[i]] output.
+bool qmv_tc_multi_supported(int64_t m, int64_t k, int count, const int64_t *n, int group_size, int bits) {
+    if (count < 2 || count > kMaxSeg || m < 1) return false;
+    int64_t tiles = 0;
+    for (int i = 0; i < count; ++i) {
+        if (n[i] < 1 || n[i] > (1 << 24)) return false;
+        tiles += (n[i] + kRows - 1) / kRows;
+    }
     TcParams p{};
     int smem = 0, grid = 0, mc = 0;
-    if (!tc_make_plan(rows, row_bytes / 144 * 256, 64, 4, static_cast<int>(tokens), p, smem, grid, mc, kRows * 144)) return false;
+    return tc_make_plan(n[0], k, group_size, bits, static_cast<int>(std::min<int64_t>(m, 8)), p, smem, grid, mc, kWBytes, 0, tiles);
+}
+
+int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
+                 const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
+                 void *const *y, unsigned flags) {
+    if (count < 2 || count > kMaxSeg) return fail(LISA_ERR_UNSUPPORTED, "qmv_tc_multi: two or three linears per launch");
+    const uint16_t *xp = reinterpret_cast<const uint16_t *>(x);
+    TcMaps maps{};
+    int64_t tiles = 0;
+    int first[kMaxSeg] = {0, 0, 0};
+    for (int i = 0; i < count; ++i) {
+        const int rc = affine_tensor_map(&maps.m[i], w[i], n[i], k, bits);
+        if (rc != LISA_OK) return rc;
+        first[i] = static_cast<int>(tiles);
+        tiles += (n[i] + kRows - 1) / kRows;
+    }
+    int mc = 0;
+    for (int64_t done = 0; done < m; done += mc) {
+        TcParams p{};
+        int smem = 0, grid = 0;
+        if (!tc_make_plan(n[0], k, group_size, bits, static_cast<int>(std::min<int64_t>(m - done, 8)), p, smem, grid, mc, kWBytes, 0, tiles))
+            return fail(LISA_ERR_UNSUPPORTED, "qmv_tc_multi: shape not supported");
+        p.x = xp + done * k;
+        p.k = static_cast<int>(k);
+        p.m = mc;
+        p.nout = 1;
+        p.col0 = 0;
+        p.nseg = count;
+        for (int i = 0; i < count; ++i) {
+            p.seg_tile[i] = first[i];
+            p.seg_n[i] = static_cast<int>(n[i]);
+            p.seg_scales[i] = reinterpret_cast<const uint16_t *>(scales[i]);
+            p.seg_biases[i] = reinterpret_cast<const uint16_t *>(biases[i]);
+            p.seg_out[i] = reinterpret_cast<uint16_t *>(y[i]) + done * n[i];
+            p.seg_w[i] = reinterpret_cast<const uint8_t *>(w[i]);
+        }
+        p.scales = p.seg_scales[0];
+        p.biases = p.seg_biases[0];
+        p.out[0] = p.seg_out[0];
+        p.n = p.seg_n[0];
+        p.ldy = p.seg_n[0];
+        const int rc = tc_launch_kernel(stream, bits, maps, p, grid, smem, flags);
+        if (rc != LISA_OK) return rc;
+    }
+    return LISA_OK;
+}
+
+// GGUF matvec through the same kernel (f32 in, f32 out): Q4_K for one or two tokens, Q2_K for one.
+static bool gguf_tc_plan(int format, int64_t tokens, int64_t rows, int64_t row_bytes, TcParams &p, int &smem, int &grid) {
+    if (tokens < 1 || rows < 1 || rows > (1 << 24)) return false;
+    int mc = 0;
+    if (format == LISA_GGUF_Q4_K) {
+        if (tokens > 2 || row_bytes % 144 != 0) return false;
+        if (!tc_make_plan(rows, row_bytes / 144 * 256, 64, 4, static_cast<int>(tokens), p, smem, grid, mc, kRows * 144, 4)) return false;
+    } else if (format == LISA_GGUF_Q2_K) {
+        if (tokens > 1 || row_bytes % 336 != 0) return false;  // whole stage rows of four blocks
+        if (!tc_make_plan(rows, row_bytes / 84 * 256, 64, 2, 1, p, smem, grid, mc, kRows * 336, 16)) return false;
+    } else {
+        return false;
+    }
     return mc == tokens;
+}
+
+bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes) {
+    TcParams p{};
+    int smem = 0, grid = 0;
+    return gguf_tc_plan(format, tokens, rows, row_bytes, p, smem, grid);
 }
 
 int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
                 int64_t tokens, float *y) {
-    (void)format;
-    const int64_t k = row_bytes / 144 * 256;
+    const bool q4 = format == LISA_GGUF_Q4_K;
+    const int64_t k = row_bytes / (q4 ? 144 : 84) * 256;
     TcParams p{};
-    int smem = 0, grid = 0, mc = 0;
-    if (!tc_make_plan(rows, k, 64, 4, static_cast<int>(tokens), p, smem, grid, mc, kRows * 144) || mc != tokens)
+    int smem = 0, grid = 0;
+    if (!gguf_tc_plan(format, tokens, rows, row_bytes, p, smem, grid))
         return fail(LISA_ERR_UNSUPPORTED, "gguf matvec: shape not supported by the tensor-memory kernel");
-    CUtensorMap map_w;
+    TcMaps maps{};
+    CUtensorMap &map_w = maps.m[0];
     {
-        const uint64_t dims[2] = {static_cast<uint64_t>(row_bytes), static_cast<uint64_t>(rows)};
+        // Q4_K: bytes, one block per box row; Q2_K: 32-bit words, four blocks (336 bytes) per box row
+        const uint64_t dims[2] = {static_cast<uint64_t>(q4 ? row_bytes : row_bytes / 4), static_cast<uint64_t>(rows)};
         const uint64_t strides[1] = {static_cast<uint64_t>(row_bytes)};
-        const uint32_t box[2] = {144, kRows};
-        const int rc = make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        const uint32_t box[2] = {static_cast<uint32_t>(q4 ? 144 : 84), kRows};
+        const int rc = make_tensor_map(&map_w, q4 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w, dims,
+                                       strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc != LISA_OK) return rc;
     }
     p.xf = x;
@@ -934,7 +1165,7 @@ int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows,
     p.row_bytes = row_bytes;
     p.n = static_cast<int>(rows);
     p.k = static_cast<int>(k);
-    p.m = mc;
+    p.m = static_cast<int>(tokens);
     p.nout = 0;
     p.ldy = static_cast<int>(rows);
     p.col0 = 0;
@@ -954,8 +1185,13 @@ int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows,
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4, 4>, map_w, p));
+    if (q4) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4, 4>, maps, p));
+    } else {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2, 2>, maps, p));
+    }
     count_launch();
     return LISA_OK;
 }

@@ -73,6 +73,36 @@ def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
     return y.reshape(*x.shape[:-1], n)
 
 
+def quantized_matmul_siblings(x: torch.Tensor, linears, transpose: bool = True, group_size: int = 64,
+                               bits: int = 4, *, stream=None, flags: int = 0):
+    """One to three quantized linears applied to the same x (q|k|v, gate|up); `linears` is a sequence of
+    (w, scales, biases).  Returns the list of outputs, each x.shape[:-1] + [N_i]: what as many
+    ``quantized_matmul`` calls return, from one launch when the rows are few."""
+    import ctypes as C
+
+    k = x.shape[-1]
+    m = x.numel() // k
+    x2 = x.reshape(m, k).contiguous()
+    count = len(linears)
+    keep, ys = [], []
+    wp, sp, bp, yp = (C.c_void_p * count)(), (C.c_void_p * count)(), (C.c_void_p * count)(), (C.c_void_p * count)()
+    ns = (C.c_int64 * count)()
+    for i, (w, sc, bi) in enumerate(linears):
+        _need_cuda(x, w, sc, bi)
+        w = _words(w)
+        sc, bi = sc.contiguous(), bi.contiguous()
+        if w.shape[-1] * 32 // bits != k or sc.shape[-1] * group_size != k:
+            raise LisaError(_cabi.ERR_BAD_ARG, "quantized_matmul_siblings: shapes of x, w and scales disagree")
+        y = torch.empty((m, w.shape[0]), dtype=x2.dtype, device=x2.device)
+        keep.append((w, sc, bi))
+        ys.append(y)
+        wp[i], sp[i], bp[i], yp[i], ns[i] = w.data_ptr(), sc.data_ptr(), bi.data_ptr(), y.data_ptr(), w.shape[0]
+    rc = lib().lisa_cuda_quantized_matmul_siblings(_stream(stream), x2.data_ptr(), m, k, count, wp, sp, bp, ns,
+                                                   int(bool(transpose)), group_size, bits, _dtype_code(x2), yp, flags)
+    check(rc)
+    return [y.reshape(*x.shape[:-1], y.shape[-1]) for y in ys]
+
+
 def quantized_matmul_serial_rows(x, w, scales, biases, transpose: bool = True, group_size: int = 64,
                                  bits: int = 4, *, stream=None) -> torch.Tensor:
     """``ops::quantized_matmul_serial_rows`` (array_ops.rs:500-555)."""

@@ -73,12 +73,9 @@ def test_full_size_row_slices_config5(cuda, name, fmt):
     ref = O.gguf_matvec(fmt, np.ascontiguousarray(w[pick]), x)
     assert util.parity(y[:, pick], ref)[0] <= 1e-4
     sub = ops.packed_matvec(name, dev_u8(np.ascontiguousarray(w[1024:1024 + 64]), cuda), tx).cpu().numpy()
-    if fmt == O.Q2_K:
-        assert np.array_equal(sub, y[:, 1024:1024 + 64])  # warp-per-row kernel: the same sum, bit for bit
-    else:
-        # Q4_K at one token takes the tensor-memory kernel, whose number of k-slices follows the row count
-        # (64 rows: 8 slices, 18432 rows: 1): the same products in another f32 summation order
-        assert util.parity(sub, y[:, 1024:1024 + 64])[0] <= 1e-5
+    # one token takes the tensor-memory kernel, whose number of k-slices follows the row count (64 rows: 8
+    # slices, 18432 rows: 1): the same products in another f32 summation order
+    assert util.parity(sub, y[:, 1024:1024 + 64])[0] <= 1e-5
 
 
 def test_layout_rejections(cuda):
@@ -156,3 +153,30 @@ def test_q4k_one_or_two_tokens_random_blocks(cuda, rows, k, tokens):
     truth = x.astype(np.float64) @ dec.T
     err, l2 = util.parity(y, truth)
     assert err <= 1e-4 and l2 <= 1e-5, (err, l2)
+
+
+@pytest.mark.parametrize("rows,width", [(16, 1024), (128, 5120), (200, 8192), (1024, 2048)])
+def test_q2k_one_token_tensor_memory_kernel_is_exact_on_dyadic_inputs(cuda, rows, width):
+    """One token of a Q2_K matrix whose rows are whole groups of four blocks takes the tensor-memory kernel
+    (2-bit codes as bytes, one accumulator column per 16-element sub-block): exact on the dyadic construction."""
+    blocks = O.gguf_dyadic_blocks(O.Q2_K, width * rows // 256)
+    w = blocks.reshape(rows, -1)
+    x = O.gguf_dyadic_inputs(width).reshape(1, width)
+    y = ops.packed_matvec("Q2K", dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
+    assert np.array_equal(y, O.gguf_matvec(O.Q2_K, w, x))
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("rows,k", [(18432, 7168), (7168, 18432), (136, 2048), (64, 1024)])
+def test_q2k_one_token_random_blocks(cuda, rows, k):
+    rng = np.random.default_rng(rows + k)
+    w = util.gguf_weights(rng, O.Q2_K, rows, k)
+    x = rng.normal(0, 1, size=(1, k)).astype(np.float32)
+    x[0, 5] = 300.0    # an outlier: the exponent is per 16-element sub-block
+    x[0, 32:48] = 0.0  # and an all-zero sub-block
+    y = ops.packed_matvec("Q2K", dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
+    dec = O.gguf_decode(O.Q2_K, w).reshape(rows, k).astype(np.float64)
+    truth = x.astype(np.float64) @ dec.T
+    err, l2 = util.parity(y, truth)
+    assert err <= 1e-4 and l2 <= 1e-5, (err, l2)
+    assert ops.device_status() == 0

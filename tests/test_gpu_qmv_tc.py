@@ -71,3 +71,45 @@ def test_unsupported_group_size_is_refused(cuda):
     with pytest.raises(_cabi.LisaError):
         ops.quantized_matmul(dev_bf16(x, cuda), dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda), True, 128, 4,
                              flags=_cabi.FLAG_FORCE_QMV_TC)
+
+
+# q|k|v and gate|up of configs[1]; ragged row counts; three linears; m up to 8 and beyond; 2-bit
+@pytest.mark.parametrize("ns,k,m,bits", [
+    ((4096, 1024, 1024), 2560, 1, 4), ((9728, 9728), 2560, 1, 4), ((200, 72), 320, 2, 4), ((128, 128, 128), 512, 8, 4),
+    ((1024, 520), 2048, 11, 4), ((17408, 17408), 5120, 1, 2), ((136, 264, 8), 1088, 3, 2)])
+def test_sibling_linears_in_one_launch_match_oracle_and_separate_calls(cuda, ns, k, m, bits):
+    """lisa_cuda_quantized_matmul_siblings: every linear's output against the oracle (the qmv bar) and against
+    its own quantized_matmul call (the same products; only the number of k-slices, hence the f32 summation
+    order, may differ: one bf16 ulp)."""
+    rng = np.random.default_rng(sum(ns) + k + m)
+    x = util.activations(rng, m, k)
+    tx = dev_bf16(x, cuda)
+    host, dev = [], []
+    for n in ns:
+        w, s, b = util.affine_weights(rng, n, k, bits, 64)
+        host.append((w, s, b))
+        dev.append((dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda)))
+    launches = ops.launch_count()
+    ys = ops.quantized_matmul_siblings(tx, dev, True, 64, bits)
+    assert ops.launch_count() - launches == (m + 7) // 8  # one launch per 8 rows for all the linears
+    for (w, s, b), (tw, ts, tb), y in zip(host, dev, ys):
+        got = O.bf16_to_f32(host_bf16_bits(y))
+        truth = O.affine_matmul(x, w, s, b, 64, bits, round_weight_bf16=False, f64=True)
+        assert util.parity(got, truth)[0] <= TOL
+        single = O.bf16_to_f32(host_bf16_bits(ops.quantized_matmul(tx, tw, ts, tb, True, 64, bits, flags=_cabi.FLAG_FORCE_QMV_TC)))
+        assert np.max(np.abs(got - single)) <= 2.0 ** -7 * np.max(np.abs(single))
+    assert ops.device_status() == 0
+
+
+def test_sibling_linears_fall_back_to_separate_calls_for_many_rows(cuda):
+    rng = np.random.default_rng(77)
+    ns, k, m = (256, 128), 512, 40
+    x = util.activations(rng, m, k)
+    tx = dev_bf16(x, cuda)
+    dev = []
+    for n in ns:
+        w, s, b = util.affine_weights(rng, n, k, 4, 64)
+        dev.append((dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda)))
+    ys = ops.quantized_matmul_siblings(tx, dev, True, 64, 4)
+    for (tw, ts, tb), y in zip(dev, ys):
+        assert torch.equal(y, ops.quantized_matmul(tx, tw, ts, tb, True, 64, 4))

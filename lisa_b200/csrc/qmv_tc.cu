@@ -98,7 +98,6 @@ struct TcParams {
     const uint16_t *seg_scales[kMaxSeg];
     const uint16_t *seg_biases[kMaxSeg];
     uint16_t *seg_out[kMaxSeg];
-    const uint8_t *seg_w[kMaxSeg];   // packed rows of segment s (affine form), for the L2 prefetch
 };
 struct TcMaps {
     CUtensorMap m[kMaxSeg];
@@ -108,13 +107,18 @@ struct TcMaps {
 struct TcPlan {
     int ring, xb, zero, xsum, sc, part, bars, total;
 };
+// Bytes of the B tile of a pair of k-blocks.  Affine form with up to four tokens: hi bytes in rows t, lo bytes
+// in rows 4 + t of ONE 8-row group (1024 bytes); the MMA still reads N = 16 rows, the second group being
+// whatever follows (the next pair's tile, or the staging area behind the last one): its eight accumulator
+// columns are never read.
+__host__ __device__ inline int tc_xtile(int m, int wbytes) { return (wbytes == kWBytes && m <= 4) ? 1024 : kXTile; }
 __host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, int m, int wbytes = kWBytes) {
     TcPlan p;
     int off = 0;
     p.ring = off;
     off += wstages * wbytes;
     p.xb = off;                       // one B tile per pair of k-blocks (swizzled)
-    off += ((max_l + 1) / 2) * kXTile;
+    off += ((max_l + 1) / 2) * tc_xtile(m, wbytes);
     p.zero = off;                     // (unused)
     p.xsum = off;                     // [max_l][8] f32 sum(x), then [max_l][8] f32 2^(E-13)
     off += 2 * max_l * 8 * 4;
@@ -307,6 +311,8 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + kNP * 2 * kACols;
     const int P = (L + 1) / 2;  // pairs of k-blocks of this slice
+    const bool compact = !GG && p.m <= 4;  // B tile of a pair in one 8-row group (see tc_xtile)
+    const uint32_t xtile = compact ? 1024u : static_cast<uint32_t>(kXTile);
     const uint32_t ring32 = smem_u32(smem + plan.ring);
     const uint32_t xb32 = smem_u32(smem + plan.xb);
     float *xsum = reinterpret_cast<float *>(smem + plan.xsum);
@@ -327,24 +333,6 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         const int ws_ring = min(ws1, ws0 + p.wstages);
         if (lane == 0)
             for (int wi = ws0; wi < ws_ring; ++wi) issue(wi);
-        // The ring holds a few stages; a load from cold DRAM takes microseconds, so the ring alone keeps too
-        // few bytes in flight per SM.  The rest of this CTA's slice -- for every row one contiguous run of
-        // the packed row -- is asked into L2 now (while the previous kernel in the stream still runs, when
-        // launched as a dependent), and the ring then refills at L2 latency.
-        if (ws_ring < ws1) {
-            const uint8_t *wb = GG ? p.wg : (seg == 0) ? p.seg_w[0] : (seg == 1) ? p.seg_w[1] : p.seg_w[2];
-            const long long rb = GG ? p.row_bytes : static_cast<long long>(p.k) * BITS / 8;
-            const long long off = static_cast<long long>(ws_ring) * ROWB;
-            const long long len = min(static_cast<long long>(ws1 - ws_ring) * ROWB, rb - off);
-            if (len > 0) {
-                for (int r = lane; r < kRows; r += 32) {
-                    if (n0 + r < seg_n)
-                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wb + static_cast<long long>(n0 + r) * rb + off),
-                                     "r"(static_cast<uint32_t>(len))
-                                     : "memory");
-                }
-            }
-        }
         if (lane == 0) {
             for (int wi = ws_ring; wi < ws1; ++wi) {
                 if (!tc_wait_relaxed(&wp_empty[s], ph, 1)) break;
@@ -370,7 +358,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 ok = __all_sync(0xffffffffu, ok && tc_wait(&a_full[st], ph, 3));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t lo0 = ((xb32 + pr * kXTile) >> 4) | (1u << 16), lo1 = lo0 + 4;  // +64 bytes: second k-block
+                const uint32_t lo0 = ((xb32 + pr * xtile) >> 4) | (1u << 16), lo1 = lo0 + 4;  // +64 bytes: second k-block
                 const uint32_t a0_addr = tmem_a + st * 2 * kACols, a1_addr = a0_addr + kACols;
                 const uint32_t d0_addr = tmem_d + st * 2 * kDCols, d1_addr = d0_addr + kDCols;
                 if (elect_one()) {
@@ -405,18 +393,13 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         // The TMEM stores of one pair complete while the next one is loaded and unpacked: their
         // completion wait, the hand-over to the MMA warp and the release of the packed stage are deferred
         // to the next trip (`pend_*`).
-        bool pending = false, pend_last = false;
-        int pend_st = 0, pend_s = 0;
+        bool pending = false;
+        int pend_st = 0;
         auto finish_pending = [&]() {
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&a_full[pend_st]);
-                // last visit of the packed stage: hand it back to the producer only now that its words are
-                // in TMEM (an arrival placed right after the loads let the refill overtake them)
-                if (pend_last) mbar_arrive(&wp_empty[pend_s]);
-            }
+            if (lane == 0) mbar_arrive(&a_full[pend_st]);
             pending = false;
         };
         constexpr int kChunksPerKb = KB_BYTES / 16;  // 16-byte chunks of one row of a k-block: 2 / 1
@@ -425,7 +408,13 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             const bool two = kbl + 1 < L;
             const int wsl = kbl / KBW, sub = kbl - wsl * KBW;  // stage of the slice, first k-block inside it (even)
             const int s = wsl % p.wstages;
-            if (sub < 4) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], (wsl / p.wstages) & 1, 4));
+            if (sub < 4) {
+                // the previous pair is handed over first if this one's packed stage has not landed yet
+                // (its hand-over is otherwise deferred to overlap the TMEM stores with this pair's unpacking)
+                const uint32_t par = (wsl / p.wstages) & 1;
+                if (pending && !__all_sync(0xffffffffu, mbar_try_wait(&wp_full[s], par))) finish_pending();
+                ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], par, 4));
+            }
             if (!ok) break;
             uint32_t o[32];
             if (GG == 2) {
@@ -480,10 +469,12 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             const uint32_t dst = a_lane + static_cast<uint32_t>(stg * 2 * kACols);
             tmem_st16(dst, o);
             if (two) tmem_st16(dst + kACols, o + 16);
+            // last visit of the packed stage: back to the producer.  The TMEM stores above were issued with
+            // the unpacked words as operands, so the shared-memory loads of the stage have completed (an
+            // arrival placed right after the loads let the refill overtake them).
+            if ((sub >= KBW - 4 || pr + 2 >= P) && lane == 0) mbar_arrive(&wp_empty[s]);
             pending = true;
             pend_st = stg;
-            pend_s = s;
-            pend_last = sub >= KBW - 4 || pr + 2 >= P;
         }
         if (pending) finish_pending();
     } else {
@@ -539,7 +530,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         // activation tiles: zero everything (rows of tokens >= m and the half of an odd last tile stay zero)
         {
             uint4 *z = reinterpret_cast<uint4 *>(smem + plan.xb);
-            const int n16 = ((L + 1) / 2) * kXTile / 16;
+            const int n16 = ((L + 1) / 2) * static_cast<int>(xtile) / 16;
             for (int i = et; i < n16; i += kEpilogueWarps * 32) z[i] = make_uint4(0, 0, 0, 0);
         }
         asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
@@ -548,7 +539,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             // one item = one word's worth of codes (CPW activations) of one token: loaded, turned into
             // integer byte pairs in the K order of the unpacked words, stored swizzled; the items of a
             // (token, k-block) are adjacent lanes and share the group's exponent and sum through
-            // shuffles.  Two rounds of loads are in flight at a time: this runs after
+            // shuffles.  Four rounds of loads are in flight at a time: this runs after
             // griddepcontrol.wait, on the critical path.
             constexpr int IPK = 64 / CPW;  // items per k-block: 8 / 4
             constexpr int NV = CPW / 8;    // 16-byte vectors per item: 1 / 2
@@ -607,16 +598,19 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                     lo[pos >> 2] |= (static_cast<uint32_t>(l) & 0xffu) << (8 * (pos & 3));
                 }
                 if (in) {
-                    const uint32_t rowaddr = xb32 + (kbl >> 1) * kXTile + t * 128;
+                    // hi bytes: row t of the first group; lo bytes: row t of the second group, or row 4 + t of the first
+                    const uint32_t tile = xb32 + (kbl >> 1) * xtile;
+                    const int rl = compact ? t + 4 : t;
+                    const uint32_t rowh = tile + t * 128, rowl = tile + (compact ? 0u : 1024u) + rl * 128;
                     const int par = kbl & 1;
                     if (BITS == 4) {
-                        const uint32_t at = rowaddr + (((par * 4 + (j >> 1)) ^ t) << 4) + (j & 1) * 8;
-                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(at), "r"(hi[0]), "r"(hi[1]) : "memory");
-                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(at + 1024), "r"(lo[0]), "r"(lo[1]) : "memory");
+                        const int chunk = par * 4 + (j >> 1), off8 = (j & 1) * 8;
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(rowh + ((chunk ^ t) << 4) + off8), "r"(hi[0]), "r"(hi[1]) : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(rowl + ((chunk ^ rl) << 4) + off8), "r"(lo[0]), "r"(lo[1]) : "memory");
                     } else {
-                        const uint32_t at = rowaddr + (((par * 4 + j) ^ t) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(hi[0]), "r"(hi[1]), "r"(hi[CPW / 4 - 2]), "r"(hi[CPW / 4 - 1]) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at + 1024), "r"(lo[0]), "r"(lo[1]), "r"(lo[CPW / 4 - 2]), "r"(lo[CPW / 4 - 1]) : "memory");
+                        const int chunk = par * 4 + j;
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rowh + ((chunk ^ t) << 4)), "r"(hi[0]), "r"(hi[1]), "r"(hi[CPW / 4 - 2]), "r"(hi[CPW / 4 - 1]) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rowl + ((chunk ^ rl) << 4)), "r"(lo[0]), "r"(lo[1]), "r"(lo[CPW / 4 - 2]), "r"(lo[CPW / 4 - 1]) : "memory");
                     }
                     if (j == 0) {
                         xsum[kbl * 8 + t] = s;
@@ -626,12 +620,16 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 }
             };
             constexpr int kStep = kEpilogueWarps * 32;
-            for (int base = 0; base < items; base += 2 * kStep) {
-                uint4 va[NV], vb[NV];
+            for (int base = 0; base < items; base += 4 * kStep) {
+                uint4 va[NV], vb[NV], vc[NV], vd[NV];
                 load_item(base + et, va);
                 load_item(base + kStep + et, vb);
+                load_item(base + 2 * kStep + et, vc);
+                load_item(base + 3 * kStep + et, vd);
                 store_item(base + et, va);
                 if (base + kStep < items) store_item(base + kStep + et, vb);
+                if (base + 2 * kStep < items) store_item(base + 2 * kStep + et, vc);
+                if (base + 3 * kStep < items) store_item(base + 3 * kStep + et, vd);
             }
         }
         if (GG) {
@@ -739,10 +737,11 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 tc_fence_after();
                 uint32_t c[2][2][MT];  // [k-block of the pair][hi, lo][token]
                 const uint32_t dp = d_lane + st * 2 * kDCols;
+                const uint32_t lo_col = compact ? 4u : 8u;  // accumulator column = row of the B tile
                 tmem_ld<MT>(dp, c[0][0]);
-                tmem_ld<MT>(dp + 8, c[0][1]);
+                tmem_ld<MT>(dp + lo_col, c[0][1]);
                 tmem_ld<MT>(dp + kDCols, c[1][0]);
-                tmem_ld<MT>(dp + kDCols + 8, c[1][1]);
+                tmem_ld<MT>(dp + kDCols + lo_col, c[1][1]);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 __syncwarp();
@@ -1030,7 +1029,6 @@ static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t 
             return fail(LISA_ERR_UNSUPPORTED, "qmv_tc: shape not supported");
         p.scales = reinterpret_cast<const uint16_t *>(scales);
         p.biases = reinterpret_cast<const uint16_t *>(biases);
-        p.seg_w[0] = reinterpret_cast<const uint8_t *>(w);
         p.x = xp + done * k;
         p.nout = nout;
         p.ldy = static_cast<int>(ldy);
@@ -1105,7 +1103,6 @@ int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int c
             p.seg_scales[i] = reinterpret_cast<const uint16_t *>(scales[i]);
             p.seg_biases[i] = reinterpret_cast<const uint16_t *>(biases[i]);
             p.seg_out[i] = reinterpret_cast<uint16_t *>(y[i]) + done * n[i];
-            p.seg_w[i] = reinterpret_cast<const uint8_t *>(w[i]);
         }
         p.scales = p.seg_scales[0];
         p.biases = p.seg_biases[0];

@@ -86,6 +86,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking poll (try_wait may suspend the thread for a while when the phase is not complete).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after `limit` polls and returns false, so a lost
 // arrival ends in an error status instead of a hung GPU.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,

@@ -66,6 +66,7 @@ constexpr int kMaxWStages = 6;        // packed-weight ring (shared memory), 16 
 constexpr int kWBytes = kRows * 128;
 constexpr int kUnpackWarps = 8, kEpilogueWarps = 4;
 constexpr int kThreads = (2 + kUnpackWarps + kEpilogueWarps) * 32;
+constexpr bool kDeferHandOver = false;  // hand a pair to the MMA warp only after the next one is unpacked
 constexpr int kMaxSeg = 3;            // linears of one launch in the sibling form (q|k|v, gate|up)
 constexpr int kXTile = 2048;          // B tile of TWO k-blocks: 16 rows (8 hi, 8 lo) x 128 bytes (2 x 64 k)
 
@@ -217,6 +218,9 @@ __device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, int code
 // The producer and the unpack warps run ahead of griddepcontrol.wait, so their waits can last as long as
 // the previous kernel in the stream: polls spaced by a short sleep, and a limit of a few seconds.
 __device__ __forceinline__ bool tc_wait_relaxed(uint64_t *bar, uint32_t parity, int code) {
+    // in the steady state a wait is short: poll first, sleep between polls only when it lasts
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
     if (mbar_wait_relaxed(bar, parity, 32, 1u << 26)) return true;
     atomicExch(&g_qmv_tc_status, code);
     return false;
@@ -353,10 +357,16 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             uint32_t ph = 0;
             // One pair of k-blocks per trip (they share a B tile), their MMAs interleaved: the two K=32 steps
             // of a k-block accumulate into the same D; steps of different k-blocks can overlap.
+            // the poll of the next pair's barrier is issued before this pair's MMAs and looked at after them
+            bool ready = false;
             for (int pr = 0; pr < P; ++pr) {
                 const bool two = 2 * pr + 1 < L;
-                ok = __all_sync(0xffffffffu, ok && tc_wait(&a_full[st], ph, 3));
+                if (!__all_sync(0xffffffffu, ready)) ok = __all_sync(0xffffffffu, ok && tc_wait(&a_full[st], ph, 3));
                 if (!ok) break;
+                {
+                    const int nst = (st + 1 == kNP) ? 0 : st + 1;
+                    ready = (pr + 1 < P) && mbar_test_wait(&a_full[nst], nst == 0 ? ph ^ 1u : ph);
+                }
                 tc_fence_after();
                 const uint32_t lo0 = ((xb32 + pr * xtile) >> 4) | (1u << 16), lo1 = lo0 + 4;  // +64 bytes: second k-block
                 const uint32_t a0_addr = tmem_a + st * 2 * kACols, a1_addr = a0_addr + kACols;
@@ -403,19 +413,28 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             pending = false;
         };
         constexpr int kChunksPerKb = KB_BYTES / 16;  // 16-byte chunks of one row of a k-block: 2 / 1
+        // packed stage of the pair, kept incrementally (no division in the loop): slot s of the ring, the
+        // parity of its `full` barrier, and the first k-block of the pair inside the stage (even)
+        int sub = 2 * set, s = 0;
+        uint32_t wpar = 0;
         for (int pr = set; pr < P; pr += 2) {
-            const int kbl = 2 * pr;
-            const bool two = kbl + 1 < L;
-            const int wsl = kbl / KBW, sub = kbl - wsl * KBW;  // stage of the slice, first k-block inside it (even)
-            const int s = wsl % p.wstages;
+            const bool two = 2 * pr + 1 < L;
             if (sub < 4) {
-                // the previous pair is handed over first if this one's packed stage has not landed yet
-                // (its hand-over is otherwise deferred to overlap the TMEM stores with this pair's unpacking)
-                const uint32_t par = (wsl / p.wstages) & 1;
-                if (pending && !__all_sync(0xffffffffu, mbar_try_wait(&wp_full[s], par))) finish_pending();
-                ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], par, 4));
+                // first visit of this set to the stage.  If it has not landed yet, the previous pair is handed
+                // over first (its hand-over is otherwise deferred to overlap the TMEM stores with this pair's
+                // unpacking)
+                if (!__all_sync(0xffffffffu, mbar_test_wait(&wp_full[s], wpar))) {
+                    if (pending) finish_pending();
+                    ok = __all_sync(0xffffffffu, tc_wait_relaxed(&wp_full[s], wpar, 4));
+                }
             }
             if (!ok) break;
+            // A stage and D buffer of this pair are free once the epilogue has read pair pr - kNP: polled here,
+            // looked at after the unpacking (a poll takes about as long as the unpacking)
+            const int stg = pr % kNP;
+            const uint32_t dpar = ((pr / kNP) - 1) & 1;
+            bool slot_free = true;
+            if (pr >= kNP) slot_free = mbar_test_wait(&d_empty[stg], dpar);
             uint32_t o[32];
             if (GG == 2) {
                 // the pair's 128 elements are the four 2-bit fields of 32 code bytes of one block
@@ -460,11 +479,8 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 }
             }
             if (pending) finish_pending();
-            // A stage and D buffer of this pair are free once the epilogue has read pair pr - kNP
-            const int stg = pr % kNP;
-            if (pr >= kNP) ok = tc_wait_relaxed(&d_empty[stg], ((pr / kNP) - 1) & 1, 6);
-            ok = __all_sync(0xffffffffu, ok);  // tcgen05.st is warp-wide
-            if (!ok) break;
+            if (!__all_sync(0xffffffffu, slot_free)) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&d_empty[stg], dpar, 6));
+            if (!ok) break;  // (warp-uniform: tcgen05.st is warp-wide)
             tc_fence_after();
             const uint32_t dst = a_lane + static_cast<uint32_t>(stg * 2 * kACols);
             tmem_st16(dst, o);
@@ -475,6 +491,13 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             if ((sub >= KBW - 4 || pr + 2 >= P) && lane == 0) mbar_arrive(&wp_empty[s]);
             pending = true;
             pend_st = stg;
+            if (!kDeferHandOver) finish_pending();
+            // next pair of this set: four k-blocks on
+            sub += 4;
+            while (sub >= KBW) {
+                sub -= KBW;
+                if (++s == p.wstages) { s = 0; wpar ^= 1; }
+            }
         }
         if (pending) finish_pending();
     } else {
@@ -730,9 +753,10 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             constexpr int MT = decltype(mt)::value;
             int st = 0;
             uint32_t ph = 0;
+            bool ready = false;  // poll of the next pair's barrier, issued before this pair's arithmetic
             for (int pr = 0; pr < P; ++pr) {
                 const bool two = 2 * pr + 1 < L;
-                ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[st], ph, 7));
+                if (!__all_sync(0xffffffffu, ready)) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[st], ph, 7));
                 if (!ok) break;
                 tc_fence_after();
                 uint32_t c[2][2][MT];  // [k-block of the pair][hi, lo][token]
@@ -746,6 +770,10 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&d_empty[st]);
+                {
+                    const int nst = (st + 1 == kNP) ? 0 : st + 1;
+                    ready = (pr + 1 < P) && mbar_test_wait(&done[nst], nst == 0 ? ph ^ 1u : ph);
+                }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (h == 1 && !two) break;

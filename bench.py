@@ -197,9 +197,12 @@ def reference_arm(args, rank: int):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus: int):
+def workload_config(n_gpus: int, launches_per_token: int = LAYERS * 7):
     return {"workload": "configs[1] decode: Qwen3-4B-shaped 4-bit gs64 linear stack, 36 layers x 7 linears, M=1",
-            "bytes_per_token": token_bytes(), "weights_per_token": token_weights(), "launches_per_token": LAYERS * 7,
+            "calls": ("q|k|v and gate|up through lisa_cuda_quantized_matmul_siblings (linears that read the same x: one "
+                      "launch), o and down through lisa_cuda_quantized_matmul"
+                      if launches_per_token < LAYERS * 7 else "one lisa_cuda_quantized_matmul call per linear"),
+            "bytes_per_token": token_bytes(), "weights_per_token": token_weights(), "launches_per_token": launches_per_token,
             "l2": "inputs larger than L2 (2.04 GB of weights per step)",
             "parallelism": "replicas only" if n_gpus > 1 else "single GPU"}
 
@@ -235,7 +238,7 @@ class DecodeStack:
         if os.environ.get("LISA_BENCH_TC", "1") == "0":  # the mma.sync kernel instead of the tensor-memory one
             self.flags |= _cabi.FLAG_FORCE_QMV
         self.graph = None
-        self.siblings = os.environ.get("LISA_BENCH_SIBLINGS", "0") == "1"
+        self.siblings = os.environ.get("LISA_BENCH_SIBLINGS", "1") == "1"
         self.calls = []  # sibling form: one argument pack per launch
         import ctypes as C
         for per in self.weights:
@@ -287,6 +290,27 @@ class DecodeStack:
             self.graph.replay()
         else:
             self.token()
+
+    def time_other_form(self, steps: int):
+        """ms per token of the other call pattern (one call per linear when the sibling form is the timed
+        one, and the reverse), graph-captured the same way."""
+        torch = self.torch
+        keep = (self.siblings, self.graph)
+        self.siblings, self.graph = (not self.siblings), None
+        try:
+            self.capture()
+            for _ in range(3):
+                self.step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                self.step()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / steps, self.launches_per_token()
+        finally:
+            self.siblings, self.graph = keep
 
     # ---- prefill: the same weights at M = PREFILL_M through the tensor-core GEMM
     def prefill_setup(self, m: int = PREFILL_M):
@@ -449,7 +473,8 @@ def main():
         line = {
             "metric": "4-bit qmv HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "u8*s8->s32, f32 epilogue", "data": "synthetic", "config": workload_config(world),
+            "vs_baseline": None, "dtype": "u8*s8->s32, f32 epilogue", "data": "synthetic",
+            "config": workload_config(world, launches_per_token),
             "pct_of_8TBps": 100.0 * per_gpu / 8000.0,
             "tokens_per_s": world * args.steps / (total_ms * 1e-3),
             "ms_per_step_median": statistics.median(step_ms),
@@ -465,6 +490,10 @@ def main():
             "clocks": clocks, "device_status": status,
             "launch": {"graph": stack.graph is not None, "pdl": bool(stack.flags & 8), "layers": args.layers},
         }
+        if args.layers == LAYERS:
+            oms, olaunch = stack.time_other_form(min(args.steps, 20))
+            line["other_call_pattern"] = {"calls": workload_config(world, olaunch)["calls"], "launches_per_token": olaunch,
+                                          "ms_per_step": oms, "value": bytes_token / (oms * 1e-3) / 1e9, "unit": "GB/s"}
         # the prefill half of the same config, briefly (full stack, M = 2048)
         stack.prefill_setup()
         pms = time_prefill(torch, stack, steps=3, warmup=2)

@@ -108,6 +108,22 @@ def test_allgather_and_peer_barrier_rejections(lib):
     assert pb(None, 0, 2, None, 1) == _cabi.ERR_BAD_ARG
 
 
+def test_sibling_linears_rejections(lib):
+    import ctypes as C
+
+    f = lib.lisa_cuda_quantized_matmul_siblings
+    ptrs = (C.c_void_p * 3)(*([0x1000] * 3))  # never dereferenced: every call below is refused on the host
+    ns = (C.c_int64 * 3)(128, 128, 128)
+    def call(count=2, w=ptrs, n=ns, tr=1, bits=4, k=256):
+        return f(None, 0x1000, 1, k, count, w, ptrs, ptrs, n, tr, 64, bits, _cabi.BF16, ptrs, 0)
+    assert call(count=0) == _cabi.ERR_BAD_ARG and call(count=4) == _cabi.ERR_BAD_ARG
+    assert call(w=None) == _cabi.ERR_BAD_ARG and call(n=None) == _cabi.ERR_BAD_ARG
+    assert call(tr=0) == _cabi.ERR_UNSUPPORTED
+    assert call(bits=3) == _cabi.ERR_UNSUPPORTED
+    assert call(k=250) == _cabi.ERR_BAD_ARG               # k not a multiple of the group size
+    assert call(n=(C.c_int64 * 3)(128, 0, 128)) == _cabi.ERR_BAD_ARG
+
+
 def test_gguf_matmul_workspace_and_rejections(lib):
     ws = lib.lisa_cuda_gguf_packed_matmul_workspace_bytes
     assert ws(512, 28 * 144, _cabi.GGUF_Q4_K) >= 2 * 512 * 7168 * 2

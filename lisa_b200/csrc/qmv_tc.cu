@@ -562,7 +562,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             // one item = one word's worth of codes (CPW activations) of one token: loaded, turned into
             // integer byte pairs in the K order of the unpacked words, stored swizzled; the items of a
             // (token, k-block) are adjacent lanes and share the group's exponent and sum through
-            // shuffles.  Four rounds of loads are in flight at a time: this runs after
+            // shuffles.  Two rounds of loads are in flight at a time: this runs after
             // griddepcontrol.wait, on the critical path.
             constexpr int IPK = 64 / CPW;  // items per k-block: 8 / 4
             constexpr int NV = CPW / 8;    // 16-byte vectors per item: 1 / 2
@@ -643,16 +643,12 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 }
             };
             constexpr int kStep = kEpilogueWarps * 32;
-            for (int base = 0; base < items; base += 4 * kStep) {
-                uint4 va[NV], vb[NV], vc[NV], vd[NV];
+            for (int base = 0; base < items; base += 2 * kStep) {
+                uint4 va[NV], vb[NV];
                 load_item(base + et, va);
                 load_item(base + kStep + et, vb);
-                load_item(base + 2 * kStep + et, vc);
-                load_item(base + 3 * kStep + et, vd);
                 store_item(base + et, va);
                 if (base + kStep < items) store_item(base + kStep + et, vb);
-                if (base + 2 * kStep < items) store_item(base + 2 * kStep + et, vc);
-                if (base + 3 * kStep < items) store_item(base + 3 * kStep + et, vd);
             }
         }
         if (GG) {

@@ -79,7 +79,7 @@ def tensor_peak():
 # ncu captures summarised in profiles/ (qmv_tc_kernel on 4 layers of the decode stack; qmm_affine_kernel
 # on 2 layers of the prefill stack).  Traffic grows in proportion to the units processed, so the ratio
 # carries over to a full launch.
-DRAM_TRAFFIC_RATIO = {"decode": 1.008, "prefill": 0.576}
+DRAM_TRAFFIC_RATIO = {"decode": 1.005, "prefill": 0.576}
 PREFILL_M = 2048
 
 

@@ -663,8 +663,15 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         if fused:
             lins = [[parallel.FusedShardedLinear(lin, max_rows=m) for lin in per] for per in lins]
 
+        # one GPU, few rows: gate and up read the same x, so they go out as one sibling launch
+        siblings = world == 1 and m <= 8 and os.environ.get("LISA_BENCH_SIBLINGS", "1") == "1"
+
         def step():
             for per in lins:
+                if siblings:
+                    ops.quantized_matmul_siblings(xs[hidden], [(l.weight, l.scales, l.biases) for l in per[:2]], True, GROUP, bits)
+                    ops.quantized_matmul(xs[inter], per[2].weight, per[2].scales, per[2].biases, True, GROUP, bits)
+                    continue
                 for lin, (k, n) in zip(per, shapes):
                     if world > 1:
                         lin.forward(xs[k])
@@ -675,7 +682,7 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         work_bytes = layers * sum(n * k * bits // 8 + 2 * n * (k // GROUP) * 2 + m * k * 2 + m * n * 2 for k, n in shapes)
         flops = 2.0 * m * weights
         name = f"configs[2]: 27B-class 2-bit gs64 MLP stack, {layers} layers x (gate, up, down), M={m}"
-        par = ("single GPU" if world == 1 else
+        par = (("single GPU, gate|up as one sibling launch" if siblings else "single GPU") if world == 1 else
                f"N-sharded over {world} ranks, all-gather fused into the GEMV epilogue (peer stores) + peer barrier" if fused
                else f"N-sharded over {world} ranks, NCCL all-gather of every output")
         scaling = "strong"

@@ -318,6 +318,8 @@ class DecodeStack:
         g = torch.Generator(device=self.dev)
         g.manual_seed(1234)
         self.pm = m
+        from lisa_b200 import _cabi
+        self.pflags = _cabi.FLAG_PDL if os.environ.get("LISA_BENCH_PREFILL_PDL", "1") != "0" else 0
         self.pin = {"h": torch.randn((m, HIDDEN), device=self.dev, generator=g).to(torch.bfloat16),
                     "a": torch.randn((m, Q_OUT), device=self.dev, generator=g).to(torch.bfloat16),
                     "i": torch.randn((m, INTER), device=self.dev, generator=g).to(torch.bfloat16)}
@@ -332,7 +334,7 @@ class DecodeStack:
             for w, s, b, _, k, n, src in per:
                 rc = lib.lisa_cuda_quantized_matmul_ex(stream, self.pin[src].data_ptr(), self.pm, k, w.data_ptr(),
                                                        s.data_ptr(), b.data_ptr(), n, 1, GROUP, BITS, 0,
-                                                       self.pout[n].data_ptr(), 0)
+                                                       self.pout[n].data_ptr(), self.pflags)
                 _cabi.check(rc)
 
     def prefill_flops(self) -> float:

@@ -71,7 +71,24 @@ struct QmmParams {
     const int32_t *tiles;
     const int32_t *tile_count;
     float *yf;        // GGUF form: f32 output [m, n]
+    // Dense affine form only: 1 or 2 k-slices per output tile.  The two CTAs of a tile (blockIdx.z) are a
+    // cluster; slice 1 hands its f32 accumulators to slice 0 through distributed shared memory.
+    int ksplit;
 };
+
+__device__ __forceinline__ uint32_t qmm_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void qmm_cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void qmm_cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// Store into the shared memory of CTA `rank` of the cluster, at the address `local_addr` has there.
+__device__ __forceinline__ void qmm_st_cluster_f32(uint32_t local_addr, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
 
 // ---- tcgen05 / TMA wrappers ----
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -284,7 +301,17 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         t0 = tile.y;
         t_end = tile.z;
     }
-    const int num_kb = p.num_kb;
+    // this CTA's k-slice: whole packed stages, [kb_off, kb_off + num_kb)
+    const bool split = !GGUF && p.ksplit > 1;
+    const uint32_t krank = split ? qmm_cluster_rank() : 0u;
+    int kb_off = 0, num_kb = p.num_kb;
+    if (split) {
+        const int total_wi = (p.num_kb + KBW - 1) / KBW;
+        const int wi0 = static_cast<int>(krank) * total_wi / p.ksplit, wi1 = static_cast<int>(krank + 1) * total_wi / p.ksplit;
+        kb_off = wi0 * KBW;
+        num_kb = min(wi1 * KBW, p.num_kb) - kb_off;
+    }
+    const int wi_off = kb_off / KBW;
 
     if (tid == 0) {
         for (int i = 0; i < ST; ++i) {
@@ -325,7 +352,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (!ok) return;
                 mbar_arrive_expect_tx(&wp_full[ws], WPB);
                 // x coordinate in elements of the map: bytes, or 32-bit words for Q2_K
-                tma_load_2d(wp + ws * WPB, &map_w, next_wi * (GGUF == 2 ? ROWB / 4 : ROWB), wrow0, &wp_full[ws]);
+                tma_load_2d(wp + ws * WPB, &map_w, (next_wi + wi_off) * (GGUF == 2 ? ROWB / 4 : ROWB), wrow0, &wp_full[ws]);
                 ++next_wi;
             };
             for (int i = 0; i < WS && next_wi < num_wi; ++i) issue_w();
@@ -336,7 +363,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (kb >= ST && ok) ok = qmm_wait(&empty[s], ph, 1);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&full[s], x_bytes);
-                tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, kb * kBK, t0, &full[s]);
+                tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, (kb + kb_off) * kBK, t0, &full[s]);
                 if (GGUF) tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + x_bytes / 2, &map_x, kb * kBK, p.m + t0, &full[s]);
                 if (++s == ST) { s = 0; ph ^= 1; }
             }
@@ -404,7 +431,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const uint32_t wp32 = smem_u32(wp) + row * ROWB;
         const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(half * 16);
         auto load_sb = [&](int kb, uint32_t &sb, uint32_t &bb) {
-            int g = (kb * kBK + half * 32) >> gshift;
+            int g = ((kb + kb_off) * kBK + half * 32) >> gshift;
             g = g < g_last ? g : g_last;
             sb = __ldg(srow + g);
             bb = __ldg(brow + g);
@@ -561,10 +588,42 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         tc_fence_after();
         const int out_row = n0 + row;
         const int chunks = p.bt / 16;
+        // Two k-slices: once both have finished their loops (both operand rings are idle), each slice
+        // writes the accumulators of the token chunks the OTHER one owns (slice 0: the first half of the
+        // chunks) as part[token of the tile][row] f32 over the owner's operand ring; the owner adds them to
+        // its own and stores that half of the tile.
+        const uint32_t part32 = smem_u32(xs);
+        const int own_lo = split ? (krank == 0 ? 0 : (chunks + 1) / 2) : 0;
+        const int own_hi = split ? (krank == 0 ? (chunks + 1) / 2 : chunks) : chunks;
+        if (split) {
+            fence_proxy_async_smem();
+            qmm_cluster_arrive();
+            qmm_cluster_wait();
+            for (int ci = dw >> 2; ci < chunks && ok; ci += kDequantWarps / 4) {
+                if (ci >= own_lo && ci < own_hi) continue;
+                uint32_t r[16];
+                tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    qmm_st_cluster_f32(part32 + static_cast<uint32_t>(((ci * 16 + j) * kBN + row) * 4), krank ^ 1u, __uint_as_float(r[j]));
+            }
+            qmm_cluster_arrive();
+            qmm_cluster_wait();
+        }
         for (int ci = dw >> 2; ci < chunks && ok; ci += kDequantWarps / 4) {
+            if (ci < own_lo || ci >= own_hi) continue;
             uint32_t r[16];
             tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
             tmem_ld_wait();
+            if (split) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float v;
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(part32 + static_cast<uint32_t>(((ci * 16 + j) * kBN + row) * 4)));
+                    r[j] = __float_as_uint(__uint_as_float(r[j]) + v);
+                }
+            }
             if (out_row < p.n) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -577,6 +636,13 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 }
             }
         }
+    }
+    if (split && warp < 2) {
+        // producer and MMA warps: both phases of the cluster barrier count every thread
+        qmm_cluster_arrive();
+        qmm_cluster_wait();
+        qmm_cluster_arrive();
+        qmm_cluster_wait();
     }
     tc_fence_before();
     __syncthreads();
@@ -642,17 +708,41 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     const size_t smem = static_cast<size_t>(QmmSmem::total(bt));
     const int64_t ytiles = tiles ? max_tiles : (m + bt - 1) / bt;
     if (ytiles > 65535) return fail(LISA_ERR_LIMIT, "qmm: too many row tiles");
-    dim3 grid(static_cast<unsigned>((n + kBN - 1) / kBN), static_cast<unsigned>(ytiles));
+    // Two k-slices per tile (a cluster of two CTAs) when the tiles fill the SMs badly: a CTA's time is its
+    // number of k-blocks (the dequantization sets the pace whatever the token tile), a launch's time the
+    // number of waves times that plus about six k-blocks of prologue and store, and the exchange of half
+    // of the 128 x bt accumulators costs about five more (measured on the configs[1] prefill shapes).
+    const int64_t ntiles = (n + kBN - 1) / kBN;
+    p.ksplit = 1;
+    if (!tiles) {
+        const int kbw = (128 * 8 / bits) / kBK;
+        const int64_t sms = sm_count(), ctas = ntiles * ytiles;
+        const int64_t t1 = ((ctas + sms - 1) / sms) * (p.num_kb + 6);          // + prologue and store
+        const int64_t t2 = ((2 * ctas + sms - 1) / sms) * (p.num_kb / 2 + 6 + 5);  // + the exchange
+        if (p.num_kb >= 4 * kbw && t2 * 100 < t1 * 93) p.ksplit = 2;
+    }
+    dim3 grid(static_cast<unsigned>(ntiles), static_cast<unsigned>(ytiles), static_cast<unsigned>(p.ksplit));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (flags & LISA_FLAG_PDL) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.ksplit > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = static_cast<unsigned>(p.ksplit);
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = (flags & LISA_FLAG_PDL) ? 1 : 0;
+    cfg.numAttrs = na;
     if (bits == 4) {
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4>, map_x, map_w, p));

@@ -334,8 +334,10 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + static_cast<uint32_t>(p.acc_cols);
+    // Launched as a dependent, only what reads or writes activations waits for the previous kernel: the
+    // activation loads of the producer and the stores of the epilogue.  Packed weights, scales and biases
+    // are constants of the model.
     pdl_launch_dependents();
-    pdl_wait();
 
     if (warp == 0) {
         // ---------------- TMA producer
@@ -356,6 +358,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 ++next_wi;
             };
             for (int i = 0; i < WS && next_wi < num_wi; ++i) issue_w();
+            pdl_wait();
             int s = 0;
             uint32_t ph = 1;  // parity of the lap before: the first lap does not wait
             for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -450,6 +453,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             // first visit of this packed-weight stage
             if (sub < 2) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wi / WS) & 1, 5));
             if (!ok) break;
+
             // packed codes of (row, k-block, half): 32 codes
             uint32_t w[4];
             uint32_t wq[8];  // GGUF: the 32 bytes whose nibble `half` are this thread's codes
@@ -583,6 +587,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
 
         // ---------------- epilogue: TMEM -> registers -> bf16 rows of y
+        pdl_wait();  // y may still be read by the previous kernel
         if (ok) ok = qmm_wait_relaxed(acc_full, 0, 7);
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-wide
         tc_fence_after();

@@ -324,12 +324,29 @@ class DecodeStack:
                     "a": torch.randn((m, Q_OUT), device=self.dev, generator=g).to(torch.bfloat16),
                     "i": torch.randn((m, INTER), device=self.dev, generator=g).to(torch.bfloat16)}
         self.pout = {n: torch.empty((m, n), dtype=torch.bfloat16, device=self.dev) for n in (Q_OUT, KV_OUT, HIDDEN, INTER)}
+        # sibling form: every linear of a launch needs its own output
+        import ctypes as C
+        self.pouts = [torch.empty((m, n), dtype=torch.bfloat16, device=self.dev) for _, _, n, _ in LINEARS]
+        self.pcalls = []
+        for per in self.weights:
+            for group in SIBLINGS:
+                c = len(group)
+                wp, sp, bp, yp, ns = (C.c_void_p * c)(), (C.c_void_p * c)(), (C.c_void_p * c)(), (C.c_void_p * c)(), (C.c_int64 * c)()
+                for j, i in enumerate(group):
+                    w, s, b, _, k, n, src = per[i]
+                    wp[j], sp[j], bp[j], yp[j], ns[j] = w.data_ptr(), s.data_ptr(), b.data_ptr(), self.pouts[i].data_ptr(), n
+                self.pcalls.append((self.pin[src].data_ptr(), k, c, wp, sp, bp, ns, yp))
 
     def prefill(self):
         from lisa_b200 import _cabi
 
         lib = _cabi.lib()
         stream = self.torch.cuda.current_stream().cuda_stream
+        if self.siblings:
+            for x, k, c, wp, sp, bp, ns, yp in self.pcalls:
+                _cabi.check(lib.lisa_cuda_quantized_matmul_siblings(stream, x, self.pm, k, c, wp, sp, bp, ns, 1, GROUP, BITS, 0, yp,
+                                                                    self.pflags))
+            return
         for per in self.weights:
             for w, s, b, _, k, n, src in per:
                 rc = lib.lisa_cuda_quantized_matmul_ex(stream, self.pin[src].data_ptr(), self.pm, k, w.data_ptr(),
@@ -503,7 +520,7 @@ def main():
         tf = stack.prefill_flops() / (pms * 1e-3) / 1e12
         line["qmm"] = {"metric": "qmm bf16 TFLOP/s", "value": tf, "m": PREFILL_M, "ms_per_pass": pms,
                        "frac_of_bf16_peak": tf / tpeak, "peak": tpeak, "peak_source": tsrc,
-                       "launches_per_pass": args.layers * 7, "kernel": "qmm_affine_kernel<4>"}
+                       "launches_per_pass": args.layers * (len(SIBLINGS) if stack.siblings else 7), "kernel": "qmm_affine_kernel<4>"}
         if not args.skip_cpu:
             layers = cpu_sample_layers()
             gbs, dt, cores = run_cpu_baseline(0, layers)
@@ -536,7 +553,7 @@ def prefill_main(args, torch, dist, stack, rank, local_rank, world, warmup):
     ms = time_prefill(torch, stack, steps=args.steps, warmup=0)
     # end to end: activations from pinned host memory in, last output back, every pass
     pinned_in = {k: v.cpu().pin_memory() for k, v in stack.pin.items()}
-    out = stack.pout[HIDDEN]
+    out = stack.pouts[-1] if stack.siblings else stack.pout[HIDDEN]
     pinned_out = torch.empty_like(out, device="cpu").pin_memory()
     h2d = sum(v.numel() * v.element_size() for v in pinned_in.values())
     d2h = pinned_out.numel() * pinned_out.element_size()

@@ -100,7 +100,9 @@ int lisa_cuda_quantized_matmul_serial_rows(lisa_stream_t stream, const void *x, 
  * output rows and writes its own [m, n[i]] output y[i]; results are those of `count` calls of
  * lisa_cuda_quantized_matmul within the f32 summation order.  For m <= 8 and shapes the
  * tensor-memory GEMV takes this is ONE launch (a decode launch costs microseconds whatever its size);
- * otherwise the linears run one after another through the dispatch of lisa_cuda_quantized_matmul. */
+ * for more than 8 rows it is one tensor-core GEMM launch whose row tiles cover all the linears (small
+ * ones no longer leave most SMs idle); otherwise the linears run one after another through the
+ * dispatch of lisa_cuda_quantized_matmul. */
 int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int64_t m, int64_t k,
                                         int count, const uint32_t *const *w,
                                         const void *const *scales, const void *const *biases,

@@ -192,6 +192,13 @@ int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int
     if (count >= 2 && m <= 8 && !(flags & (LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) &&
         qmv_tc_multi_supported(m, k, count, n, group_size, bits))
         return qmv_tc_multi(static_cast<cudaStream_t>(stream), x, m, k, count, w, scales, biases, n, group_size, bits, y, flags);
+    // many rows: one GEMM launch whose row tiles cover all the linears (they fill the waves together)
+    if (count >= 2 && m > kQmvMaxRows && !(flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE | LISA_FLAG_FORCE_QMV_TC))) {
+        bool gemm_ok = true;
+        for (int i = 0; i < count; ++i) gemm_ok = gemm_ok && qmm_affine_supported(m, k, n[i], group_size, bits);
+        if (gemm_ok)
+            return qmm_affine_multi(static_cast<cudaStream_t>(stream), x, m, k, count, w, scales, biases, n, group_size, bits, y, flags);
+    }
     for (int i = 0; i < count; ++i) {
         const int rc = quantized_matmul_impl(static_cast<cudaStream_t>(stream), x, m, k, w[i], scales[i], biases[i], n[i],
                                              transpose, group_size, bits, dtype, y[i], flags);

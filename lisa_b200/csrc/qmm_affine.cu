@@ -55,6 +55,7 @@ constexpr int kWarpsPerKb = kDequantWarps / 2;
 constexpr int kThreads = (2 + kDequantWarps) * 32;
 constexpr int kWpBytes = kBN * 128;       // 16 KiB
 
+constexpr int kMaxSeg = 3;  // linears of one launch in the sibling form (q|k|v, gate|up)
 struct QmmParams {
     const uint16_t *scales;
     const uint16_t *biases;
@@ -74,6 +75,17 @@ struct QmmParams {
     // Dense affine form only: 1 or 2 k-slices per output tile.  The two CTAs of a tile (blockIdx.z) are a
     // cluster; slice 1 hands its f32 accumulators to slice 0 through distributed shared memory.
     int ksplit;
+    // Sibling form (dense affine only): up to kMaxSeg linears that share x, m, k in one launch; segment s owns
+    // row tiles [seg_tile[s], seg_tile[s + 1]) and has its own packed rows (tensor map s), scales, biases, y.
+    int nseg;
+    int seg_tile[kMaxSeg];
+    int seg_n[kMaxSeg];
+    const uint16_t *seg_scales[kMaxSeg];
+    const uint16_t *seg_biases[kMaxSeg];
+    uint16_t *seg_y[kMaxSeg];
+};
+struct QmmMaps {
+    CUtensorMap m[kMaxSeg];
 };
 
 __device__ __forceinline__ uint32_t qmm_cluster_rank() {
@@ -264,7 +276,7 @@ struct QmmSmem {
 // byte [half_of_block*8 + shift*2], the last 16 under the next one.  The output is f32.
 template <int BITS, int GGUF = 0>
 __global__ void __launch_bounds__(kThreads, 1)
-qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ QmmMaps maps_w,
                   const QmmParams p) {
     constexpr int ST = (GGUF == 2) ? 3 : kStages;                      // operand ring stages
     constexpr int WS = (GGUF == 4) ? 3 : (GGUF == 2) ? 2 : kWpStages;  // packed ring stages
@@ -292,7 +304,16 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     constexpr int KBW = (GGUF == 2) ? 16 : (128 * 8 / BITS) / kBK;  // k-blocks per packed-weight stage: 4 (4-bit), 8 (2-bit), 16 (Q2_K)
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler too
-    const int n0 = blockIdx.x * kBN;
+    // the linear this row tile belongs to (one, unless the launch is the sibling form)
+    int xtile = blockIdx.x, seg = 0;
+    if (!GGUF && p.nseg > 1) {
+        seg = (xtile >= p.seg_tile[1]) ? 1 : 0;
+        if (p.nseg > 2 && xtile >= p.seg_tile[2]) seg = 2;
+        xtile -= (seg == 0) ? 0 : (seg == 1) ? p.seg_tile[1] : p.seg_tile[2];
+    }
+    const CUtensorMap *map_w = &maps_w.m[seg];
+    const int seg_n = (seg == 0) ? p.n : (seg == 1) ? p.seg_n[1] : p.seg_n[2];
+    const int n0 = xtile * kBN;
     int t0 = blockIdx.y * p.bt, t_end = p.m, wrow0 = n0;
     if (p.tiles) {
         if (static_cast<int>(blockIdx.y) >= __ldg(p.tile_count)) return;  // whole CTA, before any barrier
@@ -354,7 +375,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (!ok) return;
                 mbar_arrive_expect_tx(&wp_full[ws], WPB);
                 // x coordinate in elements of the map: bytes, or 32-bit words for Q2_K
-                tma_load_2d(wp + ws * WPB, &map_w, (next_wi + wi_off) * (GGUF == 2 ? ROWB / 4 : ROWB), wrow0, &wp_full[ws]);
+                tma_load_2d(wp + ws * WPB, map_w, (next_wi + wi_off) * (GGUF == 2 ? ROWB / 4 : ROWB), wrow0, &wp_full[ws]);
                 ++next_wi;
             };
             for (int i = 0; i < WS && next_wi < num_wi; ++i) issue_w();
@@ -420,9 +441,9 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // scale and bias of (k-block, half): group (kb*64 + half*32) >> log2(group_size); rows past n and
         // groups past k read a valid element instead: their products meet zero activations or unused rows
         const int gshift = (p.group_size == 32) ? 5 : (p.group_size == 64) ? 6 : 7;
-        const size_t srow_off = static_cast<size_t>(wrow0 - n0 + (grow < p.n ? grow : 0)) * p.groups;
-        const uint16_t *srow = p.scales + srow_off;
-        const uint16_t *brow = p.biases + srow_off;
+        const size_t srow_off = static_cast<size_t>(wrow0 - n0 + (grow < seg_n ? grow : 0)) * p.groups;
+        const uint16_t *srow = ((seg == 0) ? p.scales : (seg == 1) ? p.seg_scales[1] : p.seg_scales[2]) + srow_off;
+        const uint16_t *brow = ((seg == 0) ? p.biases : (seg == 1) ? p.seg_biases[1] : p.seg_biases[2]) + srow_off;
         const int g_last = p.groups - 1;
         // masks and the exponent of 2^23, pinned in registers so that every extraction is one LOP3
         uint32_t mk[8], mbits;
@@ -592,6 +613,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-wide
         tc_fence_after();
         const int out_row = n0 + row;
+        uint16_t *yseg = (seg == 0) ? p.y : (seg == 1) ? p.seg_y[1] : p.seg_y[2];
         const int chunks = p.bt / 16;
         // Two k-slices: once both have finished their loops (both operand rings are idle), each slice
         // writes the accumulators of the token chunks the OTHER one owns (slice 0: the first half of the
@@ -629,13 +651,13 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     r[j] = __float_as_uint(__uint_as_float(r[j]) + v);
                 }
             }
-            if (out_row < p.n) {
+            if (out_row < seg_n) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int tok = t0 + ci * 16 + j;
                     if (tok < t_end) {
                         if (GGUF) p.yf[static_cast<size_t>(tok) * p.n + out_row] = __uint_as_float(r[j]);
-                        else p.y[static_cast<size_t>(tok) * p.n + out_row] =
+                        else yseg[static_cast<size_t>(tok) * seg_n + out_row] =
                                  static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
                     }
                 }
@@ -680,7 +702,9 @@ bool qmm_affine_supported(int64_t m, int64_t k, int64_t n, int group_size, int b
 
 static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                       const void *biases, int64_t n, int64_t experts, int group_size, int bits, void *y, unsigned flags,
-                      int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles) {
+                      int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles, int nseg = 1,
+                      const uint32_t *const *seg_w = nullptr, const void *const *seg_scales = nullptr,
+                      const void *const *seg_biases = nullptr, const int64_t *seg_n = nullptr, void *const *seg_y = nullptr) {
     QmmParams p{};
     p.scales = reinterpret_cast<const uint16_t *>(scales);
     p.biases = reinterpret_cast<const uint16_t *>(biases);
@@ -701,14 +725,34 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     p.tiles = tiles;
     p.tile_count = tile_count;
 
-    CUtensorMap map_x, map_w;
+    CUtensorMap map_x;
+    QmmMaps maps_w{};
     int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, static_cast<uint64_t>(k),
                          static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBK, static_cast<uint32_t>(bt));
     if (rc != LISA_OK) return rc;
     const uint64_t wrow_bytes = static_cast<uint64_t>(k) * bits / 8;
-    rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, wrow_bytes, static_cast<uint64_t>(n * experts), wrow_bytes,
+    rc = make_map_2d(&maps_w.m[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, w, wrow_bytes, static_cast<uint64_t>(n * experts), wrow_bytes,
                      128, kBN);
     if (rc != LISA_OK) return rc;
+    int64_t ntiles = (n + kBN - 1) / kBN;
+    p.nseg = 1;
+    if (nseg > 1) {
+        // sibling linears: segment 0 is (w, scales, biases, n, y) above
+        p.nseg = nseg;
+        p.seg_tile[0] = 0;
+        p.seg_n[0] = static_cast<int>(n);
+        for (int i = 1; i < nseg; ++i) {
+            rc = make_map_2d(&maps_w.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, seg_w[i], wrow_bytes, static_cast<uint64_t>(seg_n[i]),
+                             wrow_bytes, 128, kBN);
+            if (rc != LISA_OK) return rc;
+            p.seg_tile[i] = static_cast<int>(ntiles);
+            p.seg_n[i] = static_cast<int>(seg_n[i]);
+            p.seg_scales[i] = reinterpret_cast<const uint16_t *>(seg_scales[i]);
+            p.seg_biases[i] = reinterpret_cast<const uint16_t *>(seg_biases[i]);
+            p.seg_y[i] = reinterpret_cast<uint16_t *>(seg_y[i]);
+            ntiles += (seg_n[i] + kBN - 1) / kBN;
+        }
+    }
 
     const size_t smem = static_cast<size_t>(QmmSmem::total(bt));
     const int64_t ytiles = tiles ? max_tiles : (m + bt - 1) / bt;
@@ -717,7 +761,6 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     // number of k-blocks (the dequantization sets the pace whatever the token tile), a launch's time the
     // number of waves times that plus about six k-blocks of prologue and store, and the exchange of half
     // of the 128 x bt accumulators costs about five more (measured on the configs[1] prefill shapes).
-    const int64_t ntiles = (n + kBN - 1) / kBN;
     p.ksplit = 1;
     if (!tiles) {
         const int kbw = (128 * 8 / bits) / kBK;
@@ -750,10 +793,10 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     cfg.numAttrs = na;
     if (bits == 4) {
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4>, map_x, map_w, p));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4>, map_x, maps_w, p));
     } else {
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<2>, map_x, map_w, p));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<2>, map_x, maps_w, p));
     }
     count_launch();
     return LISA_OK;
@@ -822,7 +865,9 @@ int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, in
     p.tmem_cols = cols;
     p.num_kb = static_cast<int>(k / kBK);
 
-    CUtensorMap map_x, map_w;
+    CUtensorMap map_x;
+    QmmMaps maps_w{};
+    CUtensorMap &map_w = maps_w.m[0];
     int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, xb, static_cast<uint64_t>(k), static_cast<uint64_t>(2 * tokens),
                          static_cast<uint64_t>(k) * 2, kBK, static_cast<uint32_t>(bt));
     if (rc != LISA_OK) return rc;
@@ -845,10 +890,10 @@ int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, in
     cfg.stream = stream;
     if (q4) {
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4, 4>, map_x, map_w, p));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4, 4>, map_x, maps_w, p));
     } else {
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<2, 2>, map_x, map_w, p));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<2, 2>, map_x, maps_w, p));
     }
     count_launch();
     return LISA_OK;
@@ -858,6 +903,17 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
                const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
     const int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
     return qmm_launch(stream, x, m, k, w, scales, biases, n, 1, group_size, bits, y, flags, bt, nullptr, nullptr, 0);
+}
+
+// Sibling linears (2 or 3 that share x, m, k, group size, bits) as one GEMM launch: linear i writes its own
+// [m, n[i]] output.  The row tiles of all of them fill the waves together.
+int qmm_affine_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
+                     const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
+                     void *const *y, unsigned flags) {
+    if (count < 2 || count > kMaxSeg) return fail(LISA_ERR_UNSUPPORTED, "qmm_affine_multi: two or three linears per launch");
+    const int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
+    return qmm_launch(stream, x, m, k, w[0], scales[0], biases[0], n[0], 1, group_size, bits, y[0], flags, bt, nullptr, nullptr, 0,
+                      count, w, scales, biases, n, y);
 }
 
 // Grouped GEMM over a tile table: rows of x sorted by expert, tile i = {expert, row_begin, row_end} with

@@ -177,3 +177,31 @@ def test_non_cuda_tensor_is_refused():
     x = torch.zeros((1, 64), dtype=torch.bfloat16)
     with pytest.raises(_cabi.LisaError):
         ops.quantized_matmul(x, w, s, s, True, 64, 4)
+
+
+@pytest.mark.parametrize("ns,k,m,bits", [((200, 1024, 72), 2048, 300, 4), ((4096, 1024, 1024), 2560, 512, 4),
+                                          ((136, 264), 1088, 40, 2), ((256, 128), 512, 40, 4)])
+def test_sibling_linears_as_one_gemm_launch(cuda, ns, k, m, bits):
+    """lisa_cuda_quantized_matmul_siblings with many rows: one tensor-core GEMM launch for all the linears;
+    every output against the oracle's GEMM law (weights rounded to bf16) and against its own
+    quantized_matmul call (same products; the number of k-slices may differ: one bf16 ulp)."""
+    from lisa_b200 import _cabi
+
+    rng = np.random.default_rng(sum(ns) + k + m)
+    x = util.activations(rng, m, k)
+    tx = dev_bf16(x, cuda)
+    host, dev = [], []
+    for n in ns:
+        w, s, b = util.affine_weights(rng, n, k, bits, 64)
+        host.append((w, s, b))
+        dev.append((dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda)))
+    launches = ops.launch_count()
+    ys = ops.quantized_matmul_siblings(tx, dev, True, 64, bits)
+    assert ops.launch_count() - launches == 1
+    for (w, s, b), (tw, ts, tb), y in zip(host, dev, ys):
+        got = O.bf16_to_f32(host_bf16_bits(y))
+        truth = O.affine_matmul(x, w, s, b, 64, bits, round_weight_bf16=True, f64=True)
+        assert util.parity(got, truth)[0] <= 1e-2
+        single = O.bf16_to_f32(host_bf16_bits(ops.quantized_matmul(tx, tw, ts, tb, True, 64, bits, flags=_cabi.FLAG_FORCE_QMM)))
+        assert np.max(np.abs(got - single)) <= 2.0 ** -7 * np.max(np.abs(single))
+    assert ops.device_status() == 0

@@ -91,17 +91,17 @@ def test_sibling_linears_in_one_launch_match_oracle_and_separate_calls(cuda, ns,
         dev.append((dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda)))
     launches = ops.launch_count()
     ys = ops.quantized_matmul_siblings(tx, dev, True, 64, bits)
-    assert ops.launch_count() - launches == (m + 7) // 8  # one launch per 8 rows for all the linears
+    assert ops.launch_count() - launches == 1  # all the linears in one launch (more than 8 rows: one GEMM launch)
     for (w, s, b), (tw, ts, tb), y in zip(host, dev, ys):
         got = O.bf16_to_f32(host_bf16_bits(y))
-        truth = O.affine_matmul(x, w, s, b, 64, bits, round_weight_bf16=False, f64=True)
+        truth = O.affine_matmul(x, w, s, b, 64, bits, round_weight_bf16=m > 8, f64=True)
         assert util.parity(got, truth)[0] <= TOL
-        single = O.bf16_to_f32(host_bf16_bits(ops.quantized_matmul(tx, tw, ts, tb, True, 64, bits, flags=_cabi.FLAG_FORCE_QMV_TC)))
+        single = O.bf16_to_f32(host_bf16_bits(ops.quantized_matmul(tx, tw, ts, tb, True, 64, bits)))
         assert np.max(np.abs(got - single)) <= 2.0 ** -7 * np.max(np.abs(single))
     assert ops.device_status() == 0
 
 
-def test_sibling_linears_fall_back_to_separate_calls_for_many_rows(cuda):
+def test_sibling_linears_with_many_rows_equal_separate_calls(cuda):
     rng = np.random.default_rng(77)
     ns, k, m = (256, 128), 512, 40
     x = util.activations(rng, m, k)

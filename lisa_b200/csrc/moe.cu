@@ -119,15 +119,24 @@ __global__ void __launch_bounds__(kSortChunk) moe_sort_hist_kernel(const int32_t
 // counts[chunk][e] -> exclusive start of (e, chunk) in the sorted order.
 __global__ void __launch_bounds__(1024) moe_sort_scan_kernel(int32_t *__restrict__ counts, int chunks, int experts) {
     extern __shared__ int32_t totals[];  // experts + 1
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    // exclusive scan over the chunks of every expert: one warp per expert, 32 chunks per trip
+    const int lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int e = threadIdx.x >> 5; e < experts; e += nwarps) {
         int run = 0;
-        for (int c = 0; c < chunks; ++c) {
+        for (int c0 = 0; c0 < chunks; c0 += 32) {
+            const int c = c0 + lane;
             const int64_t at = static_cast<int64_t>(c) * experts + e;
-            const int v = counts[at];
-            counts[at] = run;
-            run += v;
+            const int v = c < chunks ? counts[at] : 0;
+            int inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) inc += n;
+            }
+            if (c < chunks) counts[at] = run + inc - v;
+            run += __shfl_sync(0xffffffffu, inc, 31);
         }
-        totals[e] = run;
+        if (lane == 0) totals[e] = run;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -139,10 +148,8 @@ __global__ void __launch_bounds__(1024) moe_sort_scan_kernel(int32_t *__restrict
         }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-        const int base = totals[e];
-        for (int c = 0; c < chunks; ++c) counts[static_cast<int64_t>(c) * experts + e] += base;
-    }
+    const int64_t cells = static_cast<int64_t>(chunks) * experts;
+    for (int64_t i = threadIdx.x; i < cells; i += blockDim.x) counts[i] += totals[i % experts];
 }
 
 __global__ void __launch_bounds__(kSortChunk) moe_sort_scatter_kernel(const int32_t *__restrict__ idx, int slots,
@@ -255,24 +262,56 @@ int moe_gather_rows(cudaStream_t stream, const void *x, const int32_t *token_row
 // ---------------------------------------------------------------- SwiGLU
 __device__ __forceinline__ float round_bf16(float v) { return bf16_bits_to_f32(f32_to_bf16_bits(v)); }
 
+// act = bf16(silu * u), silu = bf16(g * s), s = bf16(sigmoid(g)) evaluated as 1 / (1 + exp(|g|)) mirrored by sign
+__device__ __forceinline__ uint16_t swiglu_bits(uint16_t gb, uint16_t ub) {
+    const float g = bf16_bits_to_f32(gb), u = bf16_bits_to_f32(ub);
+    const float y = 1.0f / (1.0f + expf(fabsf(g)));
+    const float s = round_bf16(g < 0.f ? y : 1.0f - y);
+    const float silu = round_bf16(g * s);
+    return static_cast<uint16_t>(f32_to_bf16_bits(silu * u));
+}
+
 __global__ void __launch_bounds__(256) moe_swiglu_kernel(const uint16_t *__restrict__ gate,
                                                          const uint16_t *__restrict__ up, int64_t count,
                                                          uint16_t *__restrict__ act) {
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= count) return;
-    const float g = bf16_bits_to_f32(__ldg(gate + i)), u = bf16_bits_to_f32(__ldg(up + i));
-    const float y = 1.0f / (1.0f + expf(fabsf(g)));
-    const float s = round_bf16(g < 0.f ? y : 1.0f - y);
-    const float silu = round_bf16(g * s);
-    act[i] = static_cast<uint16_t>(f32_to_bf16_bits(silu * u));
+    act[i] = swiglu_bits(__ldg(gate + i), __ldg(up + i));
+}
+
+// Eight elements per thread (16-byte loads and stores); count8 = count / 8.
+__global__ void __launch_bounds__(256) moe_swiglu8_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
+                                                          int64_t count8, uint4 *__restrict__ act) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count8) return;
+    const uint4 g = __ldg(gate + i), u = __ldg(up + i);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        o[j] = static_cast<uint32_t>(swiglu_bits(static_cast<uint16_t>(gw[j] & 0xffffu), static_cast<uint16_t>(uw[j] & 0xffffu))) |
+               (static_cast<uint32_t>(swiglu_bits(static_cast<uint16_t>(gw[j] >> 16), static_cast<uint16_t>(uw[j] >> 16))) << 16);
+    act[i] = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 int moe_swiglu(cudaStream_t stream, const void *gate, const void *up, int64_t count, void *act) {
-    moe_swiglu_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(
-        reinterpret_cast<const uint16_t *>(gate), reinterpret_cast<const uint16_t *>(up), count,
-        reinterpret_cast<uint16_t *>(act));
-    LISA_CUDA_TRY(cudaGetLastError());
-    count_launch();
+    const uint16_t *g16 = reinterpret_cast<const uint16_t *>(gate), *u16 = reinterpret_cast<const uint16_t *>(up);
+    uint16_t *a16 = reinterpret_cast<uint16_t *>(act);
+    int64_t done = 0;
+    if (aligned16(gate) && aligned16(up) && aligned16(act) && count >= 8) {
+        const int64_t count8 = count / 8;
+        moe_swiglu8_kernel<<<static_cast<unsigned>((count8 + 255) / 256), 256, 0, stream>>>(
+            reinterpret_cast<const uint4 *>(gate), reinterpret_cast<const uint4 *>(up), count8, reinterpret_cast<uint4 *>(act));
+        LISA_CUDA_TRY(cudaGetLastError());
+        count_launch();
+        done = count8 * 8;
+    }
+    if (done < count) {
+        moe_swiglu_kernel<<<static_cast<unsigned>((count - done + 255) / 256), 256, 0, stream>>>(g16 + done, u16 + done,
+                                                                                                count - done, a16 + done);
+        LISA_CUDA_TRY(cudaGetLastError());
+        count_launch();
+    }
     return LISA_OK;
 }
 
@@ -302,9 +341,52 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t *__rest
     out[i] = static_cast<uint16_t>(f32_to_bf16_bits(total));
 }
 
+// The same fold for eight consecutive h per thread (hidden a multiple of 8, 16-byte rows): one 16-byte load
+// per slot instead of eight 2-byte ones; every element keeps its own sum in the same order.
+__global__ void __launch_bounds__(256) moe_combine8_kernel(const uint4 *__restrict__ down, const float *__restrict__ weights,
+                                                           const int32_t *__restrict__ inverse, int64_t tokens, int top_k,
+                                                           int64_t hidden8, uint4 *__restrict__ out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= tokens * hidden8) return;
+    const int64_t t = i / hidden8, h8 = i - t * hidden8;
+    const int ty = top_k < 8 ? top_k : 8;
+    float total[8];
+    for (int y = 0; y < ty; ++y) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int rr = y; rr < top_k; rr += ty) {
+            const int64_t row = __ldg(inverse + t * top_k + rr);
+            const float w = __ldg(weights + t * top_k + rr);
+            const uint4 v = __ldg(down + row * hidden8 + h8);
+            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[2 * e] = bf16_bits_to_f32(vw[e] & 0xffffu) * w + acc[2 * e];
+                acc[2 * e + 1] = __uint_as_float(vw[e] & 0xffff0000u) * w + acc[2 * e + 1];
+            }
+        }
+        // total = part[0]; total = part[j] + total
+#pragma unroll
+        for (int e = 0; e < 8; ++e) total[e] = (y == 0) ? acc[e] : acc[e] + total[e];
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = f32_to_bf16_bits(total[2 * e]) | (f32_to_bf16_bits(total[2 * e + 1]) << 16);
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 int moe_combine(cudaStream_t stream, const void *down_sorted, const float *weights, const int32_t *inverse,
                 int64_t tokens, int top_k, int64_t hidden, void *out) {
     const int64_t total = tokens * hidden;
+    if (hidden % 8 == 0 && aligned16(down_sorted) && aligned16(out)) {
+        const int64_t total8 = total / 8;
+        moe_combine8_kernel<<<static_cast<unsigned>((total8 + 255) / 256), 256, 0, stream>>>(
+            reinterpret_cast<const uint4 *>(down_sorted), weights, inverse, tokens, top_k, hidden / 8, reinterpret_cast<uint4 *>(out));
+        LISA_CUDA_TRY(cudaGetLastError());
+        count_launch();
+        return LISA_OK;
+    }
     moe_combine_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
         reinterpret_cast<const uint16_t *>(down_sorted), weights, inverse, tokens, top_k, hidden,
         reinterpret_cast<uint16_t *>(out));

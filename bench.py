@@ -678,9 +678,9 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         xs = {hidden: torch.randn((m, hidden), device=dev, generator=g).to(torch.bfloat16),
               inter: torch.randn((m, inter), device=dev, generator=g).to(torch.bfloat16)}
 
-        # m <= 8: the GEMV whose epilogue stores into every rank's buffer + peer barrier (no NCCL on the data
-        # path); LISA_BENCH_FUSED=0 or more rows: local GEMM + NCCL all-gather
-        fused = world > 1 and m <= 8 and os.environ.get("LISA_BENCH_FUSED", "1") != "0"
+        # the GEMV (m <= 8) or GEMM whose epilogue stores into every rank's buffer + peer barrier (no NCCL on
+        # the data path); LISA_BENCH_FUSED=0: local kernel + NCCL all-gather
+        fused = world > 1 and os.environ.get("LISA_BENCH_FUSED", "1") != "0"
         if fused:
             lins = [[parallel.FusedShardedLinear(lin, max_rows=m) for lin in per] for per in lins]
 
@@ -704,7 +704,7 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         flops = 2.0 * m * weights
         name = f"configs[2]: 27B-class 2-bit gs64 MLP stack, {layers} layers x (gate, up, down), M={m}"
         par = (("single GPU, gate|up as one sibling launch" if siblings else "single GPU") if world == 1 else
-               f"N-sharded over {world} ranks, all-gather fused into the GEMV epilogue (peer stores) + peer barrier" if fused
+               f"N-sharded over {world} ranks, all-gather fused into the {'GEMV' if m <= 8 else 'GEMM'} epilogue (peer stores) + peer barrier" if fused
                else f"N-sharded over {world} ranks, NCCL all-gather of every output")
         scaling = "strong"
     else:
@@ -748,7 +748,7 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         step()
     torch.cuda.synchronize()
     graphed = False
-    fused_mode = args.mode == "shard" and world > 1 and args.m <= 8 and os.environ.get("LISA_BENCH_FUSED", "1") != "0"
+    fused_mode = args.mode == "shard" and world > 1 and os.environ.get("LISA_BENCH_FUSED", "1") != "0"
     if (world == 1 or fused_mode) and os.environ.get("LISA_BENCH_GRAPH", "1") != "0":
         # no collective library inside the step (one GPU, or the fused GEMV + peer barrier form), so it
         # replays from a CUDA graph like the decode stack (eager launches through the Python mirror are

@@ -111,7 +111,8 @@ int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int
 
 /* N-sharded decode linear fused with its all-gather (one node, up to 8 GPUs, one process per GPU).
  * No counterpart in the reference, which runs on one device: this is the multi-GPU form of
- * ops::quantized_matmul for m <= 8 rows and group size 64.  The caller holds rows
+ * ops::quantized_matmul: up to 8 rows (group size 64) through the tensor-memory GEMV, more rows through
+ * the tensor-core GEMM; in both the kernel's own epilogue does the all-gather.  The caller holds rows
  * [col0, col0 + n_local) of an n_total-row linear; y_all[r] is rank r's [m, n_total] output buffer as
  * seen from this GPU (its own buffer and peer mappings of the others', e.g. CUDA IPC or
  * cuMemMap'd symmetric memory with peer access enabled).  The kernel's epilogue stores this rank's

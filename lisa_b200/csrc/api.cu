@@ -170,8 +170,15 @@ int lisa_cuda_quantized_matmul_allgather(lisa_stream_t stream, const void *x, in
     if (rc != LISA_OK) return rc;
     if (col0 < 0 || n_total < 1 || col0 + n_local > n_total || n_total > (1ll << 30))
         return fail(LISA_ERR_BAD_ARG, "quantized_matmul_allgather: column block outside the output");
-    if (m > 8 || !qmv_tc_supported(m, k, n_local, group_size, bits))
-        return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_allgather: needs m <= 8 and a shape the tensor-memory GEMV takes");
+    if (m > kQmvMaxRows) {
+        // many rows: the tensor-core GEMM, whose epilogue stores the tile into every rank's output
+        if (!qmm_affine_supported(m, k, n_local, group_size, bits))
+            return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_allgather: shape not supported by the GEMM kernel");
+        return qmm_affine_allgather(static_cast<cudaStream_t>(stream), x, m, k, w, scales, biases, n_local, group_size, bits,
+                                    y_all, world, n_total, col0, flags);
+    }
+    if (!qmv_tc_supported(m, k, n_local, group_size, bits))
+        return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_allgather: up to 8 rows need a shape the tensor-memory GEMV takes");
     return qmv_tc_allgather(static_cast<cudaStream_t>(stream), x, m, k, w, scales, biases, n_local, group_size, bits, y_all,
                             world, n_total, col0, flags);
 }

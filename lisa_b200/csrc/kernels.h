@@ -38,6 +38,9 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
 int qmm_affine_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
                      const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
                      void *const *y, unsigned flags);
+int qmm_affine_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                         const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
+                         int64_t n_total, int64_t col0, unsigned flags);
 int qmm_affine_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
                        const void *scales, const void *biases, int64_t experts, int64_t n, int group_size, int bits,
                        void *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles);

@@ -83,6 +83,10 @@ struct QmmParams {
     const uint16_t *seg_scales[kMaxSeg];
     const uint16_t *seg_biases[kMaxSeg];
     uint16_t *seg_y[kMaxSeg];
+    // N-sharded form fused with its all-gather (dense affine, one linear): the tile is stored at columns
+    // col0 + row of every rank's [m, ldy] output (outs[0 .. nout): this GPU's buffer and peer mappings).
+    int nout, ldy, col0;
+    uint16_t *outs[8];
 };
 struct QmmMaps {
     CUtensorMap m[kMaxSeg];
@@ -656,9 +660,16 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 for (int j = 0; j < 16; ++j) {
                     const int tok = t0 + ci * 16 + j;
                     if (tok < t_end) {
-                        if (GGUF) p.yf[static_cast<size_t>(tok) * p.n + out_row] = __uint_as_float(r[j]);
-                        else yseg[static_cast<size_t>(tok) * seg_n + out_row] =
-                                 static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
+                        if (GGUF) {
+                            p.yf[static_cast<size_t>(tok) * p.n + out_row] = __uint_as_float(r[j]);
+                        } else if (p.nout > 0) {
+                            const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
+                            const size_t at = static_cast<size_t>(tok) * p.ldy + p.col0 + out_row;
+                            for (int o = 0; o < p.nout; ++o) p.outs[o][at] = v;  // plain stores, peers' memory included
+                        } else {
+                            yseg[static_cast<size_t>(tok) * seg_n + out_row] =
+                                static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
+                        }
                     }
                 }
             }
@@ -704,8 +715,13 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
                       const void *biases, int64_t n, int64_t experts, int group_size, int bits, void *y, unsigned flags,
                       int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles, int nseg = 1,
                       const uint32_t *const *seg_w = nullptr, const void *const *seg_scales = nullptr,
-                      const void *const *seg_biases = nullptr, const int64_t *seg_n = nullptr, void *const *seg_y = nullptr) {
+                      const void *const *seg_biases = nullptr, const int64_t *seg_n = nullptr, void *const *seg_y = nullptr,
+                      void *const *outs = nullptr, int nout = 0, int64_t ldy = 0, int64_t col0 = 0) {
     QmmParams p{};
+    p.nout = nout;
+    p.ldy = static_cast<int>(ldy);
+    p.col0 = static_cast<int>(col0);
+    for (int o = 0; o < nout; ++o) p.outs[o] = reinterpret_cast<uint16_t *>(outs[o]);
     p.scales = reinterpret_cast<const uint16_t *>(scales);
     p.biases = reinterpret_cast<const uint16_t *>(biases);
     p.y = reinterpret_cast<uint16_t *>(y);
@@ -903,6 +919,16 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
                const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
     const int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
     return qmm_launch(stream, x, m, k, w, scales, biases, n, 1, group_size, bits, y, flags, bt, nullptr, nullptr, 0);
+}
+
+// N-sharded GEMM fused with its all-gather: this rank's rows [col0, col0 + n) of an n_total-row linear, stored
+// by the epilogue as columns of every rank's [m, n_total] output (outs[0 .. world), peer pointers included).
+int qmm_affine_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                         const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
+                         int64_t n_total, int64_t col0, unsigned flags) {
+    const int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
+    return qmm_launch(stream, x, m, k, w, scales, biases, n, 1, group_size, bits, outs[0], flags, bt, nullptr, nullptr, 0, 1,
+                      nullptr, nullptr, nullptr, nullptr, nullptr, outs, world, n_total, col0);
 }
 
 // Sibling linears (2 or 3 that share x, m, k, group size, bits) as one GEMM launch: linear i writes its own

@@ -239,8 +239,9 @@ class PeerBuffers:
 
 
 class FusedShardedLinear:
-    """`ShardedQuantizedLinear` for m <= 8 without a collective library: the GEMV's epilogue stores this
-    rank's column block into every rank's output buffer, and `lisa_cuda_peer_barrier` orders the ranks."""
+    """`ShardedQuantizedLinear` without a collective library: the epilogue of the GEMV (up to 8 rows) or of the
+    tensor-core GEMM (more rows) stores this rank's column block into every rank's output buffer, and
+    `lisa_cuda_peer_barrier` orders the ranks."""
 
     def __init__(self, shard: ShardedQuantizedLinear, max_rows: int = 8, group=None):
         self.shard = shard

@@ -101,7 +101,6 @@ def test_allgather_and_peer_barrier_rejections(lib):
     assert call(tbl=None) == _cabi.ERR_BAD_ARG
     assert call(tr=0) == _cabi.ERR_UNSUPPORTED
     assert call(col0=200) == _cabi.ERR_BAD_ARG          # block past the end of the output
-    assert call(m=9) == _cabi.ERR_UNSUPPORTED            # more rows than the GEMV takes
     assert call(gs=128) == _cabi.ERR_UNSUPPORTED         # the tensor-memory GEMV is group size 64
     assert pb(None, 2, 2, table, 1) == _cabi.ERR_BAD_ARG  # rank outside the world
     assert pb(None, 0, 0, table, 1) == _cabi.ERR_BAD_ARG

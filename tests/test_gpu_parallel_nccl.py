@@ -48,8 +48,9 @@ def _worker(rank, world, port, out):
         # f32 summation order may too: a bf16 ulp, not equality
         ok[f"linear_m{m}"] = bool((y.float() - full.float()).abs().max() <= 1e-2 * full.float().abs().max())
     # ---- the same linear without NCCL: GEMV epilogue stores into every rank's buffer + peer barrier
-    fused = parallel.FusedShardedLinear(lin)
-    for m in (1, 8):
+    # (up to 8 rows), or the GEMM's epilogue does (more rows)
+    fused = parallel.FusedShardedLinear(lin, max_rows=300)
+    for m in (1, 8, 40, 300):
         x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
         full = ops.quantized_matmul(x, w, s, b, True, 64, bits)
         for rep in range(3):  # the buffers are reused: the barrier epochs must keep the ranks in step

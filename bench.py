@@ -681,7 +681,11 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         # the GEMV (m <= 8) or GEMM whose epilogue stores into every rank's buffer + peer barrier (no NCCL on
         # the data path); LISA_BENCH_FUSED=0: local kernel + NCCL all-gather
         fused = world > 1 and os.environ.get("LISA_BENCH_FUSED", "1") != "0"
-        if fused:
+        fused_sib = fused and m <= 8 and os.environ.get("LISA_BENCH_SIBLINGS", "1") == "1"
+        if fused_sib:  # gate|up: one launch and one barrier for both
+            lins = [[parallel.FusedShardedSiblings(per[:2], max_rows=m), parallel.FusedShardedLinear(per[2], max_rows=m)]
+                    for per in lins]
+        elif fused:
             lins = [[parallel.FusedShardedLinear(lin, max_rows=m) for lin in per] for per in lins]
 
         # one GPU, few rows: gate and up read the same x, so they go out as one sibling launch
@@ -689,6 +693,10 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
 
         def step():
             for per in lins:
+                if fused_sib:
+                    per[0].forward(xs[hidden])
+                    per[1].forward(xs[inter])
+                    continue
                 if siblings:
                     ops.quantized_matmul_siblings(xs[hidden], [(l.weight, l.scales, l.biases) for l in per[:2]], True, GROUP, bits)
                     ops.quantized_matmul(xs[inter], per[2].weight, per[2].scales, per[2].biases, True, GROUP, bits)
@@ -704,7 +712,7 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
         flops = 2.0 * m * weights
         name = f"configs[2]: 27B-class 2-bit gs64 MLP stack, {layers} layers x (gate, up, down), M={m}"
         par = (("single GPU, gate|up as one sibling launch" if siblings else "single GPU") if world == 1 else
-               f"N-sharded over {world} ranks, all-gather fused into the {'GEMV' if m <= 8 else 'GEMM'} epilogue (peer stores) + peer barrier" if fused
+               f"N-sharded over {world} ranks, all-gather fused into the {'GEMV' if m <= 8 else 'GEMM'} epilogue (peer stores) + peer barrier{', gate|up as one sibling launch' if fused_sib else ''}" if fused
                else f"N-sharded over {world} ranks, NCCL all-gather of every output")
         scaling = "strong"
     else:

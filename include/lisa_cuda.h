@@ -128,6 +128,19 @@ int lisa_cuda_quantized_matmul_allgather(lisa_stream_t stream, const void *x, in
                                          int64_t n_local, int transpose, int group_size, int bits, int dtype,
                                          void *const *y_all, int world, int64_t n_total, int64_t col0,
                                          unsigned flags);
+/* Sibling linears (lisa_cuda_quantized_matmul_siblings) that are N-sharded and fused with their
+ * all-gather: linear i holds rows [col0[i], col0[i] + n_local[i]) of an n_total[i]-row linear and
+ * y_all[i * world + r] is rank r's [m, n_total[i]] output buffer of linear i as seen from this GPU.
+ * One launch for up to 8 rows; otherwise one lisa_cuda_quantized_matmul_allgather per linear.  One
+ * lisa_cuda_peer_barrier after it covers all the linears. */
+int lisa_cuda_quantized_matmul_siblings_allgather(lisa_stream_t stream, const void *x, int64_t m, int64_t k,
+                                                  int count, const uint32_t *const *w,
+                                                  const void *const *scales, const void *const *biases,
+                                                  const int64_t *n_local, int transpose, int group_size,
+                                                  int bits, int dtype, void *const *y_all, int world,
+                                                  const int64_t *n_total, const int64_t *col0,
+                                                  unsigned flags);
+
 int lisa_cuda_peer_barrier(lisa_stream_t stream, int rank, int world, void *const *flag_arrays,
                            uint64_t epoch);
 

@@ -44,6 +44,7 @@ SIGNATURES = {
     "lisa_cuda_quantized_matmul_serial_rows": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _vp]),
     "lisa_cuda_quantized_matmul_allgather": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _vp, _int, _i64, _i64, _u]),
     "lisa_cuda_quantized_matmul_siblings": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _vp, _u]),
+    "lisa_cuda_quantized_matmul_siblings_allgather": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _vp, _int, _vp, _vp, _u]),
     "lisa_cuda_peer_barrier": (_int, [_vp, _int, _int, _vp, C.c_uint64]),
     "lisa_cuda_dequantize": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp]),
     "lisa_cuda_gather_qmm_workspace_bytes": (_sz, [_i64, _i64]),

@@ -214,6 +214,37 @@ int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int
     return LISA_OK;
 }
 
+int lisa_cuda_quantized_matmul_siblings_allgather(lisa_stream_t stream, const void *x, int64_t m, int64_t k, int count,
+                                                  const uint32_t *const *w, const void *const *scales,
+                                                  const void *const *biases, const int64_t *n_local, int transpose,
+                                                  int group_size, int bits, int dtype, void *const *y_all, int world,
+                                                  const int64_t *n_total, const int64_t *col0, unsigned flags) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_siblings_allgather: only transpose=true supported");
+    if (count < 1 || count > 3 || !w || !scales || !biases || !n_local || !y_all || !n_total || !col0)
+        return fail(LISA_ERR_BAD_ARG, "quantized_matmul_siblings_allgather: one to three linears, non-null tables");
+    if (world < 1 || world > 8) return fail(LISA_ERR_BAD_ARG, "quantized_matmul_siblings_allgather: 1 to 8 output buffers per linear");
+    for (int i = 0; i < count; ++i) {
+        for (int r = 0; r < world; ++r)
+            if (!y_all[i * world + r] || (reinterpret_cast<uintptr_t>(y_all[i * world + r]) & 1u))
+                return fail(LISA_ERR_BAD_ARG, "quantized_matmul_siblings_allgather: null or misaligned output buffer");
+        const int rc = check_affine("quantized_matmul_siblings_allgather", x, m, k, w[i], scales[i], biases[i], n_local[i], group_size,
+                                    bits, dtype, y_all[i * world]);
+        if (rc != LISA_OK) return rc;
+        if (col0[i] < 0 || n_total[i] < 1 || col0[i] + n_local[i] > n_total[i] || n_total[i] > (1ll << 30))
+            return fail(LISA_ERR_BAD_ARG, "quantized_matmul_siblings_allgather: column block outside the output");
+    }
+    // one launch when the tensor-memory GEMV takes the rows; otherwise one fused launch per linear
+    if (count >= 2 && m <= kQmvMaxRows && qmv_tc_multi_supported(m, k, count, n_local, group_size, bits))
+        return qmv_tc_multi(static_cast<cudaStream_t>(stream), x, m, k, count, w, scales, biases, n_local, group_size, bits, y_all,
+                            flags, world, n_total, col0);
+    for (int i = 0; i < count; ++i) {
+        const int rc = lisa_cuda_quantized_matmul_allgather(stream, x, m, k, w[i], scales[i], biases[i], n_local[i], transpose,
+                                                            group_size, bits, dtype, y_all + i * world, world, n_total[i], col0[i], flags);
+        if (rc != LISA_OK) return rc;
+    }
+    return LISA_OK;
+}
+
 int lisa_cuda_peer_barrier(lisa_stream_t stream, int rank, int world, void *const *flag_arrays, uint64_t epoch) {
     if (!flag_arrays || world < 1 || world > 8 || rank < 0 || rank >= world)
         return fail(LISA_ERR_BAD_ARG, "peer_barrier: bad rank or world");

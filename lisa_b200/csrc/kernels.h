@@ -24,7 +24,8 @@ int qmv_tc_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, c
 bool qmv_tc_multi_supported(int64_t m, int64_t k, int count, const int64_t *n, int group_size, int bits);
 int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
                  const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
-                 void *const *y, unsigned flags);
+                 void *const *y, unsigned flags, int world = 0, const int64_t *n_total = nullptr,
+                 const int64_t *col0 = nullptr);
 bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes);
 int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
                 int64_t tokens, float *y);

@@ -99,6 +99,12 @@ struct TcParams {
     const uint16_t *seg_scales[kMaxSeg];
     const uint16_t *seg_biases[kMaxSeg];
     uint16_t *seg_out[kMaxSeg];
+    // sibling form fused with the all-gather of N-sharded linears: segment s is stored at columns
+    // seg_col0[s] + row of every rank's [m, seg_ldy[s]] output of that linear (seg_nout of them; 0: not used)
+    int seg_nout;
+    int seg_ldy[kMaxSeg];
+    int seg_col0[kMaxSeg];
+    uint16_t *seg_outs[kMaxSeg][8];
 };
 struct TcMaps {
     CUtensorMap m[kMaxSeg];
@@ -924,6 +930,10 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                     const size_t at = static_cast<size_t>(t) * ldy + p.col0 + n0 + row;
                     if (GG) {
                         p.yf[at] = tot;
+                    } else if (p.nseg > 1 && p.seg_nout > 0) {
+                        const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(tot));
+                        const size_t ag = static_cast<size_t>(t) * p.seg_ldy[seg] + p.seg_col0[seg] + n0 + row;
+                        for (int o = 0; o < p.seg_nout; ++o) p.seg_outs[seg][o][ag] = v;  // peers' memory included
                     } else {
                         const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(tot));
                         out0[at] = v;
@@ -1095,9 +1105,11 @@ bool qmv_tc_multi_supported(int64_t m, int64_t k, int count, const int64_t *n, i
     return tc_make_plan(n[0], k, group_size, bits, static_cast<int>(std::min<int64_t>(m, 8)), p, smem, grid, mc, kWBytes, 0, tiles);
 }
 
+// With `world` > 0 the launch is also the all-gather of N-sharded siblings: y holds count x world pointers
+// (linear i, rank r at y[i * world + r]), linear i's rows are columns [col0[i], col0[i] + n[i]) of n_total[i].
 int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
                  const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
-                 void *const *y, unsigned flags) {
+                 void *const *y, unsigned flags, int world, const int64_t *n_total, const int64_t *col0) {
     if (count < 2 || count > kMaxSeg) return fail(LISA_ERR_UNSUPPORTED, "qmv_tc_multi: two or three linears per launch");
     const uint16_t *xp = reinterpret_cast<const uint16_t *>(x);
     TcMaps maps{};
@@ -1126,8 +1138,17 @@ int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int c
             p.seg_n[i] = static_cast<int>(n[i]);
             p.seg_scales[i] = reinterpret_cast<const uint16_t *>(scales[i]);
             p.seg_biases[i] = reinterpret_cast<const uint16_t *>(biases[i]);
-            p.seg_out[i] = reinterpret_cast<uint16_t *>(y[i]) + done * n[i];
+            if (world > 0) {
+                p.seg_ldy[i] = static_cast<int>(n_total[i]);
+                p.seg_col0[i] = static_cast<int>(col0[i]);
+                for (int r = 0; r < world; ++r)
+                    p.seg_outs[i][r] = reinterpret_cast<uint16_t *>(y[i * world + r]) + done * n_total[i];
+                p.seg_out[i] = p.seg_outs[i][0];
+            } else {
+                p.seg_out[i] = reinterpret_cast<uint16_t *>(y[i]) + done * n[i];
+            }
         }
+        p.seg_nout = world > 0 ? world : 0;
         p.scales = p.seg_scales[0];
         p.biases = p.seg_biases[0];
         p.out[0] = p.seg_out[0];

@@ -265,3 +265,44 @@ class FusedShardedLinear:
         # epoch 0: the barrier counts itself on the device, so the pair of launches replays from a CUDA graph
         _cabi.check(lib.lisa_cuda_peer_barrier(st, self.out.rank, self.out.world, self.flags.ptrs(), 0))
         return self.out.local[:m]
+
+
+class FusedShardedSiblings:
+    """Several `ShardedQuantizedLinear`s that read the same x (gate|up, q|k|v): one launch whose epilogue stores
+    every linear's column block into every rank's buffers, then ONE peer barrier."""
+
+    def __init__(self, shards, max_rows: int = 8, group=None):
+        import ctypes as C
+
+        self.shards = list(shards)
+        self.outs = [PeerBuffers((max_rows, sh.n_total), torch.bfloat16, group) for sh in self.shards]
+        self.flags = PeerBuffers((16,), torch.int64, group)
+        c, world = len(self.shards), self.outs[0].world
+        self.world, self.rank = world, self.outs[0].rank
+        self._w, self._s, self._b = (C.c_void_p * c)(), (C.c_void_p * c)(), (C.c_void_p * c)()
+        self._n, self._nt, self._c0 = (C.c_int64 * c)(), (C.c_int64 * c)(), (C.c_int64 * c)()
+        self._y = (C.c_void_p * (c * world))()
+        for i, sh in enumerate(self.shards):
+            self._w[i], self._s[i], self._b[i] = sh.weight.data_ptr(), sh.scales.data_ptr(), sh.biases.data_ptr()
+            self._n[i], self._nt[i], self._c0[i] = sh.n1 - sh.n0, sh.n_total, sh.n0
+            ptrs = self.outs[i].ptrs()
+            for r in range(world):
+                self._y[i * world + r] = ptrs[r]
+
+    def close(self):
+        for o in self.outs:
+            o.close()
+        self.flags.close()
+
+    def forward(self, x: torch.Tensor, stream=None):
+        from . import _cabi
+
+        sh = self.shards[0]
+        m, k = x.shape
+        st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        lib = _cabi.lib()
+        _cabi.check(lib.lisa_cuda_quantized_matmul_siblings_allgather(
+            st, x.data_ptr(), m, k, len(self.shards), self._w, self._s, self._b, self._n, 1, sh.group_size, sh.bits, _cabi.BF16,
+            self._y, self.world, self._nt, self._c0, _cabi.FLAG_PDL))
+        _cabi.check(lib.lisa_cuda_peer_barrier(st, self.rank, self.world, self.flags.ptrs(), 0))
+        return [o.local[:m] for o in self.outs]

@@ -58,6 +58,21 @@ def _worker(rank, world, port, out):
             torch.cuda.synchronize()
             ok[f"fused_m{m}_{rep}"] = bool((y.float() - full.float()).abs().max() <= 1e-2 * full.float().abs().max())
             dist.barrier()  # nobody overwrites a buffer another rank is still comparing
+    # ---- two sharded linears that read the same x: one launch, one barrier
+    w2, s2, b2 = _affine(g, dev, (), 5120, k, bits)
+    lin2 = parallel.ShardedQuantizedLinear.from_full(w2, s2, b2, world, rank, 64, bits)
+    sib = parallel.FusedShardedSiblings([lin, lin2], max_rows=8)
+    for m in (1, 3):
+        x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
+        fulls = [ops.quantized_matmul(x, w, s, b, True, 64, bits), ops.quantized_matmul(x, w2, s2, b2, True, 64, bits)]
+        for rep in range(2):
+            launches = ops.launch_count()
+            ys = sib.forward(x)
+            torch.cuda.synchronize()
+            ok[f"siblings_m{m}_{rep}_launches"] = ops.launch_count() - launches == 2  # GEMV + barrier
+            for j, (y, full) in enumerate(zip(ys, fulls)):
+                ok[f"siblings_m{m}_{rep}_{j}"] = bool((y.float() - full.float()).abs().max() <= 1e-2 * full.float().abs().max())
+            dist.barrier()
     ok["device_status"] = ops.device_status() == 0
     # ---- expert-parallel routed experts (config 4 geometry with 16 experts), tokens data-parallel
     experts, hidden, inter, top_k, tokens = 16, 2048, 768, 8, 64

@@ -219,10 +219,18 @@ class PeerBuffers:
         if dtype == torch.bfloat16:
             self.local = self.local.view(torch.bfloat16)
         self._table = (C.c_void_p * self.world)(*self._peer_ptrs)
+        # the same pointers starting with the next rank and ending with this one: a kernel that stores into all
+        # of them in table order then begins at a different peer on every rank instead of all at rank 0
+        order = [(self.rank + 1 + i) % self.world for i in range(self.world)]
+        self._table_rotated = (C.c_void_p * self.world)(*[self._peer_ptrs[r] for r in order])
         dist.barrier(group=group)
 
     def ptrs(self):
         return self._table
+
+    def ptrs_rotated(self):
+        """All ranks' pointers in the order rank+1, ..., rank (for stores whose order does not matter)."""
+        return self._table_rotated
 
     def close(self):
         """Unmaps the peers' blocks and frees this rank's (after a barrier: nobody may still write to it)."""
@@ -261,7 +269,7 @@ class FusedShardedLinear:
         lib = _cabi.lib()
         _cabi.check(lib.lisa_cuda_quantized_matmul_allgather(
             st, x.data_ptr(), m, k, sh.weight.data_ptr(), sh.scales.data_ptr(), sh.biases.data_ptr(), sh.n1 - sh.n0, 1,
-            sh.group_size, sh.bits, _cabi.BF16, self.out.ptrs(), self.out.world, sh.n_total, sh.n0, _cabi.FLAG_PDL))
+            sh.group_size, sh.bits, _cabi.BF16, self.out.ptrs_rotated(), self.out.world, sh.n_total, sh.n0, _cabi.FLAG_PDL))
         # epoch 0: the barrier counts itself on the device, so the pair of launches replays from a CUDA graph
         _cabi.check(lib.lisa_cuda_peer_barrier(st, self.out.rank, self.out.world, self.flags.ptrs(), 0))
         return self.out.local[:m]
@@ -285,7 +293,7 @@ class FusedShardedSiblings:
         for i, sh in enumerate(self.shards):
             self._w[i], self._s[i], self._b[i] = sh.weight.data_ptr(), sh.scales.data_ptr(), sh.biases.data_ptr()
             self._n[i], self._nt[i], self._c0[i] = sh.n1 - sh.n0, sh.n_total, sh.n0
-            ptrs = self.outs[i].ptrs()
+            ptrs = self.outs[i].ptrs_rotated()
             for r in range(world):
                 self._y[i * world + r] = ptrs[r]
 

@@ -119,22 +119,30 @@ __global__ void __launch_bounds__(kSortChunk) moe_sort_hist_kernel(const int32_t
 // counts[chunk][e] -> exclusive start of (e, chunk) in the sorted order.
 __global__ void __launch_bounds__(1024) moe_sort_scan_kernel(int32_t *__restrict__ counts, int chunks, int experts) {
     extern __shared__ int32_t totals[];  // experts + 1
-    // exclusive scan over the chunks of every expert: one warp per expert, 32 chunks per trip
+    // exclusive scan over the chunks of every expert: one warp per expert, 128 chunks per trip (the four
+    // loads of a trip are issued together: the table is read from global memory once, latency-bound)
     const int lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     for (int e = threadIdx.x >> 5; e < experts; e += nwarps) {
         int run = 0;
-        for (int c0 = 0; c0 < chunks; c0 += 32) {
-            const int c = c0 + lane;
-            const int64_t at = static_cast<int64_t>(c) * experts + e;
-            const int v = c < chunks ? counts[at] : 0;
-            int inc = v;
+        for (int c0 = 0; c0 < chunks; c0 += 128) {
+            int v[4];
 #pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int n = __shfl_up_sync(0xffffffffu, inc, off);
-                if (lane >= off) inc += n;
+            for (int j = 0; j < 4; ++j) {
+                const int c = c0 + 32 * j + lane;
+                v[j] = c < chunks ? counts[static_cast<int64_t>(c) * experts + e] : 0;
             }
-            if (c < chunks) counts[at] = run + inc - v;
-            run += __shfl_sync(0xffffffffu, inc, 31);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = c0 + 32 * j + lane;
+                int inc = v[j];
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, inc, off);
+                    if (lane >= off) inc += n;
+                }
+                if (c < chunks) counts[static_cast<int64_t>(c) * experts + e] = run + inc - v[j];
+                run += __shfl_sync(0xffffffffu, inc, 31);
+            }
         }
         if (lane == 0) totals[e] = run;
     }

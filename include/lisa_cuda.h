@@ -56,9 +56,12 @@ enum {
     LISA_FLAG_PDL = 1 << 3,           /* launch with programmatic stream serialization: the
                                          kernel prefetches weights before waiting on the
                                          previous kernel in the stream */
-    LISA_FLAG_FORCE_QMV_TC = 1 << 4   /* streaming kernel with the unpacked weights in tensor memory
-                                         (tcgen05, the default for group size 64): fail instead of
-                                         falling back when the shape is not supported */
+    LISA_FLAG_FORCE_QMV_TC = 1 << 4,  /* streaming kernel with the unpacked weights in tensor memory
+                                         (tcgen05): fail instead of falling back when the shape is
+                                         not supported */
+    LISA_FLAG_FORCE_QMV_I8 = 1 << 5   /* streaming kernel on the integer mma.sync path (u8 codes x s8
+                                         activation planes; group size 64, k a multiple of 512): fail
+                                         instead of falling back when the shape is not supported */
 };
 
 const char *lisa_cuda_last_error_string(void);

@@ -30,6 +30,7 @@ FLAG_FORCE_QMV_SIMPLE = 1 << 1
 FLAG_FORCE_QMM = 1 << 2
 FLAG_PDL = 1 << 3
 FLAG_FORCE_QMV_TC = 1 << 4
+FLAG_FORCE_QMV_I8 = 1 << 5
 
 _vp, _i64, _int, _sz, _u = C.c_void_p, C.c_int64, C.c_int, C.c_size_t, C.c_uint
 

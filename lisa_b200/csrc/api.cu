@@ -4,6 +4,8 @@
 // Nothing here allocates device memory or synchronises.
 #include <cuda_runtime.h>
 
+#include <stdlib.h>
+
 #include <atomic>
 #include <mutex>
 #include <sstream>
@@ -81,6 +83,17 @@ static bool prefer_qmv(int64_t m, int64_t k, bool tc_ok) {
     return m <= kQmvMaxRows && (m <= 4 || m * k <= kQmvMaxStaged);
 }
 
+// Which weight-streaming kernel takes a call that both support: the tensor-memory kernel (measured faster on
+// every decode shape of the 4-bit stack), the integer mma.sync kernel when the environment says
+// LISA_QMV_KERNEL=i8 (read once; for side-by-side measurements) or LISA_FLAG_FORCE_QMV_I8 is given.
+static bool prefer_i8() {
+    static const bool v = []() {
+        const char *e = getenv("LISA_QMV_KERNEL");
+        return e && e[0] == 'i' && e[1] == '8';
+    }();
+    return v;
+}
+
 static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
                                  const void *scales, const void *biases, int64_t n, int transpose, int group_size,
                                  int bits, int dtype, void *y, unsigned flags) {
@@ -88,19 +101,25 @@ static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, 
     int rc = check_affine("quantized_matmul", x, m, k, w, scales, biases, n, group_size, bits, dtype, y);
     if (rc != LISA_OK) return rc;
     const bool force_tc = (flags & LISA_FLAG_FORCE_QMV_TC) != 0;
-    const bool force_qmv = (flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) != 0 || force_tc;
+    const bool force_i8 = (flags & LISA_FLAG_FORCE_QMV_I8) != 0;
+    const bool force_qmv = (flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) != 0 || force_tc || force_i8;
     const bool force_qmm = (flags & LISA_FLAG_FORCE_QMM) != 0;
     if (force_qmv && force_qmm) return fail(LISA_ERR_BAD_ARG, "quantized_matmul: contradictory flags");
     const bool qmm_ok = qmm_affine_supported(m, k, n, group_size, bits);
     if (force_qmm && !qmm_ok) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the GEMM kernel");
     const bool tc_ok = qmv_tc_supported(m, k, n, group_size, bits);
-    if (force_qmm || (!force_qmv && !prefer_qmv(m, k, tc_ok) && qmm_ok))
+    const bool i8_ok = qmv_i8_supported(m, k, n, group_size, bits);
+    if (force_qmm || (!force_qmv && !prefer_qmv(m, k, tc_ok || i8_ok) && qmm_ok))
         return qmm_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
     if (force_tc && !tc_ok)
         return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the tensor-memory GEMV");
-    // The tensor-memory GEMV is the default wherever it applies (group size 64); LISA_FLAG_FORCE_QMV and
-    // LISA_FLAG_FORCE_QMV_SIMPLE select the mma.sync and the generic kernel.
+    if (force_i8 && !i8_ok)
+        return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: shape not supported by the integer GEMV");
+    // Group size 64: the tensor-memory GEMV where it applies, else the integer mma.sync GEMV (k a multiple of
+    // 512); LISA_FLAG_FORCE_QMV and LISA_FLAG_FORCE_QMV_SIMPLE select the bf16 mma.sync and the generic kernel.
     const bool plain_forced = (flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) != 0;
+    if (force_i8 || (i8_ok && !plain_forced && !force_tc && (prefer_i8() || !tc_ok)))
+        return qmv_i8(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
     if (force_tc || (tc_ok && !plain_forced)) return qmv_tc(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
     return qmv_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
 }
@@ -121,8 +140,9 @@ int lisa_cuda_device_status(void) {
     const int b = qmm_device_status();
     const int c = qmv_tc_device_status();
     const int d = peer_device_status();
-    if (a < 0 || b < 0 || c < 0 || d < 0) return -1;
-    return a | (b << 8) | (c << 16) | (d << 24);
+    const int e = qmv_i8_device_status();
+    if (a < 0 || b < 0 || c < 0 || d < 0 || e < 0) return -1;
+    return a | (e << 4) | (b << 8) | (c << 16) | (d << 24);
 }
 
 int lisa_cuda_quantized_matmul(lisa_stream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
@@ -151,6 +171,9 @@ int lisa_cuda_quantized_matmul_serial_rows(lisa_stream_t stream, const void *x, 
     if (rc != LISA_OK) return rc;
     // Both streaming kernels accumulate every input row in the same order whatever the row count, so
     // each row equals its own m=1 call bit for bit -- as long as it is the kernel an m=1 call takes.
+    if (qmv_i8_supported(1, k, n, group_size, bits) && (prefer_i8() || !qmv_tc_supported(1, k, n, group_size, bits)))
+        return qmv_i8(static_cast<cudaStream_t>(stream), x, rows, k, w, scales, biases, n, group_size, bits, y,
+                      LISA_FLAG_NONE);
     if (qmv_tc_supported(1, k, n, group_size, bits))
         return qmv_tc(static_cast<cudaStream_t>(stream), x, rows, k, w, scales, biases, n, group_size, bits, y,
                       LISA_FLAG_NONE);
@@ -196,11 +219,17 @@ int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int
     }
     // one launch when the tensor-memory GEMV takes the rows; otherwise the linears one after another,
     // each through the dispatch of quantized_matmul
-    if (count >= 2 && m <= 8 && !(flags & (LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) &&
-        qmv_tc_multi_supported(m, k, count, n, group_size, bits))
-        return qmv_tc_multi(static_cast<cudaStream_t>(stream), x, m, k, count, w, scales, biases, n, group_size, bits, y, flags);
+    if (count >= 2 && m <= 8 && !(flags & (LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE))) {
+        const bool tc_ok = !(flags & LISA_FLAG_FORCE_QMV_I8) && qmv_tc_multi_supported(m, k, count, n, group_size, bits);
+        const bool i8_ok = !(flags & LISA_FLAG_FORCE_QMV_TC) && qmv_i8_multi_supported(m, k, count, n, group_size, bits);
+        if (i8_ok && ((flags & LISA_FLAG_FORCE_QMV_I8) || prefer_i8() || !tc_ok))
+            return qmv_i8_multi(static_cast<cudaStream_t>(stream), x, m, k, count, w, scales, biases, n, group_size, bits, y, flags);
+        if (tc_ok)
+            return qmv_tc_multi(static_cast<cudaStream_t>(stream), x, m, k, count, w, scales, biases, n, group_size, bits, y, flags);
+    }
     // many rows: one GEMM launch whose row tiles cover all the linears (they fill the waves together)
-    if (count >= 2 && m > kQmvMaxRows && !(flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE | LISA_FLAG_FORCE_QMV_TC))) {
+    if (count >= 2 && m > kQmvMaxRows &&
+        !(flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE | LISA_FLAG_FORCE_QMV_TC | LISA_FLAG_FORCE_QMV_I8))) {
         bool gemm_ok = true;
         for (int i = 0; i < count; ++i) gemm_ok = gemm_ok && qmm_affine_supported(m, k, n[i], group_size, bits);
         if (gemm_ok)

@@ -32,6 +32,22 @@ int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows,
 int peer_barrier(cudaStream_t stream, int rank, int world, void *const *flag_arrays, unsigned long long epoch);
 int peer_device_status();
 
+// qmv_i8.cu: the same GEMV on the integer path of mma.sync (u8 codes x s8 activation planes), group size 64,
+// k a multiple of 512, m <= 8 per pass; one to three sibling linears per launch; all-gather form with peer outputs
+bool qmv_i8_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);
+bool qmv_i8_multi_supported(int64_t m, int64_t k, int count, const int64_t *n, int group_size, int bits);
+int qmv_i8(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
+int qmv_i8_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                     const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
+                     int64_t n_total, int64_t col0, unsigned flags);
+int qmv_i8_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
+                 const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
+                 void *const *y, unsigned flags, int world = 0, const int64_t *n_total = nullptr,
+                 const int64_t *col0 = nullptr);
+int qmv_i8_device_status();
+int qmv_i8_clear_status();
+
 // qmm_affine.cu
 bool qmm_affine_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);
 int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,

@@ -71,6 +71,10 @@ uint64_t lisa_cuda_launch_count(void);
 /* Device-side status word: 0, or non-zero after a kernel gave up on one of its bounded
  * waits (its output is then undefined).  Synchronises the current device. */
 int lisa_cuda_device_status(void);
+/* The status word is sticky: once a kernel has given up on a wait, every later query reports it.  A caller
+ * that has handled the failure (dropped the outputs of the affected calls) resets it here.  Synchronises
+ * the current device.  No counterpart in the reference, whose kernels have no bounded waits. */
+int lisa_cuda_clear_device_status(void);
 
 /* ops::quantized_matmul(x, w, scales, biases, transpose, group_size, bits)
  *   crates/lisa-mlx/src/ops/array_ops.rs:378-493

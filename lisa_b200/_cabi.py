@@ -40,6 +40,7 @@ SIGNATURES = {
     "lisa_cuda_version": (_int, []),
     "lisa_cuda_launch_count": (C.c_uint64, []),
     "lisa_cuda_device_status": (_int, []),
+    "lisa_cuda_clear_device_status": (_int, []),
     "lisa_cuda_quantized_matmul": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _vp]),
     "lisa_cuda_quantized_matmul_ex": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _vp, _u]),
     "lisa_cuda_quantized_matmul_serial_rows": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _vp]),

@@ -145,6 +145,14 @@ int lisa_cuda_device_status(void) {
     return a | (e << 4) | (b << 8) | (c << 16) | (d << 24);
 }
 
+int lisa_cuda_clear_device_status(void) {
+    // The status words are sticky: a caller that has handled a failure resets them here.
+    const int rc[5] = {qmv_clear_status(), qmm_clear_status(), qmv_tc_clear_status(), peer_clear_status(), qmv_i8_clear_status()};
+    for (int i = 0; i < 5; ++i)
+        if (rc[i] != LISA_OK) return fail(LISA_ERR_CUDA, "clear_device_status: could not reset a status word");
+    return LISA_OK;
+}
+
 int lisa_cuda_quantized_matmul(lisa_stream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w,
                                const void *scales, const void *biases, int64_t n, int transpose, int group_size,
                                int bits, int dtype, void *y) {

@@ -12,12 +12,14 @@ namespace lisa {
 int qmv_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
 int qmv_device_status();
+int qmv_clear_status();
 
 // qmv_tc.cu: the same GEMV with the unpacked weights in tensor memory (tcgen05), group size 64, m <= 8 per pass
 bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);
 int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
            const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
 int qmv_tc_device_status();
+int qmv_tc_clear_status();
 int qmv_tc_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                      const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
                      int64_t n_total, int64_t col0, unsigned flags);
@@ -31,6 +33,7 @@ int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows,
                 int64_t tokens, float *y);
 int peer_barrier(cudaStream_t stream, int rank, int world, void *const *flag_arrays, unsigned long long epoch);
 int peer_device_status();
+int peer_clear_status();
 
 // qmv_i8.cu: the same GEMV on the integer path of mma.sync (u8 codes x s8 activation planes), group size 64,
 // k a multiple of 512, m <= 8 per pass; one to three sibling linears per launch; all-gather form with peer outputs
@@ -62,6 +65,7 @@ int qmm_affine_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t
                        const void *scales, const void *biases, int64_t experts, int64_t n, int group_size, int bits,
                        void *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles);
 int qmm_device_status();
+int qmm_clear_status();
 // GGUF Q4_K GEMM on the same kernel (bf16 operands: the caller opts in by giving a workspace)
 bool qmm_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes);
 size_t qmm_gguf_workspace_bytes(int64_t tokens, int64_t k);

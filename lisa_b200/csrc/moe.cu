@@ -117,7 +117,12 @@ __global__ void __launch_bounds__(kSortChunk) moe_sort_hist_kernel(const int32_t
 }
 
 // counts[chunk][e] -> exclusive start of (e, chunk) in the sorted order.
-__global__ void __launch_bounds__(1024) moe_sort_scan_kernel(int32_t *__restrict__ counts, int chunks, int experts) {
+// Slots whose id is outside [0, experts) are not sorted: the positions behind the last valid slot are filled
+// here with id = experts (gather_qmm writes zeros for it) and token row 0, so that no consumer of the sorted
+// arrays reads an index nobody wrote.
+__global__ void __launch_bounds__(1024) moe_sort_scan_kernel(int32_t *__restrict__ counts, int chunks, int experts,
+                                                             int slots, int32_t *__restrict__ sorted_ids,
+                                                             int32_t *__restrict__ token_rows) {
     extern __shared__ int32_t totals[];  // experts + 1
     // exclusive scan over the chunks of every expert: one warp per expert, 128 chunks per trip (the four
     // loads of a trip are issued together: the table is read from global memory once, latency-bound)
@@ -154,8 +159,13 @@ __global__ void __launch_bounds__(1024) moe_sort_scan_kernel(int32_t *__restrict
             totals[e] = run;
             run += v;
         }
+        totals[experts] = run;  // slots with a valid id
     }
     __syncthreads();
+    for (int i = totals[experts] + threadIdx.x; i < slots; i += blockDim.x) {
+        sorted_ids[i] = experts;
+        token_rows[i] = 0;
+    }
     const int64_t cells = static_cast<int64_t>(chunks) * experts;
     for (int64_t i = threadIdx.x; i < cells; i += blockDim.x) counts[i] += totals[i % experts];
 }
@@ -183,6 +193,8 @@ __global__ void __launch_bounds__(kSortChunk) moe_sort_scatter_kernel(const int3
                 sorted_ids[pos] = e;
                 token_rows[pos] = i / top_k;
                 inverse[i] = pos;
+            } else if (live) {
+                inverse[i] = -1;  // not sorted: moe_combine adds nothing for this slot
             }
             __syncwarp();
             if (ok && (peers >> lane) == 1u) next[e] += __popc(peers);  // highest lane of the group
@@ -197,7 +209,8 @@ static int launch_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, i
     const size_t esm = static_cast<size_t>(experts) * sizeof(int32_t);
     moe_sort_hist_kernel<<<chunks, kSortChunk, esm, stream>>>(idx, static_cast<int>(slots), static_cast<int>(experts), counts);
     LISA_CUDA_TRY(cudaGetLastError());
-    moe_sort_scan_kernel<<<1, 1024, esm + sizeof(int32_t), stream>>>(counts, chunks, static_cast<int>(experts));
+    moe_sort_scan_kernel<<<1, 1024, esm + sizeof(int32_t), stream>>>(counts, chunks, static_cast<int>(experts),
+                                                                      static_cast<int>(slots), sorted_ids, token_rows);
     LISA_CUDA_TRY(cudaGetLastError());
     moe_sort_scatter_kernel<<<chunks, kSortChunk, esm, stream>>>(idx, static_cast<int>(slots), static_cast<int>(experts),
                                                                  top_k, counts, sorted_ids, token_rows, inverse);
@@ -230,6 +243,13 @@ int moe_sort_static(cudaStream_t stream, const int32_t *idx, int64_t slots, int6
     int dev = 0;
     LISA_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(LISA_ERR_LIMIT, "moe_sort_static: device ordinal above 63");
+    // The scratch address belongs to the CURRENT device: a stream of another GPU would hand its kernels a
+    // pointer into the wrong device's copy of the array.
+    if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+        int sdev = -1;
+        if (cudaStreamGetDevice(stream, &sdev) == cudaSuccess && sdev != dev)
+            return fail(LISA_ERR_BAD_ARG, "moe_sort_static: the stream belongs to another device than the current one");
+    }
     int32_t *counts = nullptr;
     {
         std::lock_guard<std::mutex> lock(g_sort_scratch_mutex);
@@ -339,7 +359,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t *__rest
         float acc = 0.f;
         for (int rr = y; rr < top_k; rr += ty) {
             const int64_t row = __ldg(inverse + t * top_k + rr);
-            const float r = bf16_bits_to_f32(__ldg(down + row * hidden + h)) * __ldg(weights + t * top_k + rr);
+            // a slot that was not sorted (inverse < 0: its expert id was out of range or not owned) adds zero
+            const float r = row < 0 ? 0.f : bf16_bits_to_f32(__ldg(down + row * hidden + h)) * __ldg(weights + t * top_k + rr);
             acc = r + acc;
         }
         part[y] = acc;
@@ -366,7 +387,7 @@ __global__ void __launch_bounds__(256) moe_combine8_kernel(const uint4 *__restri
         for (int rr = y; rr < top_k; rr += ty) {
             const int64_t row = __ldg(inverse + t * top_k + rr);
             const float w = __ldg(weights + t * top_k + rr);
-            const uint4 v = __ldg(down + row * hidden8 + h8);
+            const uint4 v = row < 0 ? make_uint4(0, 0, 0, 0) : __ldg(down + row * hidden8 + h8);
             const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {

@@ -42,6 +42,10 @@ int qmm_device_status() {
     if (cudaMemcpyFromSymbol(&v, g_qmm_status, sizeof(int)) != cudaSuccess) return -1;
     return v;
 }
+int qmm_clear_status() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_qmm_status, &zero, sizeof(int)) == cudaSuccess ? LISA_OK : LISA_ERR_CUDA;
+}
 
 constexpr int kBN = 128;        // weight rows per CTA (MMA M)
 constexpr int kBK = 64;         // k per MMA stage: 64 bf16 = one 128-byte swizzle row

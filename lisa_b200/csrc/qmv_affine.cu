@@ -52,6 +52,10 @@ int qmv_device_status() {
     if (cudaMemcpyFromSymbol(&v, g_qmv_status, sizeof(int)) != cudaSuccess) return -1;
     return v;
 }
+int qmv_clear_status() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_qmv_status, &zero, sizeof(int)) == cudaSuccess ? LISA_OK : LISA_ERR_CUDA;
+}
 
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumers = kConsumerWarps * 32;

@@ -19,9 +19,9 @@
 // group, token) the epilogue adds  scale * 2^(E-13) * (256 * D_hi + D_lo) + bias * sum(x)  in f32.
 // A group whose largest element towers over the rest (a massive-activation channel) would leave the rest
 // with a coarse grid.  The conversion therefore works on 22-bit integers, x_int22 = 65536 p0 + 256 p1 + p2,
-// keeps (p0, p1) as the two planes above and flags a group when the dropped bytes, sum|p2|, exceed 2^-9 of
-// sum|x_int22| without its largest element; flagged groups (rare: the largest element must be about 30
-// times the typical one) run two more MMAs on the p2 plane, which makes every element within 2^-14 of the
+// keeps (p0, p1) as the two planes above and flags a group when the dropped bytes, sum|p2|, exceed 2^-12 of
+// sum|x_int22| without its largest element; flagged groups (none among Gaussian activations: the largest
+// element must be about ten times the typical one) run two more MMAs on the p2 plane, which makes every element within 2^-14 of the
 // maximum exact and bounds the rest by 2^-22 of it.
 //
 // Structure: persistent CTAs own a contiguous range of output rows (even split at single-row granularity)
@@ -386,7 +386,7 @@ qmv_i8_kernel(const __grid_constant__ I8Maps maps, const __grid_constant__ I8Par
                     mabs = max(mabs, __shfl_xor_sync(0xffffffffu, mabs, off));
                     sp2 += __shfl_xor_sync(0xffffffffu, sp2, off);
                 }
-                const bool need3 = sp2 * 512 > sabs - mabs;  // the dropped bytes against the group without its largest element
+                const bool need3 = sp2 * 4096 > sabs - mabs;  // the dropped bytes against the group without its largest element
                 if (in) {
                     // element kk = 8 * (p8 & 1) + i of lane-group tg = p8 >> 1 of the unit
                     const int tg = p8 >> 1, odd = p8 & 1;

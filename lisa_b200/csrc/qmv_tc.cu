@@ -54,6 +54,10 @@ int qmv_tc_device_status() {
     if (cudaMemcpyFromSymbol(&v, g_qmv_tc_status, sizeof(int)) != cudaSuccess) return -1;
     return v;
 }
+int qmv_tc_clear_status() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_qmv_tc_status, &zero, sizeof(int)) == cudaSuccess ? LISA_OK : LISA_ERR_CUDA;
+}
 
 namespace {
 
@@ -1250,6 +1254,10 @@ int peer_device_status() {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_peer_status, sizeof(int)) != cudaSuccess) return -1;
     return v;
+}
+int peer_clear_status() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_peer_status, &zero, sizeof(int)) == cudaSuccess ? LISA_OK : LISA_ERR_CUDA;
 }
 
 struct PeerBarrierParams {

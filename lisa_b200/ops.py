@@ -321,3 +321,8 @@ def launch_count() -> int:
 
 def device_status() -> int:
     return int(lib().lisa_cuda_device_status())
+
+
+def clear_device_status() -> None:
+    """Resets the sticky status word after the caller has handled a reported failure."""
+    check(lib().lisa_cuda_clear_device_status())

@@ -626,7 +626,9 @@ int oracle_moe_combine(const uint16_t *down_sorted, const float *weights, const 
             float r[64], part[8];
             for (int j = 0; j < top_k; ++j) {
                 int64_t row = inverse[t * top_k + j];
-                r[j] = oracle_bf16_to_f32(down_sorted[row * hidden + h]) * weights[t * top_k + j];
+                /* a slot that was not sorted (inverse < 0: an expert outside the table or not owned by this
+                   rank, the zero rule of deepseek41.rs:204-206 and iq.metal:976-982) adds nothing */
+                r[j] = row < 0 ? 0.0f : oracle_bf16_to_f32(down_sorted[row * hidden + h]) * weights[t * top_k + j];
             }
             for (int y = 0; y < ty; ++y) {
                 float acc = 0.0f;

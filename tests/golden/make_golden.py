@@ -82,7 +82,8 @@ def moe_case(seed: int, tokens: int, experts: int, top_k: int, hidden: int, inte
     up = util.affine_weights(rng, inter, hidden, 4, 64, experts)
     down = util.affine_weights(rng, hidden, inter, 4, 64, experts)
     x = util.activations(rng, tokens, hidden)
-    y, _ = O.moe_forward(x, logits, gate, up, down, top_k)
+    # ten sorted rows: the reference runs such a block as per-run matvecs (unrounded weights, array_ops.rs:591-630)
+    y, _ = O.moe_forward(x, logits, gate, up, down, top_k, round_weight_bf16=False)
     out = {"logits": logits, "idx": idx, "weights": wts, "sorted_ids": sorted_ids, "token_rows": token_rows,
            "inverse": inverse, "x": x, "y_bf16": y, "top_k": np.int32(top_k)}
     for name, (w, s, b) in (("gate", gate), ("up", up), ("down", down)):

@@ -57,7 +57,7 @@ def test_oracle_reproduces_moe_fixture(name):
     s, t, inv = O.moe_sort(idx, experts, top_k)
     assert np.array_equal(s, g["sorted_ids"]) and np.array_equal(t, g["token_rows"]) and np.array_equal(inv, g["inverse"])
     y, _ = O.moe_forward(g["x"], g["logits"], *[(g[n + "_w"], g[n + "_s"], g[n + "_b"]) for n in ("gate", "up", "down")],
-                         top_k)
+                         top_k, round_weight_bf16=False)
     assert np.array_equal(y, g["y_bf16"])
 
 
@@ -119,4 +119,4 @@ def test_cuda_matches_moe_fixture(cuda, name):
 
     y = SwitchGlu(lin("gate"), lin("up"), lin("down"), top_k).forward(dev_bf16(g["x"], cuda), dev_f32(g["logits"], cuda))
     err, l2 = util.parity(O.bf16_to_f32(host_bf16_bits(y)), O.bf16_to_f32(g["y_bf16"]))
-    assert err <= 2e-2 and l2 <= 1e-2, (err, l2)
+    assert err <= 1e-2 and l2 <= 1e-2, (err, l2)

@@ -115,8 +115,9 @@ def test_switch_glu_block_matches_oracle(cuda, tokens):
 
     block = SwitchGlu(lin(gate), lin(up), lin(down), top_k)
     y = block.forward(dev_bf16(x, cuda), dev_f32(logits, cuda))
-    ref, _ = O.moe_forward(x, logits, gate, up, down, top_k, 64, 4, round_weight_bf16=False)
+    # 32 sorted rows and more run as the grouped GEMM (weights rounded to bf16 once), fewer as matvecs
+    ref, _ = O.moe_forward(x, logits, gate, up, down, top_k, 64, 4, round_weight_bf16=tokens * top_k >= 32)
     got = O.bf16_to_f32(host_bf16_bits(y))
     err, l2 = util.parity(got, O.bf16_to_f32(ref))
-    # three bf16 rounding points sit between input and output: 1e-2 on the block output
-    assert err <= 2e-2 and l2 <= 1e-2, (err, l2)
+    # three bf16 rounding points sit between input and output; the block output still holds 1e-2
+    assert err <= 1e-2 and l2 <= 1e-2, (err, l2)

@@ -113,3 +113,31 @@ def test_sibling_linears_with_many_rows_equal_separate_calls(cuda):
     ys = ops.quantized_matmul_siblings(tx, dev, True, 64, 4)
     for (tw, ts, tb), y in zip(dev, ys):
         assert torch.equal(y, ops.quantized_matmul(tx, tw, ts, tb, True, 64, 4))
+
+
+@pytest.mark.parametrize("ratio", [2.0 ** 6, 2.0 ** 10])
+def test_heavy_tailed_activations_stay_inside_the_stated_bound(cuda, ratio):
+    """The tensor-memory kernel puts the activations of a (token, 64-k group) on an integer grid of 2^-13 of the
+    group's largest power of two, so an element is off by at most 2^(E-14).  With one channel per group `ratio`
+    times the rest and weight rows that are zero on that channel, the row error must stay below
+    sum_k |w_k| * 2^(E_g(k) - 14) plus the bf16 rounding of the output."""
+    rng = np.random.default_rng(21)
+    n, k, m = 512, 2560, 2
+    w, s, b = util.affine_weights(rng, n, k, 4, 64)
+    x = O.bf16_to_f32(util.activations(rng, m, k))
+    hot = np.arange(0, k, 64) + rng.integers(0, 64, size=k // 64)
+    x[:, hot] *= ratio
+    xb = O.f32_to_bf16(x.astype(np.float32))
+    wq = w.copy()
+    for c in hot:
+        wq[:, c // 8] &= ~np.uint32(0xF << (4 * (c % 8)))
+    b0 = np.zeros_like(b)
+    y = ops.quantized_matmul(dev_bf16(xb, cuda), dev_u32(wq, cuda), dev_bf16(s, cuda), dev_bf16(b0, cuda), True, 64, 4,
+                             flags=_cabi.FLAG_FORCE_QMV_TC)
+    got = O.bf16_to_f32(host_bf16_bits(y)).astype(np.float64)
+    truth = O.affine_matmul(xb, wq, s, b0, 64, 4, round_weight_bf16=False, f64=True).astype(np.float64)
+    wabs = np.abs(O.affine_dequantize(wq, s, b0, 64, 4, out_f32=True).astype(np.float64))          # [n, k]
+    xf = O.bf16_to_f32(xb).astype(np.float64).reshape(m, k // 64, 64)
+    step = 2.0 ** (np.floor(np.log2(np.abs(xf).max(axis=2))) - 14)                                  # [m, groups]
+    bound = np.einsum("ngk,mg->mn", wabs.reshape(n, k // 64, 64), step) + 2.0 ** -8 * np.abs(truth) + 1e-6
+    assert np.all(np.abs(got - truth) <= bound)

@@ -75,6 +75,32 @@ def tensor_peak():
     return 1400.0, "fallback (1.4 PFLOP/s sustained, earlier measurement on this pool)"
 
 
+def tensor_peaks():
+    """(sustained, burst) dense bf16 TFLOP/s and where they come from."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["bf16_tflops_sustained"]), float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json)"
+    return 1400.0, 1590.0, "fallback (1.4 / 1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+def leg_summary(line):
+    """{workload, ms, value, unit, roofline} of a leg from its full result line."""
+    unit = line["unit"]
+    n = max(int(line.get("n_gpus", 1)), 1)
+    per_gpu = line["value"] / n
+    if unit == "TFLOP/s":
+        sus, burst, src = tensor_peaks()
+        roof = {"bound": "tensor", "frac": per_gpu / sus, "frac_of_burst": per_gpu / burst, "peak": sus, "peak_burst": burst,
+                "peak_source": src + ", per GPU"}
+    else:
+        peak, src = peaks()
+        roof = {"bound": "hbm", "frac": per_gpu / peak, "peak": peak, "peak_source": src + ", per GPU"}
+    return {"workload": line["config"]["workload"], "parallelism": line["config"].get("parallelism"), "ms": line["ms_per_step"],
+            "value": line["value"], "unit": unit, "n_gpus": n, "scaling": line.get("scaling"), "steps": line.get("steps"),
+            "gpu_launches": line.get("gpu_launches"), "roofline": roof}
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launches, from the
 # ncu captures summarised in profiles/ (qmv_tc_kernel on 4 layers of the decode stack; qmm_affine_kernel
 # on 2 layers of the prefill stack).  Traffic grows in proportion to the units processed, so the ratio
@@ -385,6 +411,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures only")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--skip-legs", action="store_true", help="headline only: skip the legs of the other workloads")
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "shard", "moe", "gguf"],
                     help="decode: M=1 GEMV stack, HBM GB/s (headline); prefill: M=2048 GEMM stack, bf16 TFLOP/s; "
                          "shard: configs[2] 2-bit MLP stack, N-sharded over the ranks with an all-gather; "
@@ -478,6 +505,16 @@ def main():
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    # ---- the same step for about a second more (the contract's K steps last tens of milliseconds: too short for
+    # a power cap to show), while the clock sampler keeps running
+    long_steps = 1000 if args.layers == LAYERS else 50
+    l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0.record()
+    for _ in range(long_steps):
+        stack.step()
+    l1.record()
+    barrier()
+    long_ms = l0.elapsed_time(l1)
     clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
@@ -486,6 +523,7 @@ def main():
     total_ms, e2e_ms = float(t[0]), float(t[1])
     status = ops.device_status()
 
+    legs = {}
     if rank == 0:
         value = world * bytes_token * args.steps / (total_ms * 1e-3) / 1e9
         e2e_value = world * bytes_token * args.steps / (e2e_ms * 1e-3) / 1e9
@@ -510,19 +548,41 @@ def main():
             "gpu_launches": launches_per_token * args.steps,
             "clocks": clocks, "device_status": status,
             "launch": {"graph": stack.graph is not None, "pdl": bool(stack.flags & 8), "layers": args.layers},
+            "long_run": {"steps": long_steps, "ms_per_step": long_ms / long_steps,
+                         "value": bytes_token * long_steps / (long_ms * 1e-3) / 1e9, "unit": "GB/s per GPU (rank 0)"},
         }
         if args.layers == LAYERS:
             oms, olaunch = stack.time_other_form(min(args.steps, 20))
             line["other_call_pattern"] = {"calls": workload_config(world, olaunch)["calls"], "launches_per_token": olaunch,
                                           "ms_per_step": oms, "value": bytes_token / (oms * 1e-3) / 1e9, "unit": "GB/s"}
-        # the prefill half of the same config, briefly (full stack, M = 2048)
+        # the prefill half of the same config (full stack, M = 2048), 20 passes
         stack.prefill_setup()
-        pms = time_prefill(torch, stack, steps=3, warmup=2)
-        tpeak, tsrc = tensor_peak()
+        psteps = 20 if args.layers == LAYERS else 3
+        pms = time_prefill(torch, stack, steps=psteps, warmup=3)
+        sus, burst, tsrc = tensor_peaks()
         tf = stack.prefill_flops() / (pms * 1e-3) / 1e12
-        line["qmm"] = {"metric": "qmm bf16 TFLOP/s", "value": tf, "m": PREFILL_M, "ms_per_pass": pms,
-                       "frac_of_bf16_peak": tf / tpeak, "peak": tpeak, "peak_source": tsrc,
+        line["qmm"] = {"metric": "qmm bf16 TFLOP/s", "value": tf, "m": PREFILL_M, "ms_per_pass": pms, "passes": psteps,
+                       "frac_of_bf16_peak": tf / sus, "peak": sus, "frac_of_burst_peak": tf / burst, "peak_burst": burst,
+                       "peak_source": tsrc,
                        "launches_per_pass": args.layers * (len(SIBLINGS) if stack.siblings else 7), "kernel": "qmm_affine_kernel<4>"}
+        legs["configs[1] prefill M=2048"] = {
+            "workload": f"configs[1] prefill: the same stack, {args.layers} layers x 7 linears, M={PREFILL_M}", "ms": pms,
+            "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": psteps,
+            "roofline": {"bound": "tensor", "frac": tf / sus, "frac_of_burst": tf / burst, "peak": sus, "peak_burst": burst,
+                         "peak_source": tsrc}}
+        del stack.pin, stack.pout, stack.pouts
+        if args.layers == LAYERS and not args.skip_legs:
+            # configs[4]: GGUF Q2_K / Q4_K, both shapes, M in {1, 512}
+            for r in gguf_legs(torch, dev, steps=20, warmup=3):
+                key = f"configs[4] {r['format']} K={r['k']} N={r['n']} M={r['m']}"
+                if r["m"] == 1:
+                    hp, hsrc = peaks()
+                    legs[key] = {"workload": key, "ms": r["us"] * 1e-3, "value": r["GB/s"], "unit": "GB/s", "n_gpus": 1, "steps": 20,
+                                 "roofline": {"bound": "hbm", "frac": r["GB/s"] / hp, "peak": hp, "peak_source": hsrc}}
+                else:
+                    legs[key] = {"workload": key, "ms": r["us"] * 1e-3, "value": r["TFLOP/s"], "unit": "TFLOP/s", "n_gpus": 1, "steps": 20,
+                                 "roofline": {"bound": "tensor", "frac": r["TFLOP/s"] / sus, "frac_of_burst": r["TFLOP/s"] / burst,
+                                              "peak": sus, "peak_burst": burst, "peak_source": tsrc}}
         if not args.skip_cpu:
             layers = cpu_sample_layers()
             gbs, dt, cores = run_cpu_baseline(0, layers)
@@ -530,6 +590,27 @@ def main():
                 "value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                 "sample": f"{layers} of {LAYERS} layers (7 linears each), M=1, seed 0, {dt:.2f} s; "
                           "restatement of the reference's Rust dequant + scalar f32 matmul"}
+    # ---- the other workloads, every rank: the 2-bit stack N-sharded over the ranks (all-gather fused into the
+    # kernels' epilogues, peer barrier) and the routed experts expert-parallel (all-to-all); with one rank the same
+    # code runs unsharded, which is the baseline of the scaling curve
+    if args.layers == LAYERS and not args.skip_legs:
+        del stack
+        torch.cuda.empty_cache()
+        if world > 1:
+            dist.barrier()
+        for m in (1, 8, 512):
+            res = sharded_leg(LegArgs("shard", m=m, steps=10), torch, dist, dev, rank, world, 3)
+            if rank == 0:
+                legs[f"configs[2] M={m}"] = leg_summary(res)
+            torch.cuda.empty_cache()
+        for tokens in (1, 64, 4096):
+            res = sharded_leg(LegArgs("moe", tokens=tokens, steps=10), torch, dist, dev, rank, world, 3)
+            if rank == 0:
+                legs[f"configs[3] T={tokens}"] = leg_summary(res)
+            torch.cuda.empty_cache()
+    if rank == 0:
+        line["configs"] = legs
+        line["device_status"] = ops.device_status()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -604,12 +685,10 @@ def prefill_main(args, torch, dist, stack, rank, local_rank, world, warmup):
         dist.destroy_process_group()
 
 
-def gguf_main(args, torch, dev, rank, warmup):
+def gguf_legs(torch, dev, steps, warmup):
     """configs[4]: GGUF Q2_K / Q4_K, K=7168 N=18432 and K=18432 N=7168, M=1 (matvec, HBM GB/s on the block
     bytes) and M=512 (tensor-core matmul with a workspace, TFLOP/s).  Uniform random code and scale bytes,
-    d, dmin ~ |N(0, 0.01)| as f16, activations ~ N(0, 1)."""
-    if rank != 0:
-        return
+    d, dmin ~ |N(0, 0.01)| as f16, activations ~ N(0, 1).  One result per (format, shape, M)."""
     from lisa_b200 import _cabi, ops
 
     g = torch.Generator(device=dev)
@@ -632,14 +711,24 @@ def gguf_main(args, torch, dev, rank, warmup):
                 torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                for _ in range(args.steps):
+                for _ in range(steps):
                     fn()
                 e1.record()
                 torch.cuda.synchronize()
-                us = e0.elapsed_time(e1) / args.steps * 1e3
+                us = e0.elapsed_time(e1) / steps * 1e3
                 results.append({"format": fmt, "k": k, "n": n, "m": m, "us": us,
                                 "GB/s": w.numel() / us / 1e3 if m == 1 else None,
                                 "TFLOP/s": 2.0 * m * n * k / us / 1e6 if m > 1 else None})
+            del w
+    return results
+
+
+def gguf_main(args, torch, dev, rank, warmup):
+    if rank != 0:
+        return
+    from lisa_b200 import ops
+
+    results = gguf_legs(torch, dev, args.steps, warmup)
     best = max(r["TFLOP/s"] for r in results if r["TFLOP/s"])
     print(json.dumps({"metric": "GGUF K-quant matmul TFLOP/s (M=512, best of the four)", "value": best, "unit": "TFLOP/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak",
@@ -649,13 +738,31 @@ def gguf_main(args, torch, dev, rank, warmup):
 
 
 def sharded_main(args, torch, dist, dev, rank, world, warmup):
+    line = sharded_leg(args, torch, dist, dev, rank, world, warmup)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+class LegArgs:
+    """The arguments sharded_leg reads, for the legs of the default line."""
+
+    def __init__(self, mode, m=1, tokens=4096, steps=10, layers=LAYERS):
+        self.mode, self.m, self.tokens, self.steps, self.layers = mode, m, tokens, steps, layers
+
+
+def sharded_leg(args, torch, dist, dev, rank, world, warmup):
     """configs[2] (N-sharded 2-bit MLP stack + all-gather) and configs[3] (expert-parallel routed experts +
-    all-to-all).  With one rank the same code runs unsharded and no collective is issued."""
+    all-to-all).  With one rank the same code runs unsharded and no collective is issued.  Returns the result
+    line on rank 0 (None elsewhere); every rank must call it."""
     from lisa_b200 import ops, parallel
     from lisa_b200.quant import QuantizedLinear, SwitchGlu
 
     g = torch.Generator(device=dev)
     g.manual_seed(0)
+    closers = []
 
     def affine(lead, n, k, bits):
         w = torch.randint(-2 ** 31, 2 ** 31 - 1, lead + (n, k * bits // 32), dtype=torch.int32, device=dev, generator=g)
@@ -687,6 +794,8 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
                     for per in lins]
         elif fused:
             lins = [[parallel.FusedShardedLinear(lin, max_rows=m) for lin in per] for per in lins]
+        if fused:
+            closers.extend(obj for per in lins for obj in per)
 
         # one GPU, few rows: gate and up read the same x, so they go out as one sibling launch
         siblings = world == 1 and m <= 8 and os.environ.get("LISA_BENCH_SIBLINGS", "1") == "1"
@@ -747,7 +856,9 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
                 block.forward(x, logits)
 
         flops = 2.0 * tokens * top_k * 3 * inter * hidden  # per rank: its own tokens
-        work_bytes = 0
+        # bytes of the distinct experts this rank's tokens touch (packed codes + scales and biases of gate, up, down)
+        distinct = int(torch.unique(ops.moe_route(logits, top_k)[0]).numel())
+        work_bytes = distinct * 3 * (inter * hidden // 2 + 2 * inter * (hidden // GROUP) * 2)
         name = f"configs[3]: routed experts 128 x top-8, hidden 2048, intermediate 768, 4-bit gs64, {tokens} tokens per rank"
         par = f"expert-parallel, {(e1 - e0)} experts per rank, NCCL all-to-all dispatch and combine" if world > 1 else "single GPU"
         scaling = "weak"
@@ -802,22 +913,24 @@ def sharded_main(args, torch, dist, dev, rank, world, warmup):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t[0])
+    line = None
+    for obj in closers:  # peer buffers are explicit allocations: give them back
+        obj.close()
     if rank == 0:
         total_flops = flops * (world if args.mode == "moe" else 1)
-        line = {"metric": "qmm bf16 TFLOP/s" if (args.mode == "moe" or args.m > 8) else "2-bit qmv HBM GB/s",
+        tensor_bound = (args.mode == "moe" and args.tokens > 64) or (args.mode == "shard" and args.m > 8)
+        line = {"metric": "qmm bf16 TFLOP/s" if tensor_bound else ("2-bit qmv HBM GB/s" if args.mode == "shard" else "4-bit gather_qmm HBM GB/s"),
                 "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
                 "scaling": scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": name, "parallelism": par, "graph": graphed}, "gpu_launches": launches,
                 "clocks": clocks,
                 "device_status": ops.device_status()}
-        if line["metric"].startswith("qmm"):
+        if tensor_bound:
             line.update(value=total_flops / (ms * 1e-3) / 1e12, unit="TFLOP/s")
         else:
-            line.update(value=work_bytes / (ms * 1e-3) / 1e9, unit="GB/s")  # whole job: all ranks' weight bytes
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+            # whole job: all ranks' weight bytes (moe: the distinct experts of rank 0's tokens, times the ranks)
+            line.update(value=work_bytes * (world if args.mode == "moe" else 1) / (ms * 1e-3) / 1e9, unit="GB/s")
+    return line
 
 
 if __name__ == "__main__":

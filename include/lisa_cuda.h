@@ -83,7 +83,15 @@ int lisa_cuda_clear_device_status(void);
  *   y [m,n] dtype.  m >= 1.  Like the reference: transpose must be non-zero and
  *   biases non-null (array_ops.rs:387-392).  bits in {2,4}, group_size in
  *   {32,64,128}, dtype LISA_BF16.  Dispatch by m mirrors array_ops.rs:405-488:
- *   small m streams the weights once on CUDA cores, large m runs the tcgen05 GEMM. */
+ *   up to 8 rows stream the weights once (group size 64: the tensor-memory GEMV; other group sizes: the
+ *   bf16 mma.sync or the generic kernel), more rows run the tcgen05 GEMM.
+ *   Numerics of the group-64 GEMV: products and sums are exact integers, but the activations of a (row of
+ *   x, 64-k group) are first put on an integer grid of 2^-13 of the group's largest power of two (two
+ *   signed bytes), so an element is off by at most 2^-14 of the group's largest magnitude; bf16
+ *   activations within 2^-6 of that maximum are exact.  For Gaussian-like activations this is below the
+ *   bf16 rounding of the output; a group with one element 2^10 times the rest loses the rest to about
+ *   10 %.  LISA_FLAG_FORCE_QMV_I8 selects a kernel that adds a third byte (2^-22) for such groups,
+ *   LISA_FLAG_FORCE_QMV one that keeps the bf16 activations exactly. */
 int lisa_cuda_quantized_matmul(lisa_stream_t stream, const void *x, int64_t m, int64_t k,
                                const uint32_t *w, const void *scales, const void *biases,
                                int64_t n, int transpose, int group_size, int bits, int dtype,
@@ -129,7 +137,13 @@ int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int
  * slots 0..7 are written by the peers, slot 8 counts this rank's barriers), `epoch` a number that
  * grows with every barrier, or 0 to use the count in slot 8 (the same launch can then be replayed
  * from a CUDA graph).  Its wait is bounded (about a second), after which
- * lisa_cuda_device_status() reports the failure. */
+ * lisa_cuda_device_status() reports the failure.
+ * Reuse of the output buffers: the barrier orders this call's stores (of all ranks) before the reads that
+ * follow it; it does NOT order one rank's reads of call i before another rank's stores of call i+1.  A
+ * caller that issues call i+1 into the same y_all buffers must either alternate between two sets of buffers
+ * (the stores of call i+2 then come after the barrier of call i+1, which no rank passes before every rank
+ * has enqueued it behind its own reads of call i) or enqueue a second lisa_cuda_peer_barrier between the
+ * reads of call i and call i+1. */
 int lisa_cuda_quantized_matmul_allgather(lisa_stream_t stream, const void *x, int64_t m, int64_t k,
                                          const uint32_t *w, const void *scales, const void *biases,
                                          int64_t n_local, int transpose, int group_size, int bits, int dtype,

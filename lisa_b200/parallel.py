@@ -249,15 +249,31 @@ class PeerBuffers:
 class FusedShardedLinear:
     """`ShardedQuantizedLinear` without a collective library: the epilogue of the GEMV (up to 8 rows) or of the
     tensor-core GEMM (more rows) stores this rank's column block into every rank's output buffer, and
-    `lisa_cuda_peer_barrier` orders the ranks."""
+    `lisa_cuda_peer_barrier` orders the ranks.
+
+    Reuse rule.  The barrier of a call orders that call's stores (all ranks) before the reads that follow it on
+    every rank; nothing orders one rank's reads of call i before another rank's stores of call i+1.  An instance
+    therefore owns TWO output buffers and alternates between them: the stores of call i+2 into the buffer of
+    call i come after the barrier of call i+1, which a rank only passes once every rank has enqueued -- behind
+    its own consumer of call i, in stream order -- that barrier.  The returned view stays valid until the
+    second-next `forward` of the same instance, provided its consumer runs on the same stream before the next
+    `forward`.  A CUDA graph that captures `forward` fixes the buffer of every captured call: capture an even
+    number of calls per instance, or a sequence in which other barriers separate two replays (a whole decoder
+    stack does)."""
 
     def __init__(self, shard: ShardedQuantizedLinear, max_rows: int = 8, group=None):
         self.shard = shard
-        self.out = PeerBuffers((max_rows, shard.n_total), torch.bfloat16, group)
+        self.outs = [PeerBuffers((max_rows, shard.n_total), torch.bfloat16, group) for _ in range(2)]
         self.flags = PeerBuffers((16,), torch.int64, group)
+        self._turn = 0
+
+    @property
+    def out(self):
+        return self.outs[0]
 
     def close(self):
-        self.out.close()
+        for o in self.outs:
+            o.close()
         self.flags.close()
 
     def forward(self, x: torch.Tensor, stream=None) -> torch.Tensor:
@@ -267,39 +283,49 @@ class FusedShardedLinear:
         m, k = x.shape
         st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
         lib = _cabi.lib()
+        out = self.outs[self._turn]
+        self._turn ^= 1
         _cabi.check(lib.lisa_cuda_quantized_matmul_allgather(
             st, x.data_ptr(), m, k, sh.weight.data_ptr(), sh.scales.data_ptr(), sh.biases.data_ptr(), sh.n1 - sh.n0, 1,
-            sh.group_size, sh.bits, _cabi.BF16, self.out.ptrs_rotated(), self.out.world, sh.n_total, sh.n0, _cabi.FLAG_PDL))
+            sh.group_size, sh.bits, _cabi.BF16, out.ptrs_rotated(), out.world, sh.n_total, sh.n0, _cabi.FLAG_PDL))
         # epoch 0: the barrier counts itself on the device, so the pair of launches replays from a CUDA graph
-        _cabi.check(lib.lisa_cuda_peer_barrier(st, self.out.rank, self.out.world, self.flags.ptrs(), 0))
-        return self.out.local[:m]
+        _cabi.check(lib.lisa_cuda_peer_barrier(st, out.rank, out.world, self.flags.ptrs(), 0))
+        return out.local[:m]
 
 
 class FusedShardedSiblings:
     """Several `ShardedQuantizedLinear`s that read the same x (gate|up, q|k|v): one launch whose epilogue stores
-    every linear's column block into every rank's buffers, then ONE peer barrier."""
+    every linear's column block into every rank's buffers, then ONE peer barrier.  Two sets of output buffers
+    taken in turn, as in `FusedShardedLinear` (same reuse rule)."""
 
     def __init__(self, shards, max_rows: int = 8, group=None):
         import ctypes as C
 
         self.shards = list(shards)
-        self.outs = [PeerBuffers((max_rows, sh.n_total), torch.bfloat16, group) for sh in self.shards]
+        self.out_sets = [[PeerBuffers((max_rows, sh.n_total), torch.bfloat16, group) for sh in self.shards] for _ in range(2)]
         self.flags = PeerBuffers((16,), torch.int64, group)
-        c, world = len(self.shards), self.outs[0].world
-        self.world, self.rank = world, self.outs[0].rank
+        c, world = len(self.shards), self.out_sets[0][0].world
+        self.world, self.rank = world, self.out_sets[0][0].rank
         self._w, self._s, self._b = (C.c_void_p * c)(), (C.c_void_p * c)(), (C.c_void_p * c)()
         self._n, self._nt, self._c0 = (C.c_int64 * c)(), (C.c_int64 * c)(), (C.c_int64 * c)()
-        self._y = (C.c_void_p * (c * world))()
+        self._ys = [(C.c_void_p * (c * world))() for _ in range(2)]
         for i, sh in enumerate(self.shards):
             self._w[i], self._s[i], self._b[i] = sh.weight.data_ptr(), sh.scales.data_ptr(), sh.biases.data_ptr()
             self._n[i], self._nt[i], self._c0[i] = sh.n1 - sh.n0, sh.n_total, sh.n0
-            ptrs = self.outs[i].ptrs_rotated()
-            for r in range(world):
-                self._y[i * world + r] = ptrs[r]
+            for turn in range(2):
+                ptrs = self.out_sets[turn][i].ptrs_rotated()
+                for r in range(world):
+                    self._ys[turn][i * world + r] = ptrs[r]
+        self._turn = 0
+
+    @property
+    def outs(self):
+        return self.out_sets[0]
 
     def close(self):
-        for o in self.outs:
-            o.close()
+        for outs in self.out_sets:
+            for o in outs:
+                o.close()
         self.flags.close()
 
     def forward(self, x: torch.Tensor, stream=None):
@@ -309,8 +335,10 @@ class FusedShardedSiblings:
         m, k = x.shape
         st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
         lib = _cabi.lib()
+        turn = self._turn
+        self._turn ^= 1
         _cabi.check(lib.lisa_cuda_quantized_matmul_siblings_allgather(
             st, x.data_ptr(), m, k, len(self.shards), self._w, self._s, self._b, self._n, 1, sh.group_size, sh.bits, _cabi.BF16,
-            self._y, self.world, self._nt, self._c0, _cabi.FLAG_PDL))
+            self._ys[turn], self.world, self._nt, self._c0, _cabi.FLAG_PDL))
         _cabi.check(lib.lisa_cuda_peer_barrier(st, self.rank, self.world, self.flags.ptrs(), 0))
-        return [o.local[:m] for o in self.outs]
+        return [o.local[:m] for o in self.out_sets[turn]]

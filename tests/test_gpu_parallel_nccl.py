@@ -58,6 +58,21 @@ def _worker(rank, world, port, out):
             torch.cuda.synchronize()
             ok[f"fused_m{m}_{rep}"] = bool((y.float() - full.float()).abs().max() <= 1e-2 * full.float().abs().max())
             dist.barrier()  # nobody overwrites a buffer another rank is still comparing
+    # ---- back-to-back calls of one instance without any host barrier between them: the instance alternates
+    # between two output buffers, so the view of call i stays intact while call i+1 is stored
+    xa = torch.randn((3, k), device=dev, generator=g).to(torch.bfloat16)
+    xb = torch.randn((3, k), device=dev, generator=g).to(torch.bfloat16)
+    fa, fb = (ops.quantized_matmul(t, w, s, b, True, 64, bits).float() for t in (xa, xb))
+    good = True
+    for rep in range(6):
+        ya = fused.forward(xa)
+        keep = ya.float()          # the consumer of call i, on the same stream, before call i+1
+        yb = fused.forward(xb)
+        good = good and bool((keep - fa).abs().max() <= 1e-2 * fa.abs().max())
+        good = good and bool((yb.float() - fb).abs().max() <= 1e-2 * fb.abs().max())
+    torch.cuda.synchronize()
+    ok["fused_back_to_back"] = good
+    dist.barrier()
     # ---- two sharded linears that read the same x: one launch, one barrier
     w2, s2, b2 = _affine(g, dev, (), 5120, k, bits)
     lin2 = parallel.ShardedQuantizedLinear.from_full(w2, s2, b2, world, rank, 64, bits)

@@ -81,8 +81,9 @@ int lisa_cuda_clear_device_status(void);
  * y[m, n] = x[m, k] . dequant(W)[n, k]^T, fp32 accumulate, output in `dtype`.
  *   x [m,k] dtype; w uint32 [n, k*bits/32]; scales, biases dtype [n, k/group_size];
  *   y [m,n] dtype.  m >= 1.  Like the reference: transpose must be non-zero and
- *   biases non-null (array_ops.rs:387-392).  bits in {2,4}, group_size in
- *   {32,64,128}, dtype LISA_BF16.  Dispatch by m mirrors array_ops.rs:405-488:
+ *   biases non-null (array_ops.rs:387-392).  bits in {2,4,8}, group_size in
+ *   {32,64,128}, dtype LISA_BF16 (8-bit weights, the lm-head case, run on the generic
+ *   weight-streaming kernel at every row count).  Dispatch by m mirrors array_ops.rs:405-488:
  *   up to 8 rows stream the weights once (group size 64: the tensor-memory GEMV; other group sizes: the
  *   bf16 mma.sync or the generic kernel), more rows run the tcgen05 GEMM.
  *   Numerics of the group-64 GEMV: products and sums are exact integers, but the activations of a (row of
@@ -172,6 +173,20 @@ int lisa_cuda_peer_barrier(lisa_stream_t stream, int rank, int world, void *cons
 int lisa_cuda_dequantize(lisa_stream_t stream, const uint32_t *w, const void *scales,
                          const void *biases, int64_t rows, int64_t k, int group_size, int bits,
                          int dtype, void *out);
+
+/* QuantizedEmbedding::forward, crates/lisa-engine/src/core/quant.rs:449-455 (take_axis of weight, scales and
+ * biases by the token ids, then ops::dequantize): out[i, :] = dequantize(row ids[i]) for `count` int32 ids into
+ * a [vocab, ...] table; an id outside [0, vocab) gives a row of zeros.  out dtype [count, k].  bits in {2,4,8}. */
+int lisa_cuda_dequantize_rows(lisa_stream_t stream, const uint32_t *w, const void *scales,
+                              const void *biases, const int32_t *ids, int64_t count, int64_t vocab,
+                              int64_t k, int group_size, int bits, int dtype, void *out);
+
+/* ops::quantize(w, group_size, bits), array_ops.rs:218-290: the MLX affine quantiser (signed scale, outer edge
+ * as bias, computed in f32; scales and biases returned in w's dtype).  w dtype [rows, k]; wq uint32
+ * [rows, k*bits/32]; scales, biases dtype [rows, k/group_size].  Same refusal as the reference when the group
+ * size does not divide k or is not a whole number of words.  Bit for bit the reference's host loop. */
+int lisa_cuda_quantize(lisa_stream_t stream, const void *w, int64_t rows, int64_t k, int group_size,
+                       int bits, int dtype, uint32_t *wq, void *scales, void *biases);
 
 /* ops::gather_qmm(x, w, scales, biases, lhs_indices, rhs_indices, transpose,
  *                 group_size, bits, sorted_indices), array_ops.rs:561-642.

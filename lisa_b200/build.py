@@ -19,7 +19,7 @@ OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "liblisa_cuda.so")
 
 SOURCES = ["api.cu", "qmv_affine.cu", "qmv_tc.cu", "qmv_i8.cu", "qmm_affine.cu", "dequantize.cu", "gather_qmm.cu", "gguf_matvec.cu",
-           "moe.cu", "tensor_map.cu"]
+           "moe.cu", "tensor_map.cu", "files.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
@@ -42,7 +42,7 @@ def _stamp(paths) -> str:
 
 
 def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(OBJDIR, src.replace(".cu", ".o"))
+    obj = os.path.join(OBJDIR, os.path.splitext(src)[0] + ".o")
     cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
@@ -58,7 +58,7 @@ def _compile(src: str, verbose: bool) -> str:
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIBDIR, exist_ok=True)
     os.makedirs(OBJDIR, exist_ok=True)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "lisa_cuda.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", f) for f in os.listdir(os.path.join(ROOT, "include"))]
     stamp = _stamp(deps)
     stamp_file = os.path.join(OBJDIR, "stamp")
     if not force and os.path.exists(LIB) and os.path.exists(stamp_file) and open(stamp_file).read() == stamp:

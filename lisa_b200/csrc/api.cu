@@ -53,12 +53,14 @@ int sm_count() { return device_info().sms > 0 ? device_info().sms : 148; }
 int max_smem_optin() { return device_info().smem_optin > 0 ? device_info().smem_optin : 232448; }
 
 static int check_affine(const char *op, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
-                        const void *biases, int64_t n, int group_size, int bits, int dtype, const void *y) {
+                        const void *biases, int64_t n, int group_size, int bits, int dtype, const void *y,
+                        bool allow8 = false) {
     std::string name(op);
     if (!biases) return fail(LISA_ERR_BAD_ARG, name + ": affine biases required");
     if (!x || !w || !scales || !y) return fail(LISA_ERR_BAD_ARG, name + ": null pointer");
     if (m < 1 || n < 1 || k < 1) return fail(LISA_ERR_BAD_ARG, name + ": sizes must be positive");
-    if (bits != 2 && bits != 4) return fail(LISA_ERR_UNSUPPORTED, name + ": bits must be 2 or 4");
+    if (bits != 2 && bits != 4 && !(allow8 && bits == 8))
+        return fail(LISA_ERR_UNSUPPORTED, name + (allow8 ? ": bits must be 2, 4 or 8" : ": bits must be 2 or 4"));
     if (group_size != 32 && group_size != 64 && group_size != 128)
         return fail(LISA_ERR_UNSUPPORTED, name + ": group_size must be 32, 64 or 128");
     if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, name + ": unsupported compute dtype (bf16 only)");
@@ -98,8 +100,14 @@ static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, 
                                  const void *scales, const void *biases, int64_t n, int transpose, int group_size,
                                  int bits, int dtype, void *y, unsigned flags) {
     if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: only transpose=true supported");
-    int rc = check_affine("quantized_matmul", x, m, k, w, scales, biases, n, group_size, bits, dtype, y);
+    int rc = check_affine("quantized_matmul", x, m, k, w, scales, biases, n, group_size, bits, dtype, y, true);
     if (rc != LISA_OK) return rc;
+    if (bits == 8) {
+        // 8-bit weights (lm heads): the generic weight-streaming kernel for every row count
+        if (flags & (LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV_TC | LISA_FLAG_FORCE_QMV_I8))
+            return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: 8-bit weights run on the generic kernel only");
+        return qmv_affine(stream, x, m, k, w, scales, biases, n, group_size, bits, y, flags);
+    }
     const bool force_tc = (flags & LISA_FLAG_FORCE_QMV_TC) != 0;
     const bool force_i8 = (flags & LISA_FLAG_FORCE_QMV_I8) != 0;
     const bool force_qmv = (flags & (LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE)) != 0 || force_tc || force_i8;
@@ -303,6 +311,39 @@ int lisa_cuda_dequantize(lisa_stream_t stream, const uint32_t *w, const void *sc
     if (!aligned16(w) || !aligned16(scales) || !aligned16(biases) || !aligned16(out))
         return fail(LISA_ERR_MISALIGNED, "dequantize: pointers must be 16-byte aligned");
     return dequantize_affine(static_cast<cudaStream_t>(stream), w, scales, biases, rows, k, group_size, bits, out);
+}
+
+int lisa_cuda_dequantize_rows(lisa_stream_t stream, const uint32_t *w, const void *scales, const void *biases,
+                              const int32_t *ids, int64_t count, int64_t vocab, int64_t k, int group_size, int bits, int dtype,
+                              void *out) {
+    if (!w || !scales || !biases || !ids || !out) return fail(LISA_ERR_BAD_ARG, "dequantize_rows: null pointer");
+    if (count < 1 || vocab < 1 || k < 1) return fail(LISA_ERR_BAD_ARG, "dequantize_rows: sizes must be positive");
+    if (bits != 2 && bits != 4 && bits != 8) return fail(LISA_ERR_UNSUPPORTED, "dequantize_rows: bits must be 2, 4 or 8");
+    if (group_size != 32 && group_size != 64 && group_size != 128)
+        return fail(LISA_ERR_UNSUPPORTED, "dequantize_rows: group_size must be 32, 64 or 128");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "dequantize_rows: unsupported dtype (bf16 only)");
+    if (k % group_size != 0) return fail(LISA_ERR_BAD_ARG, "dequantize_rows: k is not a multiple of group_size");
+    if (count * k > (1ll << 42) || vocab * k > (1ll << 44)) return fail(LISA_ERR_OVERFLOW, "dequantize_rows: shape too large");
+    if (!aligned16(w) || !aligned16(scales) || !aligned16(biases) || !aligned16(out) || (reinterpret_cast<uintptr_t>(ids) & 3u))
+        return fail(LISA_ERR_MISALIGNED, "dequantize_rows: pointers must be 16-byte aligned (ids 4-byte)");
+    return dequantize_affine_rows(static_cast<cudaStream_t>(stream), w, scales, biases, ids, count, vocab, k, group_size, bits, out);
+}
+
+int lisa_cuda_quantize(lisa_stream_t stream, const void *w, int64_t rows, int64_t k, int group_size, int bits, int dtype,
+                       uint32_t *wq, void *scales, void *biases) {
+    if (!w || !wq || !scales || !biases) return fail(LISA_ERR_BAD_ARG, "quantize: null pointer");
+    if (rows < 1 || k < 1) return fail(LISA_ERR_BAD_ARG, "quantize: sizes must be positive");
+    if (bits != 2 && bits != 4 && bits != 8) return fail(LISA_ERR_UNSUPPORTED, "quantize: bits must be 2, 4 or 8");
+    if (group_size < 1 || k % group_size != 0 || group_size % (32 / bits) != 0) {
+        std::ostringstream os;  // array_ops.rs:226-228
+        os << "quantize: group size " << group_size << " incompatible with K=" << k << ", bits=" << bits;
+        return fail(LISA_ERR_BAD_ARG, os.str());
+    }
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "quantize: unsupported dtype (bf16 only)");
+    if (rows * k > (1ll << 42)) return fail(LISA_ERR_OVERFLOW, "quantize: shape too large");
+    if (!aligned16(w) || !aligned16(wq) || !aligned16(scales) || !aligned16(biases))
+        return fail(LISA_ERR_MISALIGNED, "quantize: pointers must be 16-byte aligned");
+    return quantize_affine(static_cast<cudaStream_t>(stream), w, rows, k, group_size, bits, wq, scales, biases);
 }
 
 size_t lisa_cuda_gather_qmm_workspace_bytes(int64_t rows, int64_t experts) {

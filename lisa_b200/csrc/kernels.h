@@ -76,6 +76,11 @@ int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, in
 int dequantize_affine(cudaStream_t stream, const uint32_t *w, const void *scales, const void *biases, int64_t rows,
                       int64_t k, int group_size, int bits, void *out);
 
+int dequantize_affine_rows(cudaStream_t stream, const uint32_t *w, const void *scales, const void *biases, const int32_t *ids,
+                           int64_t count, int64_t vocab, int64_t k, int group_size, int bits, void *out);
+int quantize_affine(cudaStream_t stream, const void *w, int64_t rows, int64_t k, int group_size, int bits, uint32_t *wq,
+                    void *scales, void *biases);
+
 // gather_qmm.cu
 size_t gather_qmm_workspace_bytes(int64_t rows, int64_t experts);
 int gather_qmm_affine(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,

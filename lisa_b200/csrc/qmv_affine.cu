@@ -731,11 +731,44 @@ static int qmv_dispatch(cudaStream_t stream, const void *x, int64_t m, int64_t k
     return LISA_OK;
 }
 
+// 8-bit weights (the reference's lm-head case, array_ops.rs test loop over bits 2, 4, 8;
+// quantized.metal:102-107,288-292): the generic kernel, one warp per (output row, row of x), for any m.
+static int qmv_simple8(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+                       const void *biases, int64_t n, int group_size, void *y, unsigned flags) {
+    SimpleParams sp{};
+    sp.w = reinterpret_cast<const uint8_t *>(w);
+    sp.scales = reinterpret_cast<const uint8_t *>(scales);
+    sp.biases = reinterpret_cast<const uint8_t *>(biases);
+    sp.n = static_cast<int>(n);
+    sp.k = static_cast<int>(k);
+    sp.wrow_bytes = static_cast<int>(k);
+    sp.srow_bytes = static_cast<int>(k / group_size * 2);
+    sp.group_size = group_size;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    for (int64_t done = 0; done < m; done += 65535) {
+        const int64_t rows = std::min<int64_t>(m - done, 65535);
+        sp.x = reinterpret_cast<const uint16_t *>(x) + done * k;
+        sp.y = reinterpret_cast<uint16_t *>(y) + done * n;
+        cudaLaunchConfig_t cfg{};
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = (flags & LISA_FLAG_PDL) ? 1 : 0;
+        cfg.gridDim = dim3(static_cast<unsigned>((n + 7) / 8), static_cast<unsigned>(rows));
+        cfg.blockDim = dim3(256);
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_simple_kernel<8>, sp));
+        count_launch();
+    }
+    return LISA_OK;
+}
+
 int qmv_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
+    if (bits == 8) return qmv_simple8(stream, x, m, k, w, scales, biases, n, group_size, y, flags);
     if (bits == 4) return qmv_dispatch<4>(stream, x, m, k, w, scales, biases, n, group_size, y, flags);
     if (bits == 2) return qmv_dispatch<2>(stream, x, m, k, w, scales, biases, n, group_size, y, flags);
-    return fail(LISA_ERR_UNSUPPORTED, "qmv: bits must be 2 or 4");
+    return fail(LISA_ERR_UNSUPPORTED, "qmv: bits must be 2, 4 or 8");
 }
 
 }  // namespace lisa

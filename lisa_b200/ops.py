@@ -137,6 +137,43 @@ def dequantize(w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, grou
     return out
 
 
+def dequantize_rows(w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, ids: torch.Tensor, group_size: int = 64,
+                    bits: int = 4, *, stream=None) -> torch.Tensor:
+    """Rows ``ids`` of a quantized table, dequantized: what ``QuantizedEmbedding::forward`` computes with
+    take_axis + ``ops::dequantize`` (crates/lisa-engine/src/core/quant.rs:449-455).  ids of any integer dtype,
+    any shape; returns ids.shape + [K]; an id outside the table gives zeros."""
+    _need_cuda(w, scales, biases, ids)
+    w = _words(w)
+    vocab, kq = w.shape[0], w.shape[-1]
+    k = kq * 32 // bits
+    flat = ids.reshape(-1).to(torch.int32).contiguous()
+    out = torch.empty((flat.numel(), k), dtype=scales.dtype, device=w.device)
+    check(lib().lisa_cuda_dequantize_rows(_stream(stream), w.data_ptr(), scales.contiguous().data_ptr(),
+                                          biases.contiguous().data_ptr(), flat.data_ptr(), flat.numel(), vocab, k,
+                                          group_size, bits, _dtype_code(scales), out.data_ptr()))
+    return out.reshape(*ids.shape, k)
+
+
+def quantize(w: torch.Tensor, group_size: Optional[int] = None, bits: Optional[int] = None, *, stream=None):
+    """``ops::quantize`` (array_ops.rs:218-290): returns (wq uint32 [..., K*bits/32], scales, biases [..., K/group])
+    in w's dtype; defaults group 64, 4 bits."""
+    _need_cuda(w)
+    gs = 64 if group_size is None else int(group_size)
+    b = 4 if bits is None else int(bits)
+    k = w.shape[-1]
+    rows = w.numel() // k
+    if b not in (2, 4, 8) or gs < 1 or k % gs != 0 or gs % (32 // b) != 0:
+        raise LisaError(_cabi.ERR_BAD_ARG, f"quantize: group size {gs} incompatible with K={k}, bits={b}")
+    w2 = w.reshape(rows, k).contiguous()
+    wq = torch.empty((rows, k * b // 32), dtype=torch.int32, device=w.device)
+    sc = torch.empty((rows, k // gs), dtype=w.dtype, device=w.device)
+    bi = torch.empty_like(sc)
+    check(lib().lisa_cuda_quantize(_stream(stream), w2.data_ptr(), rows, k, gs, b, _dtype_code(w2), wq.data_ptr(),
+                                   sc.data_ptr(), bi.data_ptr()))
+    lead = w.shape[:-1]
+    return wq.reshape(*lead, k * b // 32), sc.reshape(*lead, k // gs), bi.reshape(*lead, k // gs)
+
+
 def gather_qmm(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: Optional[torch.Tensor],
                lhs_indices: Optional[torch.Tensor], rhs_indices: Optional[torch.Tensor],
                transpose: bool = True, group_size: int = 64, bits: int = 4,

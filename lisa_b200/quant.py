@@ -1,6 +1,7 @@
 """Engine-side holders of quantized weights, mirroring ``lisa-engine``'s callers of the path.
 
-``QuantizedLinear`` / ``detect_group_size`` follow crates/lisa-engine/src/core/quant.rs:273-321;
+``QuantizedLinear`` / ``QuantizedEmbedding`` / ``detect_group_size`` follow
+crates/lisa-engine/src/core/quant.rs:273-321,408-492;
 ``SwitchGlu.forward`` is the generic routed-expert block of
 crates/lisa-engine/src/models/qwen4/moe.rs:352-481 without the Qwen4-specific shared expert.
 """
@@ -49,6 +50,57 @@ class QuantizedLinear:
     def forward_serial_rows(self, x: torch.Tensor) -> torch.Tensor:
         return ops.quantized_matmul_serial_rows(x, self.weight, self.scales, self.biases, True,
                                                 self.group_size, self.bits)
+
+    def set_quant(self, group_size: int, bits: int) -> None:
+        """Overrides the geometry: the group size is re-derived from the packed shapes for `bits`,
+        `group_size` is the fallback (quant.rs:400-406)."""
+        self.bits = bits
+        self.group_size = detect_group_size(self.weight.shape[-1], self.scales.shape[-1], bits) or group_size
+
+    @classmethod
+    def load(cls, shard, prefix: str, key: str = "", device="cuda", bits: int = 4, group_size: int = 64):
+        """``{prefix}.{key}.weight/.scales/.biases`` of a safetensors shard (`lisa_b200.files.Shard`), copied to
+        `device`; the group size comes from the shapes (quant.rs:408-432)."""
+        w, s, b, gs, bits = shard.quantized_triplet(prefix, key, bits=bits, group_size_hint=group_size)
+        return cls(_to_device_words(w, device), _to_device_bf16(s, device), _to_device_bf16(b, device), gs, bits)
+
+
+def _to_device_words(a, device):
+    import numpy as np
+    return torch.from_numpy(np.array(a, copy=True).view(np.int32)).to(device)
+
+
+def _to_device_bf16(a, device):
+    import numpy as np
+    return torch.from_numpy(np.array(a, copy=True).view(np.int16)).to(device).view(torch.bfloat16)
+
+
+@dataclass
+class QuantizedEmbedding:
+    """An affine-quantized embedding table; lookups dequantize only the gathered rows (quant.rs:436-492).
+    weight uint32 [V, K*bits/32]; scales, biases bf16 [V, K/group_size]."""
+    weight: torch.Tensor
+    scales: torch.Tensor
+    biases: torch.Tensor
+    group_size: int = 64
+    bits: int = 4
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        """Token ids (any integer dtype, any shape) -> [..., K] rows."""
+        return ops.dequantize_rows(self.weight, self.scales, self.biases, ids, self.group_size, self.bits)
+
+    def as_linear(self, x: torch.Tensor) -> torch.Tensor:
+        """The tied output head: [..., K] -> [..., V]."""
+        return ops.quantized_matmul(x, self.weight, self.scales, self.biases, True, self.group_size, self.bits)
+
+    def set_quant(self, group_size: int, bits: int) -> None:
+        self.bits = bits
+        self.group_size = detect_group_size(self.weight.shape[-1], self.scales.shape[-1], bits) or group_size
+
+    @classmethod
+    def load(cls, shard, prefix: str, device="cuda", bits: int = 4, group_size: int = 64):
+        w, s, b, gs, bits = shard.quantized_triplet(prefix, "", bits=bits, group_size_hint=group_size)
+        return cls(_to_device_words(w, device), _to_device_bf16(s, device), _to_device_bf16(b, device), gs, bits)
 
 
 @dataclass

@@ -848,8 +848,15 @@ def sharded_leg(args, torch, dist, dev, rank, world, warmup):
             res[order] = dd
             return res
 
+        ep = None
+        if world > 1 and os.environ.get("LISA_BENCH_EP", "peer") == "peer":
+            ep = parallel.ExpertParallelMoe(block, experts, tokens, hidden)
+            closers.append(ep)
+
         def step():
-            if world > 1:
+            if ep is not None:
+                ep.forward(x, logits)
+            elif world > 1:
                 idx, wts = ops.moe_route(logits, top_k)
                 parallel.ep_moe_forward(x, idx, wts, experts, local_experts)
             else:
@@ -860,7 +867,9 @@ def sharded_leg(args, torch, dist, dev, rank, world, warmup):
         distinct = int(torch.unique(ops.moe_route(logits, top_k)[0]).numel())
         work_bytes = distinct * 3 * (inter * hidden // 2 + 2 * inter * (hidden // GROUP) * 2)
         name = f"configs[3]: routed experts 128 x top-8, hidden 2048, intermediate 768, 4-bit gs64, {tokens} tokens per rank"
-        par = f"expert-parallel, {(e1 - e0)} experts per rank, NCCL all-to-all dispatch and combine" if world > 1 else "single GPU"
+        par = ("single GPU" if world == 1 else
+               f"expert-parallel, {(e1 - e0)} experts per rank, dispatch and return by peer stores (library kernels) + peer barriers"
+               if ep is not None else f"expert-parallel, {(e1 - e0)} experts per rank, NCCL all-to-all dispatch and combine")
         scaling = "weak"
 
     for _ in range(warmup):

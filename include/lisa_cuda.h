@@ -209,6 +209,18 @@ int lisa_cuda_gather_qmm(lisa_stream_t stream, const void *x, int64_t rows, int6
 int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows,
                                  int64_t row_bytes, const float *x, int64_t tokens, float *y);
 
+/* N-sharded GGUF matvec fused with its all-gather (one node, up to 8 GPUs, one process per GPU): the caller holds
+ * rows [row0, row0 + rows_local) of a rows_total-row matrix (rows are independent, as in the dense case); y_all[r]
+ * is rank r's f32 [tokens, rows_total] output as seen from this GPU (own buffer + peer mappings); the kernel's
+ * epilogue stores this rank's column block into all of them with plain stores; lisa_cuda_peer_barrier after it.
+ * No counterpart in the reference (one device).  Takes what the tensor-memory kernel takes: Q4_K with one or
+ * two tokens, Q2_K with one token and rows of whole 336-byte groups; LISA_ERR_UNSUPPORTED otherwise (run the
+ * local matvec and a collective all-gather of the f32 blocks instead).  Same buffer reuse rule as
+ * lisa_cuda_quantized_matmul_allgather. */
+int lisa_cuda_gguf_packed_matvec_allgather(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows_local,
+                                           int64_t row_bytes, const float *x, int64_t tokens, void *const *y_all,
+                                           int world, int64_t rows_total, int64_t row0);
+
 /* The same operator for many tokens (prefill, target-verify: the reference runs these rows as
  * independent matvecs, deepseek41.rs:165-171) with a device workspace from the caller's pool
  * (lisa_cuda_gguf_packed_matmul_workspace_bytes, 16-byte aligned).  With a workspace and 32 tokens
@@ -271,6 +283,32 @@ int lisa_cuda_swiglu(lisa_stream_t stream, const void *gate, const void *up, int
 int lisa_cuda_moe_combine(lisa_stream_t stream, const void *down_sorted, const float *weights,
                           const int32_t *inverse, int64_t tokens, int top_k, int64_t hidden,
                           int dtype, void *out);
+
+/* Expert-parallel exchange over peer memory (one node, up to 8 GPUs, one process per GPU).  No counterpart in
+ * the reference, which runs one device; ownership is its contiguous rule first = rank * (experts / world)
+ * (crates/lisa-mlx/src/shaders/deepseek41/iq.metal:976-982).  Tokens are data-parallel, experts are owned.
+ * Every rank routes and sorts its own slots by GLOBAL expert (lisa_cuda_moe_route, lisa_cuda_moe_sort), which
+ * groups them by owner, then:
+ *   ep_counts    publishes how many of its slots belong to each owner: entry [rank * world + q] of every rank's
+ *                int32 [world, world] count matrix (count_matrices[r]: rank r's matrix as seen from this GPU);
+ *   -- lisa_cuda_peer_barrier; the caller may now read its matrix (column `rank` sums to the rows it receives) --
+ *   ep_dispatch  stores row token_rows[p] of x and the local expert id of every sorted slot p into its owner's
+ *                receive buffers (recv_x[q]: bf16 [capacity, hidden], recv_ids[q]: int32 [capacity]; capacity >= the
+ *                owner's total, at most world * slots), compactly: source ranks in order, slots in sorted order;
+ *   -- lisa_cuda_peer_barrier; the owner sorts recv_ids (moe_sort with top_k = 1: token_rows is then the index into
+ *      recv_x), runs gather_rows / gather_qmm / swiglu / gather_qmm on exactly the rows it received --
+ *   ep_return    stores result row p (sorted order; recv_index = that sort's token_rows) into the source rank's
+ *                `back` buffer (back[r]: bf16 [slots of r, hidden]) at the position the slot has in the source's own
+ *                sorted order, so that the source folds with lisa_cuda_moe_combine and its own `inverse`;
+ *   -- lisa_cuda_peer_barrier --
+ * Plain stores into peer mappings; every buffer is reused from step to step (the three barriers order the reuse). */
+int lisa_cuda_ep_counts(lisa_stream_t stream, const int32_t *sorted_ids, int64_t slots, int64_t experts, int world,
+                        int rank, void *const *count_matrices);
+int lisa_cuda_ep_dispatch(lisa_stream_t stream, const void *x, const int32_t *sorted_ids, const int32_t *token_rows,
+                          int64_t slots, int64_t hidden, int64_t experts, int world, int rank,
+                          const int32_t *count_matrix, void *const *recv_x, void *const *recv_ids, int dtype);
+int lisa_cuda_ep_return(lisa_stream_t stream, const void *rows, const int32_t *recv_index, int64_t count, int64_t hidden,
+                        int world, int rank, const int32_t *count_matrix, void *const *back, int dtype);
 
 #ifdef __cplusplus
 }

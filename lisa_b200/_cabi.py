@@ -54,6 +54,7 @@ SIGNATURES = {
     "lisa_cuda_gather_qmm_workspace_bytes": (_sz, [_i64, _i64]),
     "lisa_cuda_gather_qmm": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _int, _vp, _vp, _sz]),
     "lisa_cuda_gguf_packed_matvec": (_int, [_vp, _int, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "lisa_cuda_gguf_packed_matvec_allgather": (_int, [_vp, _int, _vp, _i64, _i64, _vp, _i64, _vp, _int, _i64, _i64]),
     "lisa_cuda_gguf_packed_matmul_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "lisa_cuda_gguf_packed_matmul": (_int, [_vp, _int, _vp, _i64, _i64, _vp, _i64, _vp, _vp, _sz]),
     "lisa_cuda_gguf_expert_matvec": (_int, [_vp, _int, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp]),
@@ -63,6 +64,9 @@ SIGNATURES = {
     "lisa_cuda_moe_sort_static": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "lisa_cuda_gather_rows": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "lisa_cuda_swiglu": (_int, [_vp, _vp, _vp, _i64, _int, _vp]),
+    "lisa_cuda_ep_counts": (_int, [_vp, _vp, _i64, _i64, _int, _int, _vp]),
+    "lisa_cuda_ep_dispatch": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _int]),
+    "lisa_cuda_ep_return": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _vp, _vp, _int]),
     "lisa_cuda_moe_combine": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _i64, _int, _vp]),
 }
 

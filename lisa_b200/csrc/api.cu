@@ -398,6 +398,27 @@ int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t
     return gguf_matvec(static_cast<cudaStream_t>(stream), format, w, 1, rows, row_bytes, x, tokens, 1, nullptr, 1, y);
 }
 
+int lisa_cuda_gguf_packed_matvec_allgather(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows_local,
+                                           int64_t row_bytes, const float *x, int64_t tokens, void *const *y_all, int world,
+                                           int64_t rows_total, int64_t row0) {
+    int block = 0;
+    int rc = gguf_geometry("packed_matvec_allgather", format, rows_local, row_bytes, &block);
+    if (rc != LISA_OK) return rc;
+    if (!w || !x || !y_all) return fail(LISA_ERR_BAD_ARG, "packed_matvec_allgather: null pointer");
+    if (world < 1 || world > 8) return fail(LISA_ERR_BAD_ARG, "packed_matvec_allgather: 1 to 8 output buffers");
+    for (int r = 0; r < world; ++r)
+        if (!y_all[r] || (reinterpret_cast<uintptr_t>(y_all[r]) & 3u)) return fail(LISA_ERR_BAD_ARG, "packed_matvec_allgather: null or misaligned output buffer");
+    if (tokens < 1 || tokens > 65535) return fail(LISA_ERR_BAD_ARG, "invalid GGUF matvec input rows");
+    if (row0 < 0 || rows_total < 1 || row0 + rows_local > rows_total || rows_total > (1ll << 30))
+        return fail(LISA_ERR_BAD_ARG, "packed_matvec_allgather: row block outside the output");
+    if (!aligned16(w) || !aligned16(x) || row_bytes % 16 != 0) return fail(LISA_ERR_MISALIGNED, "packed_matvec_allgather: w and x must be 16-byte aligned");
+    if (!qmv_tc_gguf_supported(format, tokens, rows_local, row_bytes))
+        return fail(LISA_ERR_UNSUPPORTED, "packed_matvec_allgather: the fused form takes what the tensor-memory kernel takes "
+                                          "(Q4_K: one or two tokens; Q2_K: one token, rows of whole 336-byte groups that fit its stages)");
+    return qmv_tc_gguf_allgather(static_cast<cudaStream_t>(stream), format, w, rows_local, row_bytes, x, tokens,
+                                 reinterpret_cast<float *const *>(y_all), world, rows_total, row0);
+}
+
 size_t lisa_cuda_gguf_packed_matmul_workspace_bytes(int64_t tokens, int64_t row_bytes, int format) {
     const int block = (format == LISA_GGUF_Q2_K) ? 84 : 144;
     if (tokens < 1 || row_bytes < block) return 0;
@@ -495,6 +516,51 @@ int lisa_cuda_moe_combine(lisa_stream_t stream, const void *down_sorted, const f
     if (top_k > 32) return fail(LISA_ERR_LIMIT, "moe_combine: top_k <= 32");
     if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "moe_combine: bf16 only");
     return moe_combine(static_cast<cudaStream_t>(stream), down_sorted, weights, inverse, tokens, top_k, hidden, out);
+}
+
+static int check_ep(const char *op, int world, int rank, int64_t experts, int64_t hidden, void *const *a, void *const *b) {
+    std::string name(op);
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(LISA_ERR_BAD_ARG, name + ": bad rank or world");
+    if (experts < world || experts % world != 0) return fail(LISA_ERR_BAD_ARG, name + ": the experts do not split over the ranks");
+    if (hidden < 8 || hidden % 8 != 0) return fail(LISA_ERR_MISALIGNED, name + ": hidden must be a multiple of 8");
+    for (int r = 0; r < world; ++r) {
+        if (!a || !a[r] || !aligned16(a[r])) return fail(LISA_ERR_BAD_ARG, name + ": null or misaligned peer buffer");
+        if (b && (!b[r] || (reinterpret_cast<uintptr_t>(b[r]) & 3u))) return fail(LISA_ERR_BAD_ARG, name + ": null or misaligned peer buffer");
+    }
+    return LISA_OK;
+}
+
+int lisa_cuda_ep_counts(lisa_stream_t stream, const int32_t *sorted_ids, int64_t slots, int64_t experts, int world, int rank,
+                        void *const *count_matrices) {
+    if (!sorted_ids || slots < 1 || slots > (1ll << 30)) return fail(LISA_ERR_BAD_ARG, "ep_counts: null ids or bad slot count");
+    const int rc = check_ep("ep_counts", world, rank, experts, 8, count_matrices, nullptr);
+    if (rc != LISA_OK) return rc;
+    return ep_counts(static_cast<cudaStream_t>(stream), sorted_ids, slots, experts, world, rank, count_matrices);
+}
+
+int lisa_cuda_ep_dispatch(lisa_stream_t stream, const void *x, const int32_t *sorted_ids, const int32_t *token_rows,
+                          int64_t slots, int64_t hidden, int64_t experts, int world, int rank, const int32_t *count_matrix,
+                          void *const *recv_x, void *const *recv_ids, int dtype) {
+    if (!x || !sorted_ids || !token_rows || !count_matrix || slots < 1 || slots > (1ll << 30))
+        return fail(LISA_ERR_BAD_ARG, "ep_dispatch: null pointer or bad slot count");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "ep_dispatch: bf16 only");
+    if (!aligned16(x)) return fail(LISA_ERR_MISALIGNED, "ep_dispatch: x must be 16-byte aligned");
+    const int rc = check_ep("ep_dispatch", world, rank, experts, hidden, recv_x, recv_ids);
+    if (rc != LISA_OK) return rc;
+    return ep_dispatch(static_cast<cudaStream_t>(stream), x, sorted_ids, token_rows, slots, hidden, experts, world, rank,
+                       count_matrix, recv_x, recv_ids);
+}
+
+int lisa_cuda_ep_return(lisa_stream_t stream, const void *rows, const int32_t *recv_index, int64_t count, int64_t hidden,
+                        int world, int rank, const int32_t *count_matrix, void *const *back, int dtype) {
+    if (count < 0 || count > (1ll << 30)) return fail(LISA_ERR_BAD_ARG, "ep_return: bad row count");
+    if (count > 0 && (!rows || !recv_index)) return fail(LISA_ERR_BAD_ARG, "ep_return: null pointer");
+    if (!count_matrix) return fail(LISA_ERR_BAD_ARG, "ep_return: null count matrix");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "ep_return: bf16 only");
+    if (count > 0 && !aligned16(rows)) return fail(LISA_ERR_MISALIGNED, "ep_return: rows must be 16-byte aligned");
+    const int rc = check_ep("ep_return", world, rank, world, hidden, back, nullptr);
+    if (rc != LISA_OK) return rc;
+    return ep_return(static_cast<cudaStream_t>(stream), rows, recv_index, count, hidden, world, rank, count_matrix, back);
 }
 
 }  // extern "C"

@@ -31,6 +31,8 @@ int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int c
 bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes);
 int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
                 int64_t tokens, float *y);
+int qmv_tc_gguf_allgather(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
+                          int64_t tokens, float *const *outs, int world, int64_t rows_total, int64_t col0);
 int peer_barrier(cudaStream_t stream, int rank, int world, void *const *flag_arrays, unsigned long long epoch);
 int peer_device_status();
 int peer_clear_status();
@@ -105,5 +107,14 @@ int moe_gather_rows(cudaStream_t stream, const void *x, const int32_t *token_row
 int moe_swiglu(cudaStream_t stream, const void *gate, const void *up, int64_t count, void *act);
 int moe_combine(cudaStream_t stream, const void *down_sorted, const float *weights, const int32_t *inverse,
                 int64_t tokens, int top_k, int64_t hidden, void *out);
+
+// ep.cu: expert-parallel dispatch / return over peer memory
+int ep_counts(cudaStream_t stream, const int32_t *sorted_ids, int64_t slots, int64_t experts, int world, int rank,
+              void *const *matrices);
+int ep_dispatch(cudaStream_t stream, const void *x, const int32_t *sorted_ids, const int32_t *token_rows, int64_t slots,
+                int64_t hidden, int64_t experts, int world, int rank, const int32_t *matrix, void *const *recv_x,
+                void *const *recv_ids);
+int ep_return(cudaStream_t stream, const void *rows, const int32_t *recv_index, int64_t count, int64_t hidden, int world, int rank,
+              const int32_t *matrix, void *const *back);
 
 }  // namespace lisa

@@ -933,7 +933,9 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                     for (int r = 0; r < p.splits; ++r) tot += part[(r * kRows + row) * p.m + t];
                     const size_t at = static_cast<size_t>(t) * ldy + p.col0 + n0 + row;
                     if (GG) {
+                        // f32 out; the N-sharded form stores the column block into every rank's output (plain stores)
                         p.yf[at] = tot;
+                        for (int o = 1; o < p.nout; ++o) reinterpret_cast<float *>(p.out[o])[at] = tot;
                     } else if (p.nseg > 1 && p.seg_nout > 0) {
                         const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(tot));
                         const size_t ag = static_cast<size_t>(t) * p.seg_ldy[seg] + p.seg_col0[seg] + n0 + row;
@@ -1188,6 +1190,15 @@ bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row
 
 int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
                 int64_t tokens, float *y) {
+    float *outs[1] = {y};
+    return qmv_tc_gguf_allgather(stream, format, w, rows, row_bytes, x, tokens, outs, 1, rows, 0);
+}
+
+// The same launch as the all-gather of an N-sharded GGUF matrix: rows [col0, col0 + rows) of a rows_total-row
+// matrix, stored as columns of every rank's f32 [tokens, rows_total] output (outs[0 .. world), peers included).
+int qmv_tc_gguf_allgather(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
+                          int64_t tokens, float *const *outs, int world, int64_t rows_total, int64_t col0) {
+    float *y = outs[0];
     const bool q4 = format == LISA_GGUF_Q4_K;
     const int64_t k = row_bytes / (q4 ? 144 : 84) * 256;
     TcParams p{};
@@ -1212,9 +1223,10 @@ int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows,
     p.n = static_cast<int>(rows);
     p.k = static_cast<int>(k);
     p.m = static_cast<int>(tokens);
-    p.nout = 0;
-    p.ldy = static_cast<int>(rows);
-    p.col0 = 0;
+    p.nout = world;
+    for (int o = 0; o < world; ++o) p.out[o] = reinterpret_cast<uint16_t *>(outs[o]);
+    p.ldy = static_cast<int>(rows_total);
+    p.col0 = static_cast<int>(col0);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);

@@ -79,6 +79,33 @@ def all_gather_columns(local: torch.Tensor, n_total: int, group=None) -> torch.T
     return torch.cat([out[r, :, : widths[r]] for r in range(world)], dim=1)
 
 
+@dataclass
+class ShardedGgufLinear:
+    """Rank-local rows ``W[r0:r1]`` of a GGUF K-quant matrix (uint8 ``[rows, row_bytes]`` blocks, the layout of
+    ``deepseek41::packed_matvec``); every rank holds the full f32 activation and computes ``y[:, r0:r1]``, the
+    f32 column blocks are all-gathered.  Rows are independent, so the split is the dense linear's; ranges stay
+    multiples of 8 rows (the kernels' limit, crates/lisa-mlx/src/models/deepseek41.rs:50-65)."""
+    fmt: object
+    weights: torch.Tensor
+    rows_total: int
+    r0: int
+    r1: int
+
+    @classmethod
+    def from_full(cls, fmt, weights: torch.Tensor, world: int, rank: int):
+        rows = weights.shape[0]
+        r0, r1 = shard_rows(rows, world, rank)
+        return cls(fmt, weights[r0:r1].contiguous(), rows, r0, r1)
+
+    def forward(self, x: torch.Tensor, matvec: Optional[Callable] = None, group=None) -> torch.Tensor:
+        """x f32 [tokens, K] (same on every rank) -> y f32 [tokens, rows_total] on every rank."""
+        if matvec is None:
+            from . import ops
+            matvec = ops.packed_matvec
+        local = matvec(self.fmt, self.weights, x)
+        return all_gather_columns(local, self.rows_total, group=group)
+
+
 def expert_range(experts: int, world: int, rank: int) -> Tuple[int, int]:
     """Contiguous expert ownership, iq.metal:976-982: first = rank * (E / world)."""
     if experts % world != 0:
@@ -162,7 +189,7 @@ class _DevicePtr:
                                          "strides": None}
 
 
-_TYPESTR = {torch.bfloat16: "<u2", torch.int64: "<i8", torch.float32: "<f4", torch.int32: "<i4"}
+_TYPESTR = {torch.bfloat16: "<u2", torch.int64: "<i8", torch.float32: "<f4", torch.int32: "<i4"}  # bf16 as its bit pattern
 
 
 class PeerBuffers:
@@ -293,6 +320,42 @@ class FusedShardedLinear:
         return out.local[:m]
 
 
+class FusedShardedGguf:
+    """`ShardedGgufLinear` without a collective library, for the token counts the tensor-memory matvec takes (Q4_K:
+    one or two, Q2_K: one): the kernel's epilogue stores this rank's f32 column block into every rank's output,
+    `lisa_cuda_peer_barrier` orders the ranks.  Two output buffers taken in turn (the reuse rule of
+    `FusedShardedLinear`).  `supported(tokens)` says whether the fused launch applies; otherwise use
+    ``shard.forward`` (local matvec + collective all-gather)."""
+
+    def __init__(self, shard: ShardedGgufLinear, max_tokens: int = 2, group=None):
+        self.shard = shard
+        self.outs = [PeerBuffers((max_tokens, shard.rows_total), torch.float32, group) for _ in range(2)]
+        self.flags = PeerBuffers((16,), torch.int64, group)
+        self._turn = 0
+        self.max_tokens = max_tokens
+
+    def close(self):
+        for o in self.outs:
+            o.close()
+        self.flags.close()
+
+    def forward(self, x: torch.Tensor, stream=None) -> torch.Tensor:
+        from . import _cabi, ops
+
+        sh = self.shard
+        tokens = x.shape[0]
+        st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        out = self.outs[self._turn]
+        self._turn ^= 1
+        lib = _cabi.lib()
+        code = ops._format_code(sh.fmt)
+        _cabi.check(lib.lisa_cuda_gguf_packed_matvec_allgather(
+            st, code, sh.weights.data_ptr(), sh.r1 - sh.r0, sh.weights.shape[1], x.data_ptr(), tokens, out.ptrs_rotated(),
+            out.world, sh.rows_total, sh.r0))
+        _cabi.check(lib.lisa_cuda_peer_barrier(st, out.rank, out.world, self.flags.ptrs(), 0))
+        return out.local[:tokens]
+
+
 class FusedShardedSiblings:
     """Several `ShardedQuantizedLinear`s that read the same x (gate|up, q|k|v): one launch whose epilogue stores
     every linear's column block into every rank's buffers, then ONE peer barrier.  Two sets of output buffers
@@ -342,3 +405,71 @@ class FusedShardedSiblings:
             self._ys[turn], self.world, self._nt, self._c0, _cabi.FLAG_PDL))
         _cabi.check(lib.lisa_cuda_peer_barrier(st, self.rank, self.world, self.flags.ptrs(), 0))
         return [o.local[:m] for o in self.out_sets[turn]]
+
+
+class ExpertParallelMoe:
+    """Routed experts, expert-parallel over the ranks of one node, with the exchange done by the library's own
+    kernels over peer memory (`lisa_cuda_ep_counts / ep_dispatch / ep_return` + `lisa_cuda_peer_barrier`): no
+    collective library on the data path.  Tokens are data-parallel; rank r owns experts
+    ``[r * E / world, (r + 1) * E / world)`` (iq.metal:976-982).  `block` holds this rank's experts
+    (`SwitchGlu` with E / world experts).  The only thing the host reads per call is the world x world count
+    matrix, which sizes the owner's launches."""
+
+    def __init__(self, block, experts: int, max_tokens: int, hidden: int, group=None):
+        self.block = block
+        self.experts, self.top_k, self.hidden = experts, block.top_k, hidden
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.max_slots = max_tokens * block.top_k
+        cap = self.world * self.max_slots           # every slot of every rank could land here
+        self.matrix = PeerBuffers((self.world * self.world,), torch.int32, group)
+        self.recv_x = PeerBuffers((cap, hidden), torch.bfloat16, group)
+        self.recv_ids = PeerBuffers((cap,), torch.int32, group)
+        self.back = PeerBuffers((self.max_slots, hidden), torch.bfloat16, group)
+        self.flags = PeerBuffers((16,), torch.int64, group)
+        self._host_matrix = torch.empty((self.world, self.world), dtype=torch.int32).pin_memory()
+
+    def close(self):
+        for b in (self.matrix, self.recv_x, self.recv_ids, self.back, self.flags):
+            b.close()
+
+    def _barrier(self, st):
+        from . import _cabi
+        _cabi.check(_cabi.lib().lisa_cuda_peer_barrier(st, self.rank, self.world, self.flags.ptrs(), 0))
+
+    def forward(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        """x bf16 [tokens, hidden] and router_logits f32 [tokens, E] of this rank's tokens -> [tokens, hidden]."""
+        from . import _cabi, ops
+
+        lib = _cabi.lib()
+        st = torch.cuda.current_stream().cuda_stream
+        blk, k = self.block, self.top_k
+        tokens = x.shape[0]
+        slots = tokens * k
+        if slots > self.max_slots:
+            raise _cabi.LisaError(_cabi.ERR_LIMIT, "ExpertParallelMoe: more tokens than the buffers were sized for")
+        gs, bits = blk.gate.group_size, blk.gate.bits
+        idx, weights = ops.moe_route(router_logits, k)
+        sorted_ids, token_rows, inverse = ops.moe_sort(idx, self.experts, k)   # by global expert: grouped by owner
+        _cabi.check(lib.lisa_cuda_ep_counts(st, sorted_ids.data_ptr(), slots, self.experts, self.world, self.rank,
+                                            self.matrix.ptrs()))
+        self._barrier(st)
+        self._host_matrix.copy_(self.matrix.local.view(self.world, self.world), non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the one host read: how many rows this rank receives
+        received = int(self._host_matrix[:, self.rank].sum())
+        _cabi.check(lib.lisa_cuda_ep_dispatch(st, x.data_ptr(), sorted_ids.data_ptr(), token_rows.data_ptr(), slots, self.hidden,
+                                              self.experts, self.world, self.rank, self.matrix.local.data_ptr(),
+                                              self.recv_x.ptrs(), self.recv_ids.ptrs(), _cabi.BF16))
+        self._barrier(st)
+        if received:
+            local_e = self.experts // self.world
+            ids = self.recv_ids.local[:received]
+            s2, rows2, _ = ops.moe_sort(ids, local_e, 1)                     # top_k = 1: rows2 indexes recv_x
+            xs = ops.gather_rows(self.recv_x.local[:received], rows2)
+            g = ops.gather_qmm(xs, blk.gate.weight, blk.gate.scales, blk.gate.biases, None, s2, True, gs, bits, True)
+            u = ops.gather_qmm(xs, blk.up.weight, blk.up.scales, blk.up.biases, None, s2, True, gs, bits, True)
+            d = ops.gather_qmm(ops.swiglu(g, u), blk.down.weight, blk.down.scales, blk.down.biases, None, s2, True, gs, bits, True)
+            _cabi.check(lib.lisa_cuda_ep_return(st, d.data_ptr(), rows2.data_ptr(), received, self.hidden, self.world, self.rank,
+                                                self.matrix.local.data_ptr(), self.back.ptrs(), _cabi.BF16))
+        self._barrier(st)
+        return ops.moe_combine(self.back.local[:slots], weights, inverse, k)

@@ -88,6 +88,25 @@ def _worker(rank, world, port, out):
             for j, (y, full) in enumerate(zip(ys, fulls)):
                 ok[f"siblings_m{m}_{rep}_{j}"] = bool((y.float() - full.float()).abs().max() <= 1e-2 * full.float().abs().max())
             dist.barrier()
+    # ---- GGUF K-quant matrices N-sharded: local matvec + NCCL all-gather of the f32 blocks, and the fused form
+    for fmt, block in (("Q4K", 144), ("Q2K", 84)):
+        rows_g, kg = 7168, 2048  # Q2_K rows must be whole 336-byte groups for the fused form: k a multiple of 1024
+        nb = kg // 256
+        gw = torch.randint(0, 256, (rows_g, nb, block), dtype=torch.uint8, device=dev, generator=g)
+        dd = (torch.randn((rows_g, nb, 2), device=dev, generator=g) * 0.01).abs().to(torch.float16).view(torch.uint8)
+        at = 0 if fmt == "Q4K" else 80
+        gw[:, :, at:at + 4] = dd.reshape(rows_g, nb, 4)
+        gw = gw.reshape(rows_g, nb * block).contiguous()
+        glin = parallel.ShardedGgufLinear.from_full(fmt, gw, world, rank)
+        gx = torch.randn((3, kg), device=dev, generator=g)
+        full = ops.packed_matvec(fmt, gw, gx)
+        ok[f"gguf_{fmt}_nccl"] = bool(torch.equal(glin.forward(gx), full))
+        gf = parallel.FusedShardedGguf(glin, max_tokens=2)
+        for rep in range(3):
+            y1 = gf.forward(gx[:1].contiguous())
+            torch.cuda.synchronize()
+            ok[f"gguf_{fmt}_fused_{rep}"] = bool((y1 - full[:1]).abs().max() <= 1e-4 * full.abs().max())
+            dist.barrier()
     ok["device_status"] = ops.device_status() == 0
     # ---- expert-parallel routed experts (config 4 geometry with 16 experts), tokens data-parallel
     experts, hidden, inter, top_k, tokens = 16, 2048, 768, 8, 64
@@ -113,6 +132,15 @@ def _worker(rank, world, port, out):
         res[order] = dd
         return res
 
+    # the same exchange by the library's own kernels over peer memory (no collective on the data path)
+    sl = lambda t: QuantizedLinear(*(a[e0:e1].contiguous() for a in t), 64, 4)
+    ep = parallel.ExpertParallelMoe(SwitchGlu(sl(gate), sl(up), sl(down), top_k), experts, tokens, hidden)
+    for rep in range(3):
+        yp = ep.forward(x[mine].contiguous(), logits[mine].contiguous())
+        torch.cuda.synchronize()
+        dp = (yp.float() - ref[mine].float()).abs().max().item()
+        ok[f"moe_peer_{rep}"] = dp <= 1e-2 * ref.float().abs().max().item()
+    ok["device_status_ep"] = ops.device_status() == 0
     y = parallel.ep_moe_forward(x[mine].contiguous(), idx[mine].contiguous(), wts[mine].contiguous(), experts, local_experts)
     # the grouped GEMM tiles differ between the sharded and the single-GPU run (other rows per expert),
     # the per-row accumulation order does not: equality is expected, a bf16 ulp is tolerated

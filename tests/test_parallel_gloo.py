@@ -60,6 +60,35 @@ def test_n_sharded_linear_all_gather(n, m, bits):
     assert all(ok for _, ok in res), res
 
 
+def _worker_gguf(rank, world, port, fmt, rows, k, tokens, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(2)
+    w = util.gguf_weights(rng, fmt, rows, k)
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    lin = parallel.ShardedGgufLinear.from_full(fmt, torch.from_numpy(w), world, rank)
+
+    def matvec(f, weights, xx):
+        return torch.from_numpy(O.gguf_matvec(f, weights.numpy(), xx.numpy(), threads=1))
+
+    y = lin.forward(torch.from_numpy(x), matvec=matvec)
+    full = O.gguf_matvec(fmt, w, x, threads=1)
+    out.put((rank, bool(np.array_equal(y.numpy(), full)) and (lin.r1 - lin.r0) % 8 == 0))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fmt,rows,tokens", [(O.Q4_K, 64, 1), (O.Q2_K, 72, 3)])  # 72 rows: uneven 8-row blocks
+def test_n_sharded_gguf_matvec_all_gather_f32(fmt, rows, tokens):
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_gguf, args=(r, world, port, fmt, rows, 512, tokens, q)) for r in range(world)]
+    [p.start() for p in procs]
+    res = [q.get(timeout=120) for _ in procs]
+    [p.join(timeout=60) for p in procs]
+    assert all(ok for _, ok in res), res
+
+
 def _worker_moe(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)

@@ -90,6 +90,7 @@ struct QmmParams {
     // N-sharded form fused with its all-gather (dense affine, one linear): the tile is stored at columns
     // col0 + row of every rank's [m, ldy] output (outs[0 .. nout): this GPU's buffer and peer mappings).
     int nout, ldy, col0;
+    int vec_out;  // every output 16-byte aligned, ldy, col0 and n multiples of 8: whole 16-byte runs of 8 rows
     uint16_t *outs[8];
 };
 struct QmmMaps {
@@ -630,6 +631,8 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const uint32_t part32 = smem_u32(xs);
         const int own_lo = split ? (krank == 0 ? 0 : (chunks + 1) / 2) : 0;
         const int own_hi = split ? (krank == 0 ? (chunks + 1) / 2 : chunks) : chunks;
+        // 16-byte stores of the all-gather form need 16-byte aligned runs of 8 rows and room for the stage
+        const bool vec_out = !GGUF && p.nout > 0 && p.vec_out && (!split || p.bt >= 128);
         if (split) {
             fence_proxy_async_smem();
             qmm_cluster_arrive();
@@ -646,7 +649,9 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             qmm_cluster_arrive();
             qmm_cluster_wait();
         }
-        for (int ci = dw >> 2; ci < chunks && ok; ci += kDequantWarps / 4) {
+        // (the 16-byte store path synchronises the four warps of a chunk group with a named barrier, so its
+        // trip count must not depend on a per-warp `ok`: after a timed-out wait the values are undefined anyway)
+        for (int ci = dw >> 2; ci < chunks && (ok || vec_out); ci += kDequantWarps / 4) {
             if (ci < own_lo || ci >= own_hi) continue;
             uint32_t r[16];
             tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
@@ -659,7 +664,28 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     r[j] = __float_as_uint(__uint_as_float(r[j]) + v);
                 }
             }
-            if (out_row < seg_n) {
+            if (vec_out) {
+                // All-gather form: the chunk (128 rows x 16 tokens) is transposed through shared memory so that
+                // every thread stores 16 bytes and a token's 128 rows leave as one 256-byte run per output
+                // (2-byte lanes made 64-byte writes over NVLink).  The four warps of a chunk group share a
+                // 4 KiB stage behind whatever the k-slice exchange used.
+                uint8_t *stage = xs + (split ? p.bt * kBN * 4 : 0) + (dw >> 2) * 4096;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    *reinterpret_cast<uint16_t *>(stage + j * 256 + row * 2) = static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + (dw >> 2)) : "memory");
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    const int item = v * 128 + row, j = item >> 4, sg8 = (item & 15) * 8;
+                    const int tok = t0 + ci * 16 + j;
+                    if (tok < t_end && n0 + sg8 < seg_n) {
+                        const uint4 val = *reinterpret_cast<const uint4 *>(stage + j * 256 + sg8 * 2);
+                        const size_t at = static_cast<size_t>(tok) * p.ldy + p.col0 + n0 + sg8;
+                        for (int o = 0; o < p.nout; ++o) *reinterpret_cast<uint4 *>(p.outs[o] + at) = val;  // peers' memory included
+                    }
+                }
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + (dw >> 2)) : "memory");
+            } else if (out_row < seg_n) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int tok = t0 + ci * 16 + j;
@@ -726,6 +752,9 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     p.ldy = static_cast<int>(ldy);
     p.col0 = static_cast<int>(col0);
     for (int o = 0; o < nout; ++o) p.outs[o] = reinterpret_cast<uint16_t *>(outs[o]);
+    p.vec_out = (nout > 0 && ldy % 8 == 0 && col0 % 8 == 0 && n % 8 == 0) ? 1 : 0;
+    for (int o = 0; o < nout; ++o)
+        if (!aligned16(outs[o])) p.vec_out = 0;
     p.scales = reinterpret_cast<const uint16_t *>(scales);
     p.biases = reinterpret_cast<const uint16_t *>(biases);
     p.y = reinterpret_cast<uint16_t *>(y);

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-weight matmul path on B200.
 
-Headline workload (BASELINE.json configs[1], decode): a Qwen3-4B-shaped stack of 4-bit
+Headline workload (the decode half of the Qwen3-4B-shaped config): a stack of 4-bit
 group-64 linears (36 layers x {q 2560->4096, k, v 2560->1024, o 4096->2560, gate, up
 2560->9728, down 9728->2560}), random-init, one token (M=1) per step.  Metric: HBM GB/s on
 the algorithmic bytes of a token (packed codes + bf16 scales/biases + activations in/out).
@@ -102,7 +102,7 @@ def leg_summary(line):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launches, from the
-# ncu captures summarised in profiles/ (qmv_tc_kernel on 4 layers of the decode stack; qmm_affine_kernel
+# ncu captures (qmv_tc_kernel on 4 layers of the decode stack; qmm_affine_kernel
 # on 2 layers of the prefill stack).  Traffic grows in proportion to the units processed, so the ratio
 # carries over to a full launch.
 DRAM_TRAFFIC_RATIO = {"decode": 1.005, "prefill": 0.570}

@@ -1,6 +1,6 @@
 """GPU parity of the affine path (dequantize, qmv, serial rows) against the CPU oracle,
 through the C ABI.  Tolerance on outputs: |y - ref| <= 1e-2 * max(|ref|, rms(ref)) against
-the f64 contraction (north-star tolerance, fp32 accumulate, bf16 out); dequantized weights
+the f64 contraction (max-relative 1e-2, fp32 accumulate, bf16 out); dequantized weights
 bit-exact."""
 import numpy as np
 import pytest
@@ -63,7 +63,7 @@ def _check_qmm(cuda, n, k, m, bits, gs, flags, seed=0):
 
 
 QMV_SHAPES = [
-    # (n, k) — BASELINE config 1 and the Qwen3-4B-shaped projections, then ragged cases
+    # (n, k) — 9728 x 2560 and the other Qwen3-4B-shaped projections, then ragged cases
     (9728, 2560), (1024, 2560), (2560, 4096), (2560, 9728),
     (2048, 768), (768, 2048),       # config 4 expert shapes; K=768 is not a multiple of 512
     (8, 64), (1, 128), (13, 192), (1001, 512), (300, 5120),
@@ -154,7 +154,7 @@ def test_run_twice_same_bits(cuda):
 
 
 def test_full_size_linearity_config1(cuda):
-    """Size-independent property at BASELINE config 1: y(x1 + x2) == y(x1) + y(x2) up to
+    """Size-independent property at 9728 x 2560, one row: y(x1 + x2) == y(x1) + y(x2) up to
     rounding when x1, x2 and their sum are bf16-exact, and y(0) == 0."""
     rng = np.random.default_rng(8)
     n, k = 9728, 2560

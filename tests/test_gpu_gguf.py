@@ -46,7 +46,7 @@ def test_expert_ids_and_broadcast_match_dense(cuda, name, fmt, experts):
 @pytest.mark.parametrize("name,fmt", FORMATS)
 @pytest.mark.parametrize("rows,k,tokens", [(64, 7168, 1), (72, 18432, 1), (64, 7168, 5), (8, 256, 9)])
 def test_random_blocks_within_tolerance(cuda, name, fmt, rows, k, tokens):
-    """BASELINE config 5 value distributions; f32 accumulate, so the bar is far below 1e-2."""
+    """Uniform random code bytes, d and dmin ~ |N(0, 0.01)|; f32 accumulate, so the bar is far below 1e-2."""
     rng = np.random.default_rng(rows + k + tokens)
     w = util.gguf_weights(rng, fmt, rows, k)
     x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
@@ -142,7 +142,7 @@ def test_q4k_one_or_two_tokens_tensor_memory_kernel_is_exact_on_dyadic_inputs(cu
 
 @pytest.mark.parametrize("rows,k,tokens", [(18432, 7168, 1), (7168, 18432, 2), (136, 2048, 1)])
 def test_q4k_one_or_two_tokens_random_blocks(cuda, rows, k, tokens):
-    """BASELINE config 5 shapes at M=1 (and 2) through the tensor-memory kernel: the matvec bar."""
+    """K=7168 N=18432 and K=18432 N=7168 at M=1 (and 2) through the tensor-memory kernel: the matvec bar."""
     rng = np.random.default_rng(rows + k + tokens)
     w = util.gguf_weights(rng, O.Q4_K, rows, k)
     x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)

@@ -1,5 +1,5 @@
-"""GPU parity of routing, sort, gather_qmm and the whole routed-expert block (BASELINE
-config 4 shapes at reduced expert count for the oracle's sake, and at full size through
+"""GPU parity of routing, sort, gather_qmm and the whole routed-expert block (hidden 2048, intermediate
+768, top-8 geometry at a reduced expert count for the oracle's sake, and at full size through
 properties)."""
 import numpy as np
 import pytest
@@ -74,7 +74,7 @@ def test_gather_qmm_matches_oracle(cuda, bits, n, k, rows):
 
 
 def test_grouped_gather_qmm_equals_dense_gemm_per_expert(cuda):
-    """BASELINE config 4 at full size (128 experts, 4096 tokens x top-8 = 32768 sorted rows, 2048 -> 768):
+    """The routed-expert geometry at full size (128 experts, 4096 tokens x top-8 = 32768 sorted rows, 2048 -> 768):
     every expert run of the grouped GEMM must equal the dense tensor-core GEMM on that expert's rows and
     weights: the same kernel and products; the dense call may add its k-blocks as two slices, so the f32
     sum can differ in its last bits (one bf16 ulp of the output at most)."""

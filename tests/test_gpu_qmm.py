@@ -56,7 +56,7 @@ def test_qmm_group_sizes(cuda, gs, bits):
 
 @pytest.mark.parametrize("n,k", [(4096, 2560), (2560, 9728)])
 def test_qmm_prefill_config2(cuda, n, k):
-    """BASELINE config 2 prefill, M = 2048; the oracle checks 48 weight rows spread over the
+    """The Qwen3-4B-shaped prefill, M = 2048; the oracle checks 48 weight rows spread over the
     tiles (every token), row independence covers the rest."""
     rows = np.unique(np.concatenate([np.arange(0, n, n // 40), [n - 1, 127, 128]]))
     _run(cuda, n, k, 2048, 4, 64, rows=rows)

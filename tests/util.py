@@ -1,4 +1,5 @@
-"""Seeded synthetic tensors with the distributions BASELINE.json names, and the parity metric."""
+"""Seeded synthetic tensors (codes uniform, scale = bf16(|N(0, 0.02)|), bias = bf16(N(0, 0.01)), activations
+bf16(N(0, 1)); GGUF blocks with f16 d, dmin = |N(0, 0.01)|) and the parity metric."""
 from __future__ import annotations
 
 import numpy as np

@@ -5,10 +5,14 @@
 // Unlike the reference's non-NAX path there is no host read-back of the ids: the expert of
 // every row is looked up on the device.
 //
-// Rows-per-expert decides the kernel: few rows per expert (decode, small batches) is a
-// weight-streaming problem handled by gather_qmv_kernel, one warp per (row, output column);
-// many rows per expert is a grouped GEMM over a tile table (qmm_affine.cu).
+// Rows-per-expert decides the kernel: up to eight rows per expert on average (decode, small batches) is a
+// weight-streaming problem handled by the tensor-memory matvec kernel over a table of (expert, <= 8 rows)
+// entries (qmv_tc.cu); more rows per expert is a grouped GEMM over a table of taller tiles (qmm_affine.cu);
+// without a workspace, or for shapes those two do not take, gather_qmv_kernel (one warp per output).
 #include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -137,20 +141,44 @@ static int grouped_tile_rows(int64_t rows, int64_t experts) {
 }
 
 size_t gather_qmm_workspace_bytes(int64_t rows, int64_t experts) {
-    // Tile table of the grouped GEMM: at most ceil(rows/16) + experts tiles of 4 int32, plus a counter block.
-    const int64_t tiles = (rows + 15) / 16 + experts;
+    // Tile table: entries of 4 int32, never more than one per row (every entry holds a row), plus a counter block.
+    const int64_t tiles = rows > 0 ? rows : 1;
     return static_cast<size_t>(tiles * 16 + 256);
 }
 
 int gather_qmm_affine(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
                       const void *scales, const void *biases, const int32_t *ids, int64_t experts, int64_t n,
                       int group_size, int bits, void *y, void *workspace, size_t workspace_bytes) {
-    // Grouped tensor-core GEMM once there are enough rows to fill 16-row tiles; below that the
-    // problem is weight streaming and the warp-per-output kernel is used.
+    // Few rows per expert (decode, short batches): the problem is weight streaming, and the tensor-memory matvec
+    // kernel runs one table entry of up to eight rows per CTA, so every live expert is read once.
+    const bool have_ws = workspace && workspace_bytes >= gather_qmm_workspace_bytes(rows, experts) && rows < (1ll << 30);
+    // (fewer than 24 rows -- one to two decode tokens of a top-8 router -- are quicker through the warp-per-output
+    // kernel below: no table, less set-up per CTA; measured cross-over on the 128-expert 2048 x 768 block)
+    static const int64_t tc_min_rows = [] {
+        const char *v = std::getenv("LISA_GATHER_TC_MIN_ROWS");
+        return v ? std::atoll(v) : 24ll;
+    }();
+    if (have_ws && rows >= tc_min_rows && rows <= 8 * experts && static_cast<int64_t>(experts) * n < (1ll << 31)) {
+        const int bt = qmv_tc_grouped_rows(rows, experts, k, n, group_size, bits);
+        if (bt > 0) {
+            const int64_t max_tiles = std::min<int64_t>(rows, (rows + bt - 1) / bt + experts);
+            int32_t *tile_count = reinterpret_cast<int32_t *>(workspace);
+            int32_t *tiles = tile_count + 64;
+            gather_tile_table_kernel<<<1, kTableThreads, 0, stream>>>(ids, static_cast<int>(rows), static_cast<int>(experts),
+                                                                     bt, static_cast<int>(n), tiles, tile_count,
+                                                                     reinterpret_cast<uint16_t *>(y));
+            LISA_CUDA_TRY(cudaGetLastError());
+            count_launch();
+            return qmv_tc_grouped(stream, x, rows, k, w, scales, biases, experts, n, group_size, bits, y, bt, tiles, tile_count,
+                                  max_tiles);
+        }
+    }
+    // Grouped tensor-core GEMM once there are enough rows to fill 16-row tiles; otherwise the warp-per-output
+    // kernel.
     if (workspace && workspace_bytes >= gather_qmm_workspace_bytes(rows, experts) && rows >= 32 && rows < (1ll << 30) &&
         qmm_affine_supported(rows, k, n, group_size, bits)) {
         const int bt = grouped_tile_rows(rows, experts);
-        const int64_t max_tiles = (rows + bt - 1) / bt + experts;
+        const int64_t max_tiles = std::min<int64_t>(rows, (rows + bt - 1) / bt + experts);
         if (max_tiles <= 65535) {
             int32_t *tile_count = reinterpret_cast<int32_t *>(workspace);
             int32_t *tiles = tile_count + 64;  // 256 bytes further: 16-byte aligned int4 entries

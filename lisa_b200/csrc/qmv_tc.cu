@@ -109,6 +109,13 @@ struct TcParams {
     int seg_ldy[kMaxSeg];
     int seg_col0[kMaxSeg];
     uint16_t *seg_outs[kMaxSeg][8];
+    // grouped form (gather_qmm with few rows per expert): row tile y of the grid belongs to entry g_tiles[y / g_ntiles]
+    // = {expert, row_begin, row_end} of the sorted rows (at most 8 rows per entry); the packed matrix is addressed as
+    // [experts * g_n, k], x and the output are the sorted rows; entries beyond *g_count do nothing
+    const int4 *g_tiles;
+    const int *g_count;
+    int g_ntiles;   // row tiles of one expert
+    int g_n;        // rows of one expert
 };
 struct TcMaps {
     CUtensorMap m[kMaxSeg];
@@ -286,6 +293,19 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         if (p.nseg > 2 && tile >= p.seg_tile[2]) seg = 2;
         tile -= (seg == 0) ? 0 : (seg == 1) ? p.seg_tile[1] : p.seg_tile[2];
     }
+    // grouped form: this CTA's table entry; the k-slices of a tile (one cluster) share it, so they leave together
+    int m_cta = p.m, g_row0 = 0, g_first = 0;
+    if (!GG && p.g_tiles) {
+        const int entry = tile / p.g_ntiles;
+        pdl_wait();  // the table comes from the kernel before this one
+        if (entry >= *p.g_count) return;
+        const int4 t = p.g_tiles[entry];
+        tile -= entry * p.g_ntiles;
+        g_row0 = t.x * p.g_n;     // first row of the expert in the packed matrix
+        g_first = t.y;            // first sorted row of the entry
+        m_cta = t.z - t.y;
+    }
+    const uint16_t *x_cta = p.x + static_cast<size_t>(g_first) * p.k;
     const CUtensorMap *map_w = &maps.m[seg];
     const int seg_n = (seg == 0) ? p.n : (seg == 1) ? p.seg_n[1] : p.seg_n[2];
     const int n0 = tile * kRows;
@@ -341,7 +361,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         auto issue = [&](int wi) {
             mbar_arrive_expect_tx(&wp_full[s], kRows * ROWB);
             // x coordinate in elements of the map: bytes, or 32-bit words for Q2_K
-            tma_load_2d(ring32 + s * (kRows * ROWB), map_w, wi * (GG == 2 ? ROWB / 4 : ROWB), n0, &wp_full[s]);
+            tma_load_2d(ring32 + s * (kRows * ROWB), map_w, wi * (GG == 2 ? ROWB / 4 : ROWB), g_row0 + n0, &wp_full[s]);
             if (++s == p.wstages) { s = 0; ph ^= 1; }
         };
         const int ws_ring = min(ws1, ws0 + p.wstages);
@@ -515,7 +535,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int et = tid - (2 + kUnpackWarps) * 32;  // 0..127
-        const int grow = min(n0 + row, seg_n - 1);
+        const int grow = g_row0 + min(n0 + row, seg_n - 1);
         // scales and biases of (row, group) of the slice: weights, no dependency on the previous kernel
         if (GG == 2) {
             // per block of this row: the 16 scale/min bytes ([block][row] uint4 in `sc`) and {d, dmin} (a word each, after them)
@@ -576,12 +596,12 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             // griddepcontrol.wait, on the critical path.
             constexpr int IPK = 64 / CPW;  // items per k-block: 8 / 4
             constexpr int NV = CPW / 8;    // 16-byte vectors per item: 1 / 2
-            const int items = p.m * L * IPK;
+            const int items = m_cta * L * IPK;
             const int per_token = L * IPK;
             auto load_item = [&](int item, uint4 (&v)[NV]) {
                 if (item < items) {
                     const int t = item / per_token, u = item - t * per_token;
-                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(t) * p.k + kb0 * 64 + u * CPW);
+                    const uint4 *src = reinterpret_cast<const uint4 *>(x_cta + static_cast<size_t>(t) * p.k + kb0 * 64 + u * CPW);
 #pragma unroll
                     for (int i = 0; i < NV; ++i) v[i] = __ldg(src + i);
                 }
@@ -653,7 +673,20 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 }
             };
             constexpr int kStep = kEpilogueWarps * 32;
-            for (int base = 0; base < items; base += 2 * kStep) {
+            int base = 0;
+            // several tokens: four rounds of loads in flight (each round is a round trip to L2)
+            for (; base + 2 * kStep < items; base += 4 * kStep) {
+                uint4 va[NV], vb[NV], vc[NV], vd[NV];
+                load_item(base + et, va);
+                load_item(base + kStep + et, vb);
+                load_item(base + 2 * kStep + et, vc);
+                load_item(base + 3 * kStep + et, vd);
+                store_item(base + et, va);
+                store_item(base + kStep + et, vb);
+                store_item(base + 2 * kStep + et, vc);
+                if (base + 3 * kStep < items) store_item(base + 3 * kStep + et, vd);
+            }
+            for (; base < items; base += 2 * kStep) {
                 uint4 va[NV], vb[NV];
                 load_item(base + et, va);
                 load_item(base + kStep + et, vb);
@@ -896,7 +929,8 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         } else if (GG) {
             if (p.m == 1) run_gguf(IntC<4>{});
             else run_gguf(IntC<8>{});
-        } else if (p.m == 1) run(IntC<1>{});
+        } else if (p.g_tiles) run(IntC<8>{});  // (the B tile layout is the plan's: eight tokens)
+        else if (p.m == 1) run(IntC<1>{});
         else if (p.m == 2) run(IntC<2>{});
         else if (p.m <= 4) run(IntC<4>{});
         else run(IntC<8>{});
@@ -928,10 +962,10 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             const int ldy = (p.nseg > 1) ? seg_n : p.ldy;
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
-                if (t < p.m) {
+                if (t < m_cta) {
                     float tot = 0.f;
                     for (int r = 0; r < p.splits; ++r) tot += part[(r * kRows + row) * p.m + t];
-                    const size_t at = static_cast<size_t>(t) * ldy + p.col0 + n0 + row;
+                    const size_t at = static_cast<size_t>(g_first + t) * ldy + p.col0 + n0 + row;
                     if (GG) {
                         // f32 out; the N-sharded form stores the column block into every rank's output (plain stores)
                         p.yf[at] = tot;
@@ -1081,6 +1115,52 @@ static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t 
         if (rc != LISA_OK) return rc;
     }
     return LISA_OK;
+}
+
+// Grouped form: `rows` sorted rows, expert of row r = the table entry that covers r; entries hold at most
+// `*bt_out` rows (the caller builds the table with that height after asking qmv_tc_grouped_rows).
+static int64_t grouped_live_tiles(int64_t rows, int64_t experts, int64_t n) {
+    // what the split heuristic sees: the row tiles of the experts that can be live, not the table's capacity
+    return std::max<int64_t>(1, std::min(rows, experts)) * ((n + kRows - 1) / kRows);
+}
+
+int qmv_tc_grouped_rows(int64_t rows, int64_t experts, int64_t k, int64_t n, int group_size, int bits) {
+    TcParams p{};
+    int smem = 0, grid = 0, mc = 0;
+    if (n < 1 || n > (1 << 24)) return 0;
+    if (!tc_make_plan(n, k, group_size, bits, 8, p, smem, grid, mc, kWBytes, 0, grouped_live_tiles(rows, experts, n))) return 0;
+    return mc;
+}
+
+int qmv_tc_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w, const void *scales,
+                   const void *biases, int64_t experts, int64_t n, int group_size, int bits, void *y, int bt,
+                   const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles) {
+    TcMaps maps{};
+    {
+        const int rc = affine_tensor_map(&maps.m[0], w, experts * n, k, bits);
+        if (rc != LISA_OK) return rc;
+    }
+    const int64_t ntiles = (n + kRows - 1) / kRows;
+    TcParams p{};
+    int smem = 0, grid = 0, mc = 0;
+    if (!tc_make_plan(n, k, group_size, bits, 8, p, smem, grid, mc, kWBytes, 0, grouped_live_tiles(rows, experts, n)) || mc != bt)
+        return fail(LISA_ERR_UNSUPPORTED, "qmv_tc_grouped: shape not supported");
+    if (max_tiles * ntiles * p.splits > (1ll << 30)) return fail(LISA_ERR_OVERFLOW, "qmv_tc_grouped: grid too large");
+    p.scales = reinterpret_cast<const uint16_t *>(scales);
+    p.biases = reinterpret_cast<const uint16_t *>(biases);
+    p.x = reinterpret_cast<const uint16_t *>(x);
+    p.nout = 1;
+    p.ldy = static_cast<int>(n);
+    p.col0 = 0;
+    p.out[0] = reinterpret_cast<uint16_t *>(y);
+    p.n = static_cast<int>(n);
+    p.k = static_cast<int>(k);
+    p.m = bt;
+    p.g_tiles = reinterpret_cast<const int4 *>(tiles);
+    p.g_count = tile_count;
+    p.g_ntiles = static_cast<int>(ntiles);
+    p.g_n = static_cast<int>(n);
+    return tc_launch_kernel(stream, bits, maps, p, static_cast<int>(max_tiles * ntiles * p.splits), smem, 0);
 }
 
 int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,

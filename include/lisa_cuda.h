@@ -268,7 +268,11 @@ int lisa_cuda_moe_sort(lisa_stream_t stream, const int32_t *idx, int64_t slots, 
  *   runtime query), so make that first call outside any stream capture.  All calls on a device
  *   share the one array, which keeps whatever the last call left in it; every counter a call
  *   reads is written earlier by the same call, so nothing needs clearing, but two calls that
- *   may overlap on the GPU (different streams) race on it and must be ordered by the caller. */
+ *   may overlap on the GPU (different streams) race on it and must be ordered by the caller.
+ *   `stream` must belong to the current device (checked: LISA_ERR_BAD_ARG otherwise; the array is
+ *   per device).  The looked-up address is cached per device for the life of the process: after
+ *   cudaDeviceReset() it is stale, and the library must not be called again on that device without
+ *   being reloaded. */
 int lisa_cuda_moe_sort_static(lisa_stream_t stream, const int32_t *idx, int64_t slots, int64_t experts,
                               int top_k, int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse);
 /* x_sorted[i, :] = x[token_rows[i], :] (gatherSort, moe.rs:375-377). */

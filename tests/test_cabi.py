@@ -33,6 +33,16 @@ def test_every_declared_symbol_is_exported(lib):
     assert set(names) == set(_cabi.SIGNATURES), "ctypes table and header disagree"
 
 
+def test_rust_binding_names_every_export():
+    """rust/lisa-cuda-sys (source only, never compiled here) declares every function of both headers."""
+    rust = open(os.path.join(ROOT, "rust", "lisa-cuda-sys", "src", "lib.rs")).read()
+    declared = set(re.findall(r"\bpub fn (lisa_\w+)\s*\(", rust))
+    wanted = set(declared_symbols())
+    files = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "lisa_files.h")).read(), flags=re.S)
+    wanted |= set(re.findall(r"\b(lisa_(?:gguf|safetensors|detect)\w*)\s*\(", files))
+    assert wanted and wanted <= declared, sorted(wanted - declared)
+
+
 def test_version(lib):
     assert lib.lisa_cuda_version() >= 100
 

@@ -288,6 +288,27 @@ int lisa_cuda_moe_combine(lisa_stream_t stream, const void *down_sorted, const f
                           const int32_t *inverse, int64_t tokens, int top_k, int64_t hidden,
                           int dtype, void *out);
 
+/* The routed block for a handful of tokens (decode), three launches with lisa_cuda_moe_route in front: no sort,
+ * no gathered copy of x, no tile table.  Replace moe_decode::gate_up_act and moe_decode::down_combine
+ * (crates/lisa-mlx/src/models/qwen4/moe_decode.rs:136-298; shaders/qwen4/gate_up_reuse.metal, down_combine.metal)
+ * without their shared-expert operands.
+ *   gate_up_act:  act[s, :] = swiglu(bf16(x[r] . Wg[idx[s]]^T), bf16(x[r] . Wu[idx[s]]^T)) for every slot s, with
+ *                 r = xrow[s], or s / top_k when xrow is null; idx int32 [slots] (the router's [tokens, top_k]
+ *                 output read flat), Wg / Wu [experts, inter, hidden * bits / 32], act bf16 [slots, inter];
+ *   down_combine: out[t, :] = dtype( fold_j f32(bf16(act[t * top_k + j] . Wd[idx[t, j]]^T)) * weights[t, j] ),
+ *                 slots folded in original order (exact_header.metal:12-24), Wd [experts, hidden, inter * bits / 32].
+ * Rounding points as in the reference (every matmul result, sigmoid, silu, their product and the fold to bf16).
+ * An id outside [0, experts) reads no weights and contributes zeros.  2- or 4-bit, group size a multiple of
+ * 32, bf16.  Meant for tokens * top_k below a few dozen; the sorted path (moe_sort + gather_qmm) reads every
+ * expert once and wins beyond that. */
+int lisa_cuda_moe_gate_up_act(lisa_stream_t stream, const void *x, const int32_t *idx, const int32_t *xrow, int64_t slots,
+                              int top_k, int64_t experts, int64_t hidden, int64_t inter, const uint32_t *wg, const void *sg,
+                              const void *bg, const uint32_t *wu, const void *su, const void *bu, int group_size, int bits,
+                              int dtype, void *act);
+int lisa_cuda_moe_down_combine(lisa_stream_t stream, const void *act, const int32_t *idx, const float *weights, int64_t tokens,
+                               int top_k, int64_t experts, int64_t inter, int64_t hidden, const uint32_t *wd, const void *sd,
+                               const void *bd, int group_size, int bits, int dtype, void *out);
+
 /* Expert-parallel exchange over peer memory (one node, up to 8 GPUs, one process per GPU).  No counterpart in
  * the reference, which runs one device; ownership is its contiguous rule first = rank * (experts / world)
  * (crates/lisa-mlx/src/shaders/deepseek41/iq.metal:976-982).  Tokens are data-parallel, experts are owned.

@@ -518,6 +518,43 @@ int lisa_cuda_moe_combine(lisa_stream_t stream, const void *down_sorted, const f
     return moe_combine(static_cast<cudaStream_t>(stream), down_sorted, weights, inverse, tokens, top_k, hidden, out);
 }
 
+static int check_moe_decode(const char *op, int64_t experts, int64_t k, int64_t n, int top_k, int group_size, int bits, int dtype) {
+    std::string name(op);
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, name + ": bf16 only");
+    if (experts < 1 || experts > (1 << 20) || k < 1 || n < 1) return fail(LISA_ERR_BAD_ARG, name + ": bad sizes");
+    if (experts * n * k > (1ll << 44)) return fail(LISA_ERR_OVERFLOW, name + ": shape too large");
+    if (top_k < 1 || top_k > 32) return fail(LISA_ERR_LIMIT, name + ": top_k must be 1..32");
+    if (!moe_decode_supported(k, group_size, bits, top_k))
+        return fail(LISA_ERR_UNSUPPORTED, name + ": needs 2- or 4-bit codes, a group size that is a multiple of 32, "
+                                                 "rows of whole 16-byte chunks and top_k rows of activations within 160 KiB");
+    return LISA_OK;
+}
+
+int lisa_cuda_moe_gate_up_act(lisa_stream_t stream, const void *x, const int32_t *idx, const int32_t *xrow, int64_t slots,
+                              int top_k, int64_t experts, int64_t hidden, int64_t inter, const uint32_t *wg, const void *sg,
+                              const void *bg, const uint32_t *wu, const void *su, const void *bu, int group_size, int bits,
+                              int dtype, void *act) {
+    if (!x || !idx || !wg || !sg || !bg || !wu || !su || !bu || !act) return fail(LISA_ERR_BAD_ARG, "moe_gate_up_act: null pointer");
+    if (slots < 1 || slots > (1 << 24)) return fail(LISA_ERR_BAD_ARG, "moe_gate_up_act: bad slot count");
+    const int rc = check_moe_decode("moe_gate_up_act", experts, hidden, inter, top_k, group_size, bits, dtype);
+    if (rc != LISA_OK) return rc;
+    if (!aligned16(x) || !aligned16(wg) || !aligned16(wu)) return fail(LISA_ERR_MISALIGNED, "moe_gate_up_act: pointers must be 16-byte aligned");
+    return moe_gate_up_act(static_cast<cudaStream_t>(stream), x, idx, xrow, slots, top_k, experts, hidden, inter, wg, sg, bg, wu, su,
+                           bu, group_size, bits, act);
+}
+
+int lisa_cuda_moe_down_combine(lisa_stream_t stream, const void *act, const int32_t *idx, const float *weights, int64_t tokens,
+                               int top_k, int64_t experts, int64_t inter, int64_t hidden, const uint32_t *wd, const void *sd,
+                               const void *bd, int group_size, int bits, int dtype, void *out) {
+    if (!act || !idx || !weights || !wd || !sd || !bd || !out) return fail(LISA_ERR_BAD_ARG, "moe_down_combine: null pointer");
+    if (tokens < 1 || tokens > (1 << 24)) return fail(LISA_ERR_BAD_ARG, "moe_down_combine: bad token count");
+    const int rc = check_moe_decode("moe_down_combine", experts, inter, hidden, top_k, group_size, bits, dtype);
+    if (rc != LISA_OK) return rc;
+    if (!aligned16(act) || !aligned16(wd)) return fail(LISA_ERR_MISALIGNED, "moe_down_combine: pointers must be 16-byte aligned");
+    return moe_down_combine(static_cast<cudaStream_t>(stream), act, idx, weights, tokens, top_k, experts, inter, hidden, wd, sd, bd,
+                            group_size, bits, out);
+}
+
 static int check_ep(const char *op, int world, int rank, int64_t experts, int64_t hidden, void *const *a, void *const *b) {
     std::string name(op);
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(LISA_ERR_BAD_ARG, name + ": bad rank or world");

@@ -111,6 +111,14 @@ int moe_sort_static(cudaStream_t stream, const int32_t *idx, int64_t slots, int6
 int moe_gather_rows(cudaStream_t stream, const void *x, const int32_t *token_rows, int64_t rows, int64_t width,
                     void *out);
 int moe_swiglu(cudaStream_t stream, const void *gate, const void *up, int64_t count, void *act);
+// the routed block for a handful of tokens (moe_decode.cu): per-slot gate|up + SwiGLU, per-token down + fold
+bool moe_decode_supported(int64_t k, int group_size, int bits, int top_k);
+int moe_gate_up_act(cudaStream_t stream, const void *x, const int32_t *idx, const int32_t *xrow, int64_t slots, int top_k,
+                    int64_t experts, int64_t k, int64_t n, const uint32_t *wg, const void *sg, const void *bg,
+                    const uint32_t *wu, const void *su, const void *bu, int group_size, int bits, void *act);
+int moe_down_combine(cudaStream_t stream, const void *act, const int32_t *idx, const float *weights, int64_t tokens, int top_k,
+                     int64_t experts, int64_t k, int64_t n, const uint32_t *wd, const void *sd, const void *bd, int group_size,
+                     int bits, void *out);
 int moe_combine(cudaStream_t stream, const void *down_sorted, const float *weights, const int32_t *inverse,
                 int64_t tokens, int top_k, int64_t hidden, void *out);
 

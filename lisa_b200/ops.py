@@ -352,6 +352,46 @@ def moe_combine(down_sorted: torch.Tensor, weights: torch.Tensor, inverse: torch
     return out
 
 
+def moe_gate_up_act(x: torch.Tensor, idx: torch.Tensor, gate, up, group_size: int, bits: int, *, xrow=None,
+                    stream=None) -> torch.Tensor:
+    """moe_decode::gate_up_act (crates/lisa-mlx/src/models/qwen4/moe_decode.rs:136-184) without the shared
+    expert: x [tokens, hidden], idx int32 [tokens, top_k], gate / up = (weight [E, inter, hidden*bits/32],
+    scales, biases) -> act [tokens * top_k, inter]."""
+    _need_cuda(x, idx, *gate, *up)
+    x = x.contiguous()
+    idx = idx.contiguous()
+    top_k = idx.shape[-1]
+    slots = idx.numel()
+    experts, inter = gate[0].shape[0], gate[0].shape[1]
+    hidden = x.shape[-1]
+    act = torch.empty((slots, inter), dtype=x.dtype, device=x.device)
+    check(lib().lisa_cuda_moe_gate_up_act(_stream(stream), x.data_ptr(), idx.data_ptr(),
+                                          None if xrow is None else xrow.contiguous().data_ptr(), slots, top_k, experts,
+                                          hidden, inter, gate[0].data_ptr(), gate[1].data_ptr(), gate[2].data_ptr(),
+                                          up[0].data_ptr(), up[1].data_ptr(), up[2].data_ptr(), group_size, bits,
+                                          _dtype_code(x), act.data_ptr()))
+    return act
+
+
+def moe_down_combine(act: torch.Tensor, idx: torch.Tensor, weights: torch.Tensor, down, group_size: int, bits: int, *,
+                     stream=None) -> torch.Tensor:
+    """moe_decode::down_combine (moe_decode.rs:214-298) without the shared expert and its gate: act
+    [tokens * top_k, inter], idx / weights [tokens, top_k], down = (weight [E, hidden, inter*bits/32], scales,
+    biases) -> [tokens, hidden]."""
+    _need_cuda(act, idx, weights, *down)
+    act = act.contiguous()
+    idx = idx.contiguous()
+    tokens, top_k = idx.shape
+    experts, hidden = down[0].shape[0], down[0].shape[1]
+    inter = act.shape[-1]
+    out = torch.empty((tokens, hidden), dtype=act.dtype, device=act.device)
+    check(lib().lisa_cuda_moe_down_combine(_stream(stream), act.data_ptr(), idx.data_ptr(),
+                                           weights.contiguous().data_ptr(), tokens, top_k, experts, inter, hidden,
+                                           down[0].data_ptr(), down[1].data_ptr(), down[2].data_ptr(), group_size, bits,
+                                           _dtype_code(act), out.data_ptr()))
+    return out
+
+
 def launch_count() -> int:
     return int(lib().lisa_cuda_launch_count())
 

@@ -110,6 +110,10 @@ class SwitchGlu:
     up: QuantizedLinear
     down: QuantizedLinear
     top_k: int
+    # below this many (token, expert) slots the per-slot path is used; from it on the sorted one, which reads every
+    # expert once (measured cross-over on the 128-expert top-8 block: three tokens 0.066 against 0.079 ms, four
+    # tokens 0.082 against 0.088)
+    DECODE_SLOTS = 32
 
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
         """x [tokens, hidden] bf16, router_logits f32 [tokens, E] -> [tokens, hidden]:
@@ -118,6 +122,11 @@ class SwitchGlu:
         experts = self.gate.weight.shape[0]
         gs, bits = self.gate.group_size, self.gate.bits
         idx, weights = ops.moe_route(router_logits, self.top_k)
+        if x.shape[0] * self.top_k < self.DECODE_SLOTS:
+            # a handful of tokens (forward_decode, moe.rs:116-350): three launches, every slot streams its own expert
+            g, u, d = ((l.weight, l.scales, l.biases) for l in (self.gate, self.up, self.down))
+            act = ops.moe_gate_up_act(x, idx, g, u, gs, bits)
+            return ops.moe_down_combine(act, idx, weights, d, gs, bits)
         sorted_ids, token_rows, inverse = ops.moe_sort(idx, experts, self.top_k)
         x_sorted = ops.gather_rows(x, token_rows)
         g = ops.gather_qmm(x_sorted, self.gate.weight, self.gate.scales, self.gate.biases, None, sorted_ids,

@@ -146,8 +146,14 @@ def test_routed_block_128_experts_top8(cuda, tokens):
     oy = O.moe_combine(od, rw[toks], sub_inv, top_k)
     err, l2 = util.parity(O.bf16_to_f32(yb[toks]), O.bf16_to_f32(oy))
     assert err <= TOL and l2 <= TOL, (err, l2)
-    # and SwitchGlu.forward is that chain
-    assert np.array_equal(host_bf16_bits(block.forward(tx, tl)), yb)
+    # and SwitchGlu.forward is that chain; below 24 slots it takes the per-slot path (three launches), whose
+    # dot products sum in another order: the same 1e-2 against the oracle's chain
+    fwd = host_bf16_bits(block.forward(tx, tl))
+    if tokens * top_k >= SwitchGlu.DECODE_SLOTS:
+        assert np.array_equal(fwd, yb)
+    else:
+        err, l2 = util.parity(O.bf16_to_f32(fwd[toks]), O.bf16_to_f32(oy))
+        assert err <= TOL and l2 <= TOL, (err, l2)
     assert ops.device_status() == 0
 
 

@@ -122,3 +122,104 @@ def test_switch_glu_block_matches_oracle(cuda, tokens):
     err, l2 = util.parity(got, O.bf16_to_f32(ref))
     # three bf16 rounding points sit between input and output; the block output still holds 1e-2
     assert err <= 1e-2 and l2 <= 1e-2, (err, l2)
+
+
+def _lin_triplet(t, cuda):
+    return dev_u32(t[0], cuda), dev_bf16(t[1], cuda), dev_bf16(t[2], cuda)
+
+
+@pytest.mark.parametrize("bits,gs", [(4, 64), (2, 64), (4, 32), (4, 128)])
+@pytest.mark.parametrize("tokens", [1, 2])
+def test_decode_path_stages_match_oracle(cuda, tokens, bits, gs):
+    """The per-slot path for a handful of tokens: gate|up + SwiGLU per slot against the oracle's matvecs on the
+    same rows, then down + fold per token against the oracle's matvec on the activations the GPU produced and its
+    fold on those results."""
+    rng = np.random.default_rng(40 + tokens + bits + gs)
+    experts, hidden, inter, top_k = 12, 1024, 384, 8
+    gate = util.affine_weights(rng, inter, hidden, bits, gs, experts=experts)
+    up = util.affine_weights(rng, inter, hidden, bits, gs, experts=experts)
+    down = util.affine_weights(rng, hidden, inter, bits, gs, experts=experts)
+    x = util.activations(rng, tokens, hidden)
+    idx = np.stack([rng.choice(experts, size=top_k, replace=False) for _ in range(tokens)]).astype(np.int32)
+    wts = rng.random(size=(tokens, top_k)).astype(np.float32)
+    tidx = dev_i32(idx, cuda)
+    act = ops.moe_gate_up_act(dev_bf16(x, cuda), tidx, _lin_triplet(gate, cuda), _lin_triplet(up, cuda), gs, bits)
+    ab = host_bf16_bits(act)
+    slots = idx.reshape(-1)
+    order = np.argsort(slots, kind="stable")          # the oracle wants sorted ids
+    xs = np.repeat(x, top_k, axis=0)[order]
+    og = O.gather_qmm(xs, *gate, slots[order], gs, bits, round_weight_bf16=False)
+    ou = O.gather_qmm(xs, *up, slots[order], gs, bits, round_weight_bf16=False)
+    ref = np.empty_like(ab)
+    ref[order] = O.swiglu_bf16(og, ou)
+    err, l2 = util.parity(O.bf16_to_f32(ab), O.bf16_to_f32(ref))
+    assert err <= 1e-2 and l2 <= 1e-2, (err, l2)
+    y = ops.moe_down_combine(act, tidx, dev_f32(wts, cuda), _lin_triplet(down, cuda), gs, bits)
+    od = np.empty((slots.size, hidden), dtype=np.uint16)
+    od[order] = O.gather_qmm(ab[order], *down, slots[order], gs, bits, round_weight_bf16=False)
+    inverse = np.arange(slots.size, dtype=np.int32)   # rows already in slot order
+    want = O.moe_combine(od, wts, inverse, top_k)
+    err, l2 = util.parity(O.bf16_to_f32(host_bf16_bits(y)), O.bf16_to_f32(want))
+    assert err <= 1e-2 and l2 <= 1e-2, (err, l2)
+    assert ops.device_status() == 0
+
+
+def test_decode_path_skips_ids_outside_the_table_and_honours_xrow(cuda):
+    rng = np.random.default_rng(77)
+    experts, hidden, inter, top_k, tokens = 6, 512, 256, 4, 3
+    gate = util.affine_weights(rng, inter, hidden, 4, 64, experts=experts)
+    up = util.affine_weights(rng, inter, hidden, 4, 64, experts=experts)
+    down = util.affine_weights(rng, hidden, inter, 4, 64, experts=experts)
+    x = util.activations(rng, tokens, hidden)
+    idx = rng.integers(0, experts, size=(tokens, top_k)).astype(np.int32)
+    idx[0, 1], idx[2, 3] = -1, experts
+    wts = rng.random(size=(tokens, top_k)).astype(np.float32)
+    g, u, d = (_lin_triplet(t, cuda) for t in (gate, up, down))
+    tx, tidx = dev_bf16(x, cuda), dev_i32(idx, cuda)
+    act = ops.moe_gate_up_act(tx, tidx, g, u, 64, 4)
+    ab = host_bf16_bits(act)
+    assert np.all(ab[1] == 0) and np.all(ab[11] == 0) and np.any(ab[0] != 0)
+    # an explicit row map equal to slot / top_k changes nothing; a permuted one reads the other token's row
+    rows = (np.arange(tokens * top_k) // top_k).astype(np.int32)
+    assert torch.equal(ops.moe_gate_up_act(tx, tidx, g, u, 64, 4, xrow=dev_i32(rows, cuda)), act)
+    swapped = host_bf16_bits(ops.moe_gate_up_act(tx, tidx, g, u, 64, 4, xrow=dev_i32((tokens - 1 - rows).astype(np.int32), cuda)))
+    flipped = host_bf16_bits(ops.moe_gate_up_act(dev_bf16(x[::-1].copy(), cuda), tidx, g, u, 64, 4))
+    assert np.array_equal(swapped, flipped)
+    # the fold: slots outside the table add zero, the others as if the bad ones had weight zero
+    y = host_bf16_bits(ops.moe_down_combine(act, tidx, dev_f32(wts, cuda), d, 64, 4))
+    idx2, w2 = idx.copy(), wts.copy()
+    idx2[0, 1], idx2[2, 3] = 0, 0
+    act2 = act.clone()
+    act2[1], act2[11] = 0, 0
+    y2 = host_bf16_bits(ops.moe_down_combine(act2, dev_i32(idx2, cuda), dev_f32(w2, cuda), d, 64, 4))
+    # expert 0 on a zero row gives bias * 0 = 0 as well
+    assert np.array_equal(y, y2)
+
+
+@pytest.mark.parametrize("tokens", [1, 2])
+def test_decode_path_agrees_with_the_sorted_path(cuda, tokens):
+    """128 experts, top-8, 2048 / 768: the three-launch path against the sorted chain on the same device (both
+    follow the matvec law; sums differ in order only)."""
+    rng = np.random.default_rng(300 + tokens)
+    experts, hidden, inter, top_k = 128, 2048, 768, 8
+    gate = util.affine_weights(rng, inter, hidden, 4, 64, experts=experts)
+    up = util.affine_weights(rng, inter, hidden, 4, 64, experts=experts)
+    down = util.affine_weights(rng, hidden, inter, 4, 64, experts=experts)
+
+    def lin(t):
+        return QuantizedLinear(dev_u32(t[0], cuda), dev_bf16(t[1], cuda), dev_bf16(t[2], cuda), 64, 4)
+
+    block = SwitchGlu(lin(gate), lin(up), lin(down), top_k)
+    tx = dev_bf16(util.activations(rng, tokens, hidden), cuda)
+    tl = dev_f32(rng.normal(size=(tokens, experts)).astype(np.float32), cuda)
+    before = ops.launch_count()
+    fast = block.forward(tx, tl)
+    assert ops.launch_count() - before == 3
+    old = SwitchGlu.DECODE_SLOTS
+    try:
+        SwitchGlu.DECODE_SLOTS = 0
+        chain = block.forward(tx, tl)
+    finally:
+        SwitchGlu.DECODE_SLOTS = old
+    f, c = fast.float(), chain.float()
+    assert float((f - c).abs().max()) <= 2.0 ** -6 * float(c.abs().max())

@@ -231,6 +231,46 @@ pub fn dequantize_rows<A: DeviceArray>(stream: Stream, w: &A, scales: &A, biases
     Ok(out)
 }
 
+/// `moe_decode::gate_up_act` (crates/lisa-mlx/src/models/qwen4/moe_decode.rs:136-184) without the shared
+/// expert: `x [tokens, hidden]`, `idx [tokens, top_k]`, gate / up `(w [E, inter, hidden*bits/32], scales,
+/// biases)` -> `act [tokens * top_k, inter]`; `xrow` maps slots to rows of `x` (default `slot / top_k`).
+#[allow(clippy::too_many_arguments)]
+pub fn gate_up_act<A: DeviceArray>(stream: Stream, wg: &A, sg: &A, bg: &A, wu: &A, su: &A, bu: &A, x: &A, idx: &A,
+                                   xrow: Option<&A>, group_size: i32, bits: i32) -> Result<A> {
+    let (experts, inter) = (wg.shape()[0], wg.shape()[1]);
+    let hidden = *x.shape().last().unwrap();
+    let top_k = *idx.shape().last().unwrap();
+    let slots: i64 = idx.shape().iter().product();
+    let mut act = A::alloc(&[slots, inter], x.dtype())?;
+    check(unsafe {
+        sys::lisa_cuda_moe_gate_up_act(stream.0, x.device_ptr(), idx.device_ptr() as *const i32,
+                                       xrow.map_or(std::ptr::null(), |r| r.device_ptr() as *const i32), slots, top_k as c_int,
+                                       experts, hidden, inter, wg.device_ptr() as *const u32, sg.device_ptr(), bg.device_ptr(),
+                                       wu.device_ptr() as *const u32, su.device_ptr(), bu.device_ptr(), group_size, bits,
+                                       x.dtype().code()?, act.device_ptr_mut())
+    })?;
+    Ok(act)
+}
+
+/// `moe_decode::down_combine` (moe_decode.rs:214-298) without the shared expert and its gate: `act [tokens *
+/// top_k, inter]`, `idx` / `w [tokens, top_k]`, down `(w [E, hidden, inter*bits/32], scales, biases)` ->
+/// `[tokens, hidden]`.
+#[allow(clippy::too_many_arguments)]
+pub fn down_combine<A: DeviceArray>(stream: Stream, wd: &A, sd: &A, bd: &A, act: &A, idx: &A, w: &A, group_size: i32,
+                                    bits: i32) -> Result<A> {
+    let (experts, hidden) = (wd.shape()[0], wd.shape()[1]);
+    let inter = *act.shape().last().unwrap();
+    let (tokens, top_k) = (idx.shape()[0], idx.shape()[1]);
+    let mut out = A::alloc(&[tokens, hidden], act.dtype())?;
+    check(unsafe {
+        sys::lisa_cuda_moe_down_combine(stream.0, act.device_ptr(), idx.device_ptr() as *const i32,
+                                        w.device_ptr() as *const f32, tokens, top_k as c_int, experts, inter, hidden,
+                                        wd.device_ptr() as *const u32, sd.device_ptr(), bd.device_ptr(), group_size, bits,
+                                        act.dtype().code()?, out.device_ptr_mut())
+    })?;
+    Ok(out)
+}
+
 /// `detect_group_size`, crates/lisa-engine/src/core/quant.rs:273-287.
 pub fn detect_group_size(weight_cols: i32, scales_cols: i32, bits: i32) -> Option<i32> {
     match unsafe { sys::lisa_detect_group_size(weight_cols, scales_cols, bits) } {

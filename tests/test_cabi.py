@@ -87,6 +87,34 @@ def test_gather_qmm_rejections(lib):
     assert lib.lisa_cuda_gather_qmm_workspace_bytes(512, 128) > 0
 
 
+def test_decode_block_rejections(lib):
+    def gate(**kw):
+        a = dict(x=16, idx=16, xrow=None, slots=8, top_k=8, e=4, hidden=256, inter=128, wg=16, sg=16, bg=16, wu=16, su=16,
+                 bu=16, gs=64, bits=4, dtype=0, act=16)
+        a.update(kw)
+        return lib.lisa_cuda_moe_gate_up_act(None, a["x"], a["idx"], a["xrow"], a["slots"], a["top_k"], a["e"], a["hidden"],
+                                             a["inter"], a["wg"], a["sg"], a["bg"], a["wu"], a["su"], a["bu"], a["gs"],
+                                             a["bits"], a["dtype"], a["act"])
+
+    def down(**kw):
+        a = dict(act=16, idx=16, w=16, tokens=1, top_k=8, e=4, inter=128, hidden=256, wd=16, sd=16, bd=16, gs=64, bits=4,
+                 dtype=0, out=16)
+        a.update(kw)
+        return lib.lisa_cuda_moe_down_combine(None, a["act"], a["idx"], a["w"], a["tokens"], a["top_k"], a["e"], a["inter"],
+                                              a["hidden"], a["wd"], a["sd"], a["bd"], a["gs"], a["bits"], a["dtype"], a["out"])
+    for call in (gate, down):
+        assert call(idx=None) == _cabi.ERR_BAD_ARG
+        assert call(bits=3) == _cabi.ERR_UNSUPPORTED
+        assert call(bits=8) == _cabi.ERR_UNSUPPORTED
+        assert call(gs=48) == _cabi.ERR_UNSUPPORTED
+        assert call(top_k=33) == _cabi.ERR_LIMIT
+        assert call(dtype=2) == _cabi.ERR_UNSUPPORTED
+        assert call(e=0) == _cabi.ERR_BAD_ARG
+    assert gate(x=8) == _cabi.ERR_MISALIGNED
+    assert gate(hidden=72) == _cabi.ERR_UNSUPPORTED      # packed rows that are not whole 16-byte chunks
+    assert gate(slots=0) == _cabi.ERR_BAD_ARG and down(tokens=0) == _cabi.ERR_BAD_ARG
+
+
 def test_gguf_rejections(lib):
     f = lib.lisa_cuda_gguf_packed_matvec
     # deepseek41.rs:50-65,100-101

@@ -129,6 +129,10 @@ struct TcPlan {
 // in rows 4 + t of ONE 8-row group (1024 bytes); the MMA still reads N = 16 rows, the second group being
 // whatever follows (the next pair's tile, or the staging area behind the last one): its eight accumulator
 // columns are never read.
+// Words per row of the staged scales (and of the staged biases): the bf16 values of the slice's groups as they lie
+// in memory, four per 8-byte asynchronous copy, the row pitch an odd number of such copies so that the 32 rows
+// of a warp spread over the banks (two rows per bank).
+__host__ __device__ inline int tc_sc_stride(int max_l) { return 2 * (((max_l + 3) / 4) | 1); }
 __host__ __device__ inline int tc_xtile(int m, int wbytes) { return (wbytes == kWBytes && m <= 4) ? 1024 : kXTile; }
 __host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, int m, int wbytes = kWBytes) {
     TcPlan p;
@@ -140,8 +144,8 @@ __host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, in
     p.zero = off;                     // (unused)
     p.xsum = off;                     // [max_l][8] f32 sum(x), then [max_l][8] f32 2^(E-13)
     off += 2 * max_l * 8 * 4;
-    p.sc = off;                       // [max_l][128] words {scale bf16 | bias bf16 << 16}; GGUF: block headers
-    off += max_l * kRows * 4;
+    p.sc = off;                       // affine: scales [128][S] then biases [128][S] (tc_sc_stride words a row); GGUF: block headers
+    off += (wbytes == kWBytes) ? 2 * kRows * tc_sc_stride(max_l) * 4 : max_l * kRows * 4;
     if (wbytes == kRows * 336) off += (max_l / 4 + 1) * kRows * 4;  // Q2_K: {d, dmin} of every block, after the scale bytes
     p.part = off;                     // rank 0 of the cluster: [splits][128][m] f32 partial sums of all k-slices
     off += splits * kRows * m * 4;
@@ -354,6 +358,109 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     uint32_t *sc = reinterpret_cast<uint32_t *>(smem + plan.sc);
     float *part = reinterpret_cast<float *>(smem + plan.part);
 
+    // Staging of the affine activations, callable by any warp: thread `sidx` of `kstep` staging threads (whole
+    // warps: the items of a (token, k-block) are adjacent lanes and share the group's exponent and sum through
+    // shuffles).  The epilogue warps alone stage one to four tokens (the unpack warps meanwhile run ahead of
+    // griddepcontrol.wait); with more tokens, and in the grouped form, the unpack warps help: the conversion is
+    // then the longest phase of the CTA and the unpacked stages it delays are few.
+    const bool helpers = !GG && (p.g_tiles != nullptr || p.m > 4);
+    constexpr int kStageAll = (kEpilogueWarps + kUnpackWarps) * 32;
+    auto stage_affine = [&](int sidx, int kstep) {
+        // one item = one word's worth of codes (CPW activations) of one token: loaded, turned into
+        // integer byte pairs in the K order of the unpacked words, stored swizzled; the items of a
+        // (token, k-block) are adjacent lanes and share the group's exponent and sum through
+        // shuffles.  Two rounds of loads are in flight at a time: this runs after
+        // griddepcontrol.wait, on the critical path.
+        constexpr int IPK = 64 / CPW;  // items per k-block: 8 / 4
+        constexpr int NV = CPW / 8;    // 16-byte vectors per item: 1 / 2
+        const int items = m_cta * L * IPK;
+        const int per_token = L * IPK;
+        auto load_item = [&](int item, uint4 (&v)[NV]) {
+            if (item < items) {
+                const int t = item / per_token, u = item - t * per_token;
+                const uint4 *src = reinterpret_cast<const uint4 *>(x_cta + static_cast<size_t>(t) * p.k + kb0 * 64 + u * CPW);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) v[i] = __ldg(src + i);
+            }
+        };
+        auto store_item = [&](int item, const uint4 (&v)[NV]) {
+            const bool in = item < items;
+            const int t = in ? item / per_token : 0, u = in ? item - t * per_token : 0;
+            const int kbl = u / IPK, j = u - kbl * IPK;
+            uint32_t r[CPW / 2];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                r[4 * i + 0] = in ? v[i].x : 0u;
+                r[4 * i + 1] = in ? v[i].y : 0u;
+                r[4 * i + 2] = in ? v[i].z : 0u;
+                r[4 * i + 3] = in ? v[i].w : 0u;
+            }
+            float xf[CPW];
+            float s = 0.f;
+            uint32_t amax = 0;
+#pragma unroll
+            for (int i = 0; i < CPW / 2; ++i) {
+                xf[2 * i] = bf16_bits_to_f32(r[i] & 0xffffu);
+                xf[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u);
+                s += xf[2 * i] + xf[2 * i + 1];
+                amax = max(amax, max(r[i] & 0x7fffu, (r[i] >> 16) & 0x7fffu));
+            }
+#pragma unroll
+            for (int off = 1; off < IPK; off <<= 1) {
+                s += __shfl_xor_sync(0xffffffffu, s, off);
+                amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            }
+            // E: biased exponent of the group's largest magnitude.  Groups below 2^-113 count as zero;
+            // an infinity or NaN makes the group's factor NaN.
+            const uint32_t e = amax >> 7;
+            const bool live = e >= 14u && e < 255u;
+            const float up = __uint_as_float((267u - e) << 23);  // 2^(13 - (E - 127))
+            uint32_t hi[CPW / 4], lo[CPW / 4];
+#pragma unroll
+            for (int i = 0; i < CPW / 4; ++i) hi[i] = lo[i] = 0;
+#pragma unroll
+            for (int i = 0; i < CPW; ++i) {
+                // rn(x * 2^(13-E)) through the mantissa of 1.5 * 2^23 (one full-rate FMA instead of a quarter-rate
+                // conversion; the product is exact, the sum rounds to nearest even at unit weight)
+                const int xi = live ? __float_as_int(fmaf(xf[i], up, 12582912.f)) - 0x4b400000 : 0;  // |xi| < 2^14
+                const int h = (xi + 128) >> 8, l = xi - (h << 8);      // xi = 256 h + l, both signed bytes
+                // byte position of element i in the unpacked order
+                const int pos = (BITS == 4) ? ((i & 1) * 4 + (i >> 1)) : ((i & 3) * 4 + (i >> 2));
+                hi[pos >> 2] |= (static_cast<uint32_t>(h) & 0xffu) << (8 * (pos & 3));
+                lo[pos >> 2] |= (static_cast<uint32_t>(l) & 0xffu) << (8 * (pos & 3));
+            }
+            if (in) {
+                // hi bytes: row t of the first group; lo bytes: row t of the second group, or row 4 + t of the first
+                const uint32_t tile = xb32 + (kbl >> 1) * xtile;
+                const int rl = compact ? t + 4 : t;
+                const uint32_t rowh = tile + t * 128, rowl = tile + (compact ? 0u : 1024u) + rl * 128;
+                const int par = kbl & 1;
+                if (BITS == 4) {
+                    const int chunk = par * 4 + (j >> 1), off8 = (j & 1) * 8;
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(rowh + ((chunk ^ t) << 4) + off8), "r"(hi[0]), "r"(hi[1]) : "memory");
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(rowl + ((chunk ^ rl) << 4) + off8), "r"(lo[0]), "r"(lo[1]) : "memory");
+                } else {
+                    const int chunk = par * 4 + j;
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rowh + ((chunk ^ t) << 4)), "r"(hi[0]), "r"(hi[1]), "r"(hi[CPW / 4 - 2]), "r"(hi[CPW / 4 - 1]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rowl + ((chunk ^ rl) << 4)), "r"(lo[0]), "r"(lo[1]), "r"(lo[CPW / 4 - 2]), "r"(lo[CPW / 4 - 1]) : "memory");
+                }
+                if (j == 0) {
+                    xsum[kbl * 8 + t] = s;
+                    xscale[kbl * 8 + t] = live ? __uint_as_float((e - 13u) << 23)  // 2^(E - 127 - 13)
+                                               : (e == 255u ? __uint_as_float(0x7fc00000u) : 0.f);
+                }
+            }
+        };
+        // (four rounds in flight instead of two were measured twice, alone and with the helping warps: slower)
+        for (int base = 0; base < items; base += 2 * kstep) {
+            uint4 va[NV], vb[NV];
+            load_item(base + sidx, va);
+            load_item(base + kstep + sidx, vb);
+            store_item(base + sidx, va);
+            if (base + kstep < items) store_item(base + kstep + sidx, vb);
+        }
+    };
+
     if (warp == 0) {
         // ---------------- producer: packed codes do not depend on the previous kernel in the stream
         int s = 0;
@@ -430,6 +537,13 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         const uint32_t row32 = ring32 + row * ROWB;
         const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16);
         bool ok = true;
+        if (helpers) {
+            asm volatile("bar.sync 2, %0;" ::"r"(kStageAll) : "memory");  // the tiles are zeroed
+            pdl_wait();
+            stage_affine(kEpilogueWarps * 32 + (tid - 64), kStageAll);
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 2, %0;" ::"r"(kStageAll) : "memory");
+        }
         // The TMEM stores of one pair complete while the next one is loaded and unpacked: their
         // completion wait, the hand-over to the MMA warp and the release of the packed stage are deferred
         // to the next trip (`pend_*`).
@@ -557,27 +671,36 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         } else {
             const uint16_t *sbase = (seg == 0) ? p.scales : (seg == 1) ? p.seg_scales[1] : p.seg_scales[2];
             const uint16_t *bbase = (seg == 0) ? p.biases : (seg == 1) ? p.seg_biases[1] : p.seg_biases[2];
-            const uint16_t *sr = sbase + static_cast<size_t>(grow) * p.groups + kb0;
-            const uint16_t *br = bbase + static_cast<size_t>(grow) * p.groups + kb0;
+            // as they lie in memory: row r of the scales at sc + r * S, of the biases kRows * S words further
+            const int S = tc_sc_stride(p.max_l);
             if ((p.groups & 3) == 0 && (kb0 & 3) == 0) {
-                // four groups per 8-byte load; a row holds a multiple of four groups, so the last load
-                // of a short slice stays inside the row
-                const uint2 *s4 = reinterpret_cast<const uint2 *>(sr), *b4 = reinterpret_cast<const uint2 *>(br);
-#pragma unroll 6
-                for (int g4 = 0; g4 < (L + 3) / 4; ++g4) {
-                    const uint2 sv = __ldg(s4 + g4), bv = __ldg(b4 + g4);
-                    const uint32_t w0 = (sv.x & 0xffffu) | (bv.x << 16), w1 = (sv.x >> 16) | (bv.x & 0xffff0000u);
-                    const uint32_t w2 = (sv.y & 0xffffu) | (bv.y << 16), w3 = (sv.y >> 16) | (bv.y & 0xffff0000u);
-                    const int g = 4 * g4;
-                    sc[g * kRows + row] = w0;
-                    if (g + 1 < L) sc[(g + 1) * kRows + row] = w1;
-                    if (g + 2 < L) sc[(g + 2) * kRows + row] = w2;
-                    if (g + 3 < L) sc[(g + 3) * kRows + row] = w3;
+                // four groups per 8-byte asynchronous copy (a row holds a multiple of four groups, so the last copy
+                // of a short slice stays inside the row); consecutive threads copy consecutive pieces of a row, so a
+                // warp touches a few sectors per instruction instead of one per lane.  Nothing waits for the copies
+                // until the activations are staged.
+                const int c = (L + 3) / 4;
+                const uint32_t sc32 = smem_u32(sc);
+                int r = et / c, ch = et - r * c;            // this thread's first (row, piece)
+                const int dr = (kEpilogueWarps * 32) / c, dch = (kEpilogueWarps * 32) - dr * c;
+                for (; r < kRows;) {
+                    const size_t at = static_cast<size_t>(g_row0 + min(n0 + r, seg_n - 1)) * p.groups + kb0 + 4 * ch;
+                    const uint32_t dst = sc32 + (r * S + 2 * ch) * 4;
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(sbase + at) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + kRows * S * 4), "l"(bbase + at) : "memory");
+                    r += dr;
+                    ch += dch;
+                    if (ch >= c) { ch -= c; ++r; }
                 }
+                asm volatile("cp.async.commit_group;" ::: "memory");
             } else {
+                const uint16_t *sr = sbase + static_cast<size_t>(grow) * p.groups + kb0;
+                const uint16_t *br = bbase + static_cast<size_t>(grow) * p.groups + kb0;
+                uint16_t *s16 = reinterpret_cast<uint16_t *>(sc + row * S), *b16 = reinterpret_cast<uint16_t *>(sc + (kRows + row) * S);
 #pragma unroll 4
-                for (int g = 0; g < L; ++g)
-                    sc[g * kRows + row] = static_cast<uint32_t>(__ldg(sr + g)) | (static_cast<uint32_t>(__ldg(br + g)) << 16);
+                for (int g = 0; g < L; ++g) {
+                    s16[g] = __ldg(sr + g);
+                    b16[g] = __ldg(br + g);
+                }
             }
         }
         // activation tiles: zero everything (rows of tokens >= m and the half of an odd last tile stay zero)
@@ -586,114 +709,10 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             const int n16 = ((L + 1) / 2) * static_cast<int>(xtile) / 16;
             for (int i = et; i < n16; i += kEpilogueWarps * 32) z[i] = make_uint4(0, 0, 0, 0);
         }
-        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+        if (helpers) asm volatile("bar.sync 2, %0;" ::"r"(kStageAll) : "memory");  // the unpack warps may write the tiles now
+        else asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
         pdl_wait();  // activations come from the previous kernel
-        if (!GG) {
-            // one item = one word's worth of codes (CPW activations) of one token: loaded, turned into
-            // integer byte pairs in the K order of the unpacked words, stored swizzled; the items of a
-            // (token, k-block) are adjacent lanes and share the group's exponent and sum through
-            // shuffles.  Two rounds of loads are in flight at a time: this runs after
-            // griddepcontrol.wait, on the critical path.
-            constexpr int IPK = 64 / CPW;  // items per k-block: 8 / 4
-            constexpr int NV = CPW / 8;    // 16-byte vectors per item: 1 / 2
-            const int items = m_cta * L * IPK;
-            const int per_token = L * IPK;
-            auto load_item = [&](int item, uint4 (&v)[NV]) {
-                if (item < items) {
-                    const int t = item / per_token, u = item - t * per_token;
-                    const uint4 *src = reinterpret_cast<const uint4 *>(x_cta + static_cast<size_t>(t) * p.k + kb0 * 64 + u * CPW);
-#pragma unroll
-                    for (int i = 0; i < NV; ++i) v[i] = __ldg(src + i);
-                }
-            };
-            auto store_item = [&](int item, const uint4 (&v)[NV]) {
-                const bool in = item < items;
-                const int t = in ? item / per_token : 0, u = in ? item - t * per_token : 0;
-                const int kbl = u / IPK, j = u - kbl * IPK;
-                uint32_t r[CPW / 2];
-#pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    r[4 * i + 0] = in ? v[i].x : 0u;
-                    r[4 * i + 1] = in ? v[i].y : 0u;
-                    r[4 * i + 2] = in ? v[i].z : 0u;
-                    r[4 * i + 3] = in ? v[i].w : 0u;
-                }
-                float xf[CPW];
-                float s = 0.f;
-                uint32_t amax = 0;
-#pragma unroll
-                for (int i = 0; i < CPW / 2; ++i) {
-                    xf[2 * i] = bf16_bits_to_f32(r[i] & 0xffffu);
-                    xf[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u);
-                    s += xf[2 * i] + xf[2 * i + 1];
-                    amax = max(amax, max(r[i] & 0x7fffu, (r[i] >> 16) & 0x7fffu));
-                }
-#pragma unroll
-                for (int off = 1; off < IPK; off <<= 1) {
-                    s += __shfl_xor_sync(0xffffffffu, s, off);
-                    amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-                }
-                // E: biased exponent of the group's largest magnitude.  Groups below 2^-113 count as zero;
-                // an infinity or NaN makes the group's factor NaN.
-                const uint32_t e = amax >> 7;
-                const bool live = e >= 14u && e < 255u;
-                const float up = __uint_as_float((267u - e) << 23);  // 2^(13 - (E - 127))
-                uint32_t hi[CPW / 4], lo[CPW / 4];
-#pragma unroll
-                for (int i = 0; i < CPW / 4; ++i) hi[i] = lo[i] = 0;
-#pragma unroll
-                for (int i = 0; i < CPW; ++i) {
-                    const int xi = live ? __float2int_rn(xf[i] * up) : 0;  // |xi| < 2^14
-                    const int h = (xi + 128) >> 8, l = xi - (h << 8);      // xi = 256 h + l, both signed bytes
-                    // byte position of element i in the unpacked order
-                    const int pos = (BITS == 4) ? ((i & 1) * 4 + (i >> 1)) : ((i & 3) * 4 + (i >> 2));
-                    hi[pos >> 2] |= (static_cast<uint32_t>(h) & 0xffu) << (8 * (pos & 3));
-                    lo[pos >> 2] |= (static_cast<uint32_t>(l) & 0xffu) << (8 * (pos & 3));
-                }
-                if (in) {
-                    // hi bytes: row t of the first group; lo bytes: row t of the second group, or row 4 + t of the first
-                    const uint32_t tile = xb32 + (kbl >> 1) * xtile;
-                    const int rl = compact ? t + 4 : t;
-                    const uint32_t rowh = tile + t * 128, rowl = tile + (compact ? 0u : 1024u) + rl * 128;
-                    const int par = kbl & 1;
-                    if (BITS == 4) {
-                        const int chunk = par * 4 + (j >> 1), off8 = (j & 1) * 8;
-                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(rowh + ((chunk ^ t) << 4) + off8), "r"(hi[0]), "r"(hi[1]) : "memory");
-                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(rowl + ((chunk ^ rl) << 4) + off8), "r"(lo[0]), "r"(lo[1]) : "memory");
-                    } else {
-                        const int chunk = par * 4 + j;
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rowh + ((chunk ^ t) << 4)), "r"(hi[0]), "r"(hi[1]), "r"(hi[CPW / 4 - 2]), "r"(hi[CPW / 4 - 1]) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rowl + ((chunk ^ rl) << 4)), "r"(lo[0]), "r"(lo[1]), "r"(lo[CPW / 4 - 2]), "r"(lo[CPW / 4 - 1]) : "memory");
-                    }
-                    if (j == 0) {
-                        xsum[kbl * 8 + t] = s;
-                        xscale[kbl * 8 + t] = live ? __uint_as_float((e - 13u) << 23)  // 2^(E - 127 - 13)
-                                                   : (e == 255u ? __uint_as_float(0x7fc00000u) : 0.f);
-                    }
-                }
-            };
-            constexpr int kStep = kEpilogueWarps * 32;
-            int base = 0;
-            // several tokens: four rounds of loads in flight (each round is a round trip to L2)
-            for (; base + 2 * kStep < items; base += 4 * kStep) {
-                uint4 va[NV], vb[NV], vc[NV], vd[NV];
-                load_item(base + et, va);
-                load_item(base + kStep + et, vb);
-                load_item(base + 2 * kStep + et, vc);
-                load_item(base + 3 * kStep + et, vd);
-                store_item(base + et, va);
-                store_item(base + kStep + et, vb);
-                store_item(base + 2 * kStep + et, vc);
-                if (base + 3 * kStep < items) store_item(base + 3 * kStep + et, vd);
-            }
-            for (; base < items; base += 2 * kStep) {
-                uint4 va[NV], vb[NV];
-                load_item(base + et, va);
-                load_item(base + kStep + et, vb);
-                store_item(base + et, va);
-                if (base + kStep < items) store_item(base + kStep + et, vb);
-            }
-        }
+        if (!GG) stage_affine(et, helpers ? kStageAll : kEpilogueWarps * 32);
         if (GG) {
             // one item = 8 consecutive f32 activations of one token; the four items of a 32-element
             // sub-block are adjacent lanes and share its exponent and sum through shuffles
@@ -778,7 +797,9 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             }
         }
         fence_proxy_async_smem();  // the MMA reads the tiles through the async proxy
-        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+        asm volatile("cp.async.wait_all;" ::: "memory");  // this thread's copies of scales and biases (other rows' too: hence before the barrier)
+        if (helpers) asm volatile("bar.sync 2, %0;" ::"r"(kStageAll) : "memory");
+        else asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
         if (lane == 0) mbar_arrive(x_ready);
 
         float rs[8];
@@ -793,6 +814,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             int st = 0;
             uint32_t ph = 0;
             bool ready = false;  // poll of the next pair's barrier, issued before this pair's arithmetic
+            const uint32_t *srow_e = sc + row * tc_sc_stride(p.max_l), *brow_e = srow_e + kRows * tc_sc_stride(p.max_l);
             for (int pr = 0; pr < P; ++pr) {
                 const bool two = 2 * pr + 1 < L;
                 if (!__all_sync(0xffffffffu, ready)) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[st], ph, 7));
@@ -813,12 +835,13 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                     const int nst = (st + 1 == kNP) ? 0 : st + 1;
                     ready = (pr + 1 < P) && mbar_test_wait(&done[nst], nst == 0 ? ph ^ 1u : ph);
                 }
+                const uint32_t sp = srow_e[pr], bp = brow_e[pr];  // scales / biases of the pair's two groups
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (h == 1 && !two) break;
                     const int kk = 2 * pr + h;
-                    const uint32_t sb = sc[kk * kRows + row];
-                    const float sv = bf16_bits_to_f32(sb & 0xffffu), bv = __uint_as_float(sb & 0xffff0000u);
+                    const float sv = h ? __uint_as_float(sp & 0xffff0000u) : bf16_bits_to_f32(sp & 0xffffu);
+                    const float bv = h ? __uint_as_float(bp & 0xffff0000u) : bf16_bits_to_f32(bp & 0xffffu);
 #pragma unroll
                     for (int t = 0; t < MT; ++t) {
                         // sum(q * x_int) = 256 * (hi column) + (lo column), below 2^24: exact as a float
@@ -929,7 +952,13 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         } else if (GG) {
             if (p.m == 1) run_gguf(IntC<4>{});
             else run_gguf(IntC<8>{});
-        } else if (p.g_tiles) run(IntC<8>{});  // (the B tile layout is the plan's: eight tokens)
+        } else if (p.g_tiles) {
+            // grouped form: the B tile layout is the plan's (eight tokens), the columns read are the entry's
+            if (m_cta == 1) run(IntC<1>{});
+            else if (m_cta == 2) run(IntC<2>{});
+            else if (m_cta <= 4) run(IntC<4>{});
+            else run(IntC<8>{});
+        }
         else if (p.m == 1) run(IntC<1>{});
         else if (p.m == 2) run(IntC<2>{});
         else if (p.m <= 4) run(IntC<4>{});

@@ -40,6 +40,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -112,13 +113,19 @@ struct TcParams {
     // grouped form (gather_qmm with few rows per expert): row tile y of the grid belongs to entry g_tiles[y / g_ntiles]
     // = {expert, row_begin, row_end} of the sorted rows (at most 8 rows per entry); the packed matrix is addressed as
     // [experts * g_n, k], x and the output are the sorted rows; entries beyond *g_count do nothing
+    // scales and biases of a tile by two tiled TMA copies (box sc_box groups x 128 rows, dense rows of sc_words
+    // words) instead of per-thread copies: needs rows of whole 16-byte pieces (groups a multiple of 8); a slice
+    // that starts at a group index 4 mod 8 loads from 4 groups earlier
+    int sc_tma, sc_box, sc_words;
     const int4 *g_tiles;
     const int *g_count;
     int g_ntiles;   // row tiles of one expert
     int g_n;        // rows of one expert
 };
 struct TcMaps {
-    CUtensorMap m[kMaxSeg];
+    CUtensorMap m[kMaxSeg];  // packed rows of every segment
+    CUtensorMap s[kMaxSeg];  // its scales and biases as [rows, groups] bf16 (used when TcParams::sc_tma)
+    CUtensorMap b[kMaxSeg];
 };
 
 // Shared-memory plan, bytes from the 1024-aligned base.
@@ -134,7 +141,7 @@ struct TcPlan {
 // of a warp spread over the banks (two rows per bank).
 __host__ __device__ inline int tc_sc_stride(int max_l) { return 2 * (((max_l + 3) / 4) | 1); }
 __host__ __device__ inline int tc_xtile(int m, int wbytes) { return (wbytes == kWBytes && m <= 4) ? 1024 : kXTile; }
-__host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, int m, int wbytes = kWBytes) {
+__host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, int m, int wbytes = kWBytes, int sc_words = 0) {
     TcPlan p;
     int off = 0;
     p.ring = off;
@@ -144,8 +151,9 @@ __host__ __device__ inline TcPlan tc_plan(int wstages, int max_l, int splits, in
     p.zero = off;                     // (unused)
     p.xsum = off;                     // [max_l][8] f32 sum(x), then [max_l][8] f32 2^(E-13)
     off += 2 * max_l * 8 * 4;
-    p.sc = off;                       // affine: scales [128][S] then biases [128][S] (tc_sc_stride words a row); GGUF: block headers
-    off += (wbytes == kWBytes) ? 2 * kRows * tc_sc_stride(max_l) * 4 : max_l * kRows * 4;
+    off = (off + 127) & ~127;         // (a TMA destination)
+    p.sc = off;                       // affine: scales [128][S] then biases [128][S] (S = sc_words, or tc_sc_stride words a row); GGUF: block headers
+    off += (wbytes == kWBytes) ? 2 * kRows * (sc_words ? sc_words : tc_sc_stride(max_l)) * 4 : max_l * kRows * 4;
     if (wbytes == kRows * 336) off += (max_l / 4 + 1) * kRows * 4;  // Q2_K: {d, dmin} of every block, after the scale bytes
     p.part = off;                     // rank 0 of the cluster: [splits][128][m] f32 partial sums of all k-slices
     off += splits * kRows * m * 4;
@@ -276,7 +284,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     constexpr int KB_BYTES = 64 * BITS / 8;    // packed bytes of one row of a k-block: 32 / 16
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const TcPlan plan = tc_plan(p.wstages, p.max_l, p.splits, p.m, p.wbytes);
+    const TcPlan plan = tc_plan(p.wstages, p.max_l, p.splits, p.m, p.wbytes, p.sc_words);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + plan.bars);
     uint64_t *wp_full = bars;                      // [kMaxWStages]
     uint64_t *wp_empty = wp_full + kMaxWStages;    // [kMaxWStages], 8 unpack warps
@@ -284,7 +292,8 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     uint64_t *done = a_full + kNP;                 // [kNP], tcgen05.commit of the pair's MMAs: D ready
     uint64_t *d_empty = done + kNP;                // [kNP], 4 epilogue warps: D read, hence A stage and D buffer free
     uint64_t *x_ready = d_empty + kNP;             // 4 epilogue warps
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(x_ready + 1);
+    uint64_t *sc_full = x_ready + 1;               // scales and biases of the tile (TMA)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sc_full + 1);
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler too
@@ -332,6 +341,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             mbar_init(&d_empty[i], kEpilogueWarps);
         }
         mbar_init(x_ready, kEpilogueWarps);
+        mbar_init(sc_full, 1);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -474,6 +484,14 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         const int ws_ring = min(ws1, ws0 + p.wstages);
         if (lane == 0)
             for (int wi = ws0; wi < ws_ring; ++wi) issue(wi);
+        if (!GG && p.sc_tma && lane == 0) {
+            // scales and biases of the tile: rows g_row0 + n0 .., groups from the 8-aligned index at or below kb0
+            const uint32_t bytes = static_cast<uint32_t>(kRows * p.sc_box * 2);
+            const uint32_t sc32 = smem_u32(sc);
+            mbar_arrive_expect_tx(sc_full, 2 * bytes);
+            tma_load_2d(sc32, &maps.s[seg], kb0 & ~7, g_row0 + n0, sc_full);
+            tma_load_2d(sc32 + bytes, &maps.b[seg], kb0 & ~7, g_row0 + n0, sc_full);
+        }
         if (lane == 0) {
             for (int wi = ws_ring; wi < ws1; ++wi) {
                 if (!tc_wait_relaxed(&wp_empty[s], ph, 1)) break;
@@ -668,7 +686,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             uint4 *hdr = reinterpret_cast<uint4 *>(sc);
 #pragma unroll 4
             for (int bq = 0; bq < (L + 3) / 4; ++bq) hdr[bq * kRows + row] = __ldg(reinterpret_cast<const uint4 *>(wr + bq * 144));
-        } else {
+        } else if (!p.sc_tma) {
             const uint16_t *sbase = (seg == 0) ? p.scales : (seg == 1) ? p.seg_scales[1] : p.seg_scales[2];
             const uint16_t *bbase = (seg == 0) ? p.biases : (seg == 1) ? p.seg_biases[1] : p.seg_biases[2];
             // as they lie in memory: row r of the scales at sc + r * S, of the biases kRows * S words further
@@ -809,12 +827,16 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         bool ok = true;
         // One pair of k-blocks per trip; only the columns of the tokens that exist are read (MT = m rounded
         // up to a power of two): hi bytes in columns [0, MT), lo bytes in columns [8, 8 + MT) of each D.
+        const int sc_boff = kRows * (p.sc_tma ? p.sc_words : tc_sc_stride(p.max_l));  // words from a row's scales to its biases
+        const uint32_t *sc_row = sc + row * (sc_boff / kRows) + (p.sc_tma ? (kb0 & 7) >> 1 : 0);
         auto run = [&](auto mt) {
             constexpr int MT = decltype(mt)::value;
             int st = 0;
             uint32_t ph = 0;
             bool ready = false;  // poll of the next pair's barrier, issued before this pair's arithmetic
-            const uint32_t *srow_e = sc + row * tc_sc_stride(p.max_l), *brow_e = srow_e + kRows * tc_sc_stride(p.max_l);
+            // staged scales and biases of this row, two groups a word, from the slice's first group on
+            if (p.sc_tma) ok = __all_sync(0xffffffffu, tc_wait_relaxed(sc_full, 0, 9));
+            const uint32_t *srow_e = sc_row;
             for (int pr = 0; pr < P; ++pr) {
                 const bool two = 2 * pr + 1 < L;
                 if (!__all_sync(0xffffffffu, ready)) ok = __all_sync(0xffffffffu, tc_wait_relaxed(&done[st], ph, 7));
@@ -835,7 +857,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                     const int nst = (st + 1 == kNP) ? 0 : st + 1;
                     ready = (pr + 1 < P) && mbar_test_wait(&done[nst], nst == 0 ? ph ^ 1u : ph);
                 }
-                const uint32_t sp = srow_e[pr], bp = brow_e[pr];  // scales / biases of the pair's two groups
+                const uint32_t sp = srow_e[pr], bp = srow_e[sc_boff + pr];  // scales / biases of the pair's two groups
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (h == 1 && !two) break;
@@ -1045,12 +1067,23 @@ static bool tc_make_plan(int64_t n, int64_t k, int group_size, int bits, int m, 
         const int max_ws = (total_ws + splits - 1) / splits;
         const int max_l = std::min(max_ws * kbw, num_kb);
         const int ws_min = std::min(2, max_ws);
-        if (tc_plan(ws_min, max_l, splits, 1, wbytes).total > budget) continue;
+        // scales and biases by TMA when their rows are whole 16-byte pieces; the box covers the longest slice, plus
+        // four groups when some slice starts at a group index that is 4 mod 8
+        static const bool sc_tma_on = [] { const char *v = std::getenv("LISA_TC_SC_TMA"); return !(v && v[0] == '0'); }();
+        const bool sc_tma = sc_tma_on && wbytes == kWBytes && num_kb % 8 == 0;
+        bool sc_off = false;
+        for (int r = 0; r < splits; ++r) sc_off = sc_off || ((static_cast<int64_t>(r) * total_ws / splits) * kbw) % 8 != 0;
+        const int sc_box = (max_l + (sc_off ? 4 : 0) + 7) / 8 * 8;
+        const int scw = sc_tma ? sc_box / 2 : 0;
+        if (tc_plan(ws_min, max_l, splits, 1, wbytes, scw).total > budget) continue;
         mc = std::min(m, 8);
-        while (mc > 1 && tc_plan(ws_min, max_l, splits, mc, wbytes).total > budget) mc = (mc + 1) / 2;
+        while (mc > 1 && tc_plan(ws_min, max_l, splits, mc, wbytes, scw).total > budget) mc = (mc + 1) / 2;
         for (int ws = std::min(kMaxWStages, max_ws); ws >= ws_min; --ws) {
-            const TcPlan plan = tc_plan(ws, max_l, splits, mc, wbytes);
+            const TcPlan plan = tc_plan(ws, max_l, splits, mc, wbytes, scw);
             if (plan.total <= budget) {
+                p.sc_tma = sc_tma ? 1 : 0;
+                p.sc_box = sc_box;
+                p.sc_words = scw;
                 p.splits = splits;
                 p.wstages = ws;
                 p.max_l = max_l;
@@ -1080,6 +1113,16 @@ static int affine_tensor_map(CUtensorMap *map, const uint32_t *w, int64_t n, int
     const uint64_t strides[1] = {row_bytes};
     const uint32_t box[2] = {128, kRows};
     return make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// Tensor maps of one segment's scales and biases, [rows, groups] bf16, box sc_box groups x 128 rows, no swizzle.
+static int scale_tensor_maps(TcMaps &maps, int seg, const void *scales, const void *biases, int64_t rows, int64_t groups, int box) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(groups), static_cast<uint64_t>(rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(groups) * 2};
+    const uint32_t bx[2] = {static_cast<uint32_t>(box), kRows};
+    int rc = make_tensor_map(&maps.s[seg], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, dims, strides, bx, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != LISA_OK) return rc;
+    return make_tensor_map(&maps.b[seg], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, dims, strides, bx, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 static int tc_launch_kernel(cudaStream_t stream, int bits, const TcMaps &maps, const TcParams &p, int grid, int smem, unsigned flags) {
@@ -1130,6 +1173,10 @@ static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t 
         int smem = 0, grid = 0;
         if (!tc_make_plan(n, k, group_size, bits, static_cast<int>(std::min<int64_t>(m - done, 8)), p, smem, grid, mc))
             return fail(LISA_ERR_UNSUPPORTED, "qmv_tc: shape not supported");
+        if (p.sc_tma && done == 0) {
+            const int rc = scale_tensor_maps(maps, 0, scales, biases, n, k / 64, p.sc_box);
+            if (rc != LISA_OK) return rc;
+        }
         p.scales = reinterpret_cast<const uint16_t *>(scales);
         p.biases = reinterpret_cast<const uint16_t *>(biases);
         p.x = xp + done * k;
@@ -1185,6 +1232,10 @@ int qmv_tc_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, 
     p.n = static_cast<int>(n);
     p.k = static_cast<int>(k);
     p.m = bt;
+    if (p.sc_tma) {
+        const int rc = scale_tensor_maps(maps, 0, scales, biases, experts * n, k / 64, p.sc_box);
+        if (rc != LISA_OK) return rc;
+    }
     p.g_tiles = reinterpret_cast<const int4 *>(tiles);
     p.g_count = tile_count;
     p.g_ntiles = static_cast<int>(ntiles);
@@ -1242,6 +1293,12 @@ int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int c
         int smem = 0, grid = 0;
         if (!tc_make_plan(n[0], k, group_size, bits, static_cast<int>(std::min<int64_t>(m - done, 8)), p, smem, grid, mc, kWBytes, 0, tiles))
             return fail(LISA_ERR_UNSUPPORTED, "qmv_tc_multi: shape not supported");
+        if (p.sc_tma && done == 0) {
+            for (int i = 0; i < count; ++i) {
+                const int rc = scale_tensor_maps(maps, i, scales[i], biases[i], n[i], k / 64, p.sc_box);
+                if (rc != LISA_OK) return rc;
+            }
+        }
         p.x = xp + done * k;
         p.k = static_cast<int>(k);
         p.m = mc;

@@ -598,6 +598,25 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
             bool slot_free = true;
             if (pr >= kNP) slot_free = mbar_test_wait(&d_empty[stg], dpar);
             uint32_t o[32];
+            if (GG && set == 0) {
+                // first visit of this block of the row (a block is two pairs, this set takes the even ones): its
+                // header moves from the packed stage to the epilogue's table before the pair is handed over
+                const int bq = pr >> 1;
+                if (GG == 4) {
+                    const uint32_t src = row32 + s * (kRows * ROWB);
+                    uint32_t h0, h1, h2, h3;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(src));
+                    reinterpret_cast<uint4 *>(sc)[bq * kRows + row] = make_uint4(h0, h1, h2, h3);
+                } else {
+                    const uint32_t src = row32 + s * (kRows * ROWB) + (sub >> 2) * 84;
+                    uint32_t h[5];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(h[i]) : "r"(src + 4 * i));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(h[4]) : "r"(src + 80));
+                    reinterpret_cast<uint4 *>(sc)[bq * kRows + row] = make_uint4(h[0], h[1], h[2], h[3]);
+                    sc[p.max_l * kRows + bq * kRows + row] = h[4];
+                }
+            }
             if (GG == 2) {
                 // the pair's 128 elements are the four 2-bit fields of 32 code bytes of one block
                 const uint32_t blk = row32 + s * (kRows * ROWB) + (sub >> 2) * 84 + 16 + ((sub & 3) >> 1) * 32;
@@ -669,23 +688,9 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         const int et = tid - (2 + kUnpackWarps) * 32;  // 0..127
         const int grow = g_row0 + min(n0 + row, seg_n - 1);
         // scales and biases of (row, group) of the slice: weights, no dependency on the previous kernel
-        if (GG == 2) {
-            // per block of this row: the 16 scale/min bytes ([block][row] uint4 in `sc`) and {d, dmin} (a word each, after them)
-            const uint8_t *wr = p.wg + static_cast<size_t>(grow) * p.row_bytes + static_cast<size_t>(kb0 / 4) * 84;
-            uint4 *hdr = reinterpret_cast<uint4 *>(sc);
-            uint32_t *dd = sc + p.max_l * kRows;
-#pragma unroll 2
-            for (int bq = 0; bq < (L + 3) / 4; ++bq) {
-                const uint32_t *bp = reinterpret_cast<const uint32_t *>(wr + bq * 84);  // 4-byte aligned
-                hdr[bq * kRows + row] = make_uint4(__ldg(bp), __ldg(bp + 1), __ldg(bp + 2), __ldg(bp + 3));
-                dd[bq * kRows + row] = __ldg(bp + 20);
-            }
-        } else if (GG) {
-            // the 16-byte headers {d, dmin, 6-bit scales and mins} of this row's blocks: [block][row] uint4 in `sc`
-            const uint8_t *wr = p.wg + static_cast<size_t>(grow) * p.row_bytes + static_cast<size_t>(kb0 / 4) * 144;
-            uint4 *hdr = reinterpret_cast<uint4 *>(sc);
-#pragma unroll 4
-            for (int bq = 0; bq < (L + 3) / 4; ++bq) hdr[bq * kRows + row] = __ldg(reinterpret_cast<const uint4 *>(wr + bq * 144));
+        if (GG) {
+            // the block headers (Q4_K: {d, dmin, 6-bit scales and mins}; Q2_K: 16 scale/min bytes and {d, dmin}) come
+            // with the packed stage: the unpack warp that first visits a block copies them to `sc` ([block][row])
         } else if (!p.sc_tma) {
             const uint16_t *sbase = (seg == 0) ? p.scales : (seg == 1) ? p.seg_scales[1] : p.seg_scales[2];
             const uint16_t *bbase = (seg == 0) ? p.biases : (seg == 1) ? p.seg_biases[1] : p.seg_biases[2];

@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -129,11 +130,21 @@ __global__ void __launch_bounds__(kTableThreads) gather_tile_table_kernel(const 
     for (int64_t i = tail0 + tid; i < tail1; i += kTableThreads) y[i] = 0;
 }
 
-// Rows per tile of the grouped GEMM: a CTA costs about the same for any tile up to 256 rows, so the
-// tile is as tall as the average expert run allows.
+// Rows per tile of the grouped GEMM: a CTA costs about the same for any tile up to 256 rows (the dequantization
+// sets its pace) and about 1.3 times that for the 384-row tile, so the tile is as tall as the expert runs allow.
+// Between 256 and 384 the choice goes by the expected number of tiles per expert when the rows spread evenly
+// over the experts (run lengths then scatter around the average with a standard deviation of its root).
 static int grouped_tile_rows(int64_t rows, int64_t experts) {
-    const int64_t avg = rows / (experts > 0 ? experts : 1);
-    if (avg >= 96) return 256;
+    const double avg = static_cast<double>(rows) / static_cast<double>(experts > 0 ? experts : 1);
+    if (avg >= 96) {
+        const double sd = std::sqrt(avg) + 1e-9;
+        auto tiles = [&](double bt) {  // E[ceil(r / bt)], r ~ N(avg, sd)
+            double t = 1.0;
+            for (int j = 1; j * bt < avg + 6 * sd; ++j) t += 0.5 * std::erfc((j * bt - avg) / (sd * 1.41421356));
+            return t;
+        };
+        return tiles(384.0) * 1.3 < tiles(256.0) ? 384 : 256;
+    }
     if (avg >= 40) return 128;
     if (avg >= 12) return 64;
     if (avg >= 4) return 32;

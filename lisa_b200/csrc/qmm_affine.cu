@@ -29,6 +29,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "tensor_map.h"
@@ -48,6 +50,7 @@ int qmm_clear_status() {
 }
 
 constexpr int kBN = 128;        // weight rows per CTA (MMA M)
+constexpr int kWideBt = 384;    // the tall token tile (template WIDE)
 constexpr int kBK = 64;         // k per MMA stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kStages = 5;      // operand ring: stage s = activation tile in shared memory + A tile in tensor memory
 constexpr int kWpStages = 4;    // packed-weight ring: loads run a whole ring (12+ k-blocks) ahead of their use
@@ -283,11 +286,16 @@ struct QmmSmem {
 // bytes, 64 code bytes, f16 d, f16 dmin} per stage row; the 32 elements of (k-block, half) are the 2-bit
 // fields at bit offset 2*shift of bytes 32*(kb4/2) .. +31, shift = 2*(kb4&1) + half, the first 16 under scale
 // byte [half_of_block*8 + shift*2], the last 16 under the next one.  The output is f32.
-template <int BITS, int GGUF = 0>
+//
+// WIDE: a token tile of 384 (the dequantization sets a CTA's pace whatever the token tile, so a taller tile is
+// that many fewer passes over the weights): two MMAs per k-step (N = 256 and N = 128, into columns 0 and 256
+// of the accumulator), three loads of 128 activation rows per stage, a three-stage operand ring (48 KiB
+// a stage), all 512 tensor-memory columns (384 accumulator + 3 x 32 of A).
+template <int BITS, int GGUF = 0, bool WIDE = false>
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ QmmMaps maps_w,
                   const QmmParams p) {
-    constexpr int ST = (GGUF == 2) ? 3 : kStages;                      // operand ring stages
+    constexpr int ST = (GGUF == 2 || WIDE) ? 3 : kStages;              // operand ring stages
     constexpr int WS = (GGUF == 4) ? 3 : (GGUF == 2) ? 2 : kWpStages;  // packed ring stages
     constexpr int ROWB = (GGUF == 4) ? kQ4kBlock : (GGUF == 2) ? 4 * kQ2kBlock : 128;  // bytes of a packed stage row
     constexpr int WPB = kBN * ROWB;                       // bytes of a packed stage
@@ -396,7 +404,13 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (kb >= ST && ok) ok = qmm_wait(&empty[s], ph, 1);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&full[s], x_bytes);
-                tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, (kb + kb_off) * kBK, t0, &full[s]);
+                if (WIDE) {
+#pragma unroll
+                    for (int r = 0; r < 3; ++r)  // the map's box is 128 rows
+                        tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + r * (128 * 128), &map_x, (kb + kb_off) * kBK, t0 + 128 * r, &full[s]);
+                } else {
+                    tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, (kb + kb_off) * kBK, t0, &full[s]);
+                }
                 if (GGUF) tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + x_bytes / 2, &map_x, kb * kBK, p.m + t0, &full[s]);
                 if (++s == ST) { s = 0; ph ^= 1; }
             }
@@ -407,7 +421,8 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // k-block.  (Issued from inside an `if (lane == 0)` the same loop took ~450 of the 512 clocks
         // that four N = 256 MMAs last.)
         {
-            const uint32_t idesc = umma_idesc_bf16(p.bt);
+            const uint32_t idesc = umma_idesc_bf16(WIDE ? 256 : p.bt);
+            const uint32_t idesc_b = umma_idesc_bf16(128);  // WIDE: rows 256..383 of the token tile
             const uint32_t b_lo0 = umma_desc_lo(smem_u32(xs));
             const uint32_t b_step = static_cast<uint32_t>(p.bt) * 8u * XP;  // one stage, in 16-byte units
             int s = 0;
@@ -423,6 +438,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks) {
                         umma_bf16_ts(tmem_base, a_addr + ks * 8, b_lo + ks * 2, kUmmaDescHiSw128, idesc, acc);
+                        if (WIDE) umma_bf16_ts(tmem_base + 256, a_addr + ks * 8, b_lo + (256 * 128 / 16) + ks * 2, kUmmaDescHiSw128, idesc_b, acc);
                         acc = 1;
                         if (GGUF) {
                             // x_lo (half a stage further) with w_hi, then x_hi with w_lo
@@ -764,11 +780,13 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     p.groups = static_cast<int>(k / group_size);
     p.group_size = group_size;
     p.bt = bt;
+    const bool wide = bt == kWideBt;
     int acc = 32;
     while (acc < bt) acc <<= 1;
+    if (wide) acc = kWideBt;  // the A ring follows the 384 accumulator columns
     p.acc_cols = acc;
     int cols = 32;
-    while (cols < acc + kStages * kACols) cols <<= 1;
+    while (cols < acc + (wide ? 3 : kStages) * kACols) cols <<= 1;
     p.tmem_cols = cols;
     p.num_kb = static_cast<int>((k + kBK - 1) / kBK);
     p.tiles = tiles;
@@ -777,7 +795,7 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     CUtensorMap map_x;
     QmmMaps maps_w{};
     int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, static_cast<uint64_t>(k),
-                         static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBK, static_cast<uint32_t>(bt));
+                         static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBK, static_cast<uint32_t>(wide ? 128 : bt));
     if (rc != LISA_OK) return rc;
     const uint64_t wrow_bytes = static_cast<uint64_t>(k) * bits / 8;
     rc = make_map_2d(&maps_w.m[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, w, wrow_bytes, static_cast<uint64_t>(n * experts), wrow_bytes,
@@ -803,7 +821,7 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
         }
     }
 
-    const size_t smem = static_cast<size_t>(QmmSmem::total(bt));
+    const size_t smem = static_cast<size_t>(wide ? QmmSmem::total(bt, kWpStages, kWpBytes, 1, 3) : QmmSmem::total(bt));
     const int64_t ytiles = tiles ? max_tiles : (m + bt - 1) / bt;
     if (ytiles > 65535) return fail(LISA_ERR_LIMIT, "qmm: too many row tiles");
     // Two k-slices per tile (a cluster of two CTAs) when the tiles fill the SMs badly: a CTA's time is its
@@ -811,7 +829,7 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     // number of waves times that plus about six k-blocks of prologue and store, and the exchange of half
     // of the 128 x bt accumulators costs about five more (measured on the configs[1] prefill shapes).
     p.ksplit = 1;
-    if (!tiles) {
+    if (!tiles && !wide) {
         const int kbw = (128 * 8 / bits) / kBK;
         const int64_t sms = sm_count(), ctas = ntiles * ytiles;
         const int64_t t1 = ((ctas + sms - 1) / sms) * (p.num_kb + 6);          // + prologue and store
@@ -840,7 +858,13 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    if (bits == 4) {
+    if (wide && bits == 4) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<4, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4, 0, true>, map_x, maps_w, p));
+    } else if (wide) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<2, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<2, 0, true>, map_x, maps_w, p));
+    } else if (bits == 4) {
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmm_affine_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_affine_kernel<4>, map_x, maps_w, p));
     } else {
@@ -948,9 +972,29 @@ int qmm_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, in
     return LISA_OK;
 }
 
+// Token tile of a dense launch: the whole of m up to 256; beyond that 256 or 384, whichever gives fewer
+// wave x k-block units (a CTA's time is its k-blocks, whatever the tile; the 256 form may run as two k-slices,
+// see qmm_launch; a taller tile has a longer epilogue).  LISA_QMM_BT = 256 / 384 overrides the choice.
+static int dense_tile_rows(int64_t m, int64_t ntiles, int64_t k, int bits) {
+    if (m <= 256) return static_cast<int>((m + 15) / 16 * 16);
+    static const int forced = [] {
+        const char *v = std::getenv("LISA_QMM_BT");
+        return v ? std::atoi(v) : 0;
+    }();
+    if (forced == 256 || forced == kWideBt) return forced;
+    const int64_t num_kb = (k + kBK - 1) / kBK, kbw = (128 * 8 / bits) / kBK, sms = sm_count();
+    auto waves = [&](int64_t ctas) { return (ctas + sms - 1) / sms; };
+    const int64_t y256 = (m + 255) / 256, y384 = (m + kWideBt - 1) / kWideBt;
+    int64_t t256 = waves(ntiles * y256) * (num_kb + 6);
+    const int64_t t256s = waves(2 * ntiles * y256) * (num_kb / 2 + 6 + 5);
+    if (num_kb >= 4 * kbw && t256s * 100 < t256 * 93) t256 = t256s;
+    const int64_t t384 = waves(ntiles * y384) * (num_kb + 9);
+    return t384 * 103 < t256 * 100 ? kWideBt : 256;
+}
+
 int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
-    const int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
+    const int bt = dense_tile_rows(m, (n + kBN - 1) / kBN, k, bits);
     return qmm_launch(stream, x, m, k, w, scales, biases, n, 1, group_size, bits, y, flags, bt, nullptr, nullptr, 0);
 }
 
@@ -959,7 +1003,7 @@ int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const u
 int qmm_affine_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                          const void *biases, int64_t n, int group_size, int bits, void *const *outs, int world,
                          int64_t n_total, int64_t col0, unsigned flags) {
-    const int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
+    const int bt = dense_tile_rows(m, (n + kBN - 1) / kBN, k, bits);
     return qmm_launch(stream, x, m, k, w, scales, biases, n, 1, group_size, bits, outs[0], flags, bt, nullptr, nullptr, 0, 1,
                       nullptr, nullptr, nullptr, nullptr, nullptr, outs, world, n_total, col0);
 }
@@ -970,7 +1014,9 @@ int qmm_affine_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, i
                      const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
                      void *const *y, unsigned flags) {
     if (count < 2 || count > kMaxSeg) return fail(LISA_ERR_UNSUPPORTED, "qmm_affine_multi: two or three linears per launch");
-    const int bt = static_cast<int>(m >= 256 ? 256 : ((m + 15) / 16) * 16);
+    int64_t ntiles = 0;
+    for (int i = 0; i < count; ++i) ntiles += (n[i] + kBN - 1) / kBN;
+    const int bt = dense_tile_rows(m, ntiles, k, bits);
     return qmm_launch(stream, x, m, k, w[0], scales[0], biases[0], n[0], 1, group_size, bits, y[0], flags, bt, nullptr, nullptr, 0,
                       count, w, scales, biases, n, y);
 }

@@ -988,8 +988,10 @@ static int dense_tile_rows(int64_t m, int64_t ntiles, int64_t k, int bits) {
     int64_t t256 = waves(ntiles * y256) * (num_kb + 6);
     const int64_t t256s = waves(2 * ntiles * y256) * (num_kb / 2 + 6 + 5);
     if (num_kb >= 4 * kbw && t256s * 100 < t256 * 93) t256 = t256s;
-    const int64_t t384 = waves(ntiles * y384) * (num_kb + 9);
-    return t384 * 103 < t256 * 100 ? kWideBt : 256;
+    // a 384-token CTA takes 1.25-1.3 times as long per k-block (tensor-bound, measured; the lower end inside a chain
+    // of dependent launches, where the next launch's CTAs fill the ragged last wave) and has a longer epilogue
+    const int64_t t384 = waves(ntiles * y384) * (num_kb * 125 / 100 + 9);
+    return t384 < t256 ? kWideBt : 256;
 }
 
 int qmm_affine(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,

@@ -105,7 +105,7 @@ def leg_summary(line):
 # ncu captures (qmv_tc_kernel on 4 layers of the decode stack; qmm_affine_kernel
 # on 2 layers of the prefill stack).  Traffic grows in proportion to the units processed, so the ratio
 # carries over to a full launch.
-DRAM_TRAFFIC_RATIO = {"decode": 1.005, "prefill": 0.570}
+DRAM_TRAFFIC_RATIO = {"decode": 1.005, "prefill": 0.578}
 PREFILL_M = 2048
 
 

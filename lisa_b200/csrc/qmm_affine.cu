@@ -645,8 +645,11 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // chunks) as part[token of the tile][row] f32 over the owner's operand ring; the owner adds them to
         // its own and stores that half of the tile.
         const uint32_t part32 = smem_u32(xs);
-        const int own_lo = split ? (krank == 0 ? 0 : (chunks + 1) / 2) : 0;
-        const int own_hi = split ? (krank == 0 ? (chunks + 1) / 2 : chunks) : chunks;
+        // k-slices: slice r owns the token chunks [r * chunks / S, (r + 1) * chunks / S); `own_max` bounds a share
+        const int S = split ? p.ksplit : 1;
+        const int own_lo = static_cast<int>(krank) * chunks / S, own_hi = static_cast<int>(krank + 1) * chunks / S;
+        const int own_max = (chunks + S - 1) / S;
+        const uint32_t region = static_cast<uint32_t>(own_max) * 16u * kBN * 4u;  // what one slice sends to an owner
         // 16-byte stores of the all-gather form need 16-byte aligned runs of 8 rows and room for the stage
         const bool vec_out = !GGUF && p.nout > 0 && p.vec_out && (!split || p.bt >= 128);
         if (split) {
@@ -658,9 +661,15 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 uint32_t r[16];
                 tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
                 tmem_ld_wait();
+                // the owner of chunk ci, the first chunk it owns, and this slice's slot among the owner's senders
+                int owner = 0;
+                while ((owner + 1) * chunks / S <= ci) ++owner;
+                const int olo = owner * chunks / S;
+                const uint32_t slot = krank < static_cast<uint32_t>(owner) ? krank : krank - 1u;
+                const uint32_t dst = part32 + slot * region;
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    qmm_st_cluster_f32(part32 + static_cast<uint32_t>(((ci * 16 + j) * kBN + row) * 4), krank ^ 1u, __uint_as_float(r[j]));
+                    qmm_st_cluster_f32(dst + static_cast<uint32_t>((((ci - olo) * 16 + j) * kBN + row) * 4), static_cast<uint32_t>(owner), __uint_as_float(r[j]));
             }
             qmm_cluster_arrive();
             qmm_cluster_wait();
@@ -673,11 +682,15 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
             tmem_ld_wait();
             if (split) {
+                // own partial sums first, then the other slices' in rank order
+                for (int sl = 0; sl < S - 1; ++sl) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float v;
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(part32 + static_cast<uint32_t>(((ci * 16 + j) * kBN + row) * 4)));
-                    r[j] = __float_as_uint(__uint_as_float(r[j]) + v);
+                    for (int j = 0; j < 16; ++j) {
+                        float v;
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v)
+                                     : "r"(part32 + sl * region + static_cast<uint32_t>((((ci - own_lo) * 16 + j) * kBN + row) * 4)));
+                        r[j] = __float_as_uint(__uint_as_float(r[j]) + v);
+                    }
                 }
             }
             if (vec_out) {
@@ -685,7 +698,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 // every thread stores 16 bytes and a token's 128 rows leave as one 256-byte run per output
                 // (2-byte lanes made 64-byte writes over NVLink).  The four warps of a chunk group share a
                 // 4 KiB stage behind whatever the k-slice exchange used.
-                uint8_t *stage = xs + (split ? p.bt * kBN * 4 : 0) + (dw >> 2) * 4096;
+                uint8_t *stage = xs + (split ? (S - 1) * region : 0u) + (dw >> 2) * 4096;
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
                     *reinterpret_cast<uint16_t *>(stage + j * 256 + row * 2) = static_cast<uint16_t>(f32_to_bf16_bits(__uint_as_float(r[j])));
@@ -833,8 +846,18 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
         const int kbw = (128 * 8 / bits) / kBK;
         const int64_t sms = sm_count(), ctas = ntiles * ytiles;
         const int64_t t1 = ((ctas + sms - 1) / sms) * (p.num_kb + 6);          // + prologue and store
-        const int64_t t2 = ((2 * ctas + sms - 1) / sms) * (p.num_kb / 2 + 6 + 5);  // + the exchange
-        if (p.num_kb >= 4 * kbw && t2 * 100 < t1 * 93) p.ksplit = 2;
+        int64_t best = t1 * 93;  // a split has to win by 7 %
+        for (int sl = 2; sl <= 4; ++sl) {
+            if (p.num_kb < 2 * sl * kbw) break;
+            // the slices exchange (sl - 1) / sl of the accumulators through the idle operand ring, which has to hold them
+            const int chunks = bt / 16, own_max = (chunks + sl - 1) / sl;
+            if (static_cast<int64_t>(sl - 1) * own_max * 16 * kBN * 4 + 4 * 4096 > static_cast<int64_t>(kStages) * bt * 128) continue;
+            const int64_t ts = ((sl * ctas + sms - 1) / sms) * (p.num_kb / sl + 6 + 3 + 2 * sl);  // + the exchange
+            if (ts * 100 < best) {
+                best = ts * 100;
+                p.ksplit = sl;
+            }
+        }
     }
     dim3 grid(static_cast<unsigned>(ntiles), static_cast<unsigned>(ytiles), static_cast<unsigned>(p.ksplit));
     cudaLaunchConfig_t cfg{};

@@ -61,6 +61,27 @@ def test_four_bit_prefill_shapes_sampled_rows(cuda, n, k):
     assert err <= TOL, (err, l2)
 
 
+@pytest.mark.parametrize("n,k,m,bits", [(17408, 5120, 512, 2), (5120, 17408, 512, 2), (1024, 8192, 256, 4), (2560, 9728, 640, 4),
+                                        (1024, 4096, 300, 4)])
+def test_gemm_launch_forms_sampled_rows(cuda, n, k, m, bits):
+    """The launch forms the host chooses between, each on a shape that takes it: one k-slice (17408 x 5120 at 512
+    rows), three (5120 x 17408 at 512 rows: 80 CTAs of 272 k-blocks), four (1024 x 8192 at 256 rows), and the
+    384-token tile with a ragged last tile (640 and 300 rows).  64 output columns and 96 rows of x against the
+    tile-loader law."""
+    rng = np.random.default_rng(n + k + m)
+    w, s, b = util.affine_weights(rng, n, k, bits, 64)
+    x = util.activations(rng, m, k)
+    y = ops.quantized_matmul(dev_bf16(x, cuda), dev_u32(w, cuda), dev_bf16(s, cuda), dev_bf16(b, cuda), True, 64, bits)
+    cols = np.sort(rng.choice(n, size=64, replace=False))
+    rows = np.sort(rng.choice(m, size=96, replace=False))
+    rows[-1] = m - 1
+    got = O.bf16_to_f32(host_bf16_bits(y))[np.ix_(rows, cols)]
+    truth = O.affine_matmul(x[rows], w[cols], s[cols], b[cols], 64, bits, round_weight_bf16=True, f64=True)
+    err, l2 = util.parity(got, truth)
+    assert err <= TOL, (err, l2)
+    assert ops.device_status() == 0
+
+
 @pytest.mark.parametrize("fmt,name", [(O.Q4_K, "Q4K"), (O.Q2_K, "Q2K")])
 @pytest.mark.parametrize("rows,k", [(18432, 7168), (7168, 18432)])
 def test_gguf_512_tokens_full_shapes_sampled_rows(cuda, fmt, name, rows, k):

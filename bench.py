@@ -877,6 +877,9 @@ def sharded_leg(args, torch, dist, dev, rank, world, warmup):
     torch.cuda.synchronize()
     graphed = False
     fused_mode = args.mode == "shard" and world > 1 and os.environ.get("LISA_BENCH_FUSED", "1") != "0"
+    # the peer-store expert-parallel block without its host read (small receive capacity) is graph-capturable too
+    if args.mode == "moe" and world > 1 and ep is not None and world * tokens * top_k <= ep.DEVICE_COUNT_ROWS:
+        fused_mode = os.environ.get("LISA_BENCH_EP_GRAPH", "1") != "0"
     if (world == 1 or fused_mode) and os.environ.get("LISA_BENCH_GRAPH", "1") != "0":
         # no collective library inside the step (one GPU, or the fused GEMV + peer barrier form), so it
         # replays from a CUDA graph like the decode stack (eager launches through the Python mirror are

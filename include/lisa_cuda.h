@@ -326,7 +326,11 @@ int lisa_cuda_moe_down_combine(lisa_stream_t stream, const void *act, const int3
  *                `back` buffer (back[r]: bf16 [slots of r, hidden]) at the position the slot has in the source's own
  *                sorted order, so that the source folds with lisa_cuda_moe_combine and its own `inverse`;
  *   -- lisa_cuda_peer_barrier --
- * Plain stores into peer mappings; every buffer is reused from step to step (the three barriers order the reuse). */
+ * Plain stores into peer mappings; every buffer is reused from step to step (the three barriers order the reuse).
+ * Without a host read (so that the whole step can be captured in a CUDA graph): fill recv_ids with an id outside
+ * the owner's table before the first barrier, then run the owner's sort, gather_rows, gather_qmm and ep_return
+ * over the whole capacity: unused rows sort last, get no tile and no weight access, and ep_return stops at the
+ * received count, which it reads from the matrix on the device (count may be any value >= it). */
 int lisa_cuda_ep_counts(lisa_stream_t stream, const int32_t *sorted_ids, int64_t slots, int64_t experts, int world,
                         int rank, void *const *count_matrices);
 int lisa_cuda_ep_dispatch(lisa_stream_t stream, const void *x, const int32_t *sorted_ids, const int32_t *token_rows,

@@ -71,6 +71,11 @@ __global__ void __launch_bounds__(256) ep_return_kernel(const uint4 *__restrict_
                                                         int vec_per_row, int world, int rank, const int32_t *__restrict__ matrix,
                                                         EpPeers back) {
     const int p = blockIdx.x;
+    // the received rows are the first ones of the sorted order (ids of unused buffer rows sort last): a caller
+    // that launches over its whole capacity instead of reading the count back stops here
+    int received = 0;
+    for (int q = 0; q < world; ++q) received += __ldg(matrix + q * world + rank);
+    if (p >= received) return;
     const int j = __ldg(recv_index + p);  // index of the row in this owner's receive buffer
     int r = 0, off = 0;
     for (; r < world; ++r) {

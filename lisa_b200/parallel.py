@@ -413,7 +413,11 @@ class ExpertParallelMoe:
     collective library on the data path.  Tokens are data-parallel; rank r owns experts
     ``[r * E / world, (r + 1) * E / world)`` (iq.metal:976-982).  `block` holds this rank's experts
     (`SwitchGlu` with E / world experts).  The only thing the host reads per call is the world x world count
-    matrix, which sizes the owner's launches."""
+    matrix, which sizes the owner's launches; when the receive capacity is small (`world * max_slots` up to
+    DEVICE_COUNT_ROWS rows) not even that: the owner runs over its whole capacity, rows nobody sent carry an id
+    outside its table, and the step has no host synchronisation (it can be captured in a CUDA graph)."""
+
+    DEVICE_COUNT_ROWS = 16384
 
     def __init__(self, block, experts: int, max_tokens: int, hidden: int, group=None):
         self.block = block
@@ -449,20 +453,27 @@ class ExpertParallelMoe:
         if slots > self.max_slots:
             raise _cabi.LisaError(_cabi.ERR_LIMIT, "ExpertParallelMoe: more tokens than the buffers were sized for")
         gs, bits = blk.gate.group_size, blk.gate.bits
+        local_e = self.experts // self.world
+        cap = self.world * self.max_slots
+        on_device = cap <= self.DEVICE_COUNT_ROWS
+        if on_device:
+            self.recv_ids.local.fill_(local_e)       # rows nobody sends this step: an id outside the table
         idx, weights = ops.moe_route(router_logits, k)
         sorted_ids, token_rows, inverse = ops.moe_sort(idx, self.experts, k)   # by global expert: grouped by owner
         _cabi.check(lib.lisa_cuda_ep_counts(st, sorted_ids.data_ptr(), slots, self.experts, self.world, self.rank,
                                             self.matrix.ptrs()))
         self._barrier(st)
-        self._host_matrix.copy_(self.matrix.local.view(self.world, self.world), non_blocking=True)
-        torch.cuda.current_stream().synchronize()      # the one host read: how many rows this rank receives
-        received = int(self._host_matrix[:, self.rank].sum())
+        if on_device:
+            received = cap
+        else:
+            self._host_matrix.copy_(self.matrix.local.view(self.world, self.world), non_blocking=True)
+            torch.cuda.current_stream().synchronize()      # the one host read: how many rows this rank receives
+            received = int(self._host_matrix[:, self.rank].sum())
         _cabi.check(lib.lisa_cuda_ep_dispatch(st, x.data_ptr(), sorted_ids.data_ptr(), token_rows.data_ptr(), slots, self.hidden,
                                               self.experts, self.world, self.rank, self.matrix.local.data_ptr(),
                                               self.recv_x.ptrs(), self.recv_ids.ptrs(), _cabi.BF16))
         self._barrier(st)
         if received:
-            local_e = self.experts // self.world
             ids = self.recv_ids.local[:received]
             s2, rows2, _ = ops.moe_sort(ids, local_e, 1)                     # top_k = 1: rows2 indexes recv_x
             xs = ops.gather_rows(self.recv_x.local[:received], rows2)

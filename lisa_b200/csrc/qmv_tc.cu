@@ -461,7 +461,8 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 }
             }
         };
-        // (four rounds in flight instead of two were measured twice, alone and with the helping warps: slower)
+        // (more rounds in flight -- four, or the three that a 2560-wide 4-bit slice needs -- were measured three times,
+        // alone and with the helping warps: 2 % slower every time)
         for (int base = 0; base < items; base += 2 * kstep) {
             uint4 va[NV], vb[NV];
             load_item(base + sidx, va);

@@ -330,19 +330,20 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     const int L = min(ws1 * KBW, p.num_kb) - kb0;  // k-blocks of this slice (>= 0)
 
     pdl_launch_dependents();
-    if (tid == 0) {
-        for (int i = 0; i < kMaxWStages; ++i) {
-            mbar_init(&wp_full[i], 1);
-            mbar_init(&wp_empty[i], kUnpackWarps);
+    if (warp == 0) {
+        // one barrier per lane (26 of them): a single thread took ~500 clocks over the same initialisations
+        constexpr int kNB = 2 * kMaxWStages + 3 * kNP + 2;
+        static_assert(kNB <= 32, "one lane per barrier");
+        if (lane < kNB) {
+            uint32_t count = 1;                                                       // wp_full, done, sc_full
+            if (lane >= kMaxWStages && lane < 2 * kMaxWStages) count = kUnpackWarps;  // wp_empty
+            else if (lane >= 2 * kMaxWStages && lane < 2 * kMaxWStages + kNP) count = kUnpackWarps / 2;  // a_full
+            else if (lane >= 2 * kMaxWStages + 2 * kNP && lane < 2 * kMaxWStages + 3 * kNP) count = kEpilogueWarps;  // d_empty
+            else if (lane == 2 * kMaxWStages + 3 * kNP) count = kEpilogueWarps;       // x_ready
+            mbar_init(&bars[lane], count);
         }
-        for (int i = 0; i < kNP; ++i) {
-            mbar_init(&a_full[i], kUnpackWarps / 2);
-            mbar_init(&done[i], 1);
-            mbar_init(&d_empty[i], kEpilogueWarps);
-        }
-        mbar_init(x_ready, kEpilogueWarps);
-        mbar_init(sc_full, 1);
         mbar_fence_init();
+        __syncwarp();
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),

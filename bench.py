@@ -575,6 +575,8 @@ def main():
             # configs[4]: GGUF Q2_K / Q4_K, both shapes, M in {1, 512}
             for r in gguf_legs(torch, dev, steps=20, warmup=3):
                 key = f"configs[4] {r['format']} K={r['k']} N={r['n']} M={r['m']}"
+                if "experts" in r:
+                    key = f"GGUF expert form {r['format']} K={r['k']} N={r['n']}, one token, top-{r['top_k']} of {r['experts']}"
                 if r["m"] == 1:
                     hp, hsrc = peaks()
                     legs[key] = {"workload": key, "ms": r["us"] * 1e-3, "value": r["GB/s"], "unit": "GB/s", "n_gpus": 1, "steps": 20,
@@ -720,6 +722,29 @@ def gguf_legs(torch, dev, steps, warmup):
                                 "GB/s": w.numel() / us / 1e3 if m == 1 else None,
                                 "TFLOP/s": 2.0 * m * n * k / us / 1e6 if m > 1 else None})
             del w
+        # the expert form at decode size: one token, top-8 of 64 experts, the GGUF checkpoints' routed down projection
+        # (2048 -> 4096); bytes = the eight experts' rows
+        e, k, n, top_k = 64, 2048, 4096, 8
+        nb = k // 256
+        w = torch.randint(0, 256, (e, n, nb, block), dtype=torch.uint8, device=dev, generator=g)
+        dd = (torch.randn((e, n, nb, 2), device=dev, generator=g) * 0.01).abs().to(torch.float16).view(torch.uint8)
+        w[:, :, :, d_at:d_at + 4] = dd.reshape(e, n, nb, 4)
+        w = w.reshape(e, n, nb * block).contiguous()
+        x = torch.randn((1, top_k, k), device=dev, generator=g)
+        perms = [torch.randperm(e, device=dev, generator=g)[:top_k].to(torch.int32).reshape(1, top_k) for _ in range(8)]
+        for i in range(warmup):
+            ops.expert_matvec(fmt, w, x, perms[i % 8])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            ops.expert_matvec(fmt, w, x, perms[i % 8])
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / steps * 1e3
+        results.append({"format": fmt, "k": k, "n": n, "m": 1, "experts": e, "top_k": top_k, "us": us,
+                        "GB/s": top_k * n * nb * block / us / 1e3, "TFLOP/s": None})
+        del w
     return results
 
 

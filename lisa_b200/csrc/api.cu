@@ -458,6 +458,11 @@ int lisa_cuda_gguf_expert_matvec(lisa_stream_t stream, int format, const uint8_t
     if ((reinterpret_cast<uintptr_t>(w) & 1u) != 0) return fail(LISA_ERR_MISALIGNED, "expert_matvec: weights must be 2-byte aligned");
     if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 3u) != 0 || (reinterpret_cast<uintptr_t>(ids) & 3u) != 0)
         return fail(LISA_ERR_MISALIGNED, "expert_matvec: x must be 16-byte, y and ids 4-byte aligned");
+    // decode-sized id tables: every slot as a one-token launch tile of the tensor-memory kernel (exact on dyadic
+    // inputs like the warp-per-row kernel; ids outside the table store zeros and touch no weights there too)
+    if (aligned16(w) && row_bytes % 16 == 0 && qmv_tc_gguf_expert_supported(format, tokens * top_k, experts, rows, row_bytes))
+        return qmv_tc_gguf_expert(static_cast<cudaStream_t>(stream), format, w, experts, rows, row_bytes, x, tokens, slots, ids,
+                                  top_k, y);
     return gguf_matvec(static_cast<cudaStream_t>(stream), format, w, experts, rows, row_bytes, x, tokens, slots, ids, top_k, y);
 }
 

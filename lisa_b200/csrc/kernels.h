@@ -29,6 +29,9 @@ int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int c
                  void *const *y, unsigned flags, int world = 0, const int64_t *n_total = nullptr,
                  const int64_t *col0 = nullptr);
 bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes);
+bool qmv_tc_gguf_expert_supported(int format, int64_t slots_total, int64_t experts, int64_t rows, int64_t row_bytes);
+int qmv_tc_gguf_expert(cudaStream_t stream, int format, const uint8_t *w, int64_t experts, int64_t rows, int64_t row_bytes,
+                       const float *x, int64_t tokens, int64_t slots, const int32_t *ids, int64_t top_k, float *y);
 // grouped (sorted rows, one expert per table entry) form of the tensor-memory matvec: rows per entry it can take
 // for this shape (0 = unsupported), and the launch over a device tile table {expert, row_begin, row_end, 0}
 int qmv_tc_grouped_rows(int64_t rows, int64_t experts, int64_t k, int64_t n, int group_size, int bits);

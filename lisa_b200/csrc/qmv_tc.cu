@@ -117,6 +117,12 @@ struct TcParams {
     // words) instead of per-thread copies: needs rows of whole 16-byte pieces (groups a multiple of 8); a slice
     // that starts at a group index 4 mod 8 loads from 4 groups earlier
     int sc_tma, sc_box, sc_words;
+    // GGUF expert form (one token per CTA): row tile y of the grid belongs to slot z = y / e_ntiles of the flat
+    // [tokens, top_k] id table; its expert's rows start at ids[z] * n of the packed matrix, its activations are row
+    // (z / e_topk) * e_slots + (z % e_topk) % e_slots of x, its output row z of y; an id outside [0, e_experts)
+    // stores zeros and touches no weights
+    const int *e_ids;
+    int e_experts, e_slots, e_topk, e_ntiles;
     const int4 *g_tiles;
     const int *g_count;
     int g_ntiles;   // row tiles of one expert
@@ -317,6 +323,22 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         g_row0 = t.x * p.g_n;     // first row of the expert in the packed matrix
         g_first = t.y;            // first sorted row of the entry
         m_cta = t.z - t.y;
+    }
+    const float *xf_cta = p.xf;
+    float *yf_cta = p.yf;
+    if (GG && p.e_ids) {
+        const int z = tile / p.e_ntiles;
+        tile -= z * p.e_ntiles;
+        pdl_wait();  // the ids may come from the kernel before this one
+        const int e = p.e_ids[z];
+        if (e < 0 || e >= p.e_experts) {  // the k-slices of a tile share the slot: the cluster leaves together
+            if (rank == 0 && tid < kRows && tile * kRows + tid < p.n) p.yf[static_cast<size_t>(z) * p.n + tile * kRows + tid] = 0.f;
+            return;
+        }
+        g_row0 = e * p.n;
+        const int token = z / p.e_topk, slot = z - token * p.e_topk;
+        xf_cta = p.xf + (static_cast<size_t>(token) * p.e_slots + slot % p.e_slots) * p.k;
+        yf_cta = p.yf + static_cast<size_t>(z) * p.n;
     }
     const uint16_t *x_cta = p.x + static_cast<size_t>(g_first) * p.k;
     const CUtensorMap *map_w = &maps.m[seg];
@@ -751,7 +773,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 const int kbl = u >> 3, j = u & 7;  // k-block, 8-element run of it
                 float xv[8];
                 if (in) {
-                    const float4 *src = reinterpret_cast<const float4 *>(p.xf + static_cast<size_t>(t) * p.k + (kb0 + kbl) * 64 + j * 8);
+                    const float4 *src = reinterpret_cast<const float4 *>(xf_cta + static_cast<size_t>(t) * p.k + (kb0 + kbl) * 64 + j * 8);
                     const float4 v0 = __ldg(src), v1 = __ldg(src + 1);
                     xv[0] = v0.x; xv[1] = v0.y; xv[2] = v0.z; xv[3] = v0.w;
                     xv[4] = v1.x; xv[5] = v1.y; xv[6] = v1.z; xv[7] = v1.w;
@@ -1026,7 +1048,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                     const size_t at = static_cast<size_t>(g_first + t) * ldy + p.col0 + n0 + row;
                     if (GG) {
                         // f32 out; the N-sharded form stores the column block into every rank's output (plain stores)
-                        p.yf[at] = tot;
+                        yf_cta[at] = tot;
                         for (int o = 1; o < p.nout; ++o) reinterpret_cast<float *>(p.out[o])[at] = tot;
                     } else if (p.nseg > 1 && p.seg_nout > 0) {
                         const uint16_t v = static_cast<uint16_t>(f32_to_bf16_bits(tot));
@@ -1340,15 +1362,16 @@ int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int c
 }
 
 // GGUF matvec through the same kernel (f32 in, f32 out): Q4_K for one or two tokens, Q2_K for one.
-static bool gguf_tc_plan(int format, int64_t tokens, int64_t rows, int64_t row_bytes, TcParams &p, int &smem, int &grid) {
+static bool gguf_tc_plan(int format, int64_t tokens, int64_t rows, int64_t row_bytes, TcParams &p, int &smem, int &grid,
+                         int64_t tiles_all = 0) {
     if (tokens < 1 || rows < 1 || rows > (1 << 24)) return false;
     int mc = 0;
     if (format == LISA_GGUF_Q4_K) {
         if (tokens > 2 || row_bytes % 144 != 0) return false;
-        if (!tc_make_plan(rows, row_bytes / 144 * 256, 64, 4, static_cast<int>(tokens), p, smem, grid, mc, kRows * 144, 4)) return false;
+        if (!tc_make_plan(rows, row_bytes / 144 * 256, 64, 4, static_cast<int>(tokens), p, smem, grid, mc, kRows * 144, 4, tiles_all)) return false;
     } else if (format == LISA_GGUF_Q2_K) {
         if (tokens > 1 || row_bytes % 336 != 0) return false;  // whole stage rows of four blocks
-        if (!tc_make_plan(rows, row_bytes / 84 * 256, 64, 2, 1, p, smem, grid, mc, kRows * 336, 16)) return false;
+        if (!tc_make_plan(rows, row_bytes / 84 * 256, 64, 2, 1, p, smem, grid, mc, kRows * 336, 16, tiles_all)) return false;
     } else {
         return false;
     }
@@ -1365,6 +1388,75 @@ int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows,
                 int64_t tokens, float *y) {
     float *outs[1] = {y};
     return qmv_tc_gguf_allgather(stream, format, w, rows, row_bytes, x, tokens, outs, 1, rows, 0);
+}
+
+// Expert form (deepseek41::expert_matvec): every (token, j) slot is a one-token matvec against the rows of its own
+// expert.  One launch over all slots; meant for decode-sized id tables.
+bool qmv_tc_gguf_expert_supported(int format, int64_t slots_total, int64_t experts, int64_t rows, int64_t row_bytes) {
+    TcParams p{};
+    int smem = 0, grid = 0;
+    if (slots_total < 1 || slots_total > 256 || experts * rows > (1ll << 31) - kRows) return false;
+    return gguf_tc_plan(format, 1, rows, row_bytes, p, smem, grid, slots_total * ((rows + kRows - 1) / kRows));
+}
+
+int qmv_tc_gguf_expert(cudaStream_t stream, int format, const uint8_t *w, int64_t experts, int64_t rows, int64_t row_bytes,
+                       const float *x, int64_t tokens, int64_t slots, const int32_t *ids, int64_t top_k, float *y) {
+    const bool q4 = format == LISA_GGUF_Q4_K;
+    const int64_t k = row_bytes / (q4 ? 144 : 84) * 256, z = tokens * top_k, ntiles = (rows + kRows - 1) / kRows;
+    TcParams p{};
+    int smem = 0, grid = 0;
+    if (!gguf_tc_plan(format, 1, rows, row_bytes, p, smem, grid, z * ntiles))
+        return fail(LISA_ERR_UNSUPPORTED, "gguf expert matvec: shape not supported by the tensor-memory kernel");
+    TcMaps maps{};
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(q4 ? row_bytes : row_bytes / 4), static_cast<uint64_t>(experts * rows)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(row_bytes)};
+        const uint32_t box[2] = {static_cast<uint32_t>(q4 ? 144 : 84), kRows};
+        const int rc = make_tensor_map(&maps.m[0], q4 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w, dims,
+                                       strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != LISA_OK) return rc;
+    }
+    p.xf = x;
+    p.yf = y;
+    p.wg = w;
+    p.row_bytes = row_bytes;
+    p.n = static_cast<int>(rows);
+    p.k = static_cast<int>(k);
+    p.m = 1;
+    p.nout = 1;
+    p.out[0] = reinterpret_cast<uint16_t *>(y);
+    p.ldy = static_cast<int>(rows);
+    p.col0 = 0;
+    p.e_ids = ids;
+    p.e_experts = static_cast<int>(experts);
+    p.e_slots = static_cast<int>(slots);
+    p.e_topk = static_cast<int>(top_k);
+    p.e_ntiles = static_cast<int>(ntiles);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(z * ntiles * p.splits));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (p.splits > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = p.splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    if (q4) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4, 4>, maps, p));
+    } else {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2, 2>, maps, p));
+    }
+    count_launch();
+    return LISA_OK;
 }
 
 // The same launch as the all-gather of an N-sharded GGUF matrix: rows [col0, col0 + rows) of a rows_total-row

@@ -180,3 +180,43 @@ def test_q2k_one_token_random_blocks(cuda, rows, k):
     err, l2 = util.parity(y, truth)
     assert err <= 1e-4 and l2 <= 1e-5, (err, l2)
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("name,fmt", FORMATS)
+@pytest.mark.parametrize("slots_shared", [True, False])
+def test_expert_form_decode_sized_through_the_tensor_memory_kernel(cuda, name, fmt, slots_shared):
+    """Decode-sized id tables (tokens * top_k up to 256) run every slot as a one-token tile of the tensor-memory
+    kernel: exact on the dyadic construction (rows of whole 336-byte groups for Q2_K), zeros for ids outside the
+    table, both input forms (one row per token, or one per slot)."""
+    experts, rows, width, tokens, top_k = 24, 200, 2048, 3, 8
+    blocks = O.gguf_dyadic_blocks(fmt, width * rows * experts // 256)
+    w = blocks.reshape(experts, rows, -1)
+    sel = np.array([(i * 7 + 1) % experts for i in range(tokens * top_k)], dtype=np.int32)
+    sel[3], sel[10] = -1, experts
+    ids = sel.reshape(tokens, top_k)
+    slots = 1 if slots_shared else top_k
+    x = O.gguf_dyadic_inputs(tokens * slots * width).reshape(tokens, slots, width)
+    before = ops.launch_count()
+    y = ops.expert_matvec(name, dev_u8(w, cuda), dev_f32(x, cuda), dev_i32(ids, cuda)).cpu().numpy()
+    assert ops.launch_count() - before == 1
+    assert np.array_equal(y, O.gguf_expert_matvec(fmt, w, x, ids))
+    assert np.all(y[0, 3] == 0.0) and np.all(y[1, 2] == 0.0)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("name,fmt", FORMATS)
+def test_expert_form_random_blocks(cuda, name, fmt):
+    """The routed down projection of the GGUF checkpoints' geometry (2048 -> 4096, top-8, one token) on random
+    blocks against the f64 product of the decoded rows."""
+    rng = np.random.default_rng(11 + fmt)
+    experts, rows, k, top_k = 12, 4096, 2048, 8
+    w = util.gguf_weights(rng, fmt, rows, k, experts=experts)
+    x = rng.normal(0, 1, size=(1, top_k, k)).astype(np.float32)
+    ids = rng.choice(experts, size=(1, top_k), replace=False).astype(np.int32)
+    y = ops.expert_matvec(name, dev_u8(w.reshape(experts, rows, -1), cuda), dev_f32(x, cuda), dev_i32(ids, cuda)).cpu().numpy()
+    for j in range(top_k):
+        dec = O.gguf_decode(fmt, w[ids[0, j]].reshape(rows, -1)).reshape(rows, k).astype(np.float64)
+        truth = dec @ x[0, j].astype(np.float64)
+        err, l2 = util.parity(y[0, j], truth)
+        assert err <= 1e-4 and l2 <= 1e-5, (j, err, l2)
+    assert ops.device_status() == 0

@@ -21,6 +21,9 @@ namespace lisa {
 // expert index"; weights = softmax over the k selected logits in f32.
 constexpr int kRouteMaxPerLane = 32;  // experts <= 1024
 
+// PL: logits per lane the kernel is compiled for (the loops over a lane's experts are unrolled over registers):
+// 4 serves up to 128 experts, 32 up to 1024.
+template <int PL>
 __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict__ logits, int tokens, int experts,
                                                         int top_k, int32_t *__restrict__ idx,
                                                         float *__restrict__ weights) {
@@ -28,10 +31,10 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
     const int token = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (token >= tokens) return;
     const float *l = logits + static_cast<int64_t>(token) * experts;
-    float v[kRouteMaxPerLane];
+    float v[PL];
     const int per_lane = (experts + 31) / 32;
 #pragma unroll
-    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    for (int i = 0; i < PL; ++i) {
         const int e = i * 32 + lane;
         v[i] = (i < per_lane && e < experts) ? __ldg(l + e) : -INFINITY;
     }
@@ -43,7 +46,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
         float best = -INFINITY;
         int best_e = 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < kRouteMaxPerLane; ++i) {
+        for (int i = 0; i < PL; ++i) {
             const int e = i * 32 + lane;
             const bool free_slot = i < per_lane && e < experts && !((taken >> i) & 1u);
             if (free_slot && (v[i] > best || best_e == 0x7fffffff)) {  // first free candidate or strictly larger
@@ -83,8 +86,11 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float *__restrict_
 int moe_route(cudaStream_t stream, const float *logits, int64_t tokens, int64_t experts, int top_k, int32_t *idx,
               float *weights) {
     const unsigned blocks = static_cast<unsigned>((tokens + 3) / 4);
-    moe_route_kernel<<<blocks, 128, 0, stream>>>(logits, static_cast<int>(tokens), static_cast<int>(experts), top_k,
-                                                 idx, weights);
+    const int t = static_cast<int>(tokens), e = static_cast<int>(experts);
+    if (experts <= 128) moe_route_kernel<4><<<blocks, 128, 0, stream>>>(logits, t, e, top_k, idx, weights);
+    else if (experts <= 256) moe_route_kernel<8><<<blocks, 128, 0, stream>>>(logits, t, e, top_k, idx, weights);
+    else if (experts <= 512) moe_route_kernel<16><<<blocks, 128, 0, stream>>>(logits, t, e, top_k, idx, weights);
+    else moe_route_kernel<kRouteMaxPerLane><<<blocks, 128, 0, stream>>>(logits, t, e, top_k, idx, weights);
     LISA_CUDA_TRY(cudaGetLastError());
     count_launch();
     return LISA_OK;

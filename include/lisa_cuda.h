@@ -150,6 +150,24 @@ int lisa_cuda_quantized_matmul_allgather(lisa_stream_t stream, const void *x, in
                                          int64_t n_local, int transpose, int group_size, int bits, int dtype,
                                          void *const *y_all, int world, int64_t n_total, int64_t col0,
                                          unsigned flags);
+/* Residual add + RMSNorm in front of one to three linears that read the normed row (the attention or MLP input of
+ * a transformer block): replaces the fused add + rms_norm + qmv chain, affine_qmv_fast_addnorm
+ * (crates/lisa-mlx/src/jit/matmul.rs:304-470) and its sibling form.
+ *   sum    = dtype(x + residual)                                   [m, k], always written (the new residual)
+ *   normed = dtype(norm_weight * dtype(f32(sum) * inv)),  inv = 1 / sqrt(mean(sum^2) + eps) in f32, per row
+ *   y[i]   = normed . dequant(w[i])^T
+ * The three roundings (sum, the product with inv, the product with the weight) are the reference's.  With up to 8
+ * rows and shapes the tensor-memory kernel takes, add and norm run inside its activation staging: one launch, and
+ * `normed` may be null.  Every other shape runs lisa_cuda_add_rmsnorm and then the linears, and needs `normed`
+ * (LISA_ERR_WORKSPACE without it).  norm_weight: dtype [k].  k a multiple of 8. */
+int lisa_cuda_quantized_matmul_addnorm(lisa_stream_t stream, const void *x, const void *residual, const void *norm_weight, float eps,
+                                       int64_t m, int64_t k, int count, const uint32_t *const *w, const void *const *scales,
+                                       const void *const *biases, const int64_t *n, int transpose, int group_size, int bits,
+                                       int dtype, void *const *y, void *sum, void *normed, unsigned flags);
+/* The same add and norm as a call of its own: sum and normed [m, k]. */
+int lisa_cuda_add_rmsnorm(lisa_stream_t stream, const void *x, const void *residual, const void *norm_weight, float eps, int64_t m,
+                          int64_t k, int dtype, void *sum, void *normed);
+
 /* Sibling linears (lisa_cuda_quantized_matmul_siblings) that are N-sharded and fused with their
  * all-gather: linear i holds rows [col0[i], col0[i] + n_local[i]) of an n_total[i]-row linear and
  * y_all[i * world + r] is rank r's [m, n_total[i]] output buffer of linear i as seen from this GPU.

@@ -259,6 +259,49 @@ int lisa_cuda_quantized_matmul_siblings(lisa_stream_t stream, const void *x, int
     return LISA_OK;
 }
 
+int lisa_cuda_add_rmsnorm(lisa_stream_t stream, const void *x, const void *residual, const void *norm_weight, float eps, int64_t m,
+                          int64_t k, int dtype, void *sum, void *normed) {
+    if (!x || !residual || !norm_weight || !sum || !normed) return fail(LISA_ERR_BAD_ARG, "add_rmsnorm: null pointer");
+    if (m < 1 || m > (1ll << 31) - 1 || k < 8 || k % 8 != 0 || k > (1 << 24)) return fail(LISA_ERR_BAD_ARG, "add_rmsnorm: k must be a multiple of 8");
+    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "add_rmsnorm: bf16 only");
+    if (!(eps >= 0.f)) return fail(LISA_ERR_BAD_ARG, "add_rmsnorm: eps must not be negative");
+    if (!aligned16(x) || !aligned16(residual) || !aligned16(norm_weight) || !aligned16(sum) || !aligned16(normed))
+        return fail(LISA_ERR_MISALIGNED, "add_rmsnorm: pointers must be 16-byte aligned");
+    return add_rmsnorm(static_cast<cudaStream_t>(stream), x, residual, norm_weight, eps, m, k, sum, normed);
+}
+
+int lisa_cuda_quantized_matmul_addnorm(lisa_stream_t stream, const void *x, const void *residual, const void *norm_weight, float eps,
+                                       int64_t m, int64_t k, int count, const uint32_t *const *w, const void *const *scales,
+                                       const void *const *biases, const int64_t *n, int transpose, int group_size, int bits,
+                                       int dtype, void *const *y, void *sum, void *normed, unsigned flags) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_addnorm: only transpose=true supported");
+    if (count < 1 || count > 3 || !w || !scales || !biases || !n || !y)
+        return fail(LISA_ERR_BAD_ARG, "quantized_matmul_addnorm: one to three linears, non-null tables");
+    if (!residual || !norm_weight || !sum) return fail(LISA_ERR_BAD_ARG, "quantized_matmul_addnorm: null pointer");
+    if (!(eps >= 0.f)) return fail(LISA_ERR_BAD_ARG, "quantized_matmul_addnorm: eps must not be negative");
+    for (int i = 0; i < count; ++i) {
+        const int rc = check_affine("quantized_matmul_addnorm", x, m, k, w[i], scales[i], biases[i], n[i], group_size, bits, dtype, y[i]);
+        if (rc != LISA_OK) return rc;
+    }
+    if (k % 8 != 0 || !aligned16(residual) || !aligned16(norm_weight) || !aligned16(sum) || (normed && !aligned16(normed)))
+        return fail(LISA_ERR_MISALIGNED, "quantized_matmul_addnorm: k must be a multiple of 8 and the pointers 16-byte aligned");
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned forced = LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE | LISA_FLAG_FORCE_QMV_I8;
+    // decode rows through the tensor-memory kernel: the add and the norm happen in its activation staging
+    if (m <= kQmvMaxRows && bits != 8 && !(flags & forced)) {
+        const TcNormArgs norm{residual, norm_weight, eps, sum, normed};
+        if (count == 1 && qmv_tc_supported(m, k, n[0], group_size, bits))
+            return qmv_tc(st, x, m, k, w[0], scales[0], biases[0], n[0], group_size, bits, y[0], flags, &norm);
+        if (count >= 2 && qmv_tc_multi_supported(m, k, count, n, group_size, bits))
+            return qmv_tc_multi(st, x, m, k, count, w, scales, biases, n, group_size, bits, y, flags, 0, nullptr, nullptr, &norm);
+    }
+    // every other shape: the norm as a kernel of its own (it needs somewhere to put the normed rows), then the linears
+    if (!normed) return fail(LISA_ERR_WORKSPACE, "quantized_matmul_addnorm: this shape runs unfused and needs the normed output buffer");
+    int rc = add_rmsnorm(st, x, residual, norm_weight, eps, m, k, sum, normed);
+    if (rc != LISA_OK) return rc;
+    return lisa_cuda_quantized_matmul_siblings(stream, normed, m, k, count, w, scales, biases, n, transpose, group_size, bits, dtype, y, flags);
+}
+
 int lisa_cuda_quantized_matmul_siblings_allgather(lisa_stream_t stream, const void *x, int64_t m, int64_t k, int count,
                                                   const uint32_t *const *w, const void *const *scales,
                                                   const void *const *biases, const int64_t *n_local, int transpose,

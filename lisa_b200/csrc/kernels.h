@@ -16,8 +16,17 @@ int qmv_clear_status();
 
 // qmv_tc.cu: the same GEMV with the unpacked weights in tensor memory (tcgen05), group size 64, m <= 8 per pass
 bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);
+// residual add + RMSNorm in front of the matmul (the kernel's NORM form): the activations are
+// rms_norm(bf16(x + residual)) * weight; `sum` receives bf16(x + residual), `normed` (or null) the normed rows
+struct TcNormArgs {
+    const void *residual;
+    const void *weight;
+    float eps;
+    void *sum;
+    void *normed;
+};
 int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
-           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags);
+           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags, const TcNormArgs *norm = nullptr);
 int qmv_tc_device_status();
 int qmv_tc_clear_status();
 int qmv_tc_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
@@ -27,7 +36,10 @@ bool qmv_tc_multi_supported(int64_t m, int64_t k, int count, const int64_t *n, i
 int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
                  const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
                  void *const *y, unsigned flags, int world = 0, const int64_t *n_total = nullptr,
-                 const int64_t *col0 = nullptr);
+                 const int64_t *col0 = nullptr, const TcNormArgs *norm = nullptr);
+// bf16(x + r) and rms_norm of it times w, as a kernel of its own (the unfused form)
+int add_rmsnorm(cudaStream_t stream, const void *x, const void *residual, const void *weight, float eps, int64_t m, int64_t k,
+                void *sum, void *normed);
 bool qmv_tc_gguf_supported(int format, int64_t tokens, int64_t rows, int64_t row_bytes);
 bool qmv_tc_gguf_expert_supported(int format, int64_t slots_total, int64_t experts, int64_t rows, int64_t row_bytes);
 int qmv_tc_gguf_expert(cudaStream_t stream, int format, const uint8_t *w, int64_t experts, int64_t rows, int64_t row_bytes,

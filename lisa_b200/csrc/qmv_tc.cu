@@ -123,6 +123,10 @@ struct TcParams {
     // stores zeros and touches no weights
     const int *e_ids;
     int e_experts, e_slots, e_topk, e_ntiles;
+    // NORM form: residual [m, k], norm weight [k], eps; outputs: the sum [m, k] and (or null) the normed row [m, k]
+    const uint16_t *nr, *nw;
+    float neps;
+    uint16_t *nsum, *nnorm;
     const int4 *g_tiles;
     const int *g_count;
     int g_ntiles;   // row tiles of one expert
@@ -281,7 +285,13 @@ __device__ __forceinline__ bool tc_wait_relaxed(uint64_t *bar, uint32_t parity, 
 // k-block kb4 of a block are the 2-bit fields at shifts 2*(kb4&1) and 2*(kb4&1)+1 of code bytes
 // 32*(kb4/2) .. +31, so a pair of k-blocks is the four fields of the same 32 bytes.  Sub-blocks are 16
 // elements: four per k-block, D columns 4*g + q (piece q), B rows 4*g + q non-zero only for k 16g .. 16g+15.
-template <int BITS, int GG = 0>
+//
+// NORM (affine only): the activations are rms_norm(bf16(x + r)) * w, computed by the staging warps
+// (affine_qmv_fast_addnorm, crates/lisa-mlx/src/jit/matmul.rs:304-470 and its shader's rounding points:
+// s = bf16(x + r), inv = 1 / sqrt(mean(s^2) + eps) in f32 over the whole row, normed = bf16(w * bf16(s * inv))).
+// Every CTA reads the whole row of x and r once for the mean square (its own k-slice a second time for the
+// values); the CTAs of the first row tile also write s (the new residual) and, if asked, the normed row.
+template <int BITS, int GG = 0, bool NORM = false>
 __global__ void __launch_bounds__(kThreads, 2)
 qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     constexpr int ROWB = (GG == 4) ? 144 : (GG == 2) ? 336 : 128;  // bytes of a packed stage row
@@ -408,12 +418,71 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         constexpr int NV = CPW / 8;    // 16-byte vectors per item: 1 / 2
         const int items = m_cta * L * IPK;
         const int per_token = L * IPK;
+        float *red = part;  // NORM: [staging warps][8] partial sums of squares, then 1 / rms of token t at red[96 + t]
+        if constexpr (NORM) {
+            auto rb = [](float f) { return bf16_bits_to_f32(f32_to_bf16_bits(f)); };
+            const int bar_id = (kstep == kStageAll) ? 2 : 1;
+            for (int t = 0; t < m_cta; ++t) {
+                const uint4 *xr = reinterpret_cast<const uint4 *>(x_cta + static_cast<size_t>(t) * p.k);
+                const uint4 *rr = reinterpret_cast<const uint4 *>(p.nr + static_cast<size_t>(t) * p.k);
+                float acc = 0.f;
+                for (int i = sidx; i < p.k / 8; i += kstep) {
+                    const uint4 a = __ldg(xr + i), b = __ldg(rr + i);
+                    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float s0 = rb(bf16_bits_to_f32(aw[q] & 0xffffu) + bf16_bits_to_f32(bw[q] & 0xffffu));
+                        const float s1 = rb(__uint_as_float(aw[q] & 0xffff0000u) + __uint_as_float(bw[q] & 0xffff0000u));
+                        acc = fmaf(s0, s0, acc);
+                        acc = fmaf(s1, s1, acc);
+                    }
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                if (lane == 0) red[(sidx >> 5) * 8 + t] = acc;
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(kstep) : "memory");
+            if (sidx < m_cta) {
+                float tot = 0.f;
+                for (int w = 0; w < (kstep >> 5); ++w) tot += red[w * 8 + sidx];  // fixed order
+                red[96 + sidx] = 1.0f / sqrtf(tot / static_cast<float>(p.k) + p.neps);
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(kstep) : "memory");
+        }
         auto load_item = [&](int item, uint4 (&v)[NV]) {
             if (item < items) {
                 const int t = item / per_token, u = item - t * per_token;
-                const uint4 *src = reinterpret_cast<const uint4 *>(x_cta + static_cast<size_t>(t) * p.k + kb0 * 64 + u * CPW);
+                const size_t at = static_cast<size_t>(t) * p.k + kb0 * 64 + u * CPW;
+                const uint4 *src = reinterpret_cast<const uint4 *>(x_cta + at);
 #pragma unroll
                 for (int i = 0; i < NV; ++i) v[i] = __ldg(src + i);
+                if constexpr (NORM) {
+                    auto rb = [](float f) { return bf16_bits_to_f32(f32_to_bf16_bits(f)); };
+                    const float inv = red[96 + t];
+                    const bool writer = n0 == 0 && seg == 0;  // the first row tile's k-slices cover the row once
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(p.nr + at) + i);
+                        const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(p.nw + kb0 * 64 + u * CPW) + i);
+                        const uint32_t xw[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, rw[4] = {rv.x, rv.y, rv.z, rv.w};
+                        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                        uint32_t sw[4], nd[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float s0 = rb(bf16_bits_to_f32(xw[q] & 0xffffu) + bf16_bits_to_f32(rw[q] & 0xffffu));
+                            const float s1 = rb(__uint_as_float(xw[q] & 0xffff0000u) + __uint_as_float(rw[q] & 0xffff0000u));
+                            const float y0 = bf16_bits_to_f32(ww[q] & 0xffffu) * rb(s0 * inv);
+                            const float y1 = __uint_as_float(ww[q] & 0xffff0000u) * rb(s1 * inv);
+                            sw[q] = (__float_as_uint(s0) >> 16) | (__float_as_uint(s1) & 0xffff0000u);
+                            nd[q] = f32_to_bf16_bits(y0) | (f32_to_bf16_bits(y1) << 16);
+                        }
+                        v[i] = make_uint4(nd[0], nd[1], nd[2], nd[3]);
+                        if (writer) {
+                            reinterpret_cast<uint4 *>(p.nsum + at)[i] = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+                            if (p.nnorm) reinterpret_cast<uint4 *>(p.nnorm + at)[i] = v[i];
+                        }
+                    }
+                }
             }
         };
         auto store_item = [&](int item, const uint4 (&v)[NV]) {
@@ -1176,7 +1245,13 @@ static int tc_launch_kernel(cudaStream_t stream, int bits, const TcMaps &maps, c
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    if (bits == 4) {
+    if (p.nr && bits == 4) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4, 0, true>, maps, p));
+    } else if (p.nr) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2, 0, true>, maps, p));
+    } else if (bits == 4) {
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4>, maps, p));
     } else {
@@ -1187,9 +1262,18 @@ static int tc_launch_kernel(cudaStream_t stream, int bits, const TcMaps &maps, c
     return LISA_OK;
 }
 
+static void tc_set_norm(TcParams &p, const TcNormArgs *norm, int64_t done, int64_t k) {
+    if (!norm) return;
+    p.nr = reinterpret_cast<const uint16_t *>(norm->residual) + done * k;
+    p.nw = reinterpret_cast<const uint16_t *>(norm->weight);
+    p.neps = norm->eps;
+    p.nsum = reinterpret_cast<uint16_t *>(norm->sum) + done * k;
+    p.nnorm = norm->normed ? reinterpret_cast<uint16_t *>(norm->normed) + done * k : nullptr;
+}
+
 static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                          const void *biases, int64_t n, int group_size, int bits, void *const *outs, int nout, int64_t ldy,
-                         int64_t col0, unsigned flags) {
+                         int64_t col0, unsigned flags, const TcNormArgs *norm = nullptr) {
     const uint16_t *xp = reinterpret_cast<const uint16_t *>(x);
     TcMaps maps{};
     {
@@ -1216,6 +1300,7 @@ static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t 
         p.n = static_cast<int>(n);
         p.k = static_cast<int>(k);
         p.m = mc;
+        tc_set_norm(p, norm, done, k);
         const int rc = tc_launch_kernel(stream, bits, maps, p, grid, smem, flags);
         if (rc != LISA_OK) return rc;
     }
@@ -1273,9 +1358,9 @@ int qmv_tc_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, 
 }
 
 int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
-           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags) {
+           const void *biases, int64_t n, int group_size, int bits, void *y, unsigned flags, const TcNormArgs *norm) {
     void *outs[1] = {y};
-    return qmv_tc_launch(stream, x, m, k, w, scales, biases, n, group_size, bits, outs, 1, n, 0, flags);
+    return qmv_tc_launch(stream, x, m, k, w, scales, biases, n, group_size, bits, outs, 1, n, 0, flags, norm);
 }
 
 // N-sharded GEMV fused with its all-gather: this rank's rows [col0, col0 + n) of an n_total-row linear,
@@ -1304,7 +1389,7 @@ bool qmv_tc_multi_supported(int64_t m, int64_t k, int count, const int64_t *n, i
 // (linear i, rank r at y[i * world + r]), linear i's rows are columns [col0[i], col0[i] + n[i]) of n_total[i].
 int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int count, const uint32_t *const *w,
                  const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
-                 void *const *y, unsigned flags, int world, const int64_t *n_total, const int64_t *col0) {
+                 void *const *y, unsigned flags, int world, const int64_t *n_total, const int64_t *col0, const TcNormArgs *norm) {
     if (count < 2 || count > kMaxSeg) return fail(LISA_ERR_UNSUPPORTED, "qmv_tc_multi: two or three linears per launch");
     const uint16_t *xp = reinterpret_cast<const uint16_t *>(x);
     TcMaps maps{};
@@ -1355,6 +1440,7 @@ int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int c
         p.out[0] = p.seg_out[0];
         p.n = p.seg_n[0];
         p.ldy = p.seg_n[0];
+        tc_set_norm(p, norm, done, k);
         const int rc = tc_launch_kernel(stream, bits, maps, p, grid, smem, flags);
         if (rc != LISA_OK) return rc;
     }

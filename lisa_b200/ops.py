@@ -103,6 +103,54 @@ def quantized_matmul_siblings(x: torch.Tensor, linears, transpose: bool = True, 
     return [y.reshape(*x.shape[:-1], y.shape[-1]) for y in ys]
 
 
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float, *, stream=None):
+    """(sum, normed): sum = bf16(x + residual), normed = rms_norm(sum) * norm_weight with the reference's
+    rounding points (crates/lisa-mlx/src/jit/matmul.rs:304-316)."""
+    _need_cuda(x, residual, norm_weight)
+    k = x.shape[-1]
+    m = x.numel() // k
+    x2, r2 = x.reshape(m, k).contiguous(), residual.reshape(m, k).contiguous()
+    total, normed = torch.empty_like(x2), torch.empty_like(x2)
+    check(lib().lisa_cuda_add_rmsnorm(_stream(stream), x2.data_ptr(), r2.data_ptr(), norm_weight.contiguous().data_ptr(),
+                                      float(eps), m, k, _dtype_code(x2), total.data_ptr(), normed.data_ptr()))
+    return total.reshape(x.shape), normed.reshape(x.shape)
+
+
+def quantized_matmul_addnorm(x: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float, linears,
+                             group_size: int = 64, bits: int = 4, *, write_norm: bool = True, stream=None, flags: int = 0):
+    """Residual add + RMSNorm + one to three quantized linears on the normed rows (affine_qmv_fast_addnorm,
+    crates/lisa-mlx/src/jit/matmul.rs:304-470): returns (outputs, sum, normed or None).  Decode rows run as one
+    launch; other shapes need `write_norm` (the normed rows are then the matmul's input buffer)."""
+    import ctypes as C
+
+    _need_cuda(x, residual, norm_weight)
+    k = x.shape[-1]
+    m = x.numel() // k
+    x2, r2 = x.reshape(m, k).contiguous(), residual.reshape(m, k).contiguous()
+    count = len(linears)
+    keep, ys = [], []
+    wp, sp, bp, yp = (C.c_void_p * count)(), (C.c_void_p * count)(), (C.c_void_p * count)(), (C.c_void_p * count)()
+    ns = (C.c_int64 * count)()
+    for i, (w, sc, bi) in enumerate(linears):
+        _need_cuda(w, sc, bi)
+        w = _words(w)
+        sc, bi = sc.contiguous(), bi.contiguous()
+        if w.shape[-1] * 32 // bits != k or sc.shape[-1] * group_size != k:
+            raise LisaError(_cabi.ERR_BAD_ARG, "quantized_matmul_addnorm: shapes of x, w and scales disagree")
+        y = torch.empty((m, w.shape[0]), dtype=x2.dtype, device=x2.device)
+        keep.append((w, sc, bi))
+        ys.append(y)
+        wp[i], sp[i], bp[i], yp[i], ns[i] = w.data_ptr(), sc.data_ptr(), bi.data_ptr(), y.data_ptr(), w.shape[0]
+    total = torch.empty_like(x2)
+    normed = torch.empty_like(x2) if write_norm else None
+    rc = lib().lisa_cuda_quantized_matmul_addnorm(_stream(stream), x2.data_ptr(), r2.data_ptr(), norm_weight.contiguous().data_ptr(),
+                                                  float(eps), m, k, count, wp, sp, bp, ns, 1, group_size, bits, _dtype_code(x2), yp,
+                                                  total.data_ptr(), None if normed is None else normed.data_ptr(), flags)
+    check(rc)
+    outs = [y.reshape(*x.shape[:-1], y.shape[-1]) for y in ys]
+    return outs, total.reshape(x.shape), None if normed is None else normed.reshape(x.shape)
+
+
 def quantized_matmul_serial_rows(x, w, scales, biases, transpose: bool = True, group_size: int = 64,
                                  bits: int = 4, *, stream=None) -> torch.Tensor:
     """``ops::quantized_matmul_serial_rows`` (array_ops.rs:500-555)."""

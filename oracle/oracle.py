@@ -303,3 +303,22 @@ def moe_forward(x, logits, gate, up, down, top_k: int, group_size: int = 64, bit
     return moe_combine(d, wts, inverse, top_k), dict(idx=idx, weights=wts, sorted_ids=sorted_ids,
                                                       token_rows=token_rows, inverse=inverse,
                                                       gate=g, up=u, act=act, down=d)
+
+
+def add_rmsnorm(x, residual, weight, eps: float):
+    """Residual add + RMSNorm with the rounding points of the reference's fused chain
+    (crates/lisa-mlx/src/jit/matmul.rs:304-316; crates/lisa-mlx/src/shaders/common/matmul/norm_qmv.metal:159-185):
+    sum = bf16(f32(x) + f32(r)); inv = 1 / sqrt(mean(sum^2) + eps); normed = bf16(w * bf16(f32(sum) * inv)).
+    bf16 bit arrays [m, k] (weight [k]) in and out.  The mean is taken in f64 and inv rounded to f32 once (the
+    reference accumulates in f32 in an order of its own; a kernel's inv may differ from this one in its last bits,
+    which can move a normed element by one bf16 ulp)."""
+    xs = bf16_to_f32(np.ascontiguousarray(x, dtype=np.uint16))
+    rs = bf16_to_f32(np.ascontiguousarray(residual, dtype=np.uint16))
+    ws = bf16_to_f32(np.ascontiguousarray(weight, dtype=np.uint16))
+    total = f32_to_bf16((xs + rs).astype(np.float32))
+    sf = bf16_to_f32(total)
+    mean = np.mean(sf.astype(np.float64) ** 2, axis=-1, keepdims=True)
+    inv = (1.0 / np.sqrt(mean + np.float64(np.float32(eps)))).astype(np.float32)
+    inner = bf16_to_f32(f32_to_bf16((sf * inv).astype(np.float32)))
+    normed = f32_to_bf16((ws[None, :] * inner).astype(np.float32))
+    return total, normed

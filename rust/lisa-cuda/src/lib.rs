@@ -231,6 +231,35 @@ pub fn dequantize_rows<A: DeviceArray>(stream: Stream, w: &A, scales: &A, biases
     Ok(out)
 }
 
+/// `affine_qmv_fast_addnorm` and its sibling form (crates/lisa-mlx/src/jit/matmul.rs:304-577): residual add +
+/// RMSNorm + one to three linears on the normed rows.  Returns `(outputs, sum, normed)`; `write_norm = false` is
+/// accepted for the decode shapes that run as one launch.
+#[allow(clippy::too_many_arguments)]
+pub fn quantized_matmul_addnorm<A: DeviceArray>(stream: Stream, x: &A, r: &A, norm_weight: &A, linears: &[(&A, &A, &A)], eps: f32,
+                                                group_size: i32, bits: i32, write_norm: bool) -> Result<(Vec<A>, A, Option<A>)> {
+    let k = *x.shape().last().unwrap();
+    let m: i64 = x.shape().iter().product::<i64>() / k;
+    let mut ys = Vec::with_capacity(linears.len());
+    for (w, _, _) in linears {
+        ys.push(A::alloc(&[m, w.shape()[0]], x.dtype())?);
+    }
+    let mut sum = A::alloc(&[m, k], x.dtype())?;
+    let mut normed = if write_norm { Some(A::alloc(&[m, k], x.dtype())?) } else { None };
+    let w: Vec<*const u32> = linears.iter().map(|l| l.0.device_ptr() as *const u32).collect();
+    let s: Vec<*const c_void> = linears.iter().map(|l| l.1.device_ptr()).collect();
+    let b: Vec<*const c_void> = linears.iter().map(|l| l.2.device_ptr()).collect();
+    let n: Vec<i64> = linears.iter().map(|l| l.0.shape()[0]).collect();
+    let y: Vec<*mut c_void> = ys.iter_mut().map(|a| a.device_ptr_mut()).collect();
+    check(unsafe {
+        sys::lisa_cuda_quantized_matmul_addnorm(stream.0, x.device_ptr(), r.device_ptr(), norm_weight.device_ptr(), eps, m, k,
+                                                linears.len() as c_int, w.as_ptr(), s.as_ptr(), b.as_ptr(), n.as_ptr(), 1,
+                                                group_size, bits, x.dtype().code()?, y.as_ptr(), sum.device_ptr_mut(),
+                                                normed.as_mut().map_or(std::ptr::null_mut(), |a| a.device_ptr_mut()),
+                                                sys::LISA_FLAG_PDL)
+    })?;
+    Ok((ys, sum, normed))
+}
+
 /// `moe_decode::gate_up_act` (crates/lisa-mlx/src/models/qwen4/moe_decode.rs:136-184) without the shared
 /// expert: `x [tokens, hidden]`, `idx [tokens, top_k]`, gate / up `(w [E, inter, hidden*bits/32], scales,
 /// biases)` -> `act [tokens * top_k, inter]`; `xrow` maps slots to rows of `x` (default `slot / top_k`).

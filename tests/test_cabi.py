@@ -115,6 +115,28 @@ def test_decode_block_rejections(lib):
     assert gate(slots=0) == _cabi.ERR_BAD_ARG and down(tokens=0) == _cabi.ERR_BAD_ARG
 
 
+def test_addnorm_rejections(lib):
+    import ctypes as C
+    one = (C.c_void_p * 1)(16)
+    ns = (C.c_int64 * 1)(128)
+
+    def call(x=16, r=16, nw=16, eps=1e-6, m=1, k=256, count=1, w=one, tr=1, gs=64, bits=4, dtype=0, y=one, total=16, normed=16):
+        return lib.lisa_cuda_quantized_matmul_addnorm(None, x, r, nw, eps, m, k, count, w, one, one, ns, tr, gs, bits, dtype, y, total,
+                                                      normed, 0)
+    assert call(r=None) == _cabi.ERR_BAD_ARG
+    assert call(total=None) == _cabi.ERR_BAD_ARG
+    assert call(tr=0) == _cabi.ERR_UNSUPPORTED
+    assert call(count=4) == _cabi.ERR_BAD_ARG
+    assert call(eps=-1.0) == _cabi.ERR_BAD_ARG
+    assert call(dtype=2) == _cabi.ERR_UNSUPPORTED
+    assert call(nw=8) == _cabi.ERR_MISALIGNED
+    f = lib.lisa_cuda_add_rmsnorm
+    assert f(None, 16, 16, 16, 1e-6, 1, 12, 0, 16, 16) == _cabi.ERR_BAD_ARG        # k % 8
+    assert f(None, 16, 16, 16, 1e-6, 1, 64, 0, 16, None) == _cabi.ERR_BAD_ARG
+    assert f(None, 16, 16, 16, 1e-6, 1, 64, 1, 16, 16) == _cabi.ERR_UNSUPPORTED    # bf16 only
+    assert f(None, 16, 24, 16, 1e-6, 1, 64, 0, 16, 16) == _cabi.ERR_MISALIGNED
+
+
 def test_gguf_rejections(lib):
     f = lib.lisa_cuda_gguf_packed_matvec
     # deepseek41.rs:50-65,100-101

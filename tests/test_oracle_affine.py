@@ -90,3 +90,25 @@ def test_gather_qmm_equals_per_run_matmul():
     y = O.gather_qmm(x, w, s, b, ids, 64, 4, threads=2)
     for r, ex in enumerate(ids):
         assert np.array_equal(y[r], O.affine_matmul(x[r:r + 1], w[ex], s[ex], b[ex], 64, 4, threads=1)[0])
+
+
+def test_add_rmsnorm_restatement():
+    """The add + RMSNorm restatement: unit weight and zero residual give x / rms(x) up to the two bf16 roundings;
+    the sum is the bf16 rounding of the exact f32 sum; a weight scales the normed row before the last rounding."""
+    rng = np.random.default_rng(9)
+    m, k = 3, 512
+    x = O.f32_to_bf16(rng.normal(0, 3, size=(m, k)).astype(np.float32))
+    zero = np.zeros((m, k), dtype=np.uint16)
+    one = O.f32_to_bf16(np.ones(k, dtype=np.float32))
+    total, normed = O.add_rmsnorm(x, zero, one, 0.0)
+    assert np.array_equal(total, x)
+    xf = O.bf16_to_f32(x).astype(np.float64)
+    want = xf / np.sqrt(np.mean(xf * xf, axis=1, keepdims=True))
+    got = O.bf16_to_f32(normed).astype(np.float64)
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-3)) <= 2.0 ** -8
+    r = O.f32_to_bf16(rng.normal(0, 1, size=(m, k)).astype(np.float32))
+    total, _ = O.add_rmsnorm(x, r, one, 1e-6)
+    assert np.array_equal(total, O.f32_to_bf16((O.bf16_to_f32(x) + O.bf16_to_f32(r)).astype(np.float32)))
+    two = O.f32_to_bf16(np.full(k, 2.0, dtype=np.float32))
+    _, n2 = O.add_rmsnorm(x, zero, two, 0.0)
+    assert np.array_equal(O.bf16_to_f32(n2), 2.0 * O.bf16_to_f32(normed))   # a power of two commutes with the rounding

@@ -426,15 +426,26 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 const uint4 *xr = reinterpret_cast<const uint4 *>(x_cta + static_cast<size_t>(t) * p.k);
                 const uint4 *rr = reinterpret_cast<const uint4 *>(p.nr + static_cast<size_t>(t) * p.k);
                 float acc = 0.f;
-                for (int i = sidx; i < p.k / 8; i += kstep) {
-                    const uint4 a = __ldg(xr + i), b = __ldg(rr + i);
-                    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+                // three chunks per trip, their six loads issued together (a 2560-wide row is one trip for 128 threads)
+                for (int i0 = sidx; i0 < p.k / 8; i0 += 3 * kstep) {
+                    uint4 a[3], b[3];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float s0 = rb(bf16_bits_to_f32(aw[q] & 0xffffu) + bf16_bits_to_f32(bw[q] & 0xffffu));
-                        const float s1 = rb(__uint_as_float(aw[q] & 0xffff0000u) + __uint_as_float(bw[q] & 0xffff0000u));
-                        acc = fmaf(s0, s0, acc);
-                        acc = fmaf(s1, s1, acc);
+                    for (int u = 0; u < 3; ++u) {
+                        const int i = i0 + u * kstep;
+                        const bool in = i < p.k / 8;
+                        a[u] = in ? __ldg(xr + i) : make_uint4(0, 0, 0, 0);
+                        b[u] = in ? __ldg(rr + i) : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 3; ++u) {
+                        const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float s0 = rb(bf16_bits_to_f32(aw[q] & 0xffffu) + bf16_bits_to_f32(bw[q] & 0xffffu));
+                            const float s1 = rb(__uint_as_float(aw[q] & 0xffff0000u) + __uint_as_float(bw[q] & 0xffff0000u));
+                            acc = fmaf(s0, s0, acc);
+                            acc = fmaf(s1, s1, acc);
+                        }
                     }
                 }
 #pragma unroll

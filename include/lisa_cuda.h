@@ -164,6 +164,15 @@ int lisa_cuda_quantized_matmul_addnorm(lisa_stream_t stream, const void *x, cons
                                        int64_t m, int64_t k, int count, const uint32_t *const *w, const void *const *scales,
                                        const void *const *biases, const int64_t *n, int transpose, int group_size, int bits,
                                        int dtype, void *const *y, void *sum, void *normed, unsigned flags);
+/* SwiGLU in front of a linear (the down projection of an MLP reading its gate and up outputs):
+ *   act = dtype(dtype(gate * dtype(sigmoid(gate))) * up)  (crates/lisa-mlx/src/shaders/common/exact_header.metal:2-11)
+ *   y   = act . dequant(w)^T
+ * With up to 8 rows and shapes the tensor-memory kernel takes, the activation is formed in its staging: one
+ * launch, `act` may be null (if given, it receives the activation rows).  Other shapes run lisa_cuda_swiglu and the
+ * ordinary dispatch and need `act` (LISA_ERR_WORKSPACE without it).  gate, up: dtype [m, k]. */
+int lisa_cuda_quantized_matmul_swiglu(lisa_stream_t stream, const void *gate, const void *up, int64_t m, int64_t k, const uint32_t *w,
+                                      const void *scales, const void *biases, int64_t n, int transpose, int group_size, int bits,
+                                      int dtype, void *y, void *act, unsigned flags);
 /* The same add and norm as a call of its own: sum and normed [m, k]. */
 int lisa_cuda_add_rmsnorm(lisa_stream_t stream, const void *x, const void *residual, const void *norm_weight, float eps, int64_t m,
                           int64_t k, int dtype, void *sum, void *normed);

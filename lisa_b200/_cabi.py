@@ -68,6 +68,8 @@ SIGNATURES = {
     "lisa_cuda_ep_dispatch": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _int]),
     "lisa_cuda_ep_return": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _vp, _vp, _int]),
     "lisa_cuda_moe_combine": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _i64, _int, _vp]),
+    "lisa_cuda_quantized_matmul_swiglu": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _vp, _vp,
+                                                 C.c_uint]),
     "lisa_cuda_add_rmsnorm": (_int, [_vp, _vp, _vp, _vp, C.c_float, _i64, _i64, _int, _vp, _vp]),
     "lisa_cuda_quantized_matmul_addnorm": (_int, [_vp, _vp, _vp, _vp, C.c_float, _i64, _i64, _int, _vp, _vp, _vp, _vp, _int, _int,
                                                   _int, _int, _vp, _vp, _vp, C.c_uint]),

@@ -302,6 +302,28 @@ int lisa_cuda_quantized_matmul_addnorm(lisa_stream_t stream, const void *x, cons
     return lisa_cuda_quantized_matmul_siblings(stream, normed, m, k, count, w, scales, biases, n, transpose, group_size, bits, dtype, y, flags);
 }
 
+int lisa_cuda_quantized_matmul_swiglu(lisa_stream_t stream, const void *gate, const void *up, int64_t m, int64_t k, const uint32_t *w,
+                                      const void *scales, const void *biases, int64_t n, int transpose, int group_size, int bits,
+                                      int dtype, void *y, void *act, unsigned flags) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul_swiglu: only transpose=true supported");
+    if (!up) return fail(LISA_ERR_BAD_ARG, "quantized_matmul_swiglu: null pointer");
+    const int rc = check_affine("quantized_matmul_swiglu", gate, m, k, w, scales, biases, n, group_size, bits, dtype, y);
+    if (rc != LISA_OK) return rc;
+    if (k % 8 != 0 || !aligned16(up) || (act && !aligned16(act)))
+        return fail(LISA_ERR_MISALIGNED, "quantized_matmul_swiglu: k must be a multiple of 8 and the pointers 16-byte aligned");
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned forced = LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_SIMPLE | LISA_FLAG_FORCE_QMV_I8;
+    // decode rows: the activation is formed in the staging of the tensor-memory kernel
+    if (m <= kQmvMaxRows && bits != 8 && !(flags & forced) && qmv_tc_supported(m, k, n, group_size, bits)) {
+        const TcNormArgs fuse{up, nullptr, 0.f, nullptr, act};
+        return qmv_tc(st, gate, m, k, w, scales, biases, n, group_size, bits, y, flags, &fuse);
+    }
+    if (!act) return fail(LISA_ERR_WORKSPACE, "quantized_matmul_swiglu: this shape runs unfused and needs the activation buffer");
+    const int rs = moe_swiglu(st, gate, up, m * k, act);
+    if (rs != LISA_OK) return rs;
+    return quantized_matmul_impl(st, act, m, k, w, scales, biases, n, transpose, group_size, bits, dtype, y, flags);
+}
+
 int lisa_cuda_quantized_matmul_siblings_allgather(lisa_stream_t stream, const void *x, int64_t m, int64_t k, int count,
                                                   const uint32_t *const *w, const void *const *scales,
                                                   const void *const *biases, const int64_t *n_local, int transpose,

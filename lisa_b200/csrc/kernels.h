@@ -17,7 +17,8 @@ int qmv_clear_status();
 // qmv_tc.cu: the same GEMV with the unpacked weights in tensor memory (tcgen05), group size 64, m <= 8 per pass
 bool qmv_tc_supported(int64_t m, int64_t k, int64_t n, int group_size, int bits);
 // residual add + RMSNorm in front of the matmul (the kernel's NORM form): the activations are
-// rms_norm(bf16(x + residual)) * weight; `sum` receives bf16(x + residual), `normed` (or null) the normed rows
+// rms_norm(bf16(x + residual)) * weight; `sum` receives bf16(x + residual), `normed` (or null) the normed rows.
+// With a null weight the form is the SwiGLU one: activations = swiglu(x, residual), `normed` (or null) receives them.
 struct TcNormArgs {
     const void *residual;
     const void *weight;

@@ -291,7 +291,11 @@ __device__ __forceinline__ bool tc_wait_relaxed(uint64_t *bar, uint32_t parity, 
 // s = bf16(x + r), inv = 1 / sqrt(mean(s^2) + eps) in f32 over the whole row, normed = bf16(w * bf16(s * inv))).
 // Every CTA reads the whole row of x and r once for the mean square (its own k-slice a second time for the
 // values); the CTAs of the first row tile also write s (the new residual) and, if asked, the normed row.
-template <int BITS, int GG = 0, bool NORM = false>
+//
+// NORM = 2 (affine only): the activations are swiglu(x, nr) = bf16(bf16(g * bf16(sigmoid(g))) * u) with g = x and
+// u = nr (crates/lisa-mlx/src/shaders/common/exact_header.metal:2-11): the down projection of an MLP reads the
+// gate and up outputs directly; the CTAs of the first row tile write the activation row if asked (nnorm).
+template <int BITS, int GG = 0, int NORM = 0>
 __global__ void __launch_bounds__(kThreads, 2)
 qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
     constexpr int ROWB = (GG == 4) ? 144 : (GG == 2) ? 336 : 128;  // bytes of a packed stage row
@@ -419,7 +423,7 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
         const int items = m_cta * L * IPK;
         const int per_token = L * IPK;
         float *red = part;  // NORM: [staging warps][8] partial sums of squares, then 1 / rms of token t at red[96 + t]
-        if constexpr (NORM) {
+        if constexpr (NORM == 1) {
             auto rb = [](float f) { return bf16_bits_to_f32(f32_to_bf16_bits(f)); };
             const int bar_id = (kstep == kStageAll) ? 2 : 1;
             for (int t = 0; t < m_cta; ++t) {
@@ -467,7 +471,28 @@ qmv_tc_kernel(const __grid_constant__ TcMaps maps, const TcParams p) {
                 const uint4 *src = reinterpret_cast<const uint4 *>(x_cta + at);
 #pragma unroll
                 for (int i = 0; i < NV; ++i) v[i] = __ldg(src + i);
-                if constexpr (NORM) {
+                if constexpr (NORM == 2) {
+                    auto rb = [](float f) { return bf16_bits_to_f32(f32_to_bf16_bits(f)); };
+                    auto act = [&](float gv, float uv) {  // the same function as moe_swiglu's
+                        const float y = 1.0f / (1.0f + expf(fabsf(gv)));
+                        const float sg = rb(gv < 0.f ? y : 1.0f - y);
+                        return rb(gv * sg) * uv;
+                    };
+                    const bool writer = n0 == 0 && seg == 0 && p.nnorm;
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        const uint4 uv = __ldg(reinterpret_cast<const uint4 *>(p.nr + at) + i);
+                        const uint32_t gw[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+                        uint32_t a[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            a[q] = f32_to_bf16_bits(act(bf16_bits_to_f32(gw[q] & 0xffffu), bf16_bits_to_f32(uw[q] & 0xffffu))) |
+                                   (f32_to_bf16_bits(act(__uint_as_float(gw[q] & 0xffff0000u), __uint_as_float(uw[q] & 0xffff0000u))) << 16);
+                        v[i] = make_uint4(a[0], a[1], a[2], a[3]);
+                        if (writer) reinterpret_cast<uint4 *>(p.nnorm + at)[i] = v[i];
+                    }
+                }
+                if constexpr (NORM == 1) {
                     auto rb = [](float f) { return bf16_bits_to_f32(f32_to_bf16_bits(f)); };
                     const float inv = red[96 + t];
                     const bool writer = n0 == 0 && seg == 0;  // the first row tile's k-slices cover the row once
@@ -1256,12 +1281,18 @@ static int tc_launch_kernel(cudaStream_t stream, int bits, const TcMaps &maps, c
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    if (p.nr && bits == 4) {
-        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4, 0, true>, maps, p));
+    if (p.nr && !p.nw && bits == 4) {  // (no norm weight: the second input is the up projection of a SwiGLU)
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4, 0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4, 0, 2>, maps, p));
+    } else if (p.nr && !p.nw) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2, 0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2, 0, 2>, maps, p));
+    } else if (p.nr && bits == 4) {
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4, 0, 1>, maps, p));
     } else if (p.nr) {
-        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2, 0, true>, maps, p));
+        LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<2, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<2, 0, 1>, maps, p));
     } else if (bits == 4) {
         LISA_CUDA_TRY(cudaFuncSetAttribute(qmv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         LISA_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmv_tc_kernel<4>, maps, p));
@@ -1278,7 +1309,7 @@ static void tc_set_norm(TcParams &p, const TcNormArgs *norm, int64_t done, int64
     p.nr = reinterpret_cast<const uint16_t *>(norm->residual) + done * k;
     p.nw = reinterpret_cast<const uint16_t *>(norm->weight);
     p.neps = norm->eps;
-    p.nsum = reinterpret_cast<uint16_t *>(norm->sum) + done * k;
+    p.nsum = norm->sum ? reinterpret_cast<uint16_t *>(norm->sum) + done * k : nullptr;
     p.nnorm = norm->normed ? reinterpret_cast<uint16_t *>(norm->normed) + done * k : nullptr;
 }
 

@@ -151,6 +151,24 @@ def quantized_matmul_addnorm(x: torch.Tensor, residual: torch.Tensor, norm_weigh
     return outs, total.reshape(x.shape), None if normed is None else normed.reshape(x.shape)
 
 
+def quantized_matmul_swiglu(gate: torch.Tensor, up: torch.Tensor, w, scales, biases, group_size: int = 64, bits: int = 4, *,
+                            write_act: bool = False, stream=None, flags: int = 0):
+    """swiglu(gate, up) . dequant(w)^T: the down projection of an MLP reading the gate and up outputs.  Returns
+    (y, act or None); decode rows run as one launch, other shapes need `write_act`."""
+    _need_cuda(gate, up, w, scales, biases)
+    k = gate.shape[-1]
+    m = gate.numel() // k
+    g2, u2 = gate.reshape(m, k).contiguous(), up.reshape(m, k).contiguous()
+    w = _words(w)
+    y = torch.empty((m, w.shape[0]), dtype=g2.dtype, device=g2.device)
+    act = torch.empty_like(g2) if write_act else None
+    check(lib().lisa_cuda_quantized_matmul_swiglu(_stream(stream), g2.data_ptr(), u2.data_ptr(), m, k, w.data_ptr(),
+                                                  scales.contiguous().data_ptr(), biases.contiguous().data_ptr(), w.shape[0], 1,
+                                                  group_size, bits, _dtype_code(g2), y.data_ptr(),
+                                                  None if act is None else act.data_ptr(), flags))
+    return y.reshape(*gate.shape[:-1], w.shape[0]), None if act is None else act.reshape(gate.shape)
+
+
 def quantized_matmul_serial_rows(x, w, scales, biases, transpose: bool = True, group_size: int = 64,
                                  bits: int = 4, *, stream=None) -> torch.Tensor:
     """``ops::quantized_matmul_serial_rows`` (array_ops.rs:500-555)."""

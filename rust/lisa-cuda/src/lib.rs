@@ -260,6 +260,26 @@ pub fn quantized_matmul_addnorm<A: DeviceArray>(stream: Stream, x: &A, r: &A, no
     Ok((ys, sum, normed))
 }
 
+/// SwiGLU in front of a linear: `swiglu(gate, up) . dequant(w)^T` (the down projection of an MLP; rounding points of
+/// crates/lisa-mlx/src/shaders/common/exact_header.metal:2-11).  Returns `(y, act)`; `write_act = false` is accepted
+/// for the decode shapes that run as one launch.
+#[allow(clippy::too_many_arguments)]
+pub fn quantized_matmul_swiglu<A: DeviceArray>(stream: Stream, gate: &A, up: &A, w: &A, scales: &A, biases: &A, group_size: i32,
+                                               bits: i32, write_act: bool) -> Result<(A, Option<A>)> {
+    let k = *gate.shape().last().unwrap();
+    let m: i64 = gate.shape().iter().product::<i64>() / k;
+    let n = w.shape()[0];
+    let mut y = A::alloc(&[m, n], gate.dtype())?;
+    let mut act = if write_act { Some(A::alloc(&[m, k], gate.dtype())?) } else { None };
+    check(unsafe {
+        sys::lisa_cuda_quantized_matmul_swiglu(stream.0, gate.device_ptr(), up.device_ptr(), m, k, w.device_ptr() as *const u32,
+                                               scales.device_ptr(), biases.device_ptr(), n, 1, group_size, bits,
+                                               gate.dtype().code()?, y.device_ptr_mut(),
+                                               act.as_mut().map_or(std::ptr::null_mut(), |a| a.device_ptr_mut()), sys::LISA_FLAG_PDL)
+    })?;
+    Ok((y, act))
+}
+
 /// `moe_decode::gate_up_act` (crates/lisa-mlx/src/models/qwen4/moe_decode.rs:136-184) without the shared
 /// expert: `x [tokens, hidden]`, `idx [tokens, top_k]`, gate / up `(w [E, inter, hidden*bits/32], scales,
 /// biases)` -> `act [tokens * top_k, inter]`; `xrow` maps slots to rows of `x` (default `slot / top_k`).

@@ -130,6 +130,11 @@ def test_addnorm_rejections(lib):
     assert call(eps=-1.0) == _cabi.ERR_BAD_ARG
     assert call(dtype=2) == _cabi.ERR_UNSUPPORTED
     assert call(nw=8) == _cabi.ERR_MISALIGNED
+    sw = lib.lisa_cuda_quantized_matmul_swiglu
+    assert sw(None, 16, None, 1, 256, 16, 16, 16, 128, 1, 64, 4, 0, 16, None, 0) == _cabi.ERR_BAD_ARG       # no up
+    assert sw(None, 16, 16, 1, 256, 16, 16, 16, 128, 0, 64, 4, 0, 16, None, 0) == _cabi.ERR_UNSUPPORTED   # transpose
+    assert sw(None, 16, 24, 1, 256, 16, 16, 16, 128, 1, 64, 4, 0, 16, None, 0) == _cabi.ERR_MISALIGNED
+    assert sw(None, 16, 16, 1, 256, 16, 16, None, 128, 1, 64, 4, 0, 16, None, 0) == _cabi.ERR_BAD_ARG     # affine biases required
     f = lib.lisa_cuda_add_rmsnorm
     assert f(None, 16, 16, 16, 1e-6, 1, 12, 0, 16, 16) == _cabi.ERR_BAD_ARG        # k % 8
     assert f(None, 16, 16, 16, 1e-6, 1, 64, 0, 16, None) == _cabi.ERR_BAD_ARG

@@ -102,3 +102,43 @@ def test_addnorm_unfused_shapes(cuda):
         with pytest.raises(_cabi.LisaError) as e:
             ops.quantized_matmul_addnorm(tx, tr, tw, EPS, dl, gs, 4, write_norm=False)
         assert e.value.code == _cabi.ERR_WORKSPACE
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+@pytest.mark.parametrize("m,k,n", [(1, 9728, 2560), (3, 1024, 512), (8, 17408, 5120), (1, 768, 2048)])
+def test_fused_swiglu_in_front_of_the_down_projection(cuda, m, k, n, bits):
+    """One launch for SwiGLU + linear on decode rows: the activation rows it writes equal the swiglu kernel's bit for
+    bit, and the output equals the plain matmul on them (same kernel, same activation bits)."""
+    rng = np.random.default_rng(m + k + n + bits)
+    g = O.f32_to_bf16(rng.normal(0, 2, size=(m, k)).astype(np.float32))
+    u = O.f32_to_bf16(rng.normal(0, 2, size=(m, k)).astype(np.float32))
+    a, b, c = util.affine_weights(rng, n, k, bits, 64)
+    tw, ts, tb = dev_u32(a, cuda), dev_bf16(b, cuda), dev_bf16(c, cuda)
+    tg, tu = dev_bf16(g, cuda), dev_bf16(u, cuda)
+    y, act = ops.quantized_matmul_swiglu(tg, tu, tw, ts, tb, 64, bits, write_act=True)
+    ref_act = ops.swiglu(tg, tu)
+    assert torch.equal(act, ref_act)
+    assert util.bf16_ulp_distance(host_bf16_bits(act), O.swiglu_bf16(g, u)) <= 1   # expf: host libm against the device
+    assert torch.equal(y, ops.quantized_matmul(ref_act, tw, ts, tb, True, 64, bits))
+    err, l2 = util.parity(O.bf16_to_f32(host_bf16_bits(y)),
+                          O.affine_matmul(host_bf16_bits(act), a, b, c, 64, bits, round_weight_bf16=False, f64=True))
+    assert err <= 1e-2, (err, l2)
+    y2, none = ops.quantized_matmul_swiglu(tg, tu, tw, ts, tb, 64, bits)
+    assert none is None and torch.equal(y2, y)
+    assert ops.device_status() == 0
+
+
+def test_swiglu_unfused_shapes(cuda):
+    rng = np.random.default_rng(3)
+    m, k, n = 100, 1024, 256
+    g = O.f32_to_bf16(rng.normal(0, 2, size=(m, k)).astype(np.float32))
+    u = O.f32_to_bf16(rng.normal(0, 2, size=(m, k)).astype(np.float32))
+    a, b, c = util.affine_weights(rng, n, k, 4, 64)
+    tw, ts, tb = dev_u32(a, cuda), dev_bf16(b, cuda), dev_bf16(c, cuda)
+    tg, tu = dev_bf16(g, cuda), dev_bf16(u, cuda)
+    y, act = ops.quantized_matmul_swiglu(tg, tu, tw, ts, tb, write_act=True)
+    assert torch.equal(act, ops.swiglu(tg, tu))
+    assert torch.equal(y, ops.quantized_matmul(act, tw, ts, tb, True, 64, 4))
+    with pytest.raises(_cabi.LisaError) as e:
+        ops.quantized_matmul_swiglu(tg, tu, tw, ts, tb)
+    assert e.value.code == _cabi.ERR_WORKSPACE

@@ -45,7 +45,7 @@ typedef enum lisa_status {
 typedef enum lisa_dtype { LISA_BF16 = 0, LISA_F16 = 1, LISA_F32 = 2 } lisa_dtype;
 
 /* GGML tensor type ids, crates/lisa-gguf/src/lib.rs:24-32. */
-typedef enum lisa_gguf_format { LISA_GGUF_Q2_K = 10, LISA_GGUF_Q4_K = 12 } lisa_gguf_format;
+typedef enum lisa_gguf_format { LISA_GGUF_Q2_K = 10, LISA_GGUF_Q4_K = 12, LISA_GGUF_Q5_K = 13 } lisa_gguf_format;
 
 /* Dispatch overrides for lisa_cuda_quantized_matmul_ex. */
 enum {

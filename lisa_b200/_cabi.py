@@ -22,7 +22,7 @@ ERR_WORKSPACE = -6
 ERR_LIMIT = -7
 
 BF16, F16, F32 = 0, 1, 2
-GGUF_Q2_K, GGUF_Q4_K = 10, 12
+GGUF_Q2_K, GGUF_Q4_K, GGUF_Q5_K = 10, 12, 13
 
 FLAG_NONE = 0
 FLAG_FORCE_QMV = 1 << 0

@@ -439,6 +439,7 @@ static int gguf_geometry(const char *op, int format, int64_t rows, int64_t row_b
     std::string name(op);
     if (format == LISA_GGUF_Q2_K) *block_bytes = 84;
     else if (format == LISA_GGUF_Q4_K) *block_bytes = 144;
+    else if (format == LISA_GGUF_Q5_K) *block_bytes = 176;
     else return fail(LISA_ERR_UNSUPPORTED, name + ": unsupported GGUF block format");
     // deepseek41.rs:50-65
     if (rows <= 0 || row_bytes <= 0 || rows % 8 != 0 || row_bytes % *block_bytes != 0)
@@ -485,7 +486,7 @@ int lisa_cuda_gguf_packed_matvec_allgather(lisa_stream_t stream, int format, con
 }
 
 size_t lisa_cuda_gguf_packed_matmul_workspace_bytes(int64_t tokens, int64_t row_bytes, int format) {
-    const int block = (format == LISA_GGUF_Q2_K) ? 84 : 144;
+    const int block = (format == LISA_GGUF_Q2_K) ? 84 : (format == LISA_GGUF_Q5_K) ? 176 : 144;
     if (tokens < 1 || row_bytes < block) return 0;
     return qmm_gguf_workspace_bytes(tokens, row_bytes / block * 256);
 }

@@ -75,6 +75,53 @@ __device__ __forceinline__ void q4k_row(const uint8_t *__restrict__ wrow, const 
     }
 }
 
+// Q5_K (crates/lisa-gguf/src/quant.rs:161-182; replaces lisa_gguf_q5_K_mv): the Q4_K block with a fifth bit per
+// element: {d, dmin, 12 scale/min bytes, qh[32], qs[128]}; element j of group g is the nibble (g % 2) of
+// qs[(g / 2) * 32 + j] plus 16 when bit g of qh[j] is set.  Same lane layout as q4k_row: lane = (pair of groups,
+// four consecutive elements).
+template <int TT>
+__device__ __forceinline__ void q5k_row(const uint8_t *__restrict__ wrow, const float *const (&xr)[TT], int nblocks,
+                                        int lane, float (&acc)[TT]) {
+    const int pg = lane >> 3;
+    const int l0 = (lane & 7) * 4;
+#pragma unroll(TT == 1 ? 4 : 2)
+    for (int ib = 0; ib < nblocks; ++ib) {
+        const uint8_t *blk = wrow + static_cast<size_t>(ib) * 176;
+        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+        const uint32_t qh = __ldg(reinterpret_cast<const uint32_t *>(blk + 16 + l0));
+        const uint32_t qs = __ldg(reinterpret_cast<const uint32_t *>(blk + 48) + lane);
+        const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+        float sc[2], mn[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int g = 2 * pg + h, sh = 8 * (g & 3);
+            const uint32_t b0 = (hdr.y >> sh) & 255u, b1 = (hdr.z >> sh) & 255u, b2 = (hdr.w >> sh) & 255u;
+            const uint32_t s = (g < 4) ? (b0 & 63u) : ((b2 & 15u) | ((b0 >> 6) << 4));
+            const uint32_t m = (g < 4) ? (b1 & 63u) : ((b2 >> 4) | ((b1 >> 6) << 4));
+            sc[h] = d * static_cast<float>(s);
+            mn[h] = dmin * static_cast<float>(m);
+        }
+        float ql[4], qhi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t hb = qh >> (8 * j);  // byte qh[l0 + j]
+            ql[j] = static_cast<float>(((qs >> (8 * j)) & 15u) + (((hb >> (2 * pg)) & 1u) << 4));
+            qhi[j] = static_cast<float>(((qs >> (8 * j + 4)) & 15u) + (((hb >> (2 * pg + 1)) & 1u) << 4));
+        }
+        const int e_lo = ib * 256 + (2 * pg) * 32 + l0;
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            const float4 xl = __ldg(reinterpret_cast<const float4 *>(xr[t] + e_lo));
+            const float4 xh = __ldg(reinterpret_cast<const float4 *>(xr[t] + e_lo + 32));
+            const float dl = ql[0] * xl.x + ql[1] * xl.y + ql[2] * xl.z + ql[3] * xl.w;
+            const float dh = qhi[0] * xh.x + qhi[1] * xh.y + qhi[2] * xh.z + qhi[3] * xh.w;
+            const float sl = (xl.x + xl.y) + (xl.z + xl.w);
+            const float sh = (xh.x + xh.y) + (xh.z + xh.w);
+            acc[t] += (sc[0] * dl - mn[0] * sl) + (sc[1] * dh - mn[1] * sh);
+        }
+    }
+}
+
 template <int TT>
 __device__ __forceinline__ void q2k_row(const uint8_t *__restrict__ wrow, const float *const (&xr)[TT], int nblocks,
                                         int lane, float (&acc)[TT]) {
@@ -151,6 +198,7 @@ __global__ void __launch_bounds__(256) gguf_matvec_kernel(const GgufParams p) {
 #pragma unroll
     for (int t = 0; t < TT; ++t) acc[t] = 0.f;
     if (FORMAT == LISA_GGUF_Q4_K) q4k_row<TT>(wrow, xr, p.blocks_per_row, lane, acc);
+    else if (FORMAT == LISA_GGUF_Q5_K) q5k_row<TT>(wrow, xr, p.blocks_per_row, lane, acc);
     else q2k_row<TT>(wrow, xr, p.blocks_per_row, lane, acc);
 #pragma unroll
     for (int t = 0; t < TT; ++t) {
@@ -163,7 +211,7 @@ __global__ void __launch_bounds__(256) gguf_matvec_kernel(const GgufParams p) {
 
 int gguf_matvec(cudaStream_t stream, int format, const uint8_t *w, int64_t experts, int64_t rows, int64_t row_bytes,
                 const float *x, int64_t tokens, int64_t slots, const int32_t *ids, int64_t top_k, float *y) {
-    const int block_bytes = (format == LISA_GGUF_Q2_K) ? 84 : 144;
+    const int block_bytes = (format == LISA_GGUF_Q2_K) ? 84 : (format == LISA_GGUF_Q5_K) ? 176 : 144;
     if ((reinterpret_cast<uintptr_t>(w) & 15u) != 0)
         return fail(LISA_ERR_MISALIGNED, "gguf matvec: weights must be 16-byte aligned");
     GgufParams p{};
@@ -180,19 +228,23 @@ int gguf_matvec(cudaStream_t stream, int format, const uint8_t *w, int64_t exper
     p.top_k = static_cast<int>(top_k);
     if ((rows + 7) / 8 > 65535) return fail(LISA_ERR_LIMIT, "gguf matvec: more than 524280 rows");
     const unsigned gy = static_cast<unsigned>((rows + 7) / 8);
-    if (ids) {
-        const int64_t z = tokens * top_k;
-        dim3 grid(static_cast<unsigned>(z), gy);
-        if (format == LISA_GGUF_Q4_K) gguf_matvec_kernel<LISA_GGUF_Q4_K, 1><<<grid, 256, 0, stream>>>(p);
-        else gguf_matvec_kernel<LISA_GGUF_Q2_K, 1><<<grid, 256, 0, stream>>>(p);
-    } else if (tokens == 1) {
-        dim3 grid(1, gy);
-        if (format == LISA_GGUF_Q4_K) gguf_matvec_kernel<LISA_GGUF_Q4_K, 1><<<grid, 256, 0, stream>>>(p);
-        else gguf_matvec_kernel<LISA_GGUF_Q2_K, 1><<<grid, 256, 0, stream>>>(p);
+    dim3 grid;
+    int tt = 1;
+    if (ids) grid = dim3(static_cast<unsigned>(tokens * top_k), gy);
+    else if (tokens == 1) grid = dim3(1, gy);
+    else {
+        grid = dim3(static_cast<unsigned>((tokens + 3) / 4), gy);
+        tt = 4;
+    }
+    if (format == LISA_GGUF_Q4_K) {
+        if (tt == 4) gguf_matvec_kernel<LISA_GGUF_Q4_K, 4><<<grid, 256, 0, stream>>>(p);
+        else gguf_matvec_kernel<LISA_GGUF_Q4_K, 1><<<grid, 256, 0, stream>>>(p);
+    } else if (format == LISA_GGUF_Q5_K) {
+        if (tt == 4) gguf_matvec_kernel<LISA_GGUF_Q5_K, 4><<<grid, 256, 0, stream>>>(p);
+        else gguf_matvec_kernel<LISA_GGUF_Q5_K, 1><<<grid, 256, 0, stream>>>(p);
     } else {
-        dim3 grid(static_cast<unsigned>((tokens + 3) / 4), gy);
-        if (format == LISA_GGUF_Q4_K) gguf_matvec_kernel<LISA_GGUF_Q4_K, 4><<<grid, 256, 0, stream>>>(p);
-        else gguf_matvec_kernel<LISA_GGUF_Q2_K, 4><<<grid, 256, 0, stream>>>(p);
+        if (tt == 4) gguf_matvec_kernel<LISA_GGUF_Q2_K, 4><<<grid, 256, 0, stream>>>(p);
+        else gguf_matvec_kernel<LISA_GGUF_Q2_K, 1><<<grid, 256, 0, stream>>>(p);
     }
     LISA_CUDA_TRY(cudaGetLastError());
     count_launch();

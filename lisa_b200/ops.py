@@ -16,8 +16,8 @@ import torch
 from . import _cabi
 from ._cabi import LisaError, check, lib
 
-BlockFormat = {"Q2K": _cabi.GGUF_Q2_K, "Q4K": _cabi.GGUF_Q4_K}
-_BLOCK_BYTES = {_cabi.GGUF_Q2_K: 84, _cabi.GGUF_Q4_K: 144}
+BlockFormat = {"Q2K": _cabi.GGUF_Q2_K, "Q4K": _cabi.GGUF_Q4_K, "Q5K": _cabi.GGUF_Q5_K}
+_BLOCK_BYTES = {_cabi.GGUF_Q2_K: 84, _cabi.GGUF_Q4_K: 144, _cabi.GGUF_Q5_K: 176}
 
 
 def _stream(stream=None) -> int:

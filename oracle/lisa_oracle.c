@@ -346,8 +346,20 @@ int oracle_gather_qmm(const uint16_t *x, int64_t rows, int64_t k, const uint32_t
 
 int oracle_gguf_block_bytes(int format) {
     switch (format) { /* lib.rs:46-48 */
+    case ORACLE_GGUF_Q8_0: return 34;
     case ORACLE_GGUF_Q2_K: return 84;
     case ORACLE_GGUF_Q4_K: return 144;
+    case ORACLE_GGUF_Q5_K: return 176;
+    default: return -1;
+    }
+}
+
+int oracle_gguf_block_width(int format) { /* elements of a block, lib.rs:36-70 */
+    switch (format) {
+    case ORACLE_GGUF_Q8_0: return 32;
+    case ORACLE_GGUF_Q2_K:
+    case ORACLE_GGUF_Q4_K:
+    case ORACLE_GGUF_Q5_K: return 256;
     default: return -1;
     }
 }
@@ -393,12 +405,43 @@ static void decode_q4_k(const uint8_t *b, float *out) {
     }
 }
 
+/* quant.rs:161-182 */
+static void decode_q5_k(const uint8_t *b, float *out) {
+    const float d = f16_at(b, 0), min = f16_at(b, 2);
+    const uint8_t *scales = b + 4;
+    for (int group = 0; group < 8; ++group) {
+        uint8_t scale, bias;
+        if (group < 4) {
+            scale = scales[group] & 63;
+            bias = scales[group + 4] & 63;
+        } else {
+            scale = (uint8_t)((scales[group + 4] & 15) | ((scales[group - 4] >> 6) << 4));
+            bias = (uint8_t)((scales[group + 4] >> 4) | ((scales[group] >> 6) << 4));
+        }
+        float ds = d * (float)scale;
+        float ms = min * (float)bias;
+        for (int j = 0; j < 32; ++j) {
+            int low = (b[48 + (group / 2) * 32 + j] >> (4 * (group % 2))) & 15;
+            int high = (b[16 + j] & (1 << group)) ? 16 : 0;
+            out[group * 32 + j] = ds * (float)(low + high) - ms;
+        }
+    }
+}
+
+/* quant.rs:35-40 */
+static void decode_q8_0(const uint8_t *b, float *out) {
+    const float scale = f16_at(b, 0);
+    for (int i = 0; i < 32; ++i) out[i] = scale * (float)(int8_t)b[i + 2];
+}
+
 int oracle_gguf_decode(int format, const uint8_t *packed, int64_t blocks, float *out) {
-    const int bytes = oracle_gguf_block_bytes(format);
+    const int bytes = oracle_gguf_block_bytes(format), width = oracle_gguf_block_width(format);
     if (bytes < 0 || blocks <= 0) return -1;
     for (int64_t i = 0; i < blocks; ++i) {
-        if (format == ORACLE_GGUF_Q2_K) decode_q2_k(packed + i * bytes, out + i * 256);
-        else decode_q4_k(packed + i * bytes, out + i * 256);
+        if (format == ORACLE_GGUF_Q2_K) decode_q2_k(packed + i * bytes, out + i * width);
+        else if (format == ORACLE_GGUF_Q4_K) decode_q4_k(packed + i * bytes, out + i * width);
+        else if (format == ORACLE_GGUF_Q5_K) decode_q5_k(packed + i * bytes, out + i * width);
+        else decode_q8_0(packed + i * bytes, out + i * width);
     }
     return 0;
 }
@@ -417,7 +460,8 @@ uint64_t oracle_gguf_reference_hash(int format) {
     if (bytes < 0) return 0;
     uint32_t state = 0x12345678u;
     uint64_t hash = 0xcbf29ce484222325ull;
-    uint8_t packed[144];
+    const int width = oracle_gguf_block_width(format);
+    uint8_t packed[176];
     float decoded[256];
     for (int block = 0; block < 128; ++block) {
         for (int i = 0; i < bytes; ++i) packed[i] = (uint8_t)xorshift_byte(&state);
@@ -430,11 +474,13 @@ uint64_t oracle_gguf_reference_hash(int format) {
         } else {
             packed[0] = (uint8_t)(scale & 0xff);
             packed[1] = (uint8_t)(scale >> 8);
-            packed[2] = 0x00;
-            packed[3] = 0x24;
+            if (format != ORACLE_GGUF_Q8_0) { /* quant.rs:227-230: the K-quants also get a fixed dmin */
+                packed[2] = 0x00;
+                packed[3] = 0x24;
+            }
         }
         oracle_gguf_decode(format, packed, 1, decoded);
-        for (int i = 0; i < 256; ++i) {
+        for (int i = 0; i < width; ++i) {
             uint32_t u = f32_bits(decoded[i]);
             for (int b = 0; b < 4; ++b) {
                 hash = (hash ^ (uint64_t)((u >> (8 * b)) & 0xffu)) * 0x100000001b3ull;
@@ -482,7 +528,7 @@ static float dot_f32(const float *w, const float *x, int64_t k) {
 static void gguf_rows(void *p, int64_t begin, int64_t end) {
     gguf_ctx *c = (gguf_ctx *)p;
     const int bytes = oracle_gguf_block_bytes(c->format);
-    const int64_t blocks = c->row_bytes / bytes, k = blocks * 256;
+    const int64_t blocks = c->row_bytes / bytes, k = blocks * oracle_gguf_block_width(c->format);
     float *wrow = (float *)malloc(sizeof(float) * (size_t)k);
     for (int64_t r = begin; r < end; ++r) {
         oracle_gguf_decode(c->format, c->w + r * c->row_bytes, blocks, wrow);
@@ -503,7 +549,7 @@ int oracle_gguf_matvec(int format, const uint8_t *w, int64_t rows, int64_t row_b
 static void gguf_expert_slots(void *p, int64_t begin, int64_t end) {
     gguf_ctx *c = (gguf_ctx *)p;
     const int bytes = oracle_gguf_block_bytes(c->format);
-    const int64_t blocks = c->row_bytes / bytes, k = blocks * 256;
+    const int64_t blocks = c->row_bytes / bytes, k = blocks * oracle_gguf_block_width(c->format);
     float *wrow = (float *)malloc(sizeof(float) * (size_t)k);
     for (int64_t z = begin; z < end; ++z) { /* z = token * top_k + slot */
         const int64_t token = z / c->top_k, slot = z % c->top_k;

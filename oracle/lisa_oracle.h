@@ -23,8 +23,10 @@ extern "C" {
 #endif
 
 /* GGML tensor type ids (crates/lisa-gguf/src/lib.rs:24-32). */
+#define ORACLE_GGUF_Q8_0 8
 #define ORACLE_GGUF_Q2_K 10
 #define ORACLE_GGUF_Q4_K 12
+#define ORACLE_GGUF_Q5_K 13
 
 /* ---- scalar conversions (half 2.7.1 semantics: round-to-nearest-even) ---- */
 uint16_t oracle_f32_to_bf16(float v);
@@ -75,6 +77,7 @@ int oracle_gather_qmm(const uint16_t *x, int64_t rows, int64_t k, const uint32_t
 
 /* ---- GGUF K-quants ---- */
 int oracle_gguf_block_bytes(int format);
+int oracle_gguf_block_width(int format);
 /* lisa_gguf::quant::decode, crates/lisa-gguf/src/quant.rs:21-101. */
 int oracle_gguf_decode(int format, const uint8_t *packed, int64_t blocks, float *out);
 /* The frozen-hash test, quant.rs:186-242: returns FNV-1a-64 over 128 blocks. */

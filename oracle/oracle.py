@@ -15,9 +15,12 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liblisa_oracle.so")
 
+Q8_0 = 8
 Q2_K = 10
 Q4_K = 12
-BLOCK_BYTES = {Q2_K: 84, Q4_K: 144}
+Q5_K = 13
+BLOCK_BYTES = {Q8_0: 34, Q2_K: 84, Q4_K: 144, Q5_K: 176}
+BLOCK_WIDTH = {Q8_0: 32, Q2_K: 256, Q4_K: 256, Q5_K: 256}
 
 
 def build(force: bool = False) -> str:
@@ -181,7 +184,7 @@ def gather_qmm(x, w, scales, biases, ids, group_size: int, bits: int,
 def gguf_decode(fmt: int, packed) -> np.ndarray:
     packed = np.ascontiguousarray(packed, dtype=np.uint8)
     blocks = packed.size // BLOCK_BYTES[fmt]
-    out = np.empty(blocks * 256, dtype=np.float32)
+    out = np.empty(blocks * BLOCK_WIDTH[fmt], dtype=np.float32)
     _chk(lib().oracle_gguf_decode(fmt, _p(packed), _i64(blocks), _p(out)), "gguf_decode")
     return out
 

@@ -166,23 +166,26 @@ pub fn gather_qmm<A: DeviceArray>(stream: Stream, x: &A, w: &A, scales: &A, bias
     Ok(y)
 }
 
-/// `deepseek41::BlockFormat`, crates/lisa-mlx/src/models/deepseek41.rs:23-44 (the two formats on this path).
+/// `deepseek41::BlockFormat`, crates/lisa-mlx/src/models/deepseek41.rs:23-44 (the formats on this path).
 #[derive(Clone, Copy, Debug, PartialEq, Eq)]
 pub enum BlockFormat {
     Q2K,
     Q4K,
+    Q5K,
 }
 impl BlockFormat {
     fn code(self) -> c_int {
         match self {
             BlockFormat::Q2K => sys::LISA_GGUF_Q2_K,
             BlockFormat::Q4K => sys::LISA_GGUF_Q4_K,
+            BlockFormat::Q5K => sys::LISA_GGUF_Q5_K,
         }
     }
     pub fn block_bytes(self) -> i64 {
         match self {
             BlockFormat::Q2K => 84,
             BlockFormat::Q4K => 144,
+            BlockFormat::Q5K => 176,
         }
     }
 }

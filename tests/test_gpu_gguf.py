@@ -220,3 +220,44 @@ def test_expert_form_random_blocks(cuda, name, fmt):
         err, l2 = util.parity(y[0, j], truth)
         assert err <= 1e-4 and l2 <= 1e-5, (j, err, l2)
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("width", [256, 1280, 5120])
+def test_q5k_dense_and_expert_forms_are_exact_on_dyadic_inputs(cuda, width):
+    """Q5_K (quant.rs:161-182): the warp-per-row kernel on the reference's dyadic construction, dense with 1 and 3
+    tokens and the expert form with ids outside the table."""
+    fmt, name = O.Q5_K, "Q5K"
+    rows = 16
+    blocks = O.gguf_dyadic_blocks(fmt, width * rows // 256)
+    w = blocks.reshape(rows, -1)
+    for tokens in (1, 3):
+        x = O.gguf_dyadic_inputs(tokens * width).reshape(tokens, width)
+        y = ops.packed_matvec(name, dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
+        assert np.array_equal(y, O.gguf_matvec(fmt, w, x))
+    experts, tokens, top_k = 12, 2, 4
+    eb = O.gguf_dyadic_blocks(fmt, width * 8 * experts // 256).reshape(experts, 8, -1)
+    ids = np.array([[0, 5, -1, 11], [experts, 3, 3, 7]], dtype=np.int32)
+    x = O.gguf_dyadic_inputs(tokens * top_k * width).reshape(tokens, top_k, width)
+    y = ops.expert_matvec(name, dev_u8(eb, cuda), dev_f32(x, cuda), dev_i32(ids, cuda)).cpu().numpy()
+    assert np.array_equal(y, O.gguf_expert_matvec(fmt, eb, x, ids))
+    assert np.all(y[0, 2] == 0.0) and np.all(y[1, 0] == 0.0)
+
+
+def test_q5k_random_blocks(cuda):
+    rng = np.random.default_rng(21)
+    rows, k, tokens = 72, 7168, 5
+    w = rng.integers(0, 256, size=(rows, k // 256, 176), dtype=np.uint8)
+    d = O.f32_to_f16_bits(np.abs(rng.normal(0, 0.01, size=(rows, k // 256, 2))).astype(np.float32))
+    w[..., 0], w[..., 1] = d[..., 0] & 0xFF, d[..., 0] >> 8
+    w[..., 2], w[..., 3] = d[..., 1] & 0xFF, d[..., 1] >> 8
+    w = np.ascontiguousarray(w.reshape(rows, -1))
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    y = ops.packed_matvec("Q5K", dev_u8(w, cuda), dev_f32(x, cuda)).cpu().numpy()
+    dec = O.gguf_decode(O.Q5_K, w).reshape(rows, k).astype(np.float64)
+    err, l2 = util.parity(y, x.astype(np.float64) @ dec.T)
+    assert err <= 1e-4 and l2 <= 1e-5, (err, l2)
+    # the tensor-core product has no Q5_K decoder: many tokens run as matvecs and give the same law
+    xm = rng.normal(0, 1, size=(40, k)).astype(np.float32)
+    ym = ops.packed_matmul("Q5K", dev_u8(w, cuda), dev_f32(xm, cuda)).cpu().numpy()
+    err, l2 = util.parity(ym, xm.astype(np.float64) @ dec.T)
+    assert err <= 1e-4 and l2 <= 1e-5, (err, l2)

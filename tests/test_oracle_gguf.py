@@ -5,16 +5,17 @@ import pytest
 from oracle import oracle as O
 
 
-# Frozen in crates/lisa-gguf/src/quant.rs:197-198 from the unmodified GGML C dequantizers.
-REFERENCE_HASHES = {O.Q2_K: 0x92F0E7A5DAF379E9, O.Q4_K: 0xA8FD5258D144ADD5}
+# Frozen in crates/lisa-gguf/src/quant.rs:195-198 from the unmodified GGML C dequantizers.
+REFERENCE_HASHES = {O.Q2_K: 0x92F0E7A5DAF379E9, O.Q4_K: 0xA8FD5258D144ADD5, O.Q5_K: 0xF8A0E7F3F1B1AEE0,
+                    O.Q8_0: 0xC0087397958E8331}
 
 
-@pytest.mark.parametrize("fmt", [O.Q2_K, O.Q4_K])
+@pytest.mark.parametrize("fmt", [O.Q2_K, O.Q4_K, O.Q5_K, O.Q8_0])
 def test_block_decoders_match_reference_hashes(fmt):
     assert O.gguf_reference_hash(fmt) == REFERENCE_HASHES[fmt]
 
 
-@pytest.mark.parametrize("fmt", [O.Q2_K, O.Q4_K])
+@pytest.mark.parametrize("fmt", [O.Q2_K, O.Q4_K, O.Q5_K])
 @pytest.mark.parametrize("width", [256, 1280, 2304, 5120, 8192])
 def test_dyadic_dot_is_exact(fmt, width):
     """kernel_tests.rs:178-210: with d=0x1800, dmin=0x1400 and x in {-1/8,0,1/8} every partial sum

@@ -232,7 +232,9 @@ int lisa_cuda_gather_qmm(lisa_stream_t stream, const void *x, int64_t rows, int6
 /* deepseek41::packed_matvec(format, weights, input), crates/lisa-mlx/src/models/deepseek41.rs:93-110.
  * w uint8 [rows, row_bytes] of GGUF blocks; x f32 [tokens, K], K = row_bytes/block*256;
  * y f32 [tokens, rows].  Same limits: rows % 8 == 0, row_bytes % block == 0,
- * 1 <= tokens <= 65535 (deepseek41.rs:50-65,100-101). */
+ * 1 <= tokens <= 65535 (deepseek41.rs:50-65,100-101).  Formats: Q2_K (84-byte blocks), Q4_K (144), Q5_K (176);
+ * one or two tokens of Q4_K and one token of Q2_K (rows of whole 336-byte groups) run through the tensor-memory
+ * kernel, everything else one warp per row; both are exact on inputs whose products and sums are exact. */
 int lisa_cuda_gguf_packed_matvec(lisa_stream_t stream, int format, const uint8_t *w, int64_t rows,
                                  int64_t row_bytes, const float *x, int64_t tokens, float *y);
 
@@ -251,7 +253,7 @@ int lisa_cuda_gguf_packed_matvec_allgather(lisa_stream_t stream, int format, con
 /* The same operator for many tokens (prefill, target-verify: the reference runs these rows as
  * independent matvecs, deepseek41.rs:165-171) with a device workspace from the caller's pool
  * (lisa_cuda_gguf_packed_matmul_workspace_bytes, 16-byte aligned).  With a workspace and 32 tokens
- * or more (Q2_K: row_bytes a multiple of 336) the product runs on the tensor cores: activations and
+ * or more (Q4_K; Q2_K with row_bytes a multiple of 336; not Q5_K) the product runs on the tensor cores: activations and
  * decoded weights each enter as two bf16 planes (value = hi + lo, 16 significant bits), f32
  * accumulate, f32 out; results agree with the matvec to ~1e-4 max-relative, not bit for bit (on
  * the reference's dyadic test inputs they are exact).  Any other case is the matvec above, exactly. */

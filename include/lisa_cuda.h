@@ -82,8 +82,10 @@ int lisa_cuda_clear_device_status(void);
  *   x [m,k] dtype; w uint32 [n, k*bits/32]; scales, biases dtype [n, k/group_size];
  *   y [m,n] dtype.  m >= 1.  Like the reference: transpose must be non-zero and
  *   biases non-null (array_ops.rs:387-392).  bits in {2,4,8}, group_size in
- *   {32,64,128}, dtype LISA_BF16 (8-bit weights, the lm-head case, run on the generic
- *   weight-streaming kernel at every row count).  Dispatch by m mirrors array_ops.rs:405-488:
+ *   {32,64,128}, dtype LISA_BF16, or LISA_F16 / LISA_F32 (x, scales, biases and y all in it, as the
+ *   reference casts them to the promoted dtype, array_ops.rs:398-404; these two, and 8-bit weights -- the
+ *   lm-head case -- run on generic weight-streaming kernels at every row count; the other entry points of
+ *   this header are bf16 only).  Dispatch by m mirrors array_ops.rs:405-488:
  *   up to 8 rows stream the weights once (group size 64: the tensor-memory GEMV; other group sizes: the
  *   bf16 mma.sync or the generic kernel), more rows run the tcgen05 GEMM.
  *   Numerics of the group-64 GEMV: products and sums are exact integers, but the activations of a (row of

@@ -19,7 +19,7 @@ OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "liblisa_cuda.so")
 
 SOURCES = ["api.cu", "qmv_affine.cu", "qmv_tc.cu", "qmv_i8.cu", "qmm_affine.cu", "dequantize.cu", "gather_qmm.cu", "gguf_matvec.cu",
-           "moe.cu", "moe_decode.cu", "norm.cu", "ep.cu", "tensor_map.cu", "files.cpp"]
+           "moe.cu", "moe_decode.cu", "norm.cu", "typed.cu", "ep.cu", "tensor_map.cu", "files.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 

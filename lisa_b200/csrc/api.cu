@@ -54,7 +54,7 @@ int max_smem_optin() { return device_info().smem_optin > 0 ? device_info().smem_
 
 static int check_affine(const char *op, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
                         const void *biases, int64_t n, int group_size, int bits, int dtype, const void *y,
-                        bool allow8 = false) {
+                        bool allow8 = false, bool any_dtype = false) {
     std::string name(op);
     if (!biases) return fail(LISA_ERR_BAD_ARG, name + ": affine biases required");
     if (!x || !w || !scales || !y) return fail(LISA_ERR_BAD_ARG, name + ": null pointer");
@@ -63,7 +63,8 @@ static int check_affine(const char *op, const void *x, int64_t m, int64_t k, con
         return fail(LISA_ERR_UNSUPPORTED, name + (allow8 ? ": bits must be 2, 4 or 8" : ": bits must be 2 or 4"));
     if (group_size != 32 && group_size != 64 && group_size != 128)
         return fail(LISA_ERR_UNSUPPORTED, name + ": group_size must be 32, 64 or 128");
-    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, name + ": unsupported compute dtype (bf16 only)");
+    if (dtype != LISA_BF16 && !(any_dtype && (dtype == LISA_F16 || dtype == LISA_F32)))
+        return fail(LISA_ERR_UNSUPPORTED, name + (any_dtype ? ": unsupported compute dtype" : ": unsupported compute dtype (bf16 only)"));
     if (k % group_size != 0) return fail(LISA_ERR_BAD_ARG, name + ": k is not a multiple of group_size");
     if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30) || m * n > (1ll << 40) || n * k > (1ll << 42))
         return fail(LISA_ERR_OVERFLOW, name + ": shape too large");
@@ -100,8 +101,14 @@ static int quantized_matmul_impl(cudaStream_t stream, const void *x, int64_t m, 
                                  const void *scales, const void *biases, int64_t n, int transpose, int group_size,
                                  int bits, int dtype, void *y, unsigned flags) {
     if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: only transpose=true supported");
-    int rc = check_affine("quantized_matmul", x, m, k, w, scales, biases, n, group_size, bits, dtype, y, true);
+    int rc = check_affine("quantized_matmul", x, m, k, w, scales, biases, n, group_size, bits, dtype, y, true, true);
     if (rc != LISA_OK) return rc;
+    if (dtype != LISA_BF16) {
+        // f16 / f32 activations, scales and biases (array_ops.rs:398-404): the generic kernel for every row count
+        if (flags & (LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV | LISA_FLAG_FORCE_QMV_TC | LISA_FLAG_FORCE_QMV_I8))
+            return fail(LISA_ERR_UNSUPPORTED, "quantized_matmul: f16 and f32 run on the generic kernel only");
+        return qmv_typed(stream, dtype, x, m, k, w, scales, biases, n, group_size, bits, y);
+    }
     if (bits == 8) {
         // 8-bit weights (lm heads): the generic weight-streaming kernel for every row count
         if (flags & (LISA_FLAG_FORCE_QMM | LISA_FLAG_FORCE_QMV_TC | LISA_FLAG_FORCE_QMV_I8))
@@ -370,11 +377,12 @@ int lisa_cuda_dequantize(lisa_stream_t stream, const uint32_t *w, const void *sc
     if (bits != 2 && bits != 4 && bits != 8) return fail(LISA_ERR_UNSUPPORTED, "dequantize: bits must be 2, 4 or 8");
     if (group_size != 32 && group_size != 64 && group_size != 128)
         return fail(LISA_ERR_UNSUPPORTED, "dequantize: group_size must be 32, 64 or 128");
-    if (dtype != LISA_BF16) return fail(LISA_ERR_UNSUPPORTED, "dequantize: unsupported dtype (bf16 only)");
+    if (dtype != LISA_BF16 && dtype != LISA_F16 && dtype != LISA_F32) return fail(LISA_ERR_UNSUPPORTED, "dequantize: unsupported dtype");
     if (k % group_size != 0) return fail(LISA_ERR_BAD_ARG, "dequantize: k is not a multiple of group_size");
     if (rows * k > (1ll << 42)) return fail(LISA_ERR_OVERFLOW, "dequantize: shape too large");
     if (!aligned16(w) || !aligned16(scales) || !aligned16(biases) || !aligned16(out))
         return fail(LISA_ERR_MISALIGNED, "dequantize: pointers must be 16-byte aligned");
+    if (dtype != LISA_BF16) return dequantize_typed(static_cast<cudaStream_t>(stream), dtype, w, scales, biases, rows, k, group_size, bits, out);
     return dequantize_affine(static_cast<cudaStream_t>(stream), w, scales, biases, rows, k, group_size, bits, out);
 }
 

@@ -38,6 +38,11 @@ int qmv_tc_multi(cudaStream_t stream, const void *x, int64_t m, int64_t k, int c
                  const void *const *scales, const void *const *biases, const int64_t *n, int group_size, int bits,
                  void *const *y, unsigned flags, int world = 0, const int64_t *n_total = nullptr,
                  const int64_t *col0 = nullptr, const TcNormArgs *norm = nullptr);
+// f16 / f32 compute dtypes (typed.cu): generic kernels, any m
+int qmv_typed(cudaStream_t stream, int dtype, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,
+              const void *biases, int64_t n, int group_size, int bits, void *y);
+int dequantize_typed(cudaStream_t stream, int dtype, const uint32_t *w, const void *scales, const void *biases, int64_t rows,
+                     int64_t k, int group_size, int bits, void *out);
 // bf16(x + r) and rms_norm of it times w, as a kernel of its own (the unfused form)
 int add_rmsnorm(cudaStream_t stream, const void *x, const void *residual, const void *weight, float eps, int64_t m, int64_t k,
                 void *sum, void *normed);

@@ -62,7 +62,7 @@ def test_quantized_matmul_rejections_mirror_the_reference(lib):
     assert "affine biases required" in _cabi.last_error()
     assert _qmm(lib, bits=3) == _cabi.ERR_UNSUPPORTED
     assert _qmm(lib, gs=48) == _cabi.ERR_UNSUPPORTED
-    assert _qmm(lib, dtype=2) == _cabi.ERR_UNSUPPORTED
+    assert _qmm(lib, dtype=3) == _cabi.ERR_UNSUPPORTED   # bf16, f16 and f32 are the compute dtypes
     assert _qmm(lib, k=96) == _cabi.ERR_BAD_ARG  # not a multiple of the group size
     assert _qmm(lib, m=0) == _cabi.ERR_BAD_ARG
     assert _qmm(lib, x=8) == _cabi.ERR_MISALIGNED

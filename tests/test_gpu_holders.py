@@ -116,3 +116,33 @@ def test_gguf_file_to_matvec(cuda, tmp_path, fmt, kind, name):
     ye = ops.expert_matvec(name, we, dev_f32(xe, cuda), torch.from_numpy(ids).to(cuda)).cpu().numpy()
     assert util.parity(ye, O.gguf_expert_matvec(fmt, stack, xe, ids))[0] <= 1e-4
     assert np.all(ye[1, 1] == 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("bits,gs,m", [(4, 64, 1), (2, 64, 5), (8, 32, 2), (4, 128, 40)])
+def test_f16_and_f32_compute_dtypes(cuda, dtype, bits, gs, m):
+    """ops::quantized_matmul casts x, scales and biases to the promoted dtype (array_ops.rs:398-404) and dequantize
+    returns the scales' dtype: f16 and f32 through the generic kernels, against the f64 contraction of
+    q * s + b (the matvec law) and the one-rounding dequantize law."""
+    rng = np.random.default_rng(bits + gs + m)
+    n, k = 136, 512
+    w = rng.integers(0, 1 << 32, size=(n, k * bits // 32), dtype=np.uint32)
+    s = np.abs(rng.normal(0, 0.02, size=(n, k // gs))).astype(np.float32)
+    b = rng.normal(0, 0.01, size=(n, k // gs)).astype(np.float32)
+    x = rng.normal(0, 1, size=(m, k)).astype(np.float32)
+    ts, tb, tx = (torch.from_numpy(a).to(cuda).to(dtype) for a in (s, b, x))
+    tw = dev_u32(w, cuda)
+    y = ops.quantized_matmul(tx, tw, ts, tb, True, gs, bits)
+    assert y.dtype == dtype and y.shape == (m, n)
+    # codes, and the values the kernel actually saw (rounded to the dtype)
+    codes = np.stack([(w >> (bits * j)) & ((1 << bits) - 1) for j in range(32 // bits)], axis=-1).reshape(n, k).astype(np.float64)
+    sf, bf, xf = (t.float().cpu().numpy().astype(np.float64) for t in (ts, tb, tx))
+    dense = codes * np.repeat(sf, gs, axis=1) + np.repeat(bf, gs, axis=1)
+    truth = xf @ dense.T
+    err, l2 = util.parity(y.float().cpu().numpy(), truth)
+    assert err <= (2e-3 if dtype == torch.float16 else 2e-5), (err, l2)
+    d = ops.dequantize(tw, ts, tb, gs, bits)
+    assert d.dtype == dtype
+    want = (codes.astype(np.float32) * np.repeat(sf, gs, axis=1).astype(np.float32)).astype(np.float32) + np.repeat(bf, gs, axis=1).astype(np.float32)
+    want_t = torch.from_numpy(want.astype(np.float32)).to(dtype)
+    assert torch.equal(d.cpu(), want_t)   # f32(q) * s rounded, + b rounded, then one cast: bit for bit

@@ -231,6 +231,16 @@ int lisa_cuda_gather_qmm(lisa_stream_t stream, const void *x, int64_t rows, int6
                          int64_t n, int transpose, int group_size, int bits, int sorted_indices,
                          int dtype, void *y, void *workspace, size_t workspace_bytes);
 
+/* The same for one to three linears that share x, the ids, n and k (the gate and up projections of a routed
+ * block, which the reference's prefill path runs as one grouped launch, models/qwen4/prefill_indirect.rs:127-170):
+ * one tile table, and one launch wherever a grouped kernel runs (the matvec form up to eight rows per expert on
+ * average, the GEMM form beyond).  w, scales, biases, y: tables of `count` pointers; the workspace is
+ * lisa_cuda_gather_qmm_workspace_bytes(rows, experts) as for one linear. */
+int lisa_cuda_gather_qmm_siblings(lisa_stream_t stream, const void *x, int64_t rows, int64_t k, int count, const uint32_t *const *w,
+                                  const void *const *scales, const void *const *biases, const int32_t *rhs_indices, int64_t experts,
+                                  int64_t n, int transpose, int group_size, int bits, int sorted_indices, int dtype, void *const *y,
+                                  void *workspace, size_t workspace_bytes);
+
 /* deepseek41::packed_matvec(format, weights, input), crates/lisa-mlx/src/models/deepseek41.rs:93-110.
  * w uint8 [rows, row_bytes] of GGUF blocks; x f32 [tokens, K], K = row_bytes/block*256;
  * y f32 [tokens, rows].  Same limits: rows % 8 == 0, row_bytes % block == 0,

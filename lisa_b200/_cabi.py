@@ -51,6 +51,8 @@ SIGNATURES = {
     "lisa_cuda_dequantize": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp]),
     "lisa_cuda_dequantize_rows": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp]),
     "lisa_cuda_quantize": (_int, [_vp, _vp, _i64, _i64, _int, _int, _int, _vp, _vp, _vp]),
+    "lisa_cuda_gather_qmm_siblings": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _int,
+                                             _vp, _vp, _sz]),
     "lisa_cuda_gather_qmm_workspace_bytes": (_sz, [_i64, _i64]),
     "lisa_cuda_gather_qmm": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _int, _int, _int, _vp, _vp, _sz]),
     "lisa_cuda_gguf_packed_matvec": (_int, [_vp, _int, _vp, _i64, _i64, _vp, _i64, _vp]),

@@ -443,6 +443,29 @@ int lisa_cuda_gather_qmm(lisa_stream_t stream, const void *x, int64_t rows, int6
                              group_size, bits, y, workspace, workspace_bytes);
 }
 
+int lisa_cuda_gather_qmm_siblings(lisa_stream_t stream, const void *x, int64_t rows, int64_t k, int count, const uint32_t *const *w,
+                                  const void *const *scales, const void *const *biases, const int32_t *rhs_indices, int64_t experts,
+                                  int64_t n, int transpose, int group_size, int bits, int sorted_indices, int dtype, void *const *y,
+                                  void *workspace, size_t workspace_bytes) {
+    if (!transpose) return fail(LISA_ERR_UNSUPPORTED, "gather_qmm_siblings: only transpose=true supported");
+    if (!sorted_indices) return fail(LISA_ERR_UNSUPPORTED, "gather_qmm_siblings: only sorted_indices=true supported");
+    if (!rhs_indices) return fail(LISA_ERR_BAD_ARG, "gather_qmm_siblings: rhs_indices required");
+    if (count < 1 || count > 3 || !w || !scales || !biases || !y)
+        return fail(LISA_ERR_BAD_ARG, "gather_qmm_siblings: one to three linears, non-null tables");
+    for (int i = 0; i < count; ++i) {
+        const int rc = check_affine("gather_qmm_siblings", x, rows, k, w[i], scales[i], biases[i], n, group_size, bits, dtype, y[i]);
+        if (rc != LISA_OK) return rc;
+    }
+    if (experts < 1 || experts > (1 << 20)) return fail(LISA_ERR_BAD_ARG, "gather_qmm_siblings: bad expert count");
+    if (experts * n * k > (1ll << 44)) return fail(LISA_ERR_OVERFLOW, "gather_qmm_siblings: shape too large");
+    const size_t need = gather_qmm_workspace_bytes(rows, experts);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return fail(LISA_ERR_WORKSPACE, "gather_qmm_siblings: workspace missing or too small");
+    if (workspace && !aligned16(workspace)) return fail(LISA_ERR_MISALIGNED, "gather_qmm_siblings: workspace must be 16-byte aligned");
+    return gather_qmm_affine_multi(static_cast<cudaStream_t>(stream), x, rows, k, count, w, scales, biases, rhs_indices, experts, n,
+                                   group_size, bits, y, workspace, workspace_bytes);
+}
+
 static int gguf_geometry(const char *op, int format, int64_t rows, int64_t row_bytes, int *block_bytes) {
     std::string name(op);
     if (format == LISA_GGUF_Q2_K) *block_bytes = 84;

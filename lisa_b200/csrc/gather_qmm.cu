@@ -160,6 +160,15 @@ size_t gather_qmm_workspace_bytes(int64_t rows, int64_t experts) {
 int gather_qmm_affine(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
                       const void *scales, const void *biases, const int32_t *ids, int64_t experts, int64_t n,
                       int group_size, int bits, void *y, void *workspace, size_t workspace_bytes) {
+    const uint32_t *ws[1] = {w};
+    const void *ss[1] = {scales}, *bs[1] = {biases};
+    void *ys[1] = {y};
+    return gather_qmm_affine_multi(stream, x, rows, k, 1, ws, ss, bs, ids, experts, n, group_size, bits, ys, workspace, workspace_bytes);
+}
+
+int gather_qmm_affine_multi(cudaStream_t stream, const void *x, int64_t rows, int64_t k, int count, const uint32_t *const *w,
+                            const void *const *scales, const void *const *biases, const int32_t *ids, int64_t experts, int64_t n,
+                            int group_size, int bits, void *const *y, void *workspace, size_t workspace_bytes) {
     // Few rows per expert (decode, short batches): the problem is weight streaming, and the tensor-memory matvec
     // kernel runs one table entry of up to eight rows per CTA, so every live expert is read once.
     const bool have_ws = workspace && workspace_bytes >= gather_qmm_workspace_bytes(rows, experts) && rows < (1ll << 30);
@@ -169,61 +178,68 @@ int gather_qmm_affine(cudaStream_t stream, const void *x, int64_t rows, int64_t 
         const char *v = std::getenv("LISA_GATHER_TC_MIN_ROWS");
         return v ? std::atoll(v) : 24ll;
     }();
-    if (have_ws && rows >= tc_min_rows && rows <= 8 * experts && static_cast<int64_t>(experts) * n < (1ll << 31)) {
-        const int bt = qmv_tc_grouped_rows(rows, experts, k, n, group_size, bits);
-        if (bt > 0) {
-            const int64_t max_tiles = std::min<int64_t>(rows, (rows + bt - 1) / bt + experts);
-            int32_t *tile_count = reinterpret_cast<int32_t *>(workspace);
-            int32_t *tiles = tile_count + 64;
-            gather_tile_table_kernel<<<1, kTableThreads, 0, stream>>>(ids, static_cast<int>(rows), static_cast<int>(experts),
-                                                                     bt, static_cast<int>(n), tiles, tile_count,
-                                                                     reinterpret_cast<uint16_t *>(y));
+    int32_t *tile_count = reinterpret_cast<int32_t *>(workspace);
+    int32_t *tiles = tile_count ? tile_count + 64 : nullptr;  // 256 bytes further: 16-byte aligned int4 entries
+    // the table kernel also zeroes the rows whose ids are outside the table: once per output
+    auto build_table = [&](int bt) -> int {
+        for (int i = 0; i < count; ++i) {
+            gather_tile_table_kernel<<<1, kTableThreads, 0, stream>>>(ids, static_cast<int>(rows), static_cast<int>(experts), bt,
+                                                                     static_cast<int>(n), tiles, tile_count,
+                                                                     reinterpret_cast<uint16_t *>(y[i]));
             LISA_CUDA_TRY(cudaGetLastError());
             count_launch();
-            return qmv_tc_grouped(stream, x, rows, k, w, scales, biases, experts, n, group_size, bits, y, bt, tiles, tile_count,
+        }
+        return LISA_OK;
+    };
+    if (have_ws && rows >= tc_min_rows && rows <= 8 * experts && static_cast<int64_t>(experts) * n < (1ll << 31)) {
+        const int bt = qmv_tc_grouped_rows(rows, experts, k, n, group_size, bits, count);
+        if (bt > 0) {
+            const int64_t max_tiles = std::min<int64_t>(rows, (rows + bt - 1) / bt + experts);
+            const int rc = build_table(bt);
+            if (rc != LISA_OK) return rc;
+            return qmv_tc_grouped(stream, x, rows, k, count, w, scales, biases, experts, n, group_size, bits, y, bt, tiles, tile_count,
                                   max_tiles);
         }
     }
     // Grouped tensor-core GEMM once there are enough rows to fill 16-row tiles; otherwise the warp-per-output
     // kernel.
-    if (workspace && workspace_bytes >= gather_qmm_workspace_bytes(rows, experts) && rows >= 32 && rows < (1ll << 30) &&
-        qmm_affine_supported(rows, k, n, group_size, bits)) {
+    if (have_ws && rows >= 32 && qmm_affine_supported(rows, k, n, group_size, bits)) {
         const int bt = grouped_tile_rows(rows, experts);
         const int64_t max_tiles = std::min<int64_t>(rows, (rows + bt - 1) / bt + experts);
         if (max_tiles <= 65535) {
-            int32_t *tile_count = reinterpret_cast<int32_t *>(workspace);
-            int32_t *tiles = tile_count + 64;  // 256 bytes further: 16-byte aligned int4 entries
-            gather_tile_table_kernel<<<1, kTableThreads, 0, stream>>>(ids, static_cast<int>(rows), static_cast<int>(experts),
-                                                                     bt, static_cast<int>(n), tiles, tile_count,
-                                                                     reinterpret_cast<uint16_t *>(y));
-            LISA_CUDA_TRY(cudaGetLastError());
-            count_launch();
-            return qmm_affine_grouped(stream, x, rows, k, w, scales, biases, experts, n, group_size, bits, y, bt, tiles,
-                                      tile_count, max_tiles);
+            const int rc = build_table(bt);
+            if (rc != LISA_OK) return rc;
+            if (count == 1)
+                return qmm_affine_grouped(stream, x, rows, k, w[0], scales[0], biases[0], experts, n, group_size, bits, y[0], bt, tiles,
+                                          tile_count, max_tiles);
+            return qmm_affine_grouped_multi(stream, x, rows, k, count, w, scales, biases, experts, n, group_size, bits, y, bt, tiles,
+                                            tile_count, max_tiles);
         }
     }
-    GatherParams p{};
-    p.w = w;
-    p.scales = reinterpret_cast<const uint16_t *>(scales);
-    p.biases = reinterpret_cast<const uint16_t *>(biases);
-    p.x = reinterpret_cast<const uint16_t *>(x);
-    p.ids = ids;
-    p.y = reinterpret_cast<uint16_t *>(y);
-    p.n = static_cast<int>(n);
-    p.k = static_cast<int>(k);
-    p.experts = static_cast<int>(experts);
-    p.group_size = group_size;
-    p.words_per_row = static_cast<int>(k * bits / 32);
-    p.groups_per_row = static_cast<int>(k / group_size);
-    p.expert_words = n * p.words_per_row;
-    p.expert_groups = n * p.groups_per_row;
-    const unsigned gx = static_cast<unsigned>((n + 7) / 8);
-    for (int64_t base = 0; base < rows; base += 65535) {
-        const unsigned gy = static_cast<unsigned>(rows - base < 65535 ? rows - base : 65535);
-        if (bits == 4) gather_qmv_kernel<4><<<dim3(gx, gy), 256, 0, stream>>>(p, base);
-        else gather_qmv_kernel<2><<<dim3(gx, gy), 256, 0, stream>>>(p, base);
-        LISA_CUDA_TRY(cudaGetLastError());
-        count_launch();
+    for (int i = 0; i < count; ++i) {
+        GatherParams p{};
+        p.w = w[i];
+        p.scales = reinterpret_cast<const uint16_t *>(scales[i]);
+        p.biases = reinterpret_cast<const uint16_t *>(biases[i]);
+        p.x = reinterpret_cast<const uint16_t *>(x);
+        p.ids = ids;
+        p.y = reinterpret_cast<uint16_t *>(y[i]);
+        p.n = static_cast<int>(n);
+        p.k = static_cast<int>(k);
+        p.experts = static_cast<int>(experts);
+        p.group_size = group_size;
+        p.words_per_row = static_cast<int>(k * bits / 32);
+        p.groups_per_row = static_cast<int>(k / group_size);
+        p.expert_words = n * p.words_per_row;
+        p.expert_groups = n * p.groups_per_row;
+        const unsigned gx = static_cast<unsigned>((n + 7) / 8);
+        for (int64_t base = 0; base < rows; base += 65535) {
+            const unsigned gy = static_cast<unsigned>(rows - base < 65535 ? rows - base : 65535);
+            if (bits == 4) gather_qmv_kernel<4><<<dim3(gx, gy), 256, 0, stream>>>(p, base);
+            else gather_qmv_kernel<2><<<dim3(gx, gy), 256, 0, stream>>>(p, base);
+            LISA_CUDA_TRY(cudaGetLastError());
+            count_launch();
+        }
     }
     return LISA_OK;
 }

@@ -52,10 +52,10 @@ int qmv_tc_gguf_expert(cudaStream_t stream, int format, const uint8_t *w, int64_
                        const float *x, int64_t tokens, int64_t slots, const int32_t *ids, int64_t top_k, float *y);
 // grouped (sorted rows, one expert per table entry) form of the tensor-memory matvec: rows per entry it can take
 // for this shape (0 = unsupported), and the launch over a device tile table {expert, row_begin, row_end, 0}
-int qmv_tc_grouped_rows(int64_t rows, int64_t experts, int64_t k, int64_t n, int group_size, int bits);
-int qmv_tc_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w, const void *scales,
-                   const void *biases, int64_t experts, int64_t n, int group_size, int bits, void *y, int bt,
-                   const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles);
+int qmv_tc_grouped_rows(int64_t rows, int64_t experts, int64_t k, int64_t n, int group_size, int bits, int count = 1);
+int qmv_tc_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, int count, const uint32_t *const *w,
+                   const void *const *scales, const void *const *biases, int64_t experts, int64_t n, int group_size, int bits,
+                   void *const *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles);
 int qmv_tc_gguf(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
                 int64_t tokens, float *y);
 int qmv_tc_gguf_allgather(cudaStream_t stream, int format, const uint8_t *w, int64_t rows, int64_t row_bytes, const float *x,
@@ -93,6 +93,9 @@ int qmm_affine_allgather(cudaStream_t stream, const void *x, int64_t m, int64_t 
 int qmm_affine_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
                        const void *scales, const void *biases, int64_t experts, int64_t n, int group_size, int bits,
                        void *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles);
+int qmm_affine_grouped_multi(cudaStream_t stream, const void *x, int64_t rows, int64_t k, int count, const uint32_t *const *w,
+                             const void *const *scales, const void *const *biases, int64_t experts, int64_t n, int group_size,
+                             int bits, void *const *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles);
 int qmm_device_status();
 int qmm_clear_status();
 // GGUF Q4_K GEMM on the same kernel (bf16 operands: the caller opts in by giving a workspace)
@@ -115,6 +118,10 @@ size_t gather_qmm_workspace_bytes(int64_t rows, int64_t experts);
 int gather_qmm_affine(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w,
                       const void *scales, const void *biases, const int32_t *ids, int64_t experts, int64_t n,
                       int group_size, int bits, void *y, void *workspace, size_t workspace_bytes);
+// the same for `count` sibling linears (one n, one k, one set of ids: gate | up): one table, one launch where a grouped kernel runs
+int gather_qmm_affine_multi(cudaStream_t stream, const void *x, int64_t rows, int64_t k, int count, const uint32_t *const *w,
+                            const void *const *scales, const void *const *biases, const int32_t *ids, int64_t experts, int64_t n,
+                            int group_size, int bits, void *const *y, void *workspace, size_t workspace_bytes);
 
 // gguf_matvec.cu: ids == nullptr selects the dense matvec (experts = slots = top_k = 1).
 int gguf_matvec(cudaStream_t stream, int format, const uint8_t *w, int64_t experts, int64_t rows, int64_t row_bytes,

@@ -335,7 +335,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     if (p.tiles) {
         if (static_cast<int>(blockIdx.y) >= __ldg(p.tile_count)) return;  // whole CTA, before any barrier
         const int4 tile = __ldg(reinterpret_cast<const int4 *>(p.tiles) + blockIdx.y);
-        wrow0 = tile.x * p.n + n0;
+        wrow0 = tile.x * seg_n + n0;  // (sibling linears of a grouped launch have their own [experts * n, k] matrices)
         t0 = tile.y;
         t_end = tile.z;
     }
@@ -822,7 +822,7 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
         p.seg_tile[0] = 0;
         p.seg_n[0] = static_cast<int>(n);
         for (int i = 1; i < nseg; ++i) {
-            rc = make_map_2d(&maps_w.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, seg_w[i], wrow_bytes, static_cast<uint64_t>(seg_n[i]),
+            rc = make_map_2d(&maps_w.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, seg_w[i], wrow_bytes, static_cast<uint64_t>(seg_n[i] * experts),
                              wrow_bytes, 128, kBN);
             if (rc != LISA_OK) return rc;
             p.seg_tile[i] = static_cast<int>(ntiles);
@@ -1053,6 +1053,17 @@ int qmm_affine_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t
                        void *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles) {
     return qmm_launch(stream, x, rows, k, w, scales, biases, n, experts, group_size, bits, y, 0, bt, tiles, tile_count,
                       max_tiles);
+}
+
+// The same over `count` sibling linears (2 or 3, one n: gate | up of a routed block) in one launch.
+int qmm_affine_grouped_multi(cudaStream_t stream, const void *x, int64_t rows, int64_t k, int count, const uint32_t *const *w,
+                             const void *const *scales, const void *const *biases, int64_t experts, int64_t n, int group_size,
+                             int bits, void *const *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles) {
+    if (count < 2 || count > kMaxSeg) return fail(LISA_ERR_UNSUPPORTED, "qmm_affine_grouped_multi: two or three linears per launch");
+    int64_t ns[kMaxSeg];
+    for (int i = 0; i < count; ++i) ns[i] = n;
+    return qmm_launch(stream, x, rows, k, w[0], scales[0], biases[0], n, experts, group_size, bits, y[0], 0, bt, tiles, tile_count,
+                      max_tiles, count, w, scales, biases, ns, y);
 }
 
 }  // namespace lisa

@@ -130,7 +130,7 @@ struct TcParams {
     const int4 *g_tiles;
     const int *g_count;
     int g_ntiles;   // row tiles of one expert
-    int g_n;        // rows of one expert
+    int g_n;        // rows of one expert (sibling linears of a grouped launch share it)
 };
 struct TcMaps {
     CUtensorMap m[kMaxSeg];  // packed rows of every segment
@@ -1351,52 +1351,63 @@ static int qmv_tc_launch(cudaStream_t stream, const void *x, int64_t m, int64_t 
 
 // Grouped form: `rows` sorted rows, expert of row r = the table entry that covers r; entries hold at most
 // `*bt_out` rows (the caller builds the table with that height after asking qmv_tc_grouped_rows).
-static int64_t grouped_live_tiles(int64_t rows, int64_t experts, int64_t n) {
+static int64_t grouped_live_tiles(int64_t rows, int64_t experts, int64_t n, int count) {
     // what the split heuristic sees: the row tiles of the experts that can be live, not the table's capacity
-    return std::max<int64_t>(1, std::min(rows, experts)) * ((n + kRows - 1) / kRows);
+    return std::max<int64_t>(1, std::min(rows, experts)) * ((n + kRows - 1) / kRows) * count;
 }
 
-int qmv_tc_grouped_rows(int64_t rows, int64_t experts, int64_t k, int64_t n, int group_size, int bits) {
+int qmv_tc_grouped_rows(int64_t rows, int64_t experts, int64_t k, int64_t n, int group_size, int bits, int count) {
     TcParams p{};
     int smem = 0, grid = 0, mc = 0;
-    if (n < 1 || n > (1 << 24)) return 0;
-    if (!tc_make_plan(n, k, group_size, bits, 8, p, smem, grid, mc, kWBytes, 0, grouped_live_tiles(rows, experts, n))) return 0;
+    if (n < 1 || n > (1 << 24) || count < 1 || count > kMaxSeg) return 0;
+    if (!tc_make_plan(n, k, group_size, bits, 8, p, smem, grid, mc, kWBytes, 0, grouped_live_tiles(rows, experts, n, count))) return 0;
     return mc;
 }
 
-int qmv_tc_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, const uint32_t *w, const void *scales,
-                   const void *biases, int64_t experts, int64_t n, int group_size, int bits, void *y, int bt,
-                   const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles) {
+// `count` sibling linears (1 to 3, the same n and k: gate | up of a routed block) in one launch: segment i owns the
+// i-th block of max_tiles * ntiles row tiles of the grid, and inside its block the tiles are (entry, row tile).
+int qmv_tc_grouped(cudaStream_t stream, const void *x, int64_t rows, int64_t k, int count, const uint32_t *const *w,
+                   const void *const *scales, const void *const *biases, int64_t experts, int64_t n, int group_size, int bits,
+                   void *const *y, int bt, const int32_t *tiles, const int32_t *tile_count, int64_t max_tiles) {
+    if (count < 1 || count > kMaxSeg) return fail(LISA_ERR_UNSUPPORTED, "qmv_tc_grouped: one to three linears per launch");
     TcMaps maps{};
-    {
-        const int rc = affine_tensor_map(&maps.m[0], w, experts * n, k, bits);
+    for (int i = 0; i < count; ++i) {
+        const int rc = affine_tensor_map(&maps.m[i], w[i], experts * n, k, bits);
         if (rc != LISA_OK) return rc;
     }
     const int64_t ntiles = (n + kRows - 1) / kRows;
     TcParams p{};
     int smem = 0, grid = 0, mc = 0;
-    if (!tc_make_plan(n, k, group_size, bits, 8, p, smem, grid, mc, kWBytes, 0, grouped_live_tiles(rows, experts, n)) || mc != bt)
+    if (!tc_make_plan(n, k, group_size, bits, 8, p, smem, grid, mc, kWBytes, 0, grouped_live_tiles(rows, experts, n, count)) || mc != bt)
         return fail(LISA_ERR_UNSUPPORTED, "qmv_tc_grouped: shape not supported");
-    if (max_tiles * ntiles * p.splits > (1ll << 30)) return fail(LISA_ERR_OVERFLOW, "qmv_tc_grouped: grid too large");
-    p.scales = reinterpret_cast<const uint16_t *>(scales);
-    p.biases = reinterpret_cast<const uint16_t *>(biases);
+    if (max_tiles * ntiles * count * p.splits > (1ll << 30)) return fail(LISA_ERR_OVERFLOW, "qmv_tc_grouped: grid too large");
     p.x = reinterpret_cast<const uint16_t *>(x);
     p.nout = 1;
     p.ldy = static_cast<int>(n);
     p.col0 = 0;
-    p.out[0] = reinterpret_cast<uint16_t *>(y);
     p.n = static_cast<int>(n);
     p.k = static_cast<int>(k);
     p.m = bt;
-    if (p.sc_tma) {
-        const int rc = scale_tensor_maps(maps, 0, scales, biases, experts * n, k / 64, p.sc_box);
-        if (rc != LISA_OK) return rc;
+    p.nseg = count;
+    for (int i = 0; i < count; ++i) {
+        p.seg_tile[i] = static_cast<int>(i * max_tiles * ntiles);
+        p.seg_n[i] = static_cast<int>(n);
+        p.seg_scales[i] = reinterpret_cast<const uint16_t *>(scales[i]);
+        p.seg_biases[i] = reinterpret_cast<const uint16_t *>(biases[i]);
+        p.seg_out[i] = reinterpret_cast<uint16_t *>(y[i]);
+        if (p.sc_tma) {
+            const int rc = scale_tensor_maps(maps, i, scales[i], biases[i], experts * n, k / 64, p.sc_box);
+            if (rc != LISA_OK) return rc;
+        }
     }
+    p.scales = p.seg_scales[0];
+    p.biases = p.seg_biases[0];
+    p.out[0] = p.seg_out[0];
     p.g_tiles = reinterpret_cast<const int4 *>(tiles);
     p.g_count = tile_count;
     p.g_ntiles = static_cast<int>(ntiles);
     p.g_n = static_cast<int>(n);
-    return tc_launch_kernel(stream, bits, maps, p, static_cast<int>(max_tiles * ntiles * p.splits), smem, 0);
+    return tc_launch_kernel(stream, bits, maps, p, static_cast<int>(max_tiles * ntiles * count * p.splits), smem, 0);
 }
 
 int qmv_tc(cudaStream_t stream, const void *x, int64_t m, int64_t k, const uint32_t *w, const void *scales,

@@ -270,6 +270,42 @@ def gather_qmm(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: O
     return y.reshape(*x.shape[:-1], n)
 
 
+def gather_qmm_siblings(x: torch.Tensor, linears, rhs_indices: torch.Tensor, group_size: int = 64, bits: int = 4, *, stream=None,
+                        workspace: Optional[torch.Tensor] = None):
+    """``gather_qmm`` for one to three linears that share x, the sorted ids and their shape (gate | up of a routed
+    block; the grouped gate|up launch of crates/lisa-mlx/src/models/qwen4/prefill_indirect.rs:127-170): `linears`
+    is a sequence of (w [E, N, K*bits/32], scales, biases); returns the list of outputs [rows, N]."""
+    import ctypes as C
+
+    _need_cuda(x, rhs_indices)
+    k = x.shape[-1]
+    rows = x.numel() // k
+    x2 = x.reshape(rows, k).contiguous()
+    count = len(linears)
+    experts, n = linears[0][0].shape[0], linears[0][0].shape[-2]
+    keep, ys = [], []
+    wp, sp, bp, yp = (C.c_void_p * count)(), (C.c_void_p * count)(), (C.c_void_p * count)(), (C.c_void_p * count)()
+    for i, (w, sc, bi) in enumerate(linears):
+        _need_cuda(w, sc, bi)
+        w = _words(w)
+        if w.shape[0] != experts or w.shape[-2] != n:
+            raise LisaError(_cabi.ERR_BAD_ARG, "gather_qmm_siblings: the linears must have one shape")
+        sc, bi = sc.contiguous(), bi.contiguous()
+        y = torch.empty((rows, n), dtype=x2.dtype, device=x2.device)
+        keep.append((w, sc, bi))
+        ys.append(y)
+        wp[i], sp[i], bp[i], yp[i] = w.data_ptr(), sc.data_ptr(), bi.data_ptr(), y.data_ptr()
+    need = lib().lisa_cuda_gather_qmm_workspace_bytes(rows, experts)
+    if workspace is None and need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x2.device)
+    ids = rhs_indices.to(torch.int32).contiguous()
+    check(lib().lisa_cuda_gather_qmm_siblings(_stream(stream), x2.data_ptr(), rows, k, count, wp, sp, bp, ids.data_ptr(), experts, n,
+                                              1, group_size, bits, 1, _dtype_code(x2), yp,
+                                              workspace.data_ptr() if workspace is not None else None,
+                                              workspace.numel() if workspace is not None else 0))
+    return [y.reshape(*x.shape[:-1], n) for y in ys]
+
+
 def _format_code(fmt) -> int:
     return BlockFormat[fmt] if isinstance(fmt, str) else int(fmt)
 

@@ -129,10 +129,9 @@ class SwitchGlu:
             return ops.moe_down_combine(act, idx, weights, d, gs, bits)
         sorted_ids, token_rows, inverse = ops.moe_sort(idx, experts, self.top_k)
         x_sorted = ops.gather_rows(x, token_rows)
-        g = ops.gather_qmm(x_sorted, self.gate.weight, self.gate.scales, self.gate.biases, None, sorted_ids,
-                           True, gs, bits, True)
-        u = ops.gather_qmm(x_sorted, self.up.weight, self.up.scales, self.up.biases, None, sorted_ids,
-                           True, gs, bits, True)
+        # gate and up read the same rows: one tile table, one grouped launch (prefill_indirect.rs:127-170)
+        g, u = ops.gather_qmm_siblings(x_sorted, [(self.gate.weight, self.gate.scales, self.gate.biases),
+                                                  (self.up.weight, self.up.scales, self.up.biases)], sorted_ids, gs, bits)
         act = ops.swiglu(g, u)
         d = ops.gather_qmm(act, self.down.weight, self.down.scales, self.down.biases, None, sorted_ids,
                            True, gs, bits, True)

@@ -223,3 +223,38 @@ def test_decode_path_agrees_with_the_sorted_path(cuda, tokens):
         SwitchGlu.DECODE_SLOTS = old
     f, c = fast.float(), chain.float()
     assert float((f - c).abs().max()) <= 2.0 ** -6 * float(c.abs().max())
+
+
+@pytest.mark.parametrize("rows", [8, 40, 300, 2000])
+def test_gather_qmm_siblings_equals_the_separate_calls(cuda, rows):
+    """gate | up through one table and one grouped launch (the warp-per-output kernel below 24 rows, the grouped
+    matvec up to eight rows per expert, the grouped GEMM beyond) against two gather_qmm calls: the same kernels on
+    the same tiles, ids outside the table included."""
+    rng = np.random.default_rng(60 + rows)
+    experts, n, k = 12, 768, 2048
+    gate = util.affine_weights(rng, n, k, 4, 64, experts=experts)
+    up = util.affine_weights(rng, n, k, 4, 64, experts=experts)
+    ids = np.sort(rng.integers(0, experts, size=rows)).astype(np.int32)
+    ids[0], ids[-1] = -1, experts
+    x = dev_bf16(util.activations(rng, rows, k), cuda)
+    tg = tuple(f(a, cuda) for f, a in zip((dev_u32, dev_bf16, dev_bf16), gate))
+    tu = tuple(f(a, cuda) for f, a in zip((dev_u32, dev_bf16, dev_bf16), up))
+    tid = dev_i32(ids, cuda)
+    before = ops.launch_count()
+    g, u = ops.gather_qmm_siblings(x, [tg, tu], tid)
+    fused_launches = ops.launch_count() - before
+    g2 = ops.gather_qmm(x, *tg, None, tid, True, 64, 4, True)
+    u2 = ops.gather_qmm(x, *tu, None, tid, True, 64, 4, True)
+    # the same products; the matvec form may cut k into other slices for twice the tiles (another f32 summation
+    # order: a bf16 rounding step of the output at most, measured against max(|y|, rms) because sums near zero
+    # have no meaningful ulp), the other two forms give the same bits
+    for a, b in ((g, g2), (u, u2)):
+        if 24 <= rows <= 8 * experts:
+            err, _ = util.parity(a.float().cpu().numpy(), b.float().cpu().numpy())
+            assert err <= 2.0 ** -7, err
+        else:
+            assert torch.equal(a, b)
+    assert torch.all(g[0] == 0) and torch.all(u[-1] == 0)
+    if rows >= 24:
+        assert fused_launches == 3   # a table per output (it zeroes that output's out-of-table rows) and one grouped launch
+    assert ops.device_status() == 0

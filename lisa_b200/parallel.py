@@ -477,8 +477,8 @@ class ExpertParallelMoe:
             ids = self.recv_ids.local[:received]
             s2, rows2, _ = ops.moe_sort(ids, local_e, 1)                     # top_k = 1: rows2 indexes recv_x
             xs = ops.gather_rows(self.recv_x.local[:received], rows2)
-            g = ops.gather_qmm(xs, blk.gate.weight, blk.gate.scales, blk.gate.biases, None, s2, True, gs, bits, True)
-            u = ops.gather_qmm(xs, blk.up.weight, blk.up.scales, blk.up.biases, None, s2, True, gs, bits, True)
+            g, u = ops.gather_qmm_siblings(xs, [(blk.gate.weight, blk.gate.scales, blk.gate.biases),
+                                                (blk.up.weight, blk.up.scales, blk.up.biases)], s2, gs, bits)
             d = ops.gather_qmm(ops.swiglu(g, u), blk.down.weight, blk.down.scales, blk.down.biases, None, s2, True, gs, bits, True)
             _cabi.check(lib.lisa_cuda_ep_return(st, d.data_ptr(), rows2.data_ptr(), received, self.hidden, self.world, self.rank,
                                                 self.matrix.local.data_ptr(), self.back.ptrs(), _cabi.BF16))

@@ -88,52 +88,113 @@ __device__ __forceinline__ int lower_bound_ids(const int32_t *ids, int rows, int
 }
 
 constexpr int kTableThreads = 1024;
+constexpr int kTableOutputs = 4;
 
-__global__ void __launch_bounds__(kTableThreads) gather_tile_table_kernel(const int32_t *ids, int rows, int experts, int bt,
-                                                                          int n, int32_t *tiles, int32_t *tile_count,
-                                                                          uint16_t *y) {
-    __shared__ int scan[kTableThreads];
-    __shared__ int running;
-    const int tid = threadIdx.x;
-    if (tid == 0) running = 0;
+struct TableOutputs {
+    uint16_t *y[kTableOutputs];
+    int count;
+};
+
+// One block.  With at most 1024 experts the run of every expert comes from one coalesced pass over the ids
+// (a run starts where ids[i] != ids[i-1]) and the tile counts are scanned with warp shuffles; with more
+// experts every thread searches its experts' bounds, 1024 experts per trip.  The table never grows past
+// `max_tiles` entries, whatever the ids hold (ids that are not sorted give a wrong table, not a write
+// outside it).
+__global__ void __launch_bounds__(kTableThreads) gather_tile_table_kernel(const int32_t *__restrict__ ids, int rows, int experts,
+                                                                          int bt, int n, int max_tiles, int32_t *tiles,
+                                                                          int32_t *tile_count, TableOutputs out) {
+    __shared__ int begin_s[kTableThreads], end_s[kTableThreads];
+    __shared__ int warp_sum[32];
+    __shared__ int running, first_ok_s, first_bad_s;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool one_pass = experts <= kTableThreads;
+    if (tid == 0) running = 0, first_ok_s = rows, first_bad_s = rows;
+    begin_s[tid] = 0;
+    end_s[tid] = 0;
     __syncthreads();
+    if (one_pass) {
+        for (int i0 = tid; i0 < rows; i0 += 4 * kTableThreads) {  // four rows per trip, their loads in flight together
+            int cur4[4], prev4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * kTableThreads;
+                cur4[j] = i < rows ? __ldg(ids + i) : 0;
+                prev4[j] = (i < rows && i > 0) ? __ldg(ids + i - 1) : 0;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * kTableThreads;
+                if (i >= rows) break;
+                const int cur = cur4[j], prev = prev4[j];
+                const bool head = i == 0;
+                if (head || prev != cur) {
+                    if (cur >= 0 && cur < experts) begin_s[cur] = i;
+                    if (!head && prev >= 0 && prev < experts) end_s[prev] = i;
+                    if (cur >= 0 && (head || prev < 0)) first_ok_s = i;
+                    if (cur >= experts && (head || prev < experts)) first_bad_s = i;
+                }
+                if (i == rows - 1 && cur >= 0 && cur < experts) end_s[cur] = rows;
+            }
+        }
+        __syncthreads();
+    }
     for (int base = 0; base < experts; base += kTableThreads) {
         const int e = base + tid;
         int begin = 0, end = 0;
         if (e < experts) {
-            begin = lower_bound_ids(ids, rows, e);
-            end = lower_bound_ids(ids, rows, e + 1);
+            if (one_pass) {
+                begin = begin_s[tid];
+                end = end_s[tid];
+            } else {
+                begin = lower_bound_ids(ids, rows, e);
+                end = lower_bound_ids(ids, rows, e + 1);
+            }
         }
-        const int mine = (end - begin + bt - 1) / bt;
-        scan[tid] = mine;
+        const int mine = end > begin ? (end - begin + bt - 1) / bt : 0;
+        int inc = mine;  // inclusive scan over the block: warps, then the warp sums
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= off) inc += v;
+        }
+        if (lane == 31) warp_sum[warp] = inc;
         __syncthreads();
-        for (int off = 1; off < kTableThreads; off <<= 1) {  // inclusive Hillis-Steele scan
-            const int v = (tid >= off) ? scan[tid - off] : 0;
-            __syncthreads();
-            scan[tid] += v;
-            __syncthreads();
+        if (warp == 0) {
+            const int w = warp_sum[lane];
+            int winc = w;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, winc, off);
+                if (lane >= off) winc += v;
+            }
+            warp_sum[lane] = winc - w;  // exclusive
         }
-        int at = running + scan[tid] - mine;
-        for (int r = begin; r < end; r += bt, ++at)
+        __syncthreads();
+        int at = running + warp_sum[warp] + inc - mine;
+        for (int r = begin; r < end && at < max_tiles; r += bt, ++at)
             reinterpret_cast<int4 *>(tiles)[at] = make_int4(e, r, min(r + bt, end), 0);
         __syncthreads();
-        if (tid == kTableThreads - 1) running += scan[tid];
+        if (tid == kTableThreads - 1) running += warp_sum[warp] + inc;
         __syncthreads();
     }
-    if (tid == 0) *tile_count = running;
+    if (tid == 0) *tile_count = min(running, max_tiles);
     // rows with ids outside the table: zeros (sorted ids: negatives first, ids >= experts last)
-    const int first_ok = lower_bound_ids(ids, rows, 0);
-    const int first_bad = lower_bound_ids(ids, rows, experts);
+    const int first_ok = one_pass ? first_ok_s : lower_bound_ids(ids, rows, 0);
+    const int first_bad = one_pass ? first_bad_s : lower_bound_ids(ids, rows, experts);
     const int64_t head = static_cast<int64_t>(first_ok) * n;
-    for (int64_t i = tid; i < head; i += kTableThreads) y[i] = 0;
     const int64_t tail0 = static_cast<int64_t>(first_bad) * n, tail1 = static_cast<int64_t>(rows) * n;
-    for (int64_t i = tail0 + tid; i < tail1; i += kTableThreads) y[i] = 0;
+    for (int o = 0; o < out.count; ++o) {
+        uint16_t *y = out.y[o];
+        for (int64_t i = tid; i < head; i += kTableThreads) y[i] = 0;
+        for (int64_t i = tail0 + tid; i < tail1; i += kTableThreads) y[i] = 0;
+    }
 }
 
-// Rows per tile of the grouped GEMM: a CTA costs about the same for any tile up to 256 rows (the dequantization
-// sets its pace) and about 1.3 times that for the 384-row tile, so the tile is as tall as the expert runs allow.
-// Between 256 and 384 the choice goes by the expected number of tiles per expert when the rows spread evenly
-// over the experts (run lengths then scatter around the average with a standard deviation of its root).
+// Rows per tile of the grouped GEMM: up to 256 rows the dequantization sets a CTA's pace, beyond that the MMAs, whose
+// N follows the rows of the tile; a tile table of 384-row tiles therefore costs what its rows cost plus a little
+// (a shallower operand ring), and wins as soon as it saves tiles.  Between 256 and 384 the choice goes by the
+// expected number of tiles per expert when the rows spread evenly over the experts (run lengths then scatter
+// around the average with a standard deviation of its root).
 static int grouped_tile_rows(int64_t rows, int64_t experts) {
     const double avg = static_cast<double>(rows) / static_cast<double>(experts > 0 ? experts : 1);
     if (avg >= 96) {
@@ -143,7 +204,7 @@ static int grouped_tile_rows(int64_t rows, int64_t experts) {
             for (int j = 1; j * bt < avg + 6 * sd; ++j) t += 0.5 * std::erfc((j * bt - avg) / (sd * 1.41421356));
             return t;
         };
-        return tiles(384.0) * 1.3 < tiles(256.0) ? 384 : 256;
+        return tiles(384.0) * 1.1 < tiles(256.0) ? 384 : 256;
     }
     if (avg >= 40) return 128;
     if (avg >= 12) return 64;
@@ -180,12 +241,15 @@ int gather_qmm_affine_multi(cudaStream_t stream, const void *x, int64_t rows, in
     }();
     int32_t *tile_count = reinterpret_cast<int32_t *>(workspace);
     int32_t *tiles = tile_count ? tile_count + 64 : nullptr;  // 256 bytes further: 16-byte aligned int4 entries
-    // the table kernel also zeroes the rows whose ids are outside the table: once per output
-    auto build_table = [&](int bt) -> int {
-        for (int i = 0; i < count; ++i) {
+    // the table kernel also zeroes the rows whose ids are outside the table, in every output
+    auto build_table = [&](int bt, int64_t max_tiles) -> int {
+        for (int i0 = 0; i0 < count; i0 += kTableOutputs) {
+            TableOutputs out{};
+            out.count = std::min(count - i0, kTableOutputs);
+            for (int i = 0; i < out.count; ++i) out.y[i] = reinterpret_cast<uint16_t *>(y[i0 + i]);
             gather_tile_table_kernel<<<1, kTableThreads, 0, stream>>>(ids, static_cast<int>(rows), static_cast<int>(experts), bt,
-                                                                     static_cast<int>(n), tiles, tile_count,
-                                                                     reinterpret_cast<uint16_t *>(y[i]));
+                                                                     static_cast<int>(n), static_cast<int>(max_tiles), tiles,
+                                                                     tile_count, out);
             LISA_CUDA_TRY(cudaGetLastError());
             count_launch();
         }
@@ -195,7 +259,7 @@ int gather_qmm_affine_multi(cudaStream_t stream, const void *x, int64_t rows, in
         const int bt = qmv_tc_grouped_rows(rows, experts, k, n, group_size, bits, count);
         if (bt > 0) {
             const int64_t max_tiles = std::min<int64_t>(rows, (rows + bt - 1) / bt + experts);
-            const int rc = build_table(bt);
+            const int rc = build_table(bt, max_tiles);
             if (rc != LISA_OK) return rc;
             return qmv_tc_grouped(stream, x, rows, k, count, w, scales, biases, experts, n, group_size, bits, y, bt, tiles, tile_count,
                                   max_tiles);
@@ -207,7 +271,7 @@ int gather_qmm_affine_multi(cudaStream_t stream, const void *x, int64_t rows, in
         const int bt = grouped_tile_rows(rows, experts);
         const int64_t max_tiles = std::min<int64_t>(rows, (rows + bt - 1) / bt + experts);
         if (max_tiles <= 65535) {
-            const int rc = build_table(bt);
+            const int rc = build_table(bt, max_tiles);
             if (rc != LISA_OK) return rc;
             if (count == 1)
                 return qmm_affine_grouped(stream, x, rows, k, w[0], scales[0], biases[0], experts, n, group_size, bits, y[0], bt, tiles,

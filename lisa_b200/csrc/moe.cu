@@ -209,12 +209,115 @@ __global__ void __launch_bounds__(kSortChunk) moe_sort_scatter_kernel(const int3
     }
 }
 
+// Scan and scatter in one kernel, for tables small enough that every chunk's block can read all of it
+// from L2 (chunks <= kPlaceChunks): block b sums, per expert, the counts of all chunks (the expert's total)
+// and of the chunks before b, scans the totals over the experts, and places its 256 slots.  One launch and
+// one single-block pass less than hist -> scan -> scatter.
+constexpr int kPlaceChunks = 256;
+
+__global__ void __launch_bounds__(kSortChunk) moe_sort_place_kernel(const int32_t *__restrict__ idx, int slots, int experts,
+                                                                    int top_k, int chunks,
+                                                                    const int32_t *__restrict__ counts,
+                                                                    int32_t *__restrict__ sorted_ids,
+                                                                    int32_t *__restrict__ token_rows,
+                                                                    int32_t *__restrict__ inverse) {
+    extern __shared__ int32_t place_sm[];
+    int32_t *next = place_sm;            // experts: next free position of (expert, this chunk)
+    int32_t *total = place_sm + experts;  // experts: slots of the expert over all chunks
+    __shared__ int32_t valid;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < experts; e += kSortChunk) next[e] = 0, total[e] = 0;
+    __syncthreads();
+    // column sums: thread (g, e) takes the chunks g, g + groups, ... of expert e (coalesced over e)
+    const int groups = experts >= kSortChunk ? 1 : kSortChunk / experts;
+    for (int e0 = 0; e0 < experts; e0 += kSortChunk) {
+        const int g = experts >= kSortChunk ? 0 : tid / experts;
+        const int e = experts >= kSortChunk ? e0 + tid : tid - g * experts;
+        if (e < experts && g < groups) {
+            int all = 0, before = 0;
+            for (int c0 = g; c0 < chunks; c0 += 8 * groups) {  // eight loads in flight
+                int v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int c = c0 + j * groups;
+                    v[j] = c < chunks ? __ldg(counts + static_cast<int64_t>(c) * experts + e) : 0;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    all += v[j];
+                    before += c0 + j * groups < static_cast<int>(blockIdx.x) ? v[j] : 0;
+                }
+            }
+            if (groups == 1) {
+                total[e] = all;
+                next[e] = before;
+            } else {
+                atomicAdd(&total[e], all);
+                atomicAdd(&next[e], before);
+            }
+        }
+    }
+    __syncthreads();
+    // exclusive scan of the totals over the experts (warp 0, 32 experts per trip), added to next[]
+    if (warp == 0) {
+        int run = 0;
+        for (int e0 = 0; e0 < experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int v = e < experts ? total[e] : 0;
+            int inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) inc += n;
+            }
+            if (e < experts) next[e] += run + inc - v;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) valid = run;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0) {  // positions behind the last valid slot: id = experts, token row 0
+        for (int i = valid + tid; i < slots; i += kSortChunk) {
+            sorted_ids[i] = experts;
+            token_rows[i] = 0;
+        }
+    }
+    const int i = blockIdx.x * kSortChunk + tid;
+    const bool live = i < slots;
+    const int e = live ? __ldg(idx + i) : -1;
+    const bool ok = live && e >= 0 && e < experts;
+    for (int wv = 0; wv < kSortChunk / 32; ++wv) {
+        if (warp == wv) {
+            const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+            if (ok) {
+                const int rank = __popc(peers & ((1u << lane) - 1u));
+                const int pos = next[e] + rank;
+                sorted_ids[pos] = e;
+                token_rows[pos] = i / top_k;
+                inverse[i] = pos;
+            } else if (live) {
+                inverse[i] = -1;
+            }
+            __syncwarp();
+            if (ok && (peers >> lane) == 1u) next[e] += __popc(peers);
+        }
+        __syncthreads();
+    }
+}
+
 static int launch_sort(cudaStream_t stream, const int32_t *idx, int64_t slots, int64_t experts, int top_k,
                        int32_t *sorted_ids, int32_t *token_rows, int32_t *inverse, int32_t *counts) {
     const int chunks = static_cast<int>((slots + kSortChunk - 1) / kSortChunk);
     const size_t esm = static_cast<size_t>(experts) * sizeof(int32_t);
     moe_sort_hist_kernel<<<chunks, kSortChunk, esm, stream>>>(idx, static_cast<int>(slots), static_cast<int>(experts), counts);
     LISA_CUDA_TRY(cudaGetLastError());
+    if (chunks <= kPlaceChunks && 2 * esm <= 40 * 1024) {
+        moe_sort_place_kernel<<<chunks, kSortChunk, 2 * esm, stream>>>(idx, static_cast<int>(slots), static_cast<int>(experts),
+                                                                       top_k, chunks, counts, sorted_ids, token_rows, inverse);
+        LISA_CUDA_TRY(cudaGetLastError());
+        count_launch(2);
+        return LISA_OK;
+    }
     moe_sort_scan_kernel<<<1, 1024, esm + sizeof(int32_t), stream>>>(counts, chunks, static_cast<int>(experts),
                                                                       static_cast<int>(slots), sorted_ids, token_rows);
     LISA_CUDA_TRY(cudaGetLastError());

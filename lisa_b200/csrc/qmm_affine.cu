@@ -95,6 +95,10 @@ struct QmmParams {
     int nout, ldy, col0;
     int vec_out;  // every output 16-byte aligned, ldy, col0 and n multiples of 8: whole 16-byte runs of 8 rows
     uint16_t *outs[8];
+    // Persistent form (one k-slice, no all-gather): the grid is one CTA per SM and CTA b takes the tiles
+    // b, b + gridDim.x, ... of the list (token tile major, `ntx` row tiles each, `ntotal` in all).  Barriers,
+    // tensor memory and the rings are set up once; the loads of the next tile run during the epilogue.
+    int persist, ntx, ntotal;
 };
 struct QmmMaps {
     CUtensorMap m[kMaxSeg];
@@ -316,29 +320,50 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint64_t *full = bars, *empty = bars + ST;
     uint64_t *wp_full = bars + 2 * ST, *wp_empty = wp_full + WS;
     uint64_t *acc_full = wp_empty + WS;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    uint64_t *acc_empty = acc_full + 1;  // persistent form: the sixteen epilogue warps have read the accumulator
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
 
     constexpr int KBW = (GGUF == 2) ? 16 : (128 * 8 / BITS) / kBK;  // k-blocks per packed-weight stage: 4 (4-bit), 8 (2-bit), 16 (Q2_K)
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // warp-uniform for the compiler too
-    // the linear this row tile belongs to (one, unless the launch is the sibling form)
-    int xtile = blockIdx.x, seg = 0;
-    if (!GGUF && p.nseg > 1) {
-        seg = (xtile >= p.seg_tile[1]) ? 1 : 0;
-        if (p.nseg > 2 && xtile >= p.seg_tile[2]) seg = 2;
-        xtile -= (seg == 0) ? 0 : (seg == 1) ? p.seg_tile[1] : p.seg_tile[2];
-    }
-    const CUtensorMap *map_w = &maps_w.m[seg];
-    const int seg_n = (seg == 0) ? p.n : (seg == 1) ? p.seg_n[1] : p.seg_n[2];
-    const int n0 = xtile * kBN;
-    int t0 = blockIdx.y * p.bt, t_end = p.m, wrow0 = n0;
-    if (p.tiles) {
-        if (static_cast<int>(blockIdx.y) >= __ldg(p.tile_count)) return;  // whole CTA, before any barrier
-        const int4 tile = __ldg(reinterpret_cast<const int4 *>(p.tiles) + blockIdx.y);
-        wrow0 = tile.x * seg_n + n0;  // (sibling linears of a grouped launch have their own [experts * n, k] matrices)
-        t0 = tile.y;
-        t_end = tile.z;
-    }
+    // Tiles of this CTA: tile (blockIdx.x, blockIdx.y) in the plain form, a strided walk over the list in the
+    // persistent one.
+    const int ntx = p.persist ? p.ntx : static_cast<int>(gridDim.x);
+    const int tile_first = p.persist ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.y * gridDim.x + blockIdx.x);
+    const int tile_step = p.persist ? static_cast<int>(gridDim.x) : 0x40000000;
+    const int tile_total = p.persist ? p.ntotal : tile_first + 1;
+    const int live_y = p.tiles ? __ldg(p.tile_count) : 0x7fffffff;  // grouped form: token tiles in the table
+    if (tile_first / ntx >= live_y) return;  // whole CTA, before any barrier
+    struct Tile {
+        int seg;     // the linear this row tile belongs to (0, unless the launch is the sibling form)
+        int seg_n;   // its rows
+        int n0;      // first weight row of the tile within the linear
+        int t0, t_end;  // tokens
+        int wrow0;   // first row of the packed matrix (grouped: the expert's rows)
+    };
+    auto tile_at = [&](int L, Tile &c) -> bool {
+        const int ytile = L / ntx;
+        int xtile = L - ytile * ntx;
+        if (ytile >= live_y) return false;  // token-tile major: every later tile is outside the table too
+        c.seg = 0;
+        if (!GGUF && p.nseg > 1) {
+            c.seg = (xtile >= p.seg_tile[1]) ? 1 : 0;
+            if (p.nseg > 2 && xtile >= p.seg_tile[2]) c.seg = 2;
+            xtile -= (c.seg == 0) ? 0 : (c.seg == 1) ? p.seg_tile[1] : p.seg_tile[2];
+        }
+        c.seg_n = (c.seg == 0) ? p.n : (c.seg == 1) ? p.seg_n[1] : p.seg_n[2];
+        c.n0 = xtile * kBN;
+        c.t0 = ytile * p.bt;
+        c.t_end = p.m;
+        c.wrow0 = c.n0;
+        if (p.tiles) {
+            const int4 tile = __ldg(reinterpret_cast<const int4 *>(p.tiles) + ytile);
+            c.wrow0 = tile.x * c.seg_n + c.n0;  // (sibling linears of a grouped launch have their own [experts * n, k] matrices)
+            c.t0 = tile.y;
+            c.t_end = tile.z;
+        }
+        return true;
+    };
     // this CTA's k-slice: whole packed stages, [kb_off, kb_off + num_kb)
     const bool split = !GGUF && p.ksplit > 1;
     const uint32_t krank = split ? qmm_cluster_rank() : 0u;
@@ -361,6 +386,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             mbar_init(&wp_empty[i], kDequantWarps);
         }
         mbar_init(acc_full, 1);
+        mbar_init(acc_empty, kDequantWarps);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -382,37 +408,59 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (lane == 0) {
             const int num_wi = (num_kb + KBW - 1) / KBW;
             const uint32_t x_bytes = static_cast<uint32_t>(p.bt) * 128u * XP;
-            int next_wi = 0;
-            bool ok = true;
-            // Packed weights come from HBM: their loads are issued a whole ring ahead, independent of
-            // how far the operand ring has drained.
-            auto issue_w = [&]() {
-                const int ws = next_wi % WS;
-                if (next_wi >= WS) ok = qmm_wait(&wp_empty[ws], ((next_wi / WS) - 1) & 1, 2);
-                if (!ok) return;
-                mbar_arrive_expect_tx(&wp_full[ws], WPB);
-                // x coordinate in elements of the map: bytes, or 32-bit words for Q2_K
-                tma_load_2d(wp + ws * WPB, map_w, (next_wi + wi_off) * (GGUF == 2 ? ROWB / 4 : ROWB), wrow0, &wp_full[ws]);
-                ++next_wi;
-            };
-            for (int i = 0; i < WS && next_wi < num_wi; ++i) issue_w();
-            pdl_wait();
+            int wcnt = 0;  // packed stages issued, over all tiles: stage c lives in slot c % WS
+            int xcnt = 0;  // activation stages issued
             int s = 0;
             uint32_t ph = 1;  // parity of the lap before: the first lap does not wait
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                if (kb > 0 && kb % KBW == 0 && next_wi < num_wi) issue_w();
-                if (kb >= ST && ok) ok = qmm_wait(&empty[s], ph, 1);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&full[s], x_bytes);
-                if (WIDE) {
+            bool ok = true, first = true;
+            Tile c;
+            for (int L = tile_first; L < tile_total && ok; L += tile_step) {
+                if (!tile_at(L, c)) break;
+                const CUtensorMap *map_w = &maps_w.m[c.seg];
+                const int t0 = c.t0;
+                const int boxes = (min(c.t_end - c.t0, p.bt) + 127) >> 7;
+                int next_wi = 0;
+                // Packed weights come from HBM: their loads are issued a whole ring ahead, independent of
+                // how far the operand ring has drained.
+                auto issue_w = [&]() {
+                    const int ws = wcnt % WS;
+                    if (wcnt >= WS) ok = qmm_wait(&wp_empty[ws], ((wcnt / WS) - 1) & 1, 2);
+                    if (!ok) return;
+                    mbar_arrive_expect_tx(&wp_full[ws], WPB);
+                    // x coordinate in elements of the map: bytes, or 32-bit words for Q2_K
+                    tma_load_2d(wp + ws * WPB, map_w, (next_wi + wi_off) * (GGUF == 2 ? ROWB / 4 : ROWB), c.wrow0, &wp_full[ws]);
+                    ++next_wi;
+                    ++wcnt;
+                };
+                for (int kb = 0; kb < num_kb && ok; ++kb) {
+                    if (kb % KBW == 0) {
+                        // (a later tile starts one stage short of the ring: its last slot frees only when the
+                        // tile before has been dequantized to the end, and the activation loads must not queue
+                        // behind that wait)
+                        const int want = kb / KBW + ((kb == 0 && !first) ? WS - 1 : WS);
+                        while (ok && next_wi < num_wi && next_wi < want) issue_w();
+                        if (first) {
+                            pdl_wait();
+                            first = false;
+                        }
+                    }
+                    if (xcnt >= ST && ok) ok = qmm_wait(&empty[s], ph, 1);
+                    if (!ok) break;
+                    if (WIDE) {
+                        // the map's box is 128 rows; a ragged tile (the last of a dense launch, a short expert run)
+                        // loads only the boxes that hold its rows, and the MMAs below stop at the same row
+                        mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(boxes) * (128u * 128u));
 #pragma unroll
-                    for (int r = 0; r < 3; ++r)  // the map's box is 128 rows
-                        tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + r * (128 * 128), &map_x, (kb + kb_off) * kBK, t0 + 128 * r, &full[s]);
-                } else {
-                    tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, (kb + kb_off) * kBK, t0, &full[s]);
+                        for (int r = 0; r < 3; ++r)
+                            if (r < boxes) tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + r * (128 * 128), &map_x, (kb + kb_off) * kBK, t0 + 128 * r, &full[s]);
+                    } else {
+                        mbar_arrive_expect_tx(&full[s], x_bytes);
+                        tma_load_2d(xs + static_cast<size_t>(s) * x_bytes, &map_x, (kb + kb_off) * kBK, t0, &full[s]);
+                    }
+                    if (GGUF) tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + x_bytes / 2, &map_x, kb * kBK, p.m + t0, &full[s]);
+                    ++xcnt;
+                    if (++s == ST) { s = 0; ph ^= 1; }
                 }
-                if (GGUF) tma_load_2d(xs + static_cast<size_t>(s) * x_bytes + x_bytes / 2, &map_x, kb * kBK, p.m + t0, &full[s]);
-                if (++s == ST) { s = 0; ph ^= 1; }
             }
         }
     } else if (warp == 1) {
@@ -421,13 +469,26 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // k-block.  (Issued from inside an `if (lane == 0)` the same loop took ~450 of the 512 clocks
         // that four N = 256 MMAs last.)
         {
-            const uint32_t idesc = umma_idesc_bf16(WIDE ? 256 : p.bt);
-            const uint32_t idesc_b = umma_idesc_bf16(128);  // WIDE: rows 256..383 of the token tile
             const uint32_t b_lo0 = umma_desc_lo(smem_u32(xs));
             const uint32_t b_step = static_cast<uint32_t>(p.bt) * 8u * XP;  // one stage, in 16-byte units
-            int s = 0;
+            int s = 0, it = 0;
             uint32_t ph = 0, acc = 0;
             bool ok = true;
+            Tile c;
+            for (int L = tile_first; L < tile_total; L += tile_step, ++it) {
+            if (!tile_at(L, c)) break;
+            if (it > 0) {  // the epilogue of the tile before has read the accumulator
+                ok = __all_sync(0xffffffffu, qmm_wait(acc_empty, (it - 1) & 1, 8));
+                if (!ok) break;
+                tc_fence_after();
+            }
+            acc = 0;
+            // N of the MMAs: the rows of this tile rounded up to 16 (the tensor pipe's time goes with N, and a ragged
+            // tile costs what its rows cost); WIDE: rows 256.. are a second MMA into column 256 of the accumulator
+            const int r16 = (min(c.t_end - c.t0, p.bt) + 15) & ~15;
+            const uint32_t idesc = umma_idesc_bf16(WIDE ? min(r16, 256) : r16);
+            const bool second = WIDE && r16 > 256;
+            const uint32_t idesc_b = umma_idesc_bf16(second ? r16 - 256 : 16);
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = __all_sync(0xffffffffu, qmm_wait(&full[s], ph, 3));
                 if (!ok) break;
@@ -438,7 +499,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks) {
                         umma_bf16_ts(tmem_base, a_addr + ks * 8, b_lo + ks * 2, kUmmaDescHiSw128, idesc, acc);
-                        if (WIDE) umma_bf16_ts(tmem_base + 256, a_addr + ks * 8, b_lo + (256 * 128 / 16) + ks * 2, kUmmaDescHiSw128, idesc_b, acc);
+                        if (second) umma_bf16_ts(tmem_base + 256, a_addr + ks * 8, b_lo + (256 * 128 / 16) + ks * 2, kUmmaDescHiSw128, idesc_b, acc);
                         acc = 1;
                         if (GGUF) {
                             // x_lo (half a stage further) with w_hi, then x_hi with w_lo
@@ -452,7 +513,10 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 __syncwarp();
                 if (++s == ST) { s = 0; ph ^= 1; }
             }
-            if (ok && elect_one()) umma_commit(acc_full);
+            if (!ok) break;
+            if (elect_one()) umma_commit(acc_full);
+            __syncwarp();
+            }
         }
     } else {
         // ---------------- dequantize, then epilogue
@@ -461,14 +525,10 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int half = (dw >> 2) & 1;      // which 32 of the 64 k of a k-block
         const int kpar = dw >> 3;            // this warp's k-blocks: kpar, kpar + 2, ...
         const int row = quad * 32 + lane;    // weight row of the tile = TMEM lane
-        const int grow = n0 + row;
         const int swz = row & 7;
         // scale and bias of (k-block, half): group (kb*64 + half*32) >> log2(group_size); rows past n and
         // groups past k read a valid element instead: their products meet zero activations or unused rows
         const int gshift = (p.group_size == 32) ? 5 : (p.group_size == 64) ? 6 : 7;
-        const size_t srow_off = static_cast<size_t>(wrow0 - n0 + (grow < seg_n ? grow : 0)) * p.groups;
-        const uint16_t *srow = ((seg == 0) ? p.scales : (seg == 1) ? p.seg_scales[1] : p.seg_scales[2]) + srow_off;
-        const uint16_t *brow = ((seg == 0) ? p.biases : (seg == 1) ? p.seg_biases[1] : p.seg_biases[2]) + srow_off;
         const int g_last = p.groups - 1;
         // masks and the exponent of 2^23, pinned in registers so that every extraction is one LOP3
         uint32_t mk[8], mbits;
@@ -479,6 +539,31 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const unsigned long long neg_magic2 = pack_f32x2(-8388608.0f, -8388608.0f);
         const uint32_t wp32 = smem_u32(wp) + row * ROWB;
         const uint32_t a_lane = tmem_a + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(half * 16);
+        const int num_wi = (num_kb + KBW - 1) / KBW;
+        // epilogue geometry (the same for every tile)
+        const int chunks = p.bt / 16;
+        // Two k-slices: once both have finished their loops (both operand rings are idle), each slice
+        // writes the accumulators of the token chunks the OTHER one owns (slice 0: the first half of the
+        // chunks) as part[token of the tile][row] f32 over the owner's operand ring; the owner adds them to
+        // its own and stores that half of the tile.
+        const uint32_t part32 = smem_u32(xs);
+        // k-slices: slice r owns the token chunks [r * chunks / S, (r + 1) * chunks / S); `own_max` bounds a share
+        const int S = split ? p.ksplit : 1;
+        const int own_lo = static_cast<int>(krank) * chunks / S, own_hi = static_cast<int>(krank + 1) * chunks / S;
+        const int own_max = (chunks + S - 1) / S;
+        const uint32_t region = static_cast<uint32_t>(own_max) * 16u * kBN * 4u;  // what one slice sends to an owner
+        // 16-byte stores of the all-gather form need 16-byte aligned runs of 8 rows and room for the stage
+        const bool vec_out = !GGUF && p.nout > 0 && p.vec_out && (!split || p.bt >= 128);
+        int kb_base = 0, wi_base = 0, it = 0;  // k-blocks and packed stages of the tiles before, tiles done
+        bool ok = true;
+        Tile c;
+        for (int L = tile_first; L < tile_total; L += tile_step, ++it, kb_base += num_kb, wi_base += num_wi) {
+        if (!tile_at(L, c)) break;
+        const int seg = c.seg, seg_n = c.seg_n, n0 = c.n0, t0 = c.t0, t_end = c.t_end;
+        const int grow = n0 + row;
+        const size_t srow_off = static_cast<size_t>(c.wrow0 - n0 + (grow < seg_n ? grow : 0)) * p.groups;
+        const uint16_t *srow = ((seg == 0) ? p.scales : (seg == 1) ? p.seg_scales[1] : p.seg_scales[2]) + srow_off;
+        const uint16_t *brow = ((seg == 0) ? p.biases : (seg == 1) ? p.seg_biases[1] : p.seg_biases[2]) + srow_off;
         auto load_sb = [&](int kb, uint32_t &sb, uint32_t &bb) {
             int g = ((kb + kb_off) * kBK + half * 32) >> gshift;
             g = g < g_last ? g : g_last;
@@ -487,17 +572,15 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         };
         uint32_t s_next = 0, b_next = 0;
         if (!GGUF && kpar < num_kb) load_sb(kpar, s_next, b_next);
-        int a = kpar;
-        uint32_t aph = 1;  // parity of the lap before: the first lap over the ring does not wait
-        bool ok = true;
         for (int kb = kpar; kb < num_kb; kb += 2) {
-            const int wi = kb / KBW, ws = wi % WS, sub = kb % KBW;
+            const int wi = kb / KBW, wr = wi_base + wi, ws = wr % WS, sub = kb % KBW;
+            const int ar = kb_base + kb, a = ar % ST;  // stage of the operand ring, counted over all tiles
             float sc = bf16_bits_to_f32(s_next), bi = bf16_bits_to_f32(b_next);
             float sc1 = 0.f, bi1 = 0.f;  // Q2_K: scale and bias of the second 16 elements
             int qshift = 0;              // Q2_K: which 2-bit field of every byte
             if (!GGUF && kb + 2 < num_kb) load_sb(kb + 2, s_next, b_next);
             // first visit of this packed-weight stage
-            if (sub < 2) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wi / WS) & 1, 5));
+            if (sub < 2) ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&wp_full[ws], (wr / WS) & 1, 5));
             if (!ok) break;
 
             // packed codes of (row, k-block, half): 32 codes
@@ -612,8 +695,8 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 }
             }
             // the MMAs that read this stage of the A ring a lap ago must have completed
-            if (kb >= ST) {
-                ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&empty[a], aph, 6));  // warp-uniform: tcgen05.st is warp-wide
+            if (ar >= ST) {
+                ok = __all_sync(0xffffffffu, qmm_wait_relaxed(&empty[a], ((ar / ST) - 1) & 1, 6));  // warp-uniform: tcgen05.st is warp-wide
                 if (!ok) break;
                 tc_fence_after();
             }
@@ -628,35 +711,21 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 // have been consumed (an arrival placed right after the loads let the refill overtake them)
                 if (last_visit) mbar_arrive(&wp_empty[ws]);
             }
-            a += 2;
-            if (a >= ST) { a -= ST; aph ^= 1; }
         }
 
         // ---------------- epilogue: TMEM -> registers -> bf16 rows of y
         pdl_wait();  // y may still be read by the previous kernel
-        if (ok) ok = qmm_wait_relaxed(acc_full, 0, 7);
+        if (ok) ok = qmm_wait_relaxed(acc_full, it & 1, 7);
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-wide
         tc_fence_after();
         const int out_row = n0 + row;
         uint16_t *yseg = (seg == 0) ? p.y : (seg == 1) ? p.seg_y[1] : p.seg_y[2];
-        const int chunks = p.bt / 16;
-        // Two k-slices: once both have finished their loops (both operand rings are idle), each slice
-        // writes the accumulators of the token chunks the OTHER one owns (slice 0: the first half of the
-        // chunks) as part[token of the tile][row] f32 over the owner's operand ring; the owner adds them to
-        // its own and stores that half of the tile.
-        const uint32_t part32 = smem_u32(xs);
-        // k-slices: slice r owns the token chunks [r * chunks / S, (r + 1) * chunks / S); `own_max` bounds a share
-        const int S = split ? p.ksplit : 1;
-        const int own_lo = static_cast<int>(krank) * chunks / S, own_hi = static_cast<int>(krank + 1) * chunks / S;
-        const int own_max = (chunks + S - 1) / S;
-        const uint32_t region = static_cast<uint32_t>(own_max) * 16u * kBN * 4u;  // what one slice sends to an owner
-        // 16-byte stores of the all-gather form need 16-byte aligned runs of 8 rows and room for the stage
-        const bool vec_out = !GGUF && p.nout > 0 && p.vec_out && (!split || p.bt >= 128);
+        const int live = min(chunks, (t_end - t0 + 15) >> 4);  // chunks that hold rows of the tile
         if (split) {
             fence_proxy_async_smem();
             qmm_cluster_arrive();
             qmm_cluster_wait();
-            for (int ci = dw >> 2; ci < chunks && ok; ci += kDequantWarps / 4) {
+            for (int ci = dw >> 2; ci < live && ok; ci += kDequantWarps / 4) {
                 if (ci >= own_lo && ci < own_hi) continue;
                 uint32_t r[16];
                 tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
@@ -676,7 +745,7 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         // (the 16-byte store path synchronises the four warps of a chunk group with a named barrier, so its
         // trip count must not depend on a per-warp `ok`: after a timed-out wait the values are undefined anyway)
-        for (int ci = dw >> 2; ci < chunks && (ok || vec_out); ci += kDequantWarps / 4) {
+        for (int ci = dw >> 2; ci < live && (ok || vec_out); ci += kDequantWarps / 4) {
             if (ci < own_lo || ci >= own_hi) continue;
             uint32_t r[16];
             tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(ci * 16), r);
@@ -732,6 +801,13 @@ qmm_affine_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     }
                 }
             }
+        }
+        if (!ok) break;
+        if (p.persist) {  // this warp's accumulator reads are done: the next tile's MMAs may overwrite it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty);
+        }
         }
     }
     if (split && warp < 2) {
@@ -860,6 +936,21 @@ static int qmm_launch(cudaStream_t stream, const void *x, int64_t m, int64_t k, 
         }
     }
     dim3 grid(static_cast<unsigned>(ntiles), static_cast<unsigned>(ytiles), static_cast<unsigned>(p.ksplit));
+    // More tiles than SMs, one k-slice, no all-gather stage in the operand ring: one CTA per SM walks the tile list
+    // (LISA_QMM_PERSIST=0: one CTA per tile, for comparison).
+    static const bool persist_on = [] {
+        const char *v = std::getenv("LISA_QMM_PERSIST");
+        return !(v && v[0] == '0');
+    }();
+    // (a last packed stage of one k-block is visited by one of the two dequantize sets only and never handed back in
+    // full: harmless at the end of a CTA, not in front of another tile)
+    const bool lone_kb = p.num_kb % ((128 * 8 / bits) / kBK) == 1;
+    if (persist_on && !lone_kb && p.ksplit == 1 && nout == 0 && ntiles * ytiles > sm_count() && ntiles * ytiles < (1ll << 30)) {
+        p.persist = 1;
+        p.ntx = static_cast<int>(ntiles);
+        p.ntotal = static_cast<int>(ntiles * ytiles);
+        grid = dim3(static_cast<unsigned>(sm_count()), 1, 1);
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kThreads);

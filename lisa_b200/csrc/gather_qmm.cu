@@ -113,19 +113,23 @@ __global__ void __launch_bounds__(kTableThreads) gather_tile_table_kernel(const 
     end_s[tid] = 0;
     __syncthreads();
     if (one_pass) {
-        for (int i0 = tid; i0 < rows; i0 += 4 * kTableThreads) {  // four rows per trip, their loads in flight together
-            int cur4[4], prev4[4];
+        constexpr int kFlight = 8;  // rows per thread and trip, their loads in flight together
+        // (whole warps enter a trip: the shuffle below names every lane)
+        for (int w0 = tid - lane; w0 < rows; w0 += kFlight * kTableThreads) {
+            const int i0 = w0 + lane;
+            int cur8[kFlight], edge8[kFlight];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < kFlight; ++j) {
                 const int i = i0 + j * kTableThreads;
-                cur4[j] = i < rows ? __ldg(ids + i) : 0;
-                prev4[j] = (i < rows && i > 0) ? __ldg(ids + i - 1) : 0;
+                cur8[j] = i < rows ? __ldg(ids + i) : 0;
+                edge8[j] = (lane == 0 && i < rows && i > 0) ? __ldg(ids + i - 1) : 0;  // the other lanes: their neighbour's row
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < kFlight; ++j) {
                 const int i = i0 + j * kTableThreads;
-                if (i >= rows) break;
-                const int cur = cur4[j], prev = prev4[j];
+                const int left = __shfl_up_sync(0xffffffffu, cur8[j], 1);
+                if (i >= rows) continue;
+                const int cur = cur8[j], prev = lane == 0 ? edge8[j] : left;
                 const bool head = i == 0;
                 if (head || prev != cur) {
                     if (cur >= 0 && cur < experts) begin_s[cur] = i;

@@ -487,6 +487,38 @@ __global__ void __launch_bounds__(256) moe_combine8_kernel(const uint4 *__restri
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= tokens * hidden8) return;
     const int64_t t = i / hidden8, h8 = i - t * hidden8;
+    if (top_k == 8) {
+        // the usual router: the eight slot rows are fetched together, then folded in the same order as below
+        // (part[y] = x * w with one rounding; total = part[0], total = part[y] + total)
+        int64_t row[8];
+        float w[8];
+        uint4 v[8];
+#pragma unroll
+        for (int y = 0; y < 8; ++y) {
+            row[y] = __ldg(inverse + t * 8 + y);
+            w[y] = __ldg(weights + t * 8 + y);
+        }
+#pragma unroll
+        for (int y = 0; y < 8; ++y) v[y] = row[y] < 0 ? make_uint4(0, 0, 0, 0) : __ldg(down + row[y] * hidden8 + h8);
+        float tot[8];
+#pragma unroll
+        for (int y = 0; y < 8; ++y) {
+            const uint32_t vw[4] = {v[y].x, v[y].y, v[y].z, v[y].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                // (+ 0: the one-term partial sum of the general fold, which turns -0 into +0)
+                const float p0 = __fadd_rn(__fmul_rn(bf16_bits_to_f32(vw[e] & 0xffffu), w[y]), 0.f);
+                const float p1 = __fadd_rn(__fmul_rn(__uint_as_float(vw[e] & 0xffff0000u), w[y]), 0.f);
+                tot[2 * e] = (y == 0) ? p0 : __fadd_rn(p0, tot[2 * e]);
+                tot[2 * e + 1] = (y == 0) ? p1 : __fadd_rn(p1, tot[2 * e + 1]);
+            }
+        }
+        uint32_t o8[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o8[e] = f32_to_bf16_bits(tot[2 * e]) | (f32_to_bf16_bits(tot[2 * e + 1]) << 16);
+        out[i] = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+        return;
+    }
     const int ty = top_k < 8 ? top_k : 8;
     float total[8];
     for (int y = 0; y < ty; ++y) {

@@ -90,12 +90,29 @@ __device__ __forceinline__ int lower_bound_ids(const int32_t *ids, int rows, int
 constexpr int kTableThreads = 1024;
 constexpr int kTableOutputs = 4;
 
+constexpr int kTableFillBlocks = 32;
+
 struct TableOutputs {
     uint16_t *y[kTableOutputs];
     int count;
 };
 
-// One block.  With at most 1024 experts the run of every expert comes from one coalesced pass over the ids
+// Zeros over the elements [a, b) of y, spread over `nthreads` threads: 16-byte stores between the aligned ends.
+__device__ __forceinline__ void zero_elements(uint16_t *y, int64_t a, int64_t b, int64_t tid, int64_t nthreads) {
+    if (b <= a) return;
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(y + a);
+    int64_t lead = static_cast<int64_t>(((16u - static_cast<unsigned>(addr & 15u)) & 15u) >> 1);
+    lead = lead < b - a ? lead : b - a;
+    for (int64_t i = tid; i < lead; i += nthreads) y[a + i] = 0;
+    const int64_t a2 = a + lead, nvec = (b - a2) >> 3;
+    uint4 *v = reinterpret_cast<uint4 *>(y + a2);
+    for (int64_t i = tid; i < nvec; i += nthreads) v[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int64_t i = a2 + nvec * 8 + tid; i < b; i += nthreads) y[i] = 0;
+}
+
+// Block 0 builds the table; the other blocks write the zeros of the rows whose ids are outside the table (sorted
+// ids: negatives first, ids >= experts last -- the padding of an expert-parallel receive buffer can be most of the
+// rows).  With at most 1024 experts the run of every expert comes from one coalesced pass over the ids
 // (a run starts where ids[i] != ids[i-1]) and the tile counts are scanned with warp shuffles; with more
 // experts every thread searches its experts' bounds, 1024 experts per trip.  The table never grows past
 // `max_tiles` entries, whatever the ids hold (ids that are not sorted give a wrong table, not a write
@@ -105,10 +122,22 @@ __global__ void __launch_bounds__(kTableThreads) gather_tile_table_kernel(const 
                                                                           int32_t *tile_count, TableOutputs out) {
     __shared__ int begin_s[kTableThreads], end_s[kTableThreads];
     __shared__ int warp_sum[32];
-    __shared__ int running, first_ok_s, first_bad_s;
+    __shared__ int running;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (blockIdx.x > 0) {
+        const int first_ok = lower_bound_ids(ids, rows, 0);
+        const int first_bad = lower_bound_ids(ids, rows, experts);
+        if (first_ok == 0 && first_bad == rows) return;
+        const int64_t t = static_cast<int64_t>(blockIdx.x - 1) * kTableThreads + tid;
+        const int64_t nt = static_cast<int64_t>(gridDim.x - 1) * kTableThreads;
+        for (int o = 0; o < out.count; ++o) {
+            zero_elements(out.y[o], 0, static_cast<int64_t>(first_ok) * n, t, nt);
+            zero_elements(out.y[o], static_cast<int64_t>(first_bad) * n, static_cast<int64_t>(rows) * n, t, nt);
+        }
+        return;
+    }
     const bool one_pass = experts <= kTableThreads;
-    if (tid == 0) running = 0, first_ok_s = rows, first_bad_s = rows;
+    if (tid == 0) running = 0;
     begin_s[tid] = 0;
     end_s[tid] = 0;
     __syncthreads();
@@ -134,8 +163,6 @@ __global__ void __launch_bounds__(kTableThreads) gather_tile_table_kernel(const 
                 if (head || prev != cur) {
                     if (cur >= 0 && cur < experts) begin_s[cur] = i;
                     if (!head && prev >= 0 && prev < experts) end_s[prev] = i;
-                    if (cur >= 0 && (head || prev < 0)) first_ok_s = i;
-                    if (cur >= experts && (head || prev < experts)) first_bad_s = i;
                 }
                 if (i == rows - 1 && cur >= 0 && cur < experts) end_s[cur] = rows;
             }
@@ -182,16 +209,6 @@ __global__ void __launch_bounds__(kTableThreads) gather_tile_table_kernel(const 
         __syncthreads();
     }
     if (tid == 0) *tile_count = min(running, max_tiles);
-    // rows with ids outside the table: zeros (sorted ids: negatives first, ids >= experts last)
-    const int first_ok = one_pass ? first_ok_s : lower_bound_ids(ids, rows, 0);
-    const int first_bad = one_pass ? first_bad_s : lower_bound_ids(ids, rows, experts);
-    const int64_t head = static_cast<int64_t>(first_ok) * n;
-    const int64_t tail0 = static_cast<int64_t>(first_bad) * n, tail1 = static_cast<int64_t>(rows) * n;
-    for (int o = 0; o < out.count; ++o) {
-        uint16_t *y = out.y[o];
-        for (int64_t i = tid; i < head; i += kTableThreads) y[i] = 0;
-        for (int64_t i = tail0 + tid; i < tail1; i += kTableThreads) y[i] = 0;
-    }
 }
 
 // Rows per tile of the grouped GEMM: up to 256 rows the dequantization sets a CTA's pace, beyond that the MMAs, whose
@@ -251,7 +268,7 @@ int gather_qmm_affine_multi(cudaStream_t stream, const void *x, int64_t rows, in
             TableOutputs out{};
             out.count = std::min(count - i0, kTableOutputs);
             for (int i = 0; i < out.count; ++i) out.y[i] = reinterpret_cast<uint16_t *>(y[i0 + i]);
-            gather_tile_table_kernel<<<1, kTableThreads, 0, stream>>>(ids, static_cast<int>(rows), static_cast<int>(experts), bt,
+            gather_tile_table_kernel<<<1 + kTableFillBlocks, kTableThreads, 0, stream>>>(ids, static_cast<int>(rows), static_cast<int>(experts), bt,
                                                                      static_cast<int>(n), static_cast<int>(max_tiles), tiles,
                                                                      tile_count, out);
             LISA_CUDA_TRY(cudaGetLastError());
